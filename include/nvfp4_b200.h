@@ -1,0 +1,381 @@
+/*
+ * nvfp4_b200.h -- C ABI of the B200 (sm_100a) NVFP4 projection path.
+ *
+ * Drop-in boundary for the quantization and projection entry points of the
+ * reference's `crates/cuda-kernels` (a Rust crate whose host methods launch
+ * device kernels).  Each function below replaces one reference host method; the
+ * comment in front of it gives that method's file:line (paths relative to
+ * crates/cuda-kernels/src/).  A Rust `extern "C"` block binding these symbols
+ * reproduces the reference's module structs one to one.
+ *
+ * Conventions (same as the reference):
+ *   - every pointer is a DEVICE pointer owned by the caller unless stated otherwise;
+ *     the library allocates nothing per call and keeps no per-call state;
+ *   - every call is asynchronous on `stream` (a cudaStream_t / CUstream) and is
+ *     ordered only by that stream; no call synchronises;
+ *   - the return value is 0 on success or a CUDA error number (1 =
+ *     cudaErrorInvalidValue for shape / alignment violations); nothing aborts;
+ *   - an NVFP4 tensor is the triple (bytes u8[rows*cols/2], scales u8[rows*cols/16],
+ *     global scale f32[1] or f32[rows]); element i is in byte i/2, even index = low
+ *     nibble; value = e2m1 * e4m3(scales[i/16]) * global_scale.
+ *
+ * Scale-factor layouts:
+ *   NVFP4_SCALES_LOGICAL  row-major bytes [rows][cols/16]  (the reference's tensor format)
+ *   NVFP4_SCALES_PACKED   512-byte tiles [row_block128][k_atom64], byte
+ *                         (r%32)*16 + (r/32%4)*4 + g%4 inside a tile, rows padded to 128 with
+ *                         0x38 by whoever fills the buffer -- the order tcgen05.cp consumes
+ *                         and byte-identical to the reference's packed plane
+ *                         (utils/nvfp4_tma_matmul/cute.rs:448-467).
+ */
+#ifndef NVFP4_B200_H_
+#define NVFP4_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NVFP4_DTYPE_F32 0
+#define NVFP4_DTYPE_BF16 1
+
+#define NVFP4_SCALES_LOGICAL 0
+#define NVFP4_SCALES_PACKED 1
+
+/* GEMM global-scale modes (utils/nvfp4_tma_matmul/kernels.rs:310-351). */
+#define NVFP4_GS_NONE 0        /* out = acc * weight                                   */
+#define NVFP4_GS_TENSOR 1      /* out = acc * weight * a_global[0] * b_global[0]       */
+#define NVFP4_GS_ROWWISE_A 2   /* out = acc * weight * a_global[row] * b_global[0]     */
+
+/* GEMM epilogues (gpt/projection_postop.rs:97-162). */
+#define NVFP4_EPI_NONE 0       /* out = raw                                            */
+#define NVFP4_EPI_BIAS 1       /* out = raw + bias[col]                                */
+#define NVFP4_EPI_RELU2 2      /* pre = raw + bias; out = max(pre,0)^2; pre stored if `aux` != NULL */
+#define NVFP4_EPI_RESIDUAL 3   /* out = fma(1, raw + bias, out)   (in-place residual add, f32 only)  */
+
+/* MS-EDEN source kinds. */
+#define NVFP4_SRC_F32_ROWS 0            /* x[rows][src_row_len], zero padded to dst_row_len    */
+#define NVFP4_SRC_F32_TRANSPOSED 1      /* x[source_rows][source_cols], output row = source col */
+#define NVFP4_SRC_NVFP4_TRANSPOSED 2    /* NVFP4 tensor-scale source, transposed               */
+#define NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED 3 /* NVFP4 rowwise-scale source, transposed          */
+
+/* Library / device ------------------------------------------------------------------------ */
+
+/* Version of this ABI (bumped on incompatible change). */
+int nvfp4_abi_version(void);
+/* Text for the last error recorded on the calling thread (host pointer, never NULL). */
+const char* nvfp4_last_error(void);
+/* Reads and clears the device-side status word written by kernels whose bounded waits gave
+ * up (0 = no kernel ever timed out on this device).  Synchronises `stream`.               */
+int nvfp4_read_device_status(void* stream, uint32_t* status_out /* host */);
+
+/* Sizes ----------------------------------------------------------------------------------- */
+
+/* utils/nvfp4_tc_matmul/args.rs:37-39 -- K padded to a multiple of 64. */
+uint32_t nvfp4_padded_k(uint32_t k);
+/* utils/nvfp4_tma_matmul/scale_layout.rs:26-28 -- rows padded to a multiple of 128. */
+uint32_t nvfp4_scale_padded_mn_extent(uint32_t mn_extent);
+/* utils/nvfp4_tma_matmul/scale_layout.rs:109-112 -- bytes of a packed scale plane
+ * (mn_extent is padded to 128 internally). */
+size_t nvfp4_scale_packed_len(uint32_t mn_extent, uint32_t k_dim);
+/* utils/nvfp4/quant/mod.rs:36-39 -- number of 1024-value chunks of a tensor amax. */
+uint32_t nvfp4_tensor_amax_chunks(uint32_t element_count);
+
+/* amax ------------------------------------------------------------------------------------ */
+
+/* utils/nvfp4/quant/amax.rs:8-17  Nvfp4QuantModule::row_amax_f32 */
+int nvfp4_row_amax_f32(void* stream, const float* x, float* out, uint32_t row_count, uint32_t row_len);
+/* bf16-input variant of the above (no reference counterpart: the reference is f32-only). */
+int nvfp4_row_amax_bf16(void* stream, const void* x, float* out, uint32_t row_count, uint32_t row_len);
+/* utils/nvfp4/quant/amax.rs:19-23  Nvfp4QuantModule::tensor_amax_f32
+ * chunk_amax[ceil(n/1024)] and out[1] are both written. */
+int nvfp4_tensor_amax_f32(void* stream, const float* x, float* chunk_amax, float* out, uint32_t element_count);
+int nvfp4_tensor_amax_bf16(void* stream, const void* x, float* chunk_amax, float* out, uint32_t element_count);
+/* utils/nvfp4/quant/amax.rs:25-39  Nvfp4QuantModule::tensor_amax_from_chunks_f32 */
+int nvfp4_tensor_amax_from_chunks_f32(void* stream, const float* chunk_amax, float* out, uint32_t chunk_count);
+
+/* four-six quantizer (round-to-nearest-even nibbles, error-minimising 4/6 block scale) ---- */
+
+/* utils/nvfp4/quant/four_six.rs:12-23  Nvfp4QuantModule::fp32_to_nvfp4_four_six
+ * One tensor scale from amax[0]; flat tensor of group_count*16 values; logical scales. */
+int nvfp4_fp32_to_nvfp4_four_six(void* stream, const float* x, const float* amax, uint8_t* out_fp4,
+                                 uint8_t* out_scales, float* out_global_scale, uint32_t group_count);
+/* utils/nvfp4/quant/four_six.rs:25-58  Nvfp4QuantModule::fp32_to_nvfp4_four_six_rowwise
+ * One scale per row from amax[row]; out_global_scale[row]. */
+int nvfp4_fp32_to_nvfp4_four_six_rowwise(void* stream, const float* x, const float* amax, uint8_t* out_fp4,
+                                         uint8_t* out_scales, float* out_global_scale, uint32_t group_count,
+                                         uint32_t row_len);
+/* utils/nvfp4/quant/four_six.rs:60-82  Nvfp4QuantModule::fp32_to_nvfp4_four_six_padded
+ * Output is [padded_rows][padded_cols], zero outside [rows][cols]; tensor scale. */
+int nvfp4_fp32_to_nvfp4_four_six_padded(void* stream, const float* x, const float* amax, uint8_t* out_fp4,
+                                        uint8_t* out_scales, float* out_global_scale, uint32_t rows,
+                                        uint32_t cols, uint32_t padded_rows, uint32_t padded_cols);
+/* utils/nvfp4/quant/four_six.rs:84-123  Nvfp4QuantModule::fp32_transpose_to_nvfp4_four_six_padded
+ * x is [source_rows][source_cols]; output row r, col c = x[c][r]. */
+int nvfp4_fp32_transpose_to_nvfp4_four_six_padded(void* stream, const float* x, const float* amax,
+                                                  uint8_t* out_fp4, uint8_t* out_scales,
+                                                  float* out_global_scale, uint32_t source_rows,
+                                                  uint32_t source_cols, uint32_t padded_rows,
+                                                  uint32_t padded_cols);
+/* B200-native form of the four-six quantizer: f32 or bf16 input [rows][cols] (cols % 16 == 0),
+ * tensor (rowwise = 0, amax[0]) or rowwise (amax[row]) global scale, scales written either in
+ * the logical layout or directly in the packed layout the GEMM consumes (cols % 64 == 0 then;
+ * pad rows up to the next multiple of 128 are filled with 0x38).  Same bytes as the entries
+ * above; replaces quantize + Sm120ScalePackModule::pack (scale_pack.rs:54-78) in one pass. */
+int nvfp4_quantize_four_six(void* stream, const void* x, int dtype, const float* amax, int rowwise,
+                            uint32_t rows, uint32_t cols, uint8_t* out_fp4, uint8_t* out_scales,
+                            int scale_layout, float* out_global_scale);
+
+/* MS-EDEN quantizer (random-sign Hadamard-32 rotation, RTN nibbles, EDEN-corrected block
+ * scale rounded stochastically with a counter RNG) ---------------------------------------- */
+
+typedef struct nvfp4_ms_eden_args {
+  int src_kind;                 /* NVFP4_SRC_*                                               */
+  int src_dtype;                /* NVFP4_DTYPE_* for the f32/bf16 source kinds               */
+  const void* x;                /* f32 / bf16 source                                         */
+  const uint8_t* src_bytes;     /* NVFP4 source kinds                                        */
+  const uint8_t* src_scales;    /*   scale bytes, layout given by src_scale_layout           */
+  int src_scale_layout;         /*   NVFP4_SCALES_* (packed needs source cols % 64 == 0)     */
+  const float* src_global;      /*   f32[1] or f32[source_rows]                              */
+  uint32_t rows;                /* F32_ROWS: row_count;  transposed kinds: source_rows       */
+  uint32_t cols;                /* F32_ROWS: src_row_len; transposed kinds: source_cols      */
+  uint32_t dst_row_len;         /* multiple of 32 (64 for the packed layout)                 */
+  const float* global_scale;    /* device f32[1] used when host_global_scale_valid == 0      */
+  float host_global_scale;      /* used when host_global_scale_valid != 0                    */
+  int host_global_scale_valid;
+  float scale_override;
+  uint32_t sign_seed;
+  uint32_t scale_seed;
+  uint32_t col_offset;          /* added to the K index of the sign hash (token sharding)    */
+  uint32_t group_offset;        /* added to the flat group id of the scale RNG (even)        */
+  uint8_t* out_fp4;
+  uint8_t* out_scales;
+  int scale_layout;             /* NVFP4_SCALES_*                                            */
+  float* out_global_scales;     /* f32[out_rows], every entry = the global scale             */
+  float* out_chunk_amax;        /* f32[out_rows*dst_row_len/32] or NULL                      */
+} nvfp4_ms_eden_args;
+
+/* Generic MS-EDEN entry: every reference variant below is a thin wrapper over it. */
+int nvfp4_ms_eden_quantize(void* stream, const nvfp4_ms_eden_args* args /* host */);
+
+/* utils/nvfp4/quant/ms_eden.rs:8-33  Nvfp4QuantModule::fp32_to_nvfp4_ms_eden */
+int nvfp4_fp32_to_nvfp4_ms_eden(void* stream, const float* x, uint8_t* out_fp4, uint8_t* out_scales,
+                                float* out_global_scales, float* out_chunk_amax, uint32_t row_count,
+                                uint32_t src_row_len, uint32_t dst_row_len, float global_scale,
+                                float scale_override, uint32_t sign_seed, uint32_t scale_seed);
+/* utils/nvfp4/quant/ms_eden.rs:35-60  ..._device_scale  (global_scale read from device) */
+int nvfp4_fp32_to_nvfp4_ms_eden_device_scale(void* stream, const float* x, uint8_t* out_fp4,
+                                             uint8_t* out_scales, float* out_global_scales,
+                                             float* out_chunk_amax, const float* global_scale,
+                                             uint32_t row_count, uint32_t src_row_len, uint32_t dst_row_len,
+                                             float scale_override, uint32_t sign_seed, uint32_t scale_seed);
+/* utils/nvfp4/quant/ms_eden.rs:62-91  ..._device_scale_no_chunk_amax */
+int nvfp4_fp32_to_nvfp4_ms_eden_device_scale_no_chunk_amax(void* stream, const float* x, uint8_t* out_fp4,
+                                                           uint8_t* out_scales, float* out_global_scales,
+                                                           const float* global_scale, uint32_t row_count,
+                                                           uint32_t src_row_len, uint32_t dst_row_len,
+                                                           float scale_override, uint32_t sign_seed,
+                                                           uint32_t scale_seed);
+/* utils/nvfp4/quant/ms_eden_fp32_transpose.rs  ..._fp32_transpose_to_nvfp4_ms_eden_device_scale */
+int nvfp4_fp32_transpose_to_nvfp4_ms_eden_device_scale(void* stream, const float* x, uint8_t* out_fp4,
+                                                       uint8_t* out_scales, float* out_global_scales,
+                                                       float* out_chunk_amax, const float* global_scale,
+                                                       uint32_t source_rows, uint32_t source_cols,
+                                                       uint32_t dst_row_len, float scale_override,
+                                                       uint32_t sign_seed, uint32_t scale_seed);
+int nvfp4_fp32_transpose_to_nvfp4_ms_eden_device_scale_no_chunk_amax(
+    void* stream, const float* x, uint8_t* out_fp4, uint8_t* out_scales, float* out_global_scales,
+    const float* global_scale, uint32_t source_rows, uint32_t source_cols, uint32_t dst_row_len,
+    float scale_override, uint32_t sign_seed, uint32_t scale_seed);
+/* utils/nvfp4/quant/global_scale.rs:11-26  quartet_backward_ms_eden_global_scale_from_chunks
+ * out[0] = amax == 0 ? 1 : amax * (17/16*0.93) / 1536 with amax = max(chunk_amax). */
+int nvfp4_quartet_backward_ms_eden_global_scale_from_chunks(void* stream, const float* chunk_amax,
+                                                            float* out_global_scale, uint32_t chunk_count);
+/* utils/nvfp4/quant/ms_eden_quartet.rs:10-31  tensor amax -> global scale -> MS-EDEN rows.
+ * out_chunk_amax needs max(ceil(row_count*src_row_len/1024), row_count*dst_row_len/32) floats for
+ * the first form (it receives the 32-chunk amax) and ceil(n/1024) floats for the second. */
+int nvfp4_fp32_to_nvfp4_quartet_backward_ms_eden_derived_device_scale(
+    void* stream, const float* x, uint8_t* out_fp4, uint8_t* out_scales, float* out_global_scales,
+    float* out_chunk_amax, float* out_global_scale, uint32_t row_count, uint32_t src_row_len,
+    uint32_t dst_row_len, uint32_t sign_seed, uint32_t scale_seed);
+int nvfp4_fp32_to_nvfp4_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax(
+    void* stream, const float* x, uint8_t* out_fp4, uint8_t* out_scales, float* out_global_scales,
+    float* out_chunk_amax, float* out_global_scale, uint32_t row_count, uint32_t src_row_len,
+    uint32_t dst_row_len, uint32_t sign_seed, uint32_t scale_seed);
+/* utils/nvfp4/quant/ms_eden_quartet.rs:33-56  ..._with_global_scale (host scalar scale). */
+int nvfp4_fp32_to_nvfp4_quartet_backward_ms_eden_with_global_scale(
+    void* stream, const float* x, uint8_t* out_fp4, uint8_t* out_scales, float* out_global_scales,
+    float* out_chunk_amax, uint32_t row_count, uint32_t src_row_len, uint32_t dst_row_len,
+    uint32_t sign_seed, uint32_t scale_seed, float global_scale);
+/* utils/nvfp4/quant/ms_eden_pair.rs:13-45  one call quantizes dY rows (for dX) and dY
+ * transposed (for dW) with one shared tensor scale.  precomputed_chunk_count = 0 computes
+ * the 1024-value chunk amax of x into out_chunk_amax first; otherwise out_chunk_amax already
+ * holds that many chunk values. */
+int nvfp4_fp32_pair_to_nvfp4_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax(
+    void* stream, const float* x, uint8_t* out_fp4, uint8_t* out_scales, float* out_global_scales,
+    uint8_t* transpose_out_fp4, uint8_t* transpose_out_scales, float* transpose_out_global_scales,
+    float* out_chunk_amax, float* out_global_scale, uint32_t row_count, uint32_t src_row_len,
+    uint32_t dst_row_len, uint32_t transpose_dst_row_len, uint32_t sign_seed, uint32_t scale_seed,
+    uint32_t transpose_scale_seed, uint32_t precomputed_chunk_count);
+/* utils/nvfp4/quant/ms_eden_transpose.rs:9-84  NVFP4 weight W[source_rows][source_cols] ->
+ * amax of the decoded tensor -> global scale -> MS-EDEN of the transpose. */
+int nvfp4_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale(
+    void* stream, const uint8_t* in_bytes, const uint8_t* in_scales, const float* in_global_scale,
+    uint8_t* out_fp4, uint8_t* out_scales, float* out_global_scales, float* out_chunk_amax,
+    float* out_global_scale, uint32_t source_rows, uint32_t source_cols, uint32_t dst_row_len,
+    uint32_t sign_seed, uint32_t scale_seed);
+int nvfp4_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax(
+    void* stream, const uint8_t* in_bytes, const uint8_t* in_scales, const float* in_global_scale,
+    uint8_t* out_fp4, uint8_t* out_scales, float* out_global_scales, float* out_chunk_amax,
+    float* out_global_scale, uint32_t source_rows, uint32_t source_cols, uint32_t dst_row_len,
+    uint32_t sign_seed, uint32_t scale_seed);
+/* utils/nvfp4/quant/ms_eden_transpose_rowwise.rs:14-54  same for a rowwise-scaled NVFP4
+ * activation X[source_rows][source_cols] saved on the tape. */
+int nvfp4_rowwise_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale(
+    void* stream, const uint8_t* in_bytes, const uint8_t* in_scales, const float* in_global_scales,
+    uint8_t* out_fp4, uint8_t* out_scales, float* out_global_scales, float* out_chunk_amax,
+    float* out_global_scale, uint32_t source_rows, uint32_t source_cols, uint32_t dst_row_len,
+    uint32_t sign_seed, uint32_t scale_seed);
+int nvfp4_rowwise_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax(
+    void* stream, const uint8_t* in_bytes, const uint8_t* in_scales, const float* in_global_scales,
+    uint8_t* out_fp4, uint8_t* out_scales, float* out_global_scales, float* out_chunk_amax,
+    float* out_global_scale, uint32_t source_rows, uint32_t source_cols, uint32_t dst_row_len,
+    uint32_t sign_seed, uint32_t scale_seed);
+
+/* decode / layout helpers ----------------------------------------------------------------- */
+
+/* utils/nvfp4/decode/launcher.rs  Nvfp4DecodeModule::decode_transpose_f32 : out[c][r] = value(r,c) */
+int nvfp4_decode_transpose_f32(void* stream, const uint8_t* bytes, const uint8_t* scales,
+                               const float* global_scale, float* output, uint32_t rows, uint32_t cols);
+/* utils/nvfp4/decode/launcher.rs  Nvfp4DecodeModule::decode_rowwise_transpose_f32 */
+int nvfp4_decode_rowwise_transpose_f32(void* stream, const uint8_t* bytes, const uint8_t* scales,
+                                       const float* global_scales, float* output, uint32_t rows,
+                                       uint32_t cols);
+/* Untransposed decode (rowwise = 0/1); used for NVFP4-encoded biases. */
+int nvfp4_decode_f32(void* stream, const uint8_t* bytes, const uint8_t* scales, const float* global_scales,
+                     int rowwise, float* output, uint32_t rows, uint32_t cols);
+/* utils/nvfp4_tma_matmul/scale_pack.rs:54-78  Sm120ScalePackModule::pack : logical -> packed,
+ * pad rows filled with 0x38. */
+int nvfp4_scale_pack(void* stream, const uint8_t* logical, uint8_t* packed, uint32_t mn_extent,
+                     uint32_t k_dim);
+/* utils/nvfp4_tma_matmul/pad.rs:49-107  TmaMatrixPadModule */
+int nvfp4_pad_u4_rows(void* stream, const uint8_t* src, uint8_t* dst, uint32_t rows, uint32_t padded_rows,
+                      uint32_t cols);
+int nvfp4_pad_f32(void* stream, const float* src, float* dst, uint32_t rows, uint32_t cols,
+                  uint32_t padded_rows, uint32_t padded_cols);
+int nvfp4_transpose_pad_f32(void* stream, const float* src, float* dst, uint32_t rows, uint32_t cols,
+                            uint32_t padded_rows, uint32_t padded_cols);
+int nvfp4_crop_f32(void* stream, const float* src, float* dst, uint32_t rows, uint32_t src_cols,
+                   uint32_t dst_cols);
+
+/* block-scaled GEMM ----------------------------------------------------------------------- */
+
+typedef struct nvfp4_gemm_args {
+  const uint8_t* a_bytes;       /* A [m][k] nibbles, K-major, row pitch k/2 bytes (16-byte aligned) */
+  const uint8_t* a_scales;      /* packed layout, rows padded to 128                          */
+  const float* a_global;        /* f32[1] (mode 1) or f32[m] (mode 2); unused in mode 0       */
+  const uint8_t* b_bytes;       /* B [n][k] nibbles, K-major                                  */
+  const uint8_t* b_scales;      /* packed layout                                              */
+  const float* b_global;        /* f32[1]; unused in mode 0                                   */
+  void* out;                    /* [m][ldo] f32 or bf16                                       */
+  void* aux;                    /* RELU2: pre-activation [m][ldo] (same dtype) or NULL        */
+  const float* bias;            /* f32[n] for epilogues 1..3, else NULL                       */
+  uint32_t m, n, k;             /* k % 64 == 0                                                */
+  uint32_t ldo;                 /* output row pitch in elements (>= n)                        */
+  int global_scale_mode;        /* NVFP4_GS_*                                                 */
+  float weight_global_scale;    /* the reference passes 1.0                                   */
+  int epilogue;                 /* NVFP4_EPI_*                                                */
+  int out_dtype;                /* NVFP4_DTYPE_*                                              */
+} nvfp4_gemm_args;
+
+/* out[m][n] = epilogue( (sum_k A*sa * B*sb) * weight * ga * gb ), FP32 accumulation in tensor
+ * memory by tcgen05.mma kind::mxf4nvf4.  Replaces pack + prepare_tma + gemm_tma + post-op
+ * (utils/nvfp4_tma_matmul/launcher.rs:106-328, gpt/projection_postop.rs:50-162).           */
+int nvfp4_gemm(void* stream, const nvfp4_gemm_args* args /* host */);
+
+/* utils/nvfp4_tma_matmul/launcher.rs:172-222  gemm_tma_nvfp4_device_scales_and_global_scale_buffers */
+int nvfp4_gemm_tma_nvfp4_device_scales_and_global_scale_buffers(
+    void* stream, const uint8_t* a_bytes, const uint8_t* a_scales_packed, const uint8_t* b_bytes,
+    const uint8_t* b_scales_packed, float* out, uint32_t token_count, uint32_t input_dim,
+    uint32_t output_dim, const float* a_global_scale, const float* b_global_scale);
+/* utils/nvfp4_tma_matmul/launcher.rs:224-274  gemm_tma_nvfp4_rowwise_a_scale_and_global_scale_buffer */
+int nvfp4_gemm_tma_nvfp4_rowwise_a_scale_and_global_scale_buffer(
+    void* stream, const uint8_t* a_bytes, const uint8_t* a_scales_packed, const uint8_t* b_bytes,
+    const uint8_t* b_scales_packed, float* out, uint32_t token_count, uint32_t input_dim,
+    uint32_t output_dim, const float* a_global_scales, const float* b_global_scale);
+/* utils/nvfp4_tma_matmul/launcher.rs:276-328  gemm_tma_nvfp4_rowwise_a_scale_padded_output
+ * (B holds padded_output_dim rows; only output_dim columns are written, row pitch output_dim). */
+int nvfp4_gemm_tma_nvfp4_rowwise_a_scale_padded_output(
+    void* stream, const uint8_t* a_bytes, const uint8_t* a_scales_packed, const uint8_t* b_bytes,
+    const uint8_t* b_scales_packed, float* out, uint32_t token_count, uint32_t input_dim,
+    uint32_t output_dim, uint32_t padded_output_dim, const float* a_global_scales,
+    const float* b_global_scale);
+
+/* post-ops as separate passes (gpt/projection_postop.rs:50-162); bias is NVFP4 encoded ----- */
+int nvfp4_projection_bias_inplace(void* stream, float* raw, const uint8_t* bias_bytes,
+                                  const uint8_t* bias_scales, const float* bias_global_scale,
+                                  uint32_t rows, uint32_t cols);
+int nvfp4_projection_residual_add(void* stream, const float* raw, const uint8_t* bias_bytes,
+                                  const uint8_t* bias_scales, const float* bias_global_scale,
+                                  float* residual, uint32_t rows, uint32_t cols);
+int nvfp4_projection_relu2_inplace(void* stream, float* pre_activation, float* out,
+                                   const uint8_t* bias_bytes, const uint8_t* bias_scales,
+                                   const float* bias_global_scale, uint32_t rows, uint32_t cols);
+
+/* linear backward ------------------------------------------------------------------------- */
+
+/* gpt/linear_backward/bias.rs:18-69 + kernels/bias.rs:10  dbias[col] = sum_rows e[row][col],
+ * summed in the reference's fixed order (bit-exact). */
+int nvfp4_linear_bias_grad(void* stream, const float* e, float* dbias, uint32_t token_count,
+                           uint32_t output_dim);
+
+/* Scratch of one linear backward (gpt/linear_backward/args/ms_eden/scratch.rs:11-160).  All
+ * buffers are caller owned; sizes with ok = padded_k(output_dim), tk = padded_k(token_count):
+ *   e_h      : bytes token*ok/2, scales_packed packed_len(token, ok), global_scales token
+ *   e_t_h    : bytes out*tk/2,   scales_packed packed_len(out, tk),   global_scales out
+ *   weight_t : bytes in*ok/2,    scales_packed packed_len(in, ok),    global_scales in
+ *   input_t  : bytes in*tk/2,    scales_packed packed_len(in, tk),    global_scales in
+ *   chunk_amax: max over the operands of ceil(elements/1024) floats; global_scale f32[1] each */
+typedef struct nvfp4_ms_eden_operand {
+  uint8_t* bytes;
+  uint8_t* scales_packed;
+  float* global_scales;
+  float* global_scale;   /* f32[1] */
+  float* chunk_amax;
+} nvfp4_ms_eden_operand;
+
+typedef struct nvfp4_linear_backward_args {
+  const void* e;                     /* dY [token][out], f32 or bf16 (e_dtype)                */
+  int e_dtype;
+  /* weight: NVFP4 tensor-scale W[out][in] */
+  const uint8_t* w_bytes;
+  const uint8_t* w_scales;
+  int w_scale_layout;                /* NVFP4_SCALES_*                                        */
+  const float* w_global;
+  /* saved activation: NVFP4 rowwise X[token][in] */
+  const uint8_t* x_bytes;
+  const uint8_t* x_scales;
+  int x_scale_layout;                /* NVFP4_SCALES_*                                        */
+  const float* x_globals;
+  nvfp4_ms_eden_operand e_h, e_t_h, weight_t_h, input_t_h;
+  void* dinput;                      /* [token][in]                                           */
+  void* dweight;                     /* [out][in]                                             */
+  int grad_dtype;                    /* NVFP4_DTYPE_* of dinput / dweight                     */
+  float* dbias;                      /* f32[out] or NULL                                      */
+  uint32_t token_count, input_dim, output_dim;
+  uint32_t sign_seed, scale_seed;
+  uint32_t precomputed_e_amax_chunks; /* 0 = compute the dY chunk amax here                   */
+  uint32_t token_offset;             /* first token of this shard (sign / RNG index spaces)   */
+  const float* e_global_scale_override; /* device f32[1] shared across shards, or NULL        */
+} nvfp4_linear_backward_args;
+
+/* gpt/linear_backward/ms_eden.rs:15-55  LinearBackwardModule::backward_ms_eden :
+ * dbias, MS-EDEN quantization of dY (rows + transposed), W^T, X^T, then
+ * dX = dY.W and dW = dY^T.X on the tcgen05 GEMM. */
+int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args* args /* host */);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVFP4_B200_H_ */

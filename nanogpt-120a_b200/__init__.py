@@ -1,0 +1,678 @@
+"""Host-side mirror of the reference's NVFP4 projection-path modules on top of the C ABI.
+
+The product is `libnvfp4_b200.so` (hand-written sm_100a kernels behind `extern "C"`
+entry points, declared in include/nvfp4_b200.h).  This package binds it with ctypes and
+mirrors the reference's per-op module structs (`Nvfp4QuantModule`, `Nvfp4GemmModule`,
+`Sm120ScalePackModule`, `Nvfp4DecodeModule`, `ProjectionPostOpModule`,
+`LinearBackwardModule`, crates/cuda-kernels/src/lib.rs:80-92) with the same method names
+and argument meaning.  PyTorch only provides device memory and streams: every method takes
+torch CUDA tensors, passes raw pointers and enqueues on the current stream.
+
+There is no CPU path: importing works anywhere, but every operation raises if the
+library is missing or no CUDA device is present.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_size_t, c_uint8, c_uint32, c_void_p
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libnvfp4_b200.so")
+
+DTYPE_F32, DTYPE_BF16 = 0, 1
+SCALES_LOGICAL, SCALES_PACKED = 0, 1
+GS_NONE, GS_TENSOR, GS_ROWWISE_A = 0, 1, 2
+EPI_NONE, EPI_BIAS, EPI_RELU2, EPI_RESIDUAL = 0, 1, 2, 3
+SRC_F32_ROWS, SRC_F32_TRANSPOSED, SRC_NVFP4_TRANSPOSED, SRC_ROWWISE_NVFP4_TRANSPOSED = 0, 1, 2, 3
+
+QUARTET_MS_EDEN_SCALE_OVERRIDE = float(torch.tensor(17.0 / 16.0, dtype=torch.float32) * torch.tensor(0.93, dtype=torch.float32))
+
+
+class Nvfp4Error(RuntimeError):
+    """A C-ABI call returned a non-zero CUDA error number (the reference's DriverError)."""
+
+    def __init__(self, code: int, text: str):
+        super().__init__(f"nvfp4 call failed with CUDA error {code}: {text}")
+        self.code = code
+
+
+class MsEdenArgs(Structure):
+    _fields_ = [
+        ("src_kind", c_int), ("src_dtype", c_int), ("x", c_void_p), ("src_bytes", c_void_p),
+        ("src_scales", c_void_p), ("src_scale_layout", c_int), ("src_global", c_void_p), ("rows", c_uint32),
+        ("cols", c_uint32),
+        ("dst_row_len", c_uint32), ("global_scale", c_void_p), ("host_global_scale", c_float),
+        ("host_global_scale_valid", c_int), ("scale_override", c_float), ("sign_seed", c_uint32),
+        ("scale_seed", c_uint32), ("col_offset", c_uint32), ("group_offset", c_uint32), ("out_fp4", c_void_p),
+        ("out_scales", c_void_p), ("scale_layout", c_int), ("out_global_scales", c_void_p),
+        ("out_chunk_amax", c_void_p),
+    ]
+
+
+class GemmArgs(Structure):
+    _fields_ = [
+        ("a_bytes", c_void_p), ("a_scales", c_void_p), ("a_global", c_void_p), ("b_bytes", c_void_p),
+        ("b_scales", c_void_p), ("b_global", c_void_p), ("out", c_void_p), ("aux", c_void_p), ("bias", c_void_p),
+        ("m", c_uint32), ("n", c_uint32), ("k", c_uint32), ("ldo", c_uint32), ("global_scale_mode", c_int),
+        ("weight_global_scale", c_float), ("epilogue", c_int), ("out_dtype", c_int),
+    ]
+
+
+class MsEdenOperand(Structure):
+    _fields_ = [("bytes", c_void_p), ("scales_packed", c_void_p), ("global_scales", c_void_p),
+                ("global_scale", c_void_p), ("chunk_amax", c_void_p)]
+
+
+class LinearBackwardArgs(Structure):
+    _fields_ = [
+        ("e", c_void_p), ("e_dtype", c_int), ("w_bytes", c_void_p), ("w_scales", c_void_p), ("w_scale_layout", c_int),
+        ("w_global", c_void_p), ("x_bytes", c_void_p), ("x_scales", c_void_p), ("x_scale_layout", c_int),
+        ("x_globals", c_void_p), ("e_h", MsEdenOperand),
+        ("e_t_h", MsEdenOperand), ("weight_t_h", MsEdenOperand), ("input_t_h", MsEdenOperand), ("dinput", c_void_p),
+        ("dweight", c_void_p), ("grad_dtype", c_int), ("dbias", c_void_p), ("token_count", c_uint32),
+        ("input_dim", c_uint32), ("output_dim", c_uint32), ("sign_seed", c_uint32), ("scale_seed", c_uint32),
+        ("precomputed_e_amax_chunks", c_uint32), ("token_offset", c_uint32), ("e_global_scale_override", c_void_p),
+    ]
+
+
+_P, _U, _F = c_void_p, c_uint32, c_float
+# name -> argument ctypes (all return int unless listed in _SPECIAL_RESTYPE)
+_SIGNATURES = {
+    "nvfp4_read_device_status": [_P, POINTER(c_uint32)],
+    "nvfp4_row_amax_f32": [_P, _P, _P, _U, _U],
+    "nvfp4_row_amax_bf16": [_P, _P, _P, _U, _U],
+    "nvfp4_tensor_amax_f32": [_P, _P, _P, _P, _U],
+    "nvfp4_tensor_amax_bf16": [_P, _P, _P, _P, _U],
+    "nvfp4_tensor_amax_from_chunks_f32": [_P, _P, _P, _U],
+    "nvfp4_fp32_to_nvfp4_four_six": [_P, _P, _P, _P, _P, _P, _U],
+    "nvfp4_fp32_to_nvfp4_four_six_rowwise": [_P, _P, _P, _P, _P, _P, _U, _U],
+    "nvfp4_fp32_to_nvfp4_four_six_padded": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _U],
+    "nvfp4_fp32_transpose_to_nvfp4_four_six_padded": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _U],
+    "nvfp4_quantize_four_six": [_P, _P, c_int, _P, c_int, _U, _U, _P, _P, c_int, _P],
+    "nvfp4_ms_eden_quantize": [_P, POINTER(MsEdenArgs)],
+    "nvfp4_fp32_to_nvfp4_ms_eden": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _F, _F, _U, _U],
+    "nvfp4_fp32_to_nvfp4_ms_eden_device_scale": [_P, _P, _P, _P, _P, _P, _P, _U, _U, _U, _F, _U, _U],
+    "nvfp4_fp32_to_nvfp4_ms_eden_device_scale_no_chunk_amax": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _F, _U, _U],
+    "nvfp4_fp32_transpose_to_nvfp4_ms_eden_device_scale": [_P, _P, _P, _P, _P, _P, _P, _U, _U, _U, _F, _U, _U],
+    "nvfp4_fp32_transpose_to_nvfp4_ms_eden_device_scale_no_chunk_amax": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _F, _U, _U],
+    "nvfp4_quartet_backward_ms_eden_global_scale_from_chunks": [_P, _P, _P, _U],
+    "nvfp4_fp32_to_nvfp4_quartet_backward_ms_eden_derived_device_scale": [_P, _P, _P, _P, _P, _P, _P, _U, _U, _U, _U, _U],
+    "nvfp4_fp32_to_nvfp4_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax": [_P, _P, _P, _P, _P, _P, _P, _U, _U, _U, _U, _U],
+    "nvfp4_fp32_to_nvfp4_quartet_backward_ms_eden_with_global_scale": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _U, _U, _F],
+    "nvfp4_fp32_pair_to_nvfp4_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax":
+        [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _U, _U, _U, _U, _U, _U, _U, _U],
+    "nvfp4_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale": [_P] * 9 + [_U] * 5,
+    "nvfp4_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax": [_P] * 9 + [_U] * 5,
+    "nvfp4_rowwise_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale": [_P] * 9 + [_U] * 5,
+    "nvfp4_rowwise_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax": [_P] * 9 + [_U] * 5,
+    "nvfp4_decode_transpose_f32": [_P, _P, _P, _P, _P, _U, _U],
+    "nvfp4_decode_rowwise_transpose_f32": [_P, _P, _P, _P, _P, _U, _U],
+    "nvfp4_decode_f32": [_P, _P, _P, _P, c_int, _P, _U, _U],
+    "nvfp4_scale_pack": [_P, _P, _P, _U, _U],
+    "nvfp4_pad_u4_rows": [_P, _P, _P, _U, _U, _U],
+    "nvfp4_pad_f32": [_P, _P, _P, _U, _U, _U, _U],
+    "nvfp4_transpose_pad_f32": [_P, _P, _P, _U, _U, _U, _U],
+    "nvfp4_crop_f32": [_P, _P, _P, _U, _U, _U],
+    "nvfp4_gemm": [_P, POINTER(GemmArgs)],
+    "nvfp4_gemm_tma_nvfp4_device_scales_and_global_scale_buffers": [_P] * 6 + [_U] * 3 + [_P] * 2,
+    "nvfp4_gemm_tma_nvfp4_rowwise_a_scale_and_global_scale_buffer": [_P] * 6 + [_U] * 3 + [_P] * 2,
+    "nvfp4_gemm_tma_nvfp4_rowwise_a_scale_padded_output": [_P] * 6 + [_U] * 4 + [_P] * 2,
+    "nvfp4_projection_bias_inplace": [_P, _P, _P, _P, _P, _U, _U],
+    "nvfp4_projection_residual_add": [_P, _P, _P, _P, _P, _P, _U, _U],
+    "nvfp4_projection_relu2_inplace": [_P, _P, _P, _P, _P, _P, _U, _U],
+    "nvfp4_linear_bias_grad": [_P, _P, _P, _U, _U],
+    "nvfp4_linear_backward_ms_eden": [_P, POINTER(LinearBackwardArgs)],
+}
+_SPECIAL = {
+    "nvfp4_abi_version": (c_int, []),
+    "nvfp4_last_error": (c_char_p, []),
+    "nvfp4_padded_k": (c_uint32, [_U]),
+    "nvfp4_scale_padded_mn_extent": (c_uint32, [_U]),
+    "nvfp4_scale_packed_len": (c_size_t, [_U, _U]),
+    "nvfp4_tensor_amax_chunks": (c_uint32, [_U]),
+}
+EXPORTED_SYMBOLS = sorted(list(_SIGNATURES) + list(_SPECIAL))
+
+_lib = None
+
+
+def library() -> ctypes.CDLL:
+    """Loads libnvfp4_b200.so (built in-tree by build.py); raises if it is missing."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python nanogpt-120a_b200/build.py` "
+                "(there is no CPU or PyTorch fallback for the NVFP4 projection path)")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = c_int
+            fn.argtypes = argtypes
+        for name, (restype, argtypes) in _SPECIAL.items():
+            fn = getattr(lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = lib
+    return _lib
+
+
+def _call(name: str, *args) -> None:
+    lib = library()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        raise Nvfp4Error(rc, lib.nvfp4_last_error().decode())
+
+
+def _require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise RuntimeError("the NVFP4 projection path needs a CUDA device (sm_100a); no fallback exists")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    if t is None:
+        return c_void_p(None)
+    assert t.is_cuda and t.is_contiguous(), "tensors crossing the C ABI must be contiguous CUDA tensors"
+    return c_void_p(t.data_ptr())
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return DTYPE_F32
+    if t.dtype == torch.bfloat16:
+        return DTYPE_BF16
+    raise TypeError(f"unsupported dtype {t.dtype}; the path takes float32 or bfloat16")
+
+
+def padded_k(k: int) -> int:
+    return (k + 63) // 64 * 64
+
+
+def scale_packed_len(mn: int, k: int) -> int:
+    return (mn + 127) // 128 * (k // 64) * 512
+
+
+def tensor_amax_chunks(n: int) -> int:
+    return (n + 1023) // 1024
+
+
+def read_device_status() -> int:
+    """Status word set by kernels whose bounded waits expired (0 = healthy); clears it."""
+    _require_cuda()
+    out = c_uint32(0)
+    _call("nvfp4_read_device_status", _stream(), ctypes.byref(out))
+    return int(out.value)
+
+
+@dataclass
+class Nvfp4Tensor:
+    """The reference's (bytes, scales, global scale) triple, utils/nvfp4/tensor.rs:5-45."""
+    bytes: torch.Tensor          # u8 [rows*cols/2]
+    scales: torch.Tensor         # u8, logical [rows*cols/16] or packed layout
+    global_scales: torch.Tensor  # f32 [1] (tensor scale) or [rows]
+    rows: int
+    cols: int
+    packed: bool = False
+    rowwise: bool = False
+
+
+def _empty_u8(n: int, device) -> torch.Tensor:
+    return torch.empty(n, dtype=torch.uint8, device=device)
+
+
+# =============================================================================================
+# Module mirrors
+# =============================================================================================
+
+class Nvfp4QuantModule:
+    """utils/nvfp4/quant/launcher.rs:18-34 and the methods of utils/nvfp4/quant/*.rs."""
+
+    # ---- amax ---------------------------------------------------------------------------
+    def row_amax(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda()
+        rows, cols = x.shape
+        out = torch.empty(rows, dtype=torch.float32, device=x.device) if out is None else out
+        name = "nvfp4_row_amax_f32" if x.dtype == torch.float32 else "nvfp4_row_amax_bf16"
+        _dtype_code(x)
+        _call(name, _stream(), _ptr(x), _ptr(out), rows, cols)
+        return out
+
+    row_amax_f32 = row_amax
+
+    def tensor_amax(self, x: torch.Tensor, chunk_amax: Optional[torch.Tensor] = None,
+                    out: Optional[torch.Tensor] = None):
+        _require_cuda()
+        n = x.numel()
+        chunk_amax = torch.empty(tensor_amax_chunks(n), dtype=torch.float32, device=x.device) \
+            if chunk_amax is None else chunk_amax
+        out = torch.empty(1, dtype=torch.float32, device=x.device) if out is None else out
+        name = "nvfp4_tensor_amax_f32" if x.dtype == torch.float32 else "nvfp4_tensor_amax_bf16"
+        _dtype_code(x)
+        _call(name, _stream(), _ptr(x), _ptr(chunk_amax), _ptr(out), n)
+        return chunk_amax, out
+
+    tensor_amax_f32 = tensor_amax
+
+    def tensor_amax_from_chunks_f32(self, chunk_amax: torch.Tensor, chunk_count: int,
+                                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda()
+        out = torch.empty(1, dtype=torch.float32, device=chunk_amax.device) if out is None else out
+        _call("nvfp4_tensor_amax_from_chunks_f32", _stream(), _ptr(chunk_amax), _ptr(out), chunk_count)
+        return out
+
+    # ---- four-six -----------------------------------------------------------------------
+    def fp32_to_nvfp4_four_six(self, x: torch.Tensor, amax: torch.Tensor) -> Nvfp4Tensor:
+        _require_cuda()
+        assert x.dtype == torch.float32 and x.numel() % 16 == 0
+        n = x.numel()
+        t = Nvfp4Tensor(_empty_u8(n // 2, x.device), _empty_u8(n // 16, x.device),
+                        torch.empty(1, dtype=torch.float32, device=x.device), 1, n)
+        _call("nvfp4_fp32_to_nvfp4_four_six", _stream(), _ptr(x), _ptr(amax), _ptr(t.bytes), _ptr(t.scales),
+              _ptr(t.global_scales), n // 16)
+        return t
+
+    def fp32_to_nvfp4_four_six_rowwise(self, x: torch.Tensor, amax: torch.Tensor) -> Nvfp4Tensor:
+        _require_cuda()
+        assert x.dtype == torch.float32
+        rows, cols = x.shape
+        n = rows * cols
+        t = Nvfp4Tensor(_empty_u8(n // 2, x.device), _empty_u8(n // 16, x.device),
+                        torch.empty(rows, dtype=torch.float32, device=x.device), rows, cols, rowwise=True)
+        _call("nvfp4_fp32_to_nvfp4_four_six_rowwise", _stream(), _ptr(x), _ptr(amax), _ptr(t.bytes), _ptr(t.scales),
+              _ptr(t.global_scales), n // 16, cols)
+        return t
+
+    def fp32_to_nvfp4_four_six_padded(self, x, amax, padded_rows, padded_cols, transposed=False) -> Nvfp4Tensor:
+        _require_cuda()
+        assert x.dtype == torch.float32
+        rows, cols = x.shape
+        n = padded_rows * padded_cols
+        t = Nvfp4Tensor(_empty_u8(n // 2, x.device), _empty_u8(n // 16, x.device),
+                        torch.empty(1, dtype=torch.float32, device=x.device), padded_rows, padded_cols)
+        name = "nvfp4_fp32_transpose_to_nvfp4_four_six_padded" if transposed else "nvfp4_fp32_to_nvfp4_four_six_padded"
+        _call(name, _stream(), _ptr(x), _ptr(amax), _ptr(t.bytes), _ptr(t.scales), _ptr(t.global_scales), rows, cols,
+              padded_rows, padded_cols)
+        return t
+
+    def fp32_transpose_to_nvfp4_four_six_padded(self, x, amax, padded_rows, padded_cols) -> Nvfp4Tensor:
+        return self.fp32_to_nvfp4_four_six_padded(x, amax, padded_rows, padded_cols, transposed=True)
+
+    def quantize_four_six(self, x: torch.Tensor, amax: Optional[torch.Tensor] = None, rowwise: bool = False,
+                          packed: bool = True, out: Optional[Nvfp4Tensor] = None) -> Nvfp4Tensor:
+        """B200-native form: f32 / bf16 input, scales written in the layout the GEMM reads."""
+        _require_cuda()
+        rows, cols = x.shape
+        if amax is None:
+            amax = self.row_amax(x) if rowwise else self.tensor_amax(x)[1]
+        if out is None:
+            n = rows * cols
+            nsc = scale_packed_len(rows, cols) if packed else n // 16
+            out = Nvfp4Tensor(_empty_u8(n // 2, x.device), _empty_u8(nsc, x.device),
+                              torch.empty(rows if rowwise else 1, dtype=torch.float32, device=x.device), rows, cols,
+                              packed=packed, rowwise=rowwise)
+        _call("nvfp4_quantize_four_six", _stream(), _ptr(x), _dtype_code(x), _ptr(amax), 1 if rowwise else 0, rows,
+              cols, _ptr(out.bytes), _ptr(out.scales), SCALES_PACKED if packed else SCALES_LOGICAL,
+              _ptr(out.global_scales))
+        return out
+
+    # ---- MS-EDEN ------------------------------------------------------------------------
+    def ms_eden_quantize(self, *, src_kind: int, x: Optional[torch.Tensor] = None, src: Optional[Nvfp4Tensor] = None,
+                         rows: int, cols: int, dst_row_len: int, global_scale, sign_seed: int, scale_seed: int,
+                         scale_override: float = QUARTET_MS_EDEN_SCALE_OVERRIDE, packed: bool = False,
+                         want_chunk_amax: bool = False, col_offset: int = 0, group_offset: int = 0) -> tuple:
+        """Generic entry.  Returns (Nvfp4Tensor with per-row copies of the global scale, chunk_amax|None)."""
+        _require_cuda()
+        dev = x.device if x is not None else src.bytes.device
+        out_rows = rows if src_kind == SRC_F32_ROWS else cols
+        n = out_rows * dst_row_len
+        nsc = scale_packed_len(out_rows, dst_row_len) if packed else n // 16
+        out = Nvfp4Tensor(_empty_u8(n // 2, dev), _empty_u8(nsc, dev),
+                          torch.empty(out_rows, dtype=torch.float32, device=dev), out_rows, dst_row_len,
+                          packed=packed, rowwise=True)
+        chunk_amax = torch.empty(n // 32, dtype=torch.float32, device=dev) if want_chunk_amax else None
+        a = MsEdenArgs()
+        a.src_kind = src_kind
+        a.src_dtype = _dtype_code(x) if x is not None else DTYPE_F32
+        a.x = _ptr(x)
+        if src is not None:
+            a.src_bytes, a.src_scales, a.src_global = _ptr(src.bytes), _ptr(src.scales), _ptr(src.global_scales)
+            a.src_scale_layout = SCALES_PACKED if src.packed else SCALES_LOGICAL
+        a.rows, a.cols, a.dst_row_len = rows, cols, dst_row_len
+        if isinstance(global_scale, torch.Tensor):
+            a.global_scale = _ptr(global_scale)
+            a.host_global_scale_valid = 0
+        else:
+            a.host_global_scale = float(global_scale)
+            a.host_global_scale_valid = 1
+        a.scale_override = scale_override
+        a.sign_seed, a.scale_seed = sign_seed & 0xFFFFFFFF, scale_seed & 0xFFFFFFFF
+        a.col_offset, a.group_offset = col_offset, group_offset
+        a.out_fp4, a.out_scales = _ptr(out.bytes), _ptr(out.scales)
+        a.scale_layout = SCALES_PACKED if packed else SCALES_LOGICAL
+        a.out_global_scales = _ptr(out.global_scales)
+        a.out_chunk_amax = _ptr(chunk_amax)
+        _call("nvfp4_ms_eden_quantize", _stream(), ctypes.byref(a))
+        return out, chunk_amax
+
+    def fp32_to_nvfp4_ms_eden(self, x, dst_row_len, global_scale: float, scale_override, sign_seed, scale_seed):
+        rows, cols = x.shape
+        return self.ms_eden_quantize(src_kind=SRC_F32_ROWS, x=x, rows=rows, cols=cols, dst_row_len=dst_row_len,
+                                     global_scale=float(global_scale), sign_seed=sign_seed, scale_seed=scale_seed,
+                                     scale_override=scale_override, want_chunk_amax=True)
+
+    def quartet_backward_ms_eden_global_scale_from_chunks(self, chunk_amax, chunk_count, out=None):
+        _require_cuda()
+        out = torch.empty(1, dtype=torch.float32, device=chunk_amax.device) if out is None else out
+        _call("nvfp4_quartet_backward_ms_eden_global_scale_from_chunks", _stream(), _ptr(chunk_amax), _ptr(out),
+              chunk_count)
+        return out
+
+    def _named_rows(self, name, x, dst_row_len, sign_seed, scale_seed, want_chunk_amax):
+        _require_cuda()
+        assert x.dtype == torch.float32
+        rows, cols = x.shape
+        n = rows * dst_row_len
+        out = Nvfp4Tensor(_empty_u8(n // 2, x.device), _empty_u8(n // 16, x.device),
+                          torch.empty(rows, dtype=torch.float32, device=x.device), rows, dst_row_len, rowwise=True)
+        chunk = torch.empty(max(tensor_amax_chunks(rows * cols), n // 32), dtype=torch.float32, device=x.device)
+        gs = torch.empty(1, dtype=torch.float32, device=x.device)
+        _call(name, _stream(), _ptr(x), _ptr(out.bytes), _ptr(out.scales), _ptr(out.global_scales), _ptr(chunk),
+              _ptr(gs), rows, cols, dst_row_len, sign_seed & 0xFFFFFFFF, scale_seed & 0xFFFFFFFF)
+        return out, gs, (chunk[: n // 32] if want_chunk_amax else None)
+
+    def fp32_to_nvfp4_quartet_backward_ms_eden_derived_device_scale(self, x, dst_row_len, sign_seed, scale_seed):
+        return self._named_rows("nvfp4_fp32_to_nvfp4_quartet_backward_ms_eden_derived_device_scale", x, dst_row_len,
+                                sign_seed, scale_seed, True)
+
+    def fp32_to_nvfp4_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax(self, x, dst_row_len, sign_seed,
+                                                                                   scale_seed):
+        return self._named_rows("nvfp4_fp32_to_nvfp4_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax", x,
+                                dst_row_len, sign_seed, scale_seed, False)
+
+    def fp32_pair_to_nvfp4_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax(
+            self, x, dst_row_len, transpose_dst_row_len, sign_seed, scale_seed, transpose_scale_seed):
+        """utils/nvfp4/quant/ms_eden_pair.rs:13-45.  Returns (rows, transposed, global_scale[1])."""
+        _require_cuda()
+        assert x.dtype == torch.float32
+        rows, cols = x.shape
+        dev = x.device
+        n1, n2 = rows * dst_row_len, cols * transpose_dst_row_len
+        o1 = Nvfp4Tensor(_empty_u8(n1 // 2, dev), _empty_u8(n1 // 16, dev),
+                         torch.empty(rows, dtype=torch.float32, device=dev), rows, dst_row_len, rowwise=True)
+        o2 = Nvfp4Tensor(_empty_u8(n2 // 2, dev), _empty_u8(n2 // 16, dev),
+                         torch.empty(cols, dtype=torch.float32, device=dev), cols, transpose_dst_row_len, rowwise=True)
+        chunk = torch.empty(tensor_amax_chunks(rows * cols), dtype=torch.float32, device=dev)
+        gs = torch.empty(1, dtype=torch.float32, device=dev)
+        _call("nvfp4_fp32_pair_to_nvfp4_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax", _stream(),
+              _ptr(x), _ptr(o1.bytes), _ptr(o1.scales), _ptr(o1.global_scales), _ptr(o2.bytes), _ptr(o2.scales),
+              _ptr(o2.global_scales), _ptr(chunk), _ptr(gs), rows, cols, dst_row_len, transpose_dst_row_len,
+              sign_seed & 0xFFFFFFFF, scale_seed & 0xFFFFFFFF, transpose_scale_seed & 0xFFFFFFFF, 0)
+        return o1, o2, gs
+
+    def _named_transpose(self, name, src: Nvfp4Tensor, dst_row_len, sign_seed, scale_seed):
+        _require_cuda()
+        dev = src.bytes.device
+        n = src.cols * dst_row_len
+        out = Nvfp4Tensor(_empty_u8(n // 2, dev), _empty_u8(n // 16, dev),
+                          torch.empty(src.cols, dtype=torch.float32, device=dev), src.cols, dst_row_len, rowwise=True)
+        chunk = torch.empty(max(tensor_amax_chunks(src.rows * src.cols), n // 32), dtype=torch.float32, device=dev)
+        gs = torch.empty(1, dtype=torch.float32, device=dev)
+        _call(name, _stream(), _ptr(src.bytes), _ptr(src.scales), _ptr(src.global_scales), _ptr(out.bytes),
+              _ptr(out.scales), _ptr(out.global_scales), _ptr(chunk), _ptr(gs), src.rows, src.cols, dst_row_len,
+              sign_seed & 0xFFFFFFFF, scale_seed & 0xFFFFFFFF)
+        return out, gs, chunk[: n // 32]
+
+    def nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale(self, src, dst_row_len, sign_seed, scale_seed):
+        return self._named_transpose("nvfp4_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale", src,
+                                     dst_row_len, sign_seed, scale_seed)
+
+    def rowwise_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale(self, src, dst_row_len, sign_seed,
+                                                                                  scale_seed):
+        return self._named_transpose("nvfp4_rowwise_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale",
+                                     src, dst_row_len, sign_seed, scale_seed)
+
+
+class Nvfp4DecodeModule:
+    """utils/nvfp4/decode/launcher.rs."""
+
+    def decode(self, t: Nvfp4Tensor, transpose: bool = False) -> torch.Tensor:
+        _require_cuda()
+        assert not t.packed, "decode reads the logical scale layout"
+        shape = (t.cols, t.rows) if transpose else (t.rows, t.cols)
+        out = torch.empty(shape, dtype=torch.float32, device=t.bytes.device)
+        if transpose:
+            name = "nvfp4_decode_rowwise_transpose_f32" if t.rowwise else "nvfp4_decode_transpose_f32"
+            _call(name, _stream(), _ptr(t.bytes), _ptr(t.scales), _ptr(t.global_scales), _ptr(out), t.rows, t.cols)
+        else:
+            _call("nvfp4_decode_f32", _stream(), _ptr(t.bytes), _ptr(t.scales), _ptr(t.global_scales),
+                  1 if t.rowwise else 0, _ptr(out), t.rows, t.cols)
+        return out
+
+    def decode_transpose_f32(self, t: Nvfp4Tensor) -> torch.Tensor:
+        return self.decode(t, transpose=True)
+
+    decode_rowwise_transpose_f32 = decode_transpose_f32
+
+
+class Sm120ScalePackModule:
+    """utils/nvfp4_tma_matmul/scale_pack.rs:54-78 (name kept for drop-in; the layout is the
+    tcgen05 128x4 scale-factor tile order)."""
+
+    def pack(self, logical: torch.Tensor, mn_extent: int, k_dim: int, packed: Optional[torch.Tensor] = None):
+        _require_cuda()
+        packed = _empty_u8(scale_packed_len(mn_extent, k_dim), logical.device) if packed is None else packed
+        _call("nvfp4_scale_pack", _stream(), _ptr(logical), _ptr(packed), mn_extent, k_dim)
+        return packed
+
+
+class TmaMatrixPadModule:
+    """utils/nvfp4_tma_matmul/pad.rs:49-107."""
+
+    def pad_u4_rows(self, src, rows, padded_rows, cols):
+        _require_cuda()
+        dst = _empty_u8(padded_rows * cols // 2, src.device)
+        _call("nvfp4_pad_u4_rows", _stream(), _ptr(src), _ptr(dst), rows, padded_rows, cols)
+        return dst
+
+    def pad_f32(self, src, padded_rows, padded_cols, transpose=False):
+        _require_cuda()
+        rows, cols = src.shape
+        dst = torch.empty((padded_rows, padded_cols), dtype=torch.float32, device=src.device)
+        _call("nvfp4_transpose_pad_f32" if transpose else "nvfp4_pad_f32", _stream(), _ptr(src), _ptr(dst), rows, cols,
+              padded_rows, padded_cols)
+        return dst
+
+    def transpose_pad_f32(self, src, padded_rows, padded_cols):
+        return self.pad_f32(src, padded_rows, padded_cols, transpose=True)
+
+    def crop_f32(self, src, dst_cols):
+        _require_cuda()
+        rows, cols = src.shape
+        dst = torch.empty((rows, dst_cols), dtype=torch.float32, device=src.device)
+        _call("nvfp4_crop_f32", _stream(), _ptr(src), _ptr(dst), rows, cols, dst_cols)
+        return dst
+
+
+def _packed_scales(t: Nvfp4Tensor) -> torch.Tensor:
+    return t.scales if t.packed else Sm120ScalePackModule().pack(t.scales, t.rows, t.cols)
+
+
+class Nvfp4GemmModule:
+    """utils/nvfp4_tma_matmul/launcher.rs:23-328.  The tensor maps the reference prepares in a
+    separate call are encoded inside each launch and passed as kernel parameters."""
+
+    def gemm(self, a: Nvfp4Tensor, b: Nvfp4Tensor, *, mode: Optional[int] = None, bias: Optional[torch.Tensor] = None,
+             epilogue: int = EPI_NONE, out_dtype: torch.dtype = torch.float32, out: Optional[torch.Tensor] = None,
+             aux: Optional[torch.Tensor] = None, weight_global_scale: float = 1.0, n: Optional[int] = None,
+             ldo: Optional[int] = None) -> torch.Tensor:
+        """out[m][n] = epilogue((A . B^T) * weight * ga * gb); A [m][k], B [n][k] NVFP4."""
+        _require_cuda()
+        assert a.cols == b.cols, "A and B must share K"
+        m, k = a.rows, a.cols
+        n = b.rows if n is None else n
+        ldo = n if ldo is None else ldo
+        if mode is None:
+            mode = GS_ROWWISE_A if a.rowwise else GS_TENSOR
+        if out is None:
+            out = torch.empty((m, ldo), dtype=out_dtype, device=a.bytes.device)
+        g = GemmArgs()
+        g.a_bytes, g.a_scales, g.a_global = _ptr(a.bytes), _ptr(_packed_scales(a)), _ptr(a.global_scales)
+        g.b_bytes, g.b_scales, g.b_global = _ptr(b.bytes), _ptr(_packed_scales(b)), _ptr(b.global_scales)
+        g.out, g.aux, g.bias = _ptr(out), _ptr(aux), _ptr(bias)
+        g.m, g.n, g.k, g.ldo = m, n, k, ldo
+        g.global_scale_mode = mode
+        g.weight_global_scale = weight_global_scale
+        g.epilogue = epilogue
+        g.out_dtype = _dtype_code(out)
+        _call("nvfp4_gemm", _stream(), ctypes.byref(g))
+        return out
+
+    def _named(self, name, a, b, extra_dims=()):
+        _require_cuda()
+        out = torch.empty((a.rows, b.rows if not extra_dims else extra_dims[0]), dtype=torch.float32,
+                          device=a.bytes.device)
+        dims = [a.rows, a.cols, out.shape[1]] + ([b.rows] if extra_dims else [])
+        _call(name, _stream(), _ptr(a.bytes), _ptr(_packed_scales(a)), _ptr(b.bytes), _ptr(_packed_scales(b)),
+              _ptr(out), *dims, _ptr(a.global_scales), _ptr(b.global_scales))
+        return out
+
+    def gemm_tma_nvfp4_device_scales_and_global_scale_buffers(self, a, b):
+        return self._named("nvfp4_gemm_tma_nvfp4_device_scales_and_global_scale_buffers", a, b)
+
+    def gemm_tma_nvfp4_rowwise_a_scale_and_global_scale_buffer(self, a, b):
+        return self._named("nvfp4_gemm_tma_nvfp4_rowwise_a_scale_and_global_scale_buffer", a, b)
+
+    def gemm_tma_nvfp4_rowwise_a_scale_padded_output(self, a, b, output_dim):
+        return self._named("nvfp4_gemm_tma_nvfp4_rowwise_a_scale_padded_output", a, b, extra_dims=(output_dim,))
+
+
+class ProjectionPostOpModule:
+    """gpt/projection_postop.rs:50-162 (separate-pass post-ops; bias is NVFP4 encoded)."""
+
+    def bias_inplace(self, raw, bias: Nvfp4Tensor):
+        _require_cuda()
+        rows, cols = raw.shape
+        _call("nvfp4_projection_bias_inplace", _stream(), _ptr(raw), _ptr(bias.bytes), _ptr(bias.scales),
+              _ptr(bias.global_scales), rows, cols)
+        return raw
+
+    def residual_add(self, raw, bias: Nvfp4Tensor, residual):
+        _require_cuda()
+        rows, cols = raw.shape
+        _call("nvfp4_projection_residual_add", _stream(), _ptr(raw), _ptr(bias.bytes), _ptr(bias.scales),
+              _ptr(bias.global_scales), _ptr(residual), rows, cols)
+        return residual
+
+    def relu2_inplace(self, pre_activation, bias: Nvfp4Tensor, out=None):
+        _require_cuda()
+        rows, cols = pre_activation.shape
+        out = torch.empty_like(pre_activation) if out is None else out
+        _call("nvfp4_projection_relu2_inplace", _stream(), _ptr(pre_activation), _ptr(out), _ptr(bias.bytes),
+              _ptr(bias.scales), _ptr(bias.global_scales), rows, cols)
+        return out
+
+
+class LinearBackwardScratch:
+    """Caller-owned scratch of one linear backward
+    (gpt/linear_backward/args/ms_eden/scratch.rs:91-115), sized for (tokens, in, out)."""
+
+    def __init__(self, token_count: int, input_dim: int, output_dim: int, device):
+        ok, tk = padded_k(output_dim), padded_k(token_count)
+        f32 = dict(dtype=torch.float32, device=device)
+
+        def operand(rows, k, amax_elems):
+            return dict(bytes=_empty_u8(rows * k // 2, device), scales_packed=_empty_u8(scale_packed_len(rows, k), device),
+                        global_scales=torch.empty(rows, **f32), global_scale=torch.empty(1, **f32),
+                        chunk_amax=torch.empty(max(1, tensor_amax_chunks(amax_elems)), **f32))
+
+        self.e_h = operand(token_count, ok, token_count * output_dim)
+        self.e_t_h = operand(output_dim, tk, 1)
+        self.weight_t_h = operand(input_dim, ok, output_dim * input_dim)
+        self.input_t_h = operand(input_dim, tk, token_count * input_dim)
+        self.dims = (token_count, input_dim, output_dim)
+
+    @staticmethod
+    def _c(op) -> MsEdenOperand:
+        return MsEdenOperand(_ptr(op["bytes"]), _ptr(op["scales_packed"]), _ptr(op["global_scales"]),
+                             _ptr(op["global_scale"]), _ptr(op["chunk_amax"]))
+
+    def as_tensor(self, name: str) -> Nvfp4Tensor:
+        op = getattr(self, name)
+        t, i, o = self.dims
+        rows, k = {"e_h": (t, padded_k(o)), "e_t_h": (o, padded_k(t)), "weight_t_h": (i, padded_k(o)),
+                   "input_t_h": (i, padded_k(t))}[name]
+        return Nvfp4Tensor(op["bytes"], op["scales_packed"], op["global_scales"], rows, k, packed=True, rowwise=True)
+
+
+class LinearBackwardModule:
+    """gpt/linear_backward.rs:31-67, gpt/linear_backward/ms_eden.rs:15-55."""
+
+    def linear_bias_grad(self, e: torch.Tensor, dbias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda()
+        assert e.dtype == torch.float32
+        tokens, n = e.shape
+        dbias = torch.empty(n, dtype=torch.float32, device=e.device) if dbias is None else dbias
+        _call("nvfp4_linear_bias_grad", _stream(), _ptr(e), _ptr(dbias), tokens, n)
+        return dbias
+
+    def backward_ms_eden(self, *, e: torch.Tensor, weight: Nvfp4Tensor, input: Nvfp4Tensor,
+                         scratch: LinearBackwardScratch, sign_seed: int, scale_seed: int, want_dbias: bool = True,
+                         grad_dtype: torch.dtype = torch.float32, dinput=None, dweight=None, dbias=None,
+                         token_offset: int = 0, e_global_scale: Optional[torch.Tensor] = None,
+                         precomputed_e_amax_chunks: int = 0):
+        """dbias, dX = dY.W, dW = dY^T.X with MS-EDEN quantized operands.  `weight` is the NVFP4
+        tensor-scale W[out][in], `input` the rowwise NVFP4 X[tokens][in] saved by the forward."""
+        _require_cuda()
+        tokens, out_dim = e.shape
+        in_dim = weight.cols
+        assert weight.rows == out_dim and input.rows == tokens and input.cols == in_dim
+        assert scratch.dims == (tokens, in_dim, out_dim)
+        dev = e.device
+        dinput = torch.empty((tokens, in_dim), dtype=grad_dtype, device=dev) if dinput is None else dinput
+        dweight = torch.empty((out_dim, in_dim), dtype=grad_dtype, device=dev) if dweight is None else dweight
+        if want_dbias and dbias is None:
+            dbias = torch.empty(out_dim, dtype=torch.float32, device=dev)
+        a = LinearBackwardArgs()
+        a.e, a.e_dtype = _ptr(e), _dtype_code(e)
+        a.w_bytes, a.w_scales, a.w_global = _ptr(weight.bytes), _ptr(weight.scales), _ptr(weight.global_scales)
+        a.w_scale_layout = SCALES_PACKED if weight.packed else SCALES_LOGICAL
+        a.x_bytes, a.x_scales, a.x_globals = _ptr(input.bytes), _ptr(input.scales), _ptr(input.global_scales)
+        a.x_scale_layout = SCALES_PACKED if input.packed else SCALES_LOGICAL
+        a.e_h, a.e_t_h = scratch._c(scratch.e_h), scratch._c(scratch.e_t_h)
+        a.weight_t_h, a.input_t_h = scratch._c(scratch.weight_t_h), scratch._c(scratch.input_t_h)
+        a.dinput, a.dweight, a.grad_dtype = _ptr(dinput), _ptr(dweight), _dtype_code(dinput)
+        a.dbias = _ptr(dbias if want_dbias else None)
+        a.token_count, a.input_dim, a.output_dim = tokens, in_dim, out_dim
+        a.sign_seed, a.scale_seed = sign_seed & 0xFFFFFFFF, scale_seed & 0xFFFFFFFF
+        a.precomputed_e_amax_chunks = precomputed_e_amax_chunks
+        a.token_offset = token_offset
+        a.e_global_scale_override = _ptr(e_global_scale)
+        _call("nvfp4_linear_backward_ms_eden", _stream(), ctypes.byref(a))
+        return dinput, dweight, (dbias if want_dbias else None)
+
+
+# =============================================================================================
+# Convenience: one projection, forward, the way the model graph calls it
+# (crates/gpt2-nvfp4/src/types/l3_mlp/forward.rs:15-67).
+# =============================================================================================
+
+def projection_forward(x: torch.Tensor, weight: Nvfp4Tensor, bias: Optional[torch.Tensor] = None,
+                       epilogue: Optional[int] = None, out_dtype: torch.dtype = torch.bfloat16,
+                       rowwise: bool = True, out: Optional[torch.Tensor] = None, keep_logical: bool = False):
+    """Y = X.W^T + b: quantize X (four-six, rowwise or tensor scale) then the block-scaled GEMM
+    with the fused epilogue.  Returns (Y, quantized X) so the caller can keep X for backward."""
+    q = Nvfp4QuantModule()
+    xq = q.quantize_four_six(x, rowwise=rowwise, packed=not keep_logical)
+    if epilogue is None:
+        epilogue = EPI_BIAS if bias is not None else EPI_NONE
+    y = Nvfp4GemmModule().gemm(xq, weight, bias=bias, epilogue=epilogue, out_dtype=out_dtype, out=out)
+    return y, xq

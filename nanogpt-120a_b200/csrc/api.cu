@@ -1,0 +1,550 @@
+// extern "C" boundary of the NVFP4 projection path: argument checks, composition of the
+// kernels into the reference's host-level operations, and nothing else.  Each entry cites
+// the reference method it replaces in include/nvfp4_b200.h.
+#include <cstdio>
+#include <cstring>
+
+#include "kernels.h"
+
+namespace nvfp4 {
+
+static thread_local char g_last_error[256] = "";
+
+void set_last_error(const char* msg) {
+  std::strncpy(g_last_error, msg, sizeof(g_last_error) - 1);
+  g_last_error[sizeof(g_last_error) - 1] = '\0';
+}
+
+static int invalid(const char* msg) {
+  set_last_error(msg);
+  return static_cast<int>(cudaErrorInvalidValue);
+}
+
+static inline cudaStream_t S(void* stream) { return static_cast<cudaStream_t>(stream); }
+
+static inline uint32_t padded_k(uint32_t k) { return (k + 63u) / 64u * 64u; }
+static inline uint32_t chunks1024(uint64_t n) { return static_cast<uint32_t>((n + 1023) / 1024); }
+static const float kQuartetSO = (17.0f / 16.0f) * 0.93f;  // utils/quartet.rs:1
+
+}  // namespace nvfp4
+
+using namespace nvfp4;
+
+extern "C" {
+
+int nvfp4_abi_version(void) { return 1; }
+const char* nvfp4_last_error(void) { return g_last_error; }
+
+int nvfp4_read_device_status(void* stream, uint32_t* status_out) {
+  uint32_t* word = device_status_word();
+  if (!word || !status_out) return invalid("device status word unavailable");
+  cudaError_t e = cudaMemcpyAsync(status_out, word, sizeof(uint32_t), cudaMemcpyDeviceToHost, S(stream));
+  if (e == cudaSuccess) e = cudaMemsetAsync(word, 0, sizeof(uint32_t), S(stream));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(S(stream));
+  return static_cast<int>(e);
+}
+
+uint32_t nvfp4_padded_k(uint32_t k) { return padded_k(k); }
+uint32_t nvfp4_scale_padded_mn_extent(uint32_t mn) { return (mn + 127u) / 128u * 128u; }
+size_t nvfp4_scale_packed_len(uint32_t mn, uint32_t k) {
+  return static_cast<size_t>((mn + 127u) / 128u) * (k / 64u) * 512u;
+}
+uint32_t nvfp4_tensor_amax_chunks(uint32_t n) { return chunks1024(n); }
+
+// ---- amax -------------------------------------------------------------------------------
+int nvfp4_row_amax_f32(void* stream, const float* x, float* out, uint32_t rows, uint32_t row_len) {
+  return launch_row_amax(S(stream), x, NVFP4_DTYPE_F32, out, rows, row_len);
+}
+int nvfp4_row_amax_bf16(void* stream, const void* x, float* out, uint32_t rows, uint32_t row_len) {
+  return launch_row_amax(S(stream), x, NVFP4_DTYPE_BF16, out, rows, row_len);
+}
+int nvfp4_tensor_amax_f32(void* stream, const float* x, float* chunk_amax, float* out, uint32_t n) {
+  return launch_tensor_amax(S(stream), x, NVFP4_DTYPE_F32, chunk_amax, out, n);
+}
+int nvfp4_tensor_amax_bf16(void* stream, const void* x, float* chunk_amax, float* out, uint32_t n) {
+  return launch_tensor_amax(S(stream), x, NVFP4_DTYPE_BF16, chunk_amax, out, n);
+}
+int nvfp4_tensor_amax_from_chunks_f32(void* stream, const float* chunk_amax, float* out, uint32_t chunk_count) {
+  return launch_amax_from_chunks(S(stream), chunk_amax, out, chunk_count, 0);
+}
+
+// ---- four-six ---------------------------------------------------------------------------
+int nvfp4_fp32_to_nvfp4_four_six(void* stream, const float* x, const float* amax, uint8_t* out_fp4,
+                                 uint8_t* out_scales, float* out_gs, uint32_t group_count) {
+  return launch_four_six(S(stream), x, NVFP4_DTYPE_F32, amax, 0, 1, group_count * 16u, out_fp4, out_scales, 0, out_gs);
+}
+int nvfp4_fp32_to_nvfp4_four_six_rowwise(void* stream, const float* x, const float* amax, uint8_t* out_fp4,
+                                         uint8_t* out_scales, float* out_gs, uint32_t group_count, uint32_t row_len) {
+  if (row_len == 0 || row_len % 16 != 0 || (static_cast<uint64_t>(group_count) * 16) % row_len != 0)
+    return invalid("four_six_rowwise: row_len must be a multiple of 16 dividing the element count");
+  const uint32_t rows = static_cast<uint32_t>(static_cast<uint64_t>(group_count) * 16 / row_len);
+  return launch_four_six(S(stream), x, NVFP4_DTYPE_F32, amax, 1, rows, row_len, out_fp4, out_scales, 0, out_gs);
+}
+int nvfp4_fp32_to_nvfp4_four_six_padded(void* stream, const float* x, const float* amax, uint8_t* out_fp4,
+                                        uint8_t* out_scales, float* out_gs, uint32_t rows, uint32_t cols,
+                                        uint32_t padded_rows, uint32_t padded_cols) {
+  if (padded_cols % 16 != 0 || padded_rows < rows || padded_cols < cols) return invalid("four_six_padded: bad padding");
+  return launch_four_six_padded(S(stream), x, amax, out_fp4, out_scales, out_gs, rows, cols, padded_rows, padded_cols, 0);
+}
+int nvfp4_fp32_transpose_to_nvfp4_four_six_padded(void* stream, const float* x, const float* amax, uint8_t* out_fp4,
+                                                  uint8_t* out_scales, float* out_gs, uint32_t source_rows,
+                                                  uint32_t source_cols, uint32_t padded_rows, uint32_t padded_cols) {
+  if (padded_cols % 16 != 0 || padded_rows < source_cols || padded_cols < source_rows)
+    return invalid("four_six_transpose_padded: bad padding");
+  return launch_four_six_padded(S(stream), x, amax, out_fp4, out_scales, out_gs, source_rows, source_cols, padded_rows,
+                                padded_cols, 1);
+}
+int nvfp4_quantize_four_six(void* stream, const void* x, int dtype, const float* amax, int rowwise, uint32_t rows,
+                            uint32_t cols, uint8_t* out_fp4, uint8_t* out_scales, int scale_layout, float* out_gs) {
+  if (cols % 16 != 0) return invalid("quantize_four_six: cols must be a multiple of 16");
+  if (scale_layout == NVFP4_SCALES_PACKED && cols % 64 != 0)
+    return invalid("quantize_four_six: the packed scale layout needs cols % 64 == 0");
+  if (dtype != NVFP4_DTYPE_F32 && dtype != NVFP4_DTYPE_BF16) return invalid("quantize_four_six: unknown dtype");
+  if (reinterpret_cast<uintptr_t>(x) & 15u) return invalid("quantize_four_six: input must be 16-byte aligned");
+  return launch_four_six(S(stream), x, dtype, amax, rowwise, rows, cols, out_fp4, out_scales,
+                         scale_layout == NVFP4_SCALES_PACKED, out_gs);
+}
+
+// ---- MS-EDEN ----------------------------------------------------------------------------
+int nvfp4_ms_eden_quantize(void* stream, const nvfp4_ms_eden_args* a) {
+  if (!a) return invalid("ms_eden: null args");
+  if (a->dst_row_len % 32 != 0) return invalid("ms_eden: dst_row_len must be a multiple of 32");
+  if (a->scale_layout == NVFP4_SCALES_PACKED && a->dst_row_len % 64 != 0)
+    return invalid("ms_eden: the packed scale layout needs dst_row_len % 64 == 0");
+  if (a->group_offset & 1u) return invalid("ms_eden: group_offset must be even");
+  const uint32_t src_len = a->src_kind == NVFP4_SRC_F32_ROWS ? a->cols : a->rows;
+  if (src_len > a->dst_row_len) return invalid("ms_eden: source row longer than dst_row_len");
+  if (!a->host_global_scale_valid && !a->global_scale) return invalid("ms_eden: no global scale given");
+  return launch_ms_eden(S(stream), *a);
+}
+
+static nvfp4_ms_eden_args rows_args(const float* x, uint8_t* out_fp4, uint8_t* out_scales, float* out_gss,
+                                    float* out_chunk_amax, uint32_t row_count, uint32_t src_row_len,
+                                    uint32_t dst_row_len, float so, uint32_t sign_seed, uint32_t scale_seed) {
+  nvfp4_ms_eden_args a;
+  std::memset(&a, 0, sizeof(a));
+  a.src_kind = NVFP4_SRC_F32_ROWS;
+  a.src_dtype = NVFP4_DTYPE_F32;
+  a.x = x;
+  a.rows = row_count;
+  a.cols = src_row_len;
+  a.dst_row_len = dst_row_len;
+  a.scale_override = so;
+  a.sign_seed = sign_seed;
+  a.scale_seed = scale_seed;
+  a.out_fp4 = out_fp4;
+  a.out_scales = out_scales;
+  a.scale_layout = NVFP4_SCALES_LOGICAL;
+  a.out_global_scales = out_gss;
+  a.out_chunk_amax = out_chunk_amax;
+  return a;
+}
+
+int nvfp4_fp32_to_nvfp4_ms_eden(void* stream, const float* x, uint8_t* out_fp4, uint8_t* out_scales,
+                                float* out_global_scales, float* out_chunk_amax, uint32_t row_count,
+                                uint32_t src_row_len, uint32_t dst_row_len, float global_scale, float scale_override,
+                                uint32_t sign_seed, uint32_t scale_seed) {
+  nvfp4_ms_eden_args a = rows_args(x, out_fp4, out_scales, out_global_scales, out_chunk_amax, row_count, src_row_len,
+                                   dst_row_len, scale_override, sign_seed, scale_seed);
+  a.host_global_scale = global_scale;
+  a.host_global_scale_valid = 1;
+  return nvfp4_ms_eden_quantize(stream, &a);
+}
+int nvfp4_fp32_to_nvfp4_ms_eden_device_scale(void* stream, const float* x, uint8_t* out_fp4, uint8_t* out_scales,
+                                             float* out_global_scales, float* out_chunk_amax,
+                                             const float* global_scale, uint32_t row_count, uint32_t src_row_len,
+                                             uint32_t dst_row_len, float scale_override, uint32_t sign_seed,
+                                             uint32_t scale_seed) {
+  nvfp4_ms_eden_args a = rows_args(x, out_fp4, out_scales, out_global_scales, out_chunk_amax, row_count, src_row_len,
+                                   dst_row_len, scale_override, sign_seed, scale_seed);
+  a.global_scale = global_scale;
+  return nvfp4_ms_eden_quantize(stream, &a);
+}
+int nvfp4_fp32_to_nvfp4_ms_eden_device_scale_no_chunk_amax(void* stream, const float* x, uint8_t* out_fp4,
+                                                           uint8_t* out_scales, float* out_global_scales,
+                                                           const float* global_scale, uint32_t row_count,
+                                                           uint32_t src_row_len, uint32_t dst_row_len,
+                                                           float scale_override, uint32_t sign_seed,
+                                                           uint32_t scale_seed) {
+  return nvfp4_fp32_to_nvfp4_ms_eden_device_scale(stream, x, out_fp4, out_scales, out_global_scales, nullptr,
+                                                  global_scale, row_count, src_row_len, dst_row_len, scale_override,
+                                                  sign_seed, scale_seed);
+}
+int nvfp4_fp32_transpose_to_nvfp4_ms_eden_device_scale(void* stream, const float* x, uint8_t* out_fp4,
+                                                       uint8_t* out_scales, float* out_global_scales,
+                                                       float* out_chunk_amax, const float* global_scale,
+                                                       uint32_t source_rows, uint32_t source_cols,
+                                                       uint32_t dst_row_len, float scale_override, uint32_t sign_seed,
+                                                       uint32_t scale_seed) {
+  nvfp4_ms_eden_args a = rows_args(x, out_fp4, out_scales, out_global_scales, out_chunk_amax, source_rows, source_cols,
+                                   dst_row_len, scale_override, sign_seed, scale_seed);
+  a.src_kind = NVFP4_SRC_F32_TRANSPOSED;
+  a.global_scale = global_scale;
+  return nvfp4_ms_eden_quantize(stream, &a);
+}
+int nvfp4_fp32_transpose_to_nvfp4_ms_eden_device_scale_no_chunk_amax(
+    void* stream, const float* x, uint8_t* out_fp4, uint8_t* out_scales, float* out_global_scales,
+    const float* global_scale, uint32_t source_rows, uint32_t source_cols, uint32_t dst_row_len, float scale_override,
+    uint32_t sign_seed, uint32_t scale_seed) {
+  return nvfp4_fp32_transpose_to_nvfp4_ms_eden_device_scale(stream, x, out_fp4, out_scales, out_global_scales, nullptr,
+                                                            global_scale, source_rows, source_cols, dst_row_len,
+                                                            scale_override, sign_seed, scale_seed);
+}
+int nvfp4_quartet_backward_ms_eden_global_scale_from_chunks(void* stream, const float* chunk_amax,
+                                                            float* out_global_scale, uint32_t chunk_count) {
+  return launch_amax_from_chunks(S(stream), chunk_amax, out_global_scale, chunk_count, 1);
+}
+
+// tensor chunk amax -> global scale -> rows.  The chunk-amax buffer first receives the
+// 1024-value chunk maxima and, in the first form, is then overwritten by the 32-chunk maxima
+// (utils/nvfp4/quant/global_scale.rs:76-93 followed by ms_eden.rs:35-60).
+static int quartet_derived(void* stream, const float* x, uint8_t* out_fp4, uint8_t* out_scales, float* out_gss,
+                           float* out_chunk_amax, float* out_gs, uint32_t row_count, uint32_t src_row_len,
+                           uint32_t dst_row_len, uint32_t sign_seed, uint32_t scale_seed, bool chunk_amax_out) {
+  const uint64_t n = static_cast<uint64_t>(row_count) * src_row_len;
+  int rc = launch_tensor_amax(S(stream), x, NVFP4_DTYPE_F32, out_chunk_amax, out_gs, n);
+  if (rc) return rc;
+  rc = launch_amax_from_chunks(S(stream), out_chunk_amax, out_gs, chunks1024(n), 1);
+  if (rc) return rc;
+  return nvfp4_fp32_to_nvfp4_ms_eden_device_scale(stream, x, out_fp4, out_scales, out_gss,
+                                                  chunk_amax_out ? out_chunk_amax : nullptr, out_gs, row_count,
+                                                  src_row_len, dst_row_len, kQuartetSO, sign_seed, scale_seed);
+}
+int nvfp4_fp32_to_nvfp4_quartet_backward_ms_eden_derived_device_scale(
+    void* stream, const float* x, uint8_t* out_fp4, uint8_t* out_scales, float* out_global_scales,
+    float* out_chunk_amax, float* out_global_scale, uint32_t row_count, uint32_t src_row_len, uint32_t dst_row_len,
+    uint32_t sign_seed, uint32_t scale_seed) {
+  return quartet_derived(stream, x, out_fp4, out_scales, out_global_scales, out_chunk_amax, out_global_scale, row_count,
+                         src_row_len, dst_row_len, sign_seed, scale_seed, true);
+}
+int nvfp4_fp32_to_nvfp4_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax(
+    void* stream, const float* x, uint8_t* out_fp4, uint8_t* out_scales, float* out_global_scales,
+    float* out_chunk_amax, float* out_global_scale, uint32_t row_count, uint32_t src_row_len, uint32_t dst_row_len,
+    uint32_t sign_seed, uint32_t scale_seed) {
+  return quartet_derived(stream, x, out_fp4, out_scales, out_global_scales, out_chunk_amax, out_global_scale, row_count,
+                         src_row_len, dst_row_len, sign_seed, scale_seed, false);
+}
+int nvfp4_fp32_to_nvfp4_quartet_backward_ms_eden_with_global_scale(
+    void* stream, const float* x, uint8_t* out_fp4, uint8_t* out_scales, float* out_global_scales,
+    float* out_chunk_amax, uint32_t row_count, uint32_t src_row_len, uint32_t dst_row_len, uint32_t sign_seed,
+    uint32_t scale_seed, float global_scale) {
+  return nvfp4_fp32_to_nvfp4_ms_eden(stream, x, out_fp4, out_scales, out_global_scales, out_chunk_amax, row_count,
+                                     src_row_len, dst_row_len, global_scale, kQuartetSO, sign_seed, scale_seed);
+}
+
+int nvfp4_fp32_pair_to_nvfp4_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax(
+    void* stream, const float* x, uint8_t* out_fp4, uint8_t* out_scales, float* out_global_scales,
+    uint8_t* transpose_out_fp4, uint8_t* transpose_out_scales, float* transpose_out_global_scales,
+    float* out_chunk_amax, float* out_global_scale, uint32_t row_count, uint32_t src_row_len, uint32_t dst_row_len,
+    uint32_t transpose_dst_row_len, uint32_t sign_seed, uint32_t scale_seed, uint32_t transpose_scale_seed,
+    uint32_t precomputed_chunk_count) {
+  const uint64_t n = static_cast<uint64_t>(row_count) * src_row_len;
+  uint32_t chunk_count = precomputed_chunk_count;
+  int rc;
+  if (chunk_count == 0) {
+    rc = launch_tensor_amax(S(stream), x, NVFP4_DTYPE_F32, out_chunk_amax, out_global_scale, n);
+    if (rc) return rc;
+    chunk_count = chunks1024(n);
+  }
+  rc = launch_amax_from_chunks(S(stream), out_chunk_amax, out_global_scale, chunk_count, 1);
+  if (rc) return rc;
+  rc = nvfp4_fp32_to_nvfp4_ms_eden_device_scale(stream, x, out_fp4, out_scales, out_global_scales, nullptr,
+                                                out_global_scale, row_count, src_row_len, dst_row_len, kQuartetSO,
+                                                sign_seed, scale_seed);
+  if (rc) return rc;
+  return nvfp4_fp32_transpose_to_nvfp4_ms_eden_device_scale(stream, x, transpose_out_fp4, transpose_out_scales,
+                                                            transpose_out_global_scales, nullptr, out_global_scale,
+                                                            row_count, src_row_len, transpose_dst_row_len, kQuartetSO,
+                                                            sign_seed, transpose_scale_seed);
+}
+
+static int nvfp4_source_transpose(void* stream, int kind, const uint8_t* in_bytes, const uint8_t* in_scales,
+                                  const float* in_global, uint8_t* out_fp4, uint8_t* out_scales, float* out_gss,
+                                  float* out_chunk_amax, float* out_gs, uint32_t source_rows, uint32_t source_cols,
+                                  uint32_t dst_row_len, uint32_t sign_seed, uint32_t scale_seed, bool chunk_amax_out,
+                                  int scale_layout, uint32_t col_offset, uint32_t group_offset,
+                                  int src_scale_layout = NVFP4_SCALES_LOGICAL) {
+  const uint64_t n = static_cast<uint64_t>(source_rows) * source_cols;
+  if (source_cols % 16 != 0) return invalid("nvfp4 transpose: source_cols must be a multiple of 16");
+  if (src_scale_layout == NVFP4_SCALES_PACKED && source_cols % 64 != 0)
+    return invalid("nvfp4 transpose: a packed source scale layout needs source_cols % 64 == 0");
+  int rc = launch_nvfp4_amax(S(stream), in_bytes, in_scales, in_global, source_rows, source_cols,
+                             kind == NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED, src_scale_layout == NVFP4_SCALES_PACKED,
+                             out_chunk_amax, out_gs);
+  if (rc) return rc;
+  rc = launch_amax_from_chunks(S(stream), out_chunk_amax, out_gs, chunks1024(n), 1);
+  if (rc) return rc;
+  nvfp4_ms_eden_args a;
+  std::memset(&a, 0, sizeof(a));
+  a.src_kind = kind;
+  a.src_bytes = in_bytes;
+  a.src_scales = in_scales;
+  a.src_scale_layout = src_scale_layout;
+  a.src_global = in_global;
+  a.rows = source_rows;
+  a.cols = source_cols;
+  a.dst_row_len = dst_row_len;
+  a.global_scale = out_gs;
+  a.scale_override = kQuartetSO;
+  a.sign_seed = sign_seed;
+  a.scale_seed = scale_seed;
+  a.col_offset = col_offset;
+  a.group_offset = group_offset;
+  a.out_fp4 = out_fp4;
+  a.out_scales = out_scales;
+  a.scale_layout = scale_layout;
+  a.out_global_scales = out_gss;
+  a.out_chunk_amax = chunk_amax_out ? out_chunk_amax : nullptr;
+  return nvfp4_ms_eden_quantize(stream, &a);
+}
+
+int nvfp4_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale(
+    void* stream, const uint8_t* in_bytes, const uint8_t* in_scales, const float* in_global_scale, uint8_t* out_fp4,
+    uint8_t* out_scales, float* out_global_scales, float* out_chunk_amax, float* out_global_scale,
+    uint32_t source_rows, uint32_t source_cols, uint32_t dst_row_len, uint32_t sign_seed, uint32_t scale_seed) {
+  return nvfp4_source_transpose(stream, NVFP4_SRC_NVFP4_TRANSPOSED, in_bytes, in_scales, in_global_scale, out_fp4,
+                                out_scales, out_global_scales, out_chunk_amax, out_global_scale, source_rows,
+                                source_cols, dst_row_len, sign_seed, scale_seed, true, NVFP4_SCALES_LOGICAL, 0, 0);
+}
+int nvfp4_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax(
+    void* stream, const uint8_t* in_bytes, const uint8_t* in_scales, const float* in_global_scale, uint8_t* out_fp4,
+    uint8_t* out_scales, float* out_global_scales, float* out_chunk_amax, float* out_global_scale,
+    uint32_t source_rows, uint32_t source_cols, uint32_t dst_row_len, uint32_t sign_seed, uint32_t scale_seed) {
+  return nvfp4_source_transpose(stream, NVFP4_SRC_NVFP4_TRANSPOSED, in_bytes, in_scales, in_global_scale, out_fp4,
+                                out_scales, out_global_scales, out_chunk_amax, out_global_scale, source_rows,
+                                source_cols, dst_row_len, sign_seed, scale_seed, false, NVFP4_SCALES_LOGICAL, 0, 0);
+}
+int nvfp4_rowwise_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale(
+    void* stream, const uint8_t* in_bytes, const uint8_t* in_scales, const float* in_global_scales, uint8_t* out_fp4,
+    uint8_t* out_scales, float* out_global_scales, float* out_chunk_amax, float* out_global_scale,
+    uint32_t source_rows, uint32_t source_cols, uint32_t dst_row_len, uint32_t sign_seed, uint32_t scale_seed) {
+  return nvfp4_source_transpose(stream, NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED, in_bytes, in_scales, in_global_scales,
+                                out_fp4, out_scales, out_global_scales, out_chunk_amax, out_global_scale, source_rows,
+                                source_cols, dst_row_len, sign_seed, scale_seed, true, NVFP4_SCALES_LOGICAL, 0, 0);
+}
+int nvfp4_rowwise_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax(
+    void* stream, const uint8_t* in_bytes, const uint8_t* in_scales, const float* in_global_scales, uint8_t* out_fp4,
+    uint8_t* out_scales, float* out_global_scales, float* out_chunk_amax, float* out_global_scale,
+    uint32_t source_rows, uint32_t source_cols, uint32_t dst_row_len, uint32_t sign_seed, uint32_t scale_seed) {
+  return nvfp4_source_transpose(stream, NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED, in_bytes, in_scales, in_global_scales,
+                                out_fp4, out_scales, out_global_scales, out_chunk_amax, out_global_scale, source_rows,
+                                source_cols, dst_row_len, sign_seed, scale_seed, false, NVFP4_SCALES_LOGICAL, 0, 0);
+}
+
+// ---- decode / layout --------------------------------------------------------------------
+int nvfp4_decode_transpose_f32(void* stream, const uint8_t* bytes, const uint8_t* scales, const float* global_scale,
+                               float* output, uint32_t rows, uint32_t cols) {
+  return launch_decode(S(stream), bytes, scales, global_scale, 0, 1, output, rows, cols);
+}
+int nvfp4_decode_rowwise_transpose_f32(void* stream, const uint8_t* bytes, const uint8_t* scales,
+                                       const float* global_scales, float* output, uint32_t rows, uint32_t cols) {
+  return launch_decode(S(stream), bytes, scales, global_scales, 1, 1, output, rows, cols);
+}
+int nvfp4_decode_f32(void* stream, const uint8_t* bytes, const uint8_t* scales, const float* global_scales,
+                     int rowwise, float* output, uint32_t rows, uint32_t cols) {
+  return launch_decode(S(stream), bytes, scales, global_scales, rowwise, 0, output, rows, cols);
+}
+int nvfp4_scale_pack(void* stream, const uint8_t* logical, uint8_t* packed, uint32_t mn_extent, uint32_t k_dim) {
+  if (k_dim % 64 != 0) return invalid("scale_pack: k_dim must be a multiple of 64");
+  return launch_scale_pack(S(stream), logical, packed, mn_extent, k_dim);
+}
+int nvfp4_pad_u4_rows(void* stream, const uint8_t* src, uint8_t* dst, uint32_t rows, uint32_t padded_rows,
+                      uint32_t cols) {
+  if (padded_rows < rows || cols % 2 != 0) return invalid("pad_u4_rows: bad shape");
+  return launch_pad_u4_rows(S(stream), src, dst, rows, padded_rows, cols);
+}
+int nvfp4_pad_f32(void* stream, const float* src, float* dst, uint32_t rows, uint32_t cols, uint32_t padded_rows,
+                  uint32_t padded_cols) {
+  if (padded_rows < rows || padded_cols < cols) return invalid("pad_f32: bad shape");
+  return launch_pad_f32(S(stream), src, dst, rows, cols, padded_rows, padded_cols, 0);
+}
+int nvfp4_transpose_pad_f32(void* stream, const float* src, float* dst, uint32_t rows, uint32_t cols,
+                            uint32_t padded_rows, uint32_t padded_cols) {
+  if (padded_rows < cols || padded_cols < rows) return invalid("transpose_pad_f32: bad shape");
+  return launch_pad_f32(S(stream), src, dst, rows, cols, padded_rows, padded_cols, 1);
+}
+int nvfp4_crop_f32(void* stream, const float* src, float* dst, uint32_t rows, uint32_t src_cols, uint32_t dst_cols) {
+  if (dst_cols > src_cols) return invalid("crop_f32: dst_cols > src_cols");
+  return launch_crop_f32(S(stream), src, dst, rows, src_cols, dst_cols);
+}
+
+// ---- GEMM -------------------------------------------------------------------------------
+int nvfp4_gemm(void* stream, const nvfp4_gemm_args* args) {
+  if (!args) return invalid("nvfp4_gemm: null args");
+  return launch_gemm(S(stream), *args);
+}
+
+static int gemm_plain(void* stream, const uint8_t* a_bytes, const uint8_t* a_scales, const uint8_t* b_bytes,
+                      const uint8_t* b_scales, float* out, uint32_t m, uint32_t k, uint32_t n, uint32_t ldo, int mode,
+                      const float* ag, const float* bg) {
+  nvfp4_gemm_args g;
+  std::memset(&g, 0, sizeof(g));
+  g.a_bytes = a_bytes;
+  g.a_scales = a_scales;
+  g.a_global = ag;
+  g.b_bytes = b_bytes;
+  g.b_scales = b_scales;
+  g.b_global = bg;
+  g.out = out;
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  g.ldo = ldo;
+  g.global_scale_mode = mode;
+  g.weight_global_scale = 1.0f;
+  g.epilogue = NVFP4_EPI_NONE;
+  g.out_dtype = NVFP4_DTYPE_F32;
+  return launch_gemm(S(stream), g);
+}
+int nvfp4_gemm_tma_nvfp4_device_scales_and_global_scale_buffers(
+    void* stream, const uint8_t* a_bytes, const uint8_t* a_scales_packed, const uint8_t* b_bytes,
+    const uint8_t* b_scales_packed, float* out, uint32_t token_count, uint32_t input_dim, uint32_t output_dim,
+    const float* a_global_scale, const float* b_global_scale) {
+  return gemm_plain(stream, a_bytes, a_scales_packed, b_bytes, b_scales_packed, out, token_count, input_dim,
+                    output_dim, output_dim, NVFP4_GS_TENSOR, a_global_scale, b_global_scale);
+}
+int nvfp4_gemm_tma_nvfp4_rowwise_a_scale_and_global_scale_buffer(
+    void* stream, const uint8_t* a_bytes, const uint8_t* a_scales_packed, const uint8_t* b_bytes,
+    const uint8_t* b_scales_packed, float* out, uint32_t token_count, uint32_t input_dim, uint32_t output_dim,
+    const float* a_global_scales, const float* b_global_scale) {
+  return gemm_plain(stream, a_bytes, a_scales_packed, b_bytes, b_scales_packed, out, token_count, input_dim,
+                    output_dim, output_dim, NVFP4_GS_ROWWISE_A, a_global_scales, b_global_scale);
+}
+int nvfp4_gemm_tma_nvfp4_rowwise_a_scale_padded_output(
+    void* stream, const uint8_t* a_bytes, const uint8_t* a_scales_packed, const uint8_t* b_bytes,
+    const uint8_t* b_scales_packed, float* out, uint32_t token_count, uint32_t input_dim, uint32_t output_dim,
+    uint32_t padded_output_dim, const float* a_global_scales, const float* b_global_scale) {
+  if (output_dim > padded_output_dim) return invalid("gemm padded_output: output_dim > padded_output_dim");
+  // Only output_dim columns exist in `out`; the pad rows of B are simply never stored.
+  return gemm_plain(stream, a_bytes, a_scales_packed, b_bytes, b_scales_packed, out, token_count, input_dim,
+                    output_dim, output_dim, NVFP4_GS_ROWWISE_A, a_global_scales, b_global_scale);
+}
+
+// ---- post-ops ---------------------------------------------------------------------------
+int nvfp4_projection_bias_inplace(void* stream, float* raw, const uint8_t* bias_bytes, const uint8_t* bias_scales,
+                                  const float* bias_gs, uint32_t rows, uint32_t cols) {
+  return launch_postop(S(stream), raw, nullptr, bias_bytes, bias_scales, bias_gs, rows, cols, 0);
+}
+int nvfp4_projection_residual_add(void* stream, const float* raw, const uint8_t* bias_bytes,
+                                  const uint8_t* bias_scales, const float* bias_gs, float* residual, uint32_t rows,
+                                  uint32_t cols) {
+  return launch_postop(S(stream), const_cast<float*>(raw), residual, bias_bytes, bias_scales, bias_gs, rows, cols, 1);
+}
+int nvfp4_projection_relu2_inplace(void* stream, float* pre_activation, float* out, const uint8_t* bias_bytes,
+                                   const uint8_t* bias_scales, const float* bias_gs, uint32_t rows, uint32_t cols) {
+  return launch_postop(S(stream), pre_activation, out, bias_bytes, bias_scales, bias_gs, rows, cols, 2);
+}
+
+// ---- linear backward --------------------------------------------------------------------
+int nvfp4_linear_bias_grad(void* stream, const float* e, float* dbias, uint32_t token_count, uint32_t output_dim) {
+  return launch_bias_grad(S(stream), e, dbias, token_count, output_dim);
+}
+
+int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args* a) {
+  if (!a) return invalid("linear_backward: null args");
+  const uint32_t T = a->token_count, I = a->input_dim, O = a->output_dim;
+  if (I % 16 != 0) return invalid("linear_backward: input_dim must be a multiple of 16");
+  const uint32_t ok = padded_k(O), tk = padded_k(T);
+  cudaStream_t s = S(stream);
+  int rc;
+
+  // 1. dbias (reference order; f32 dY only)
+  if (a->dbias) {
+    if (a->e_dtype != NVFP4_DTYPE_F32) return invalid("linear_backward: dbias needs an f32 dY");
+    rc = launch_bias_grad(s, static_cast<const float*>(a->e), a->dbias, T, O);
+    if (rc) return rc;
+  }
+
+  // 2. dY: tensor amax -> one global scale shared by the row and the transposed operand
+  const uint64_t ne = static_cast<uint64_t>(T) * O;
+  const float* e_gs = a->e_global_scale_override;
+  if (!e_gs) {
+    if (a->precomputed_e_amax_chunks == 0) {
+      rc = launch_tensor_amax(s, a->e, a->e_dtype, a->e_h.chunk_amax, a->e_h.global_scale, ne);
+      if (rc) return rc;
+      rc = launch_ms_eden_scale_from_amax(s, a->e_h.global_scale, a->e_h.global_scale);
+    } else {
+      rc = launch_amax_from_chunks(s, a->e_h.chunk_amax, a->e_h.global_scale, a->precomputed_e_amax_chunks, 1);
+    }
+    if (rc) return rc;
+    e_gs = a->e_h.global_scale;
+  }
+  nvfp4_ms_eden_args q;
+  std::memset(&q, 0, sizeof(q));
+  q.src_dtype = a->e_dtype;
+  q.x = a->e;
+  q.rows = T;
+  q.cols = O;
+  q.global_scale = e_gs;
+  q.scale_override = kQuartetSO;
+  q.sign_seed = a->sign_seed;
+  q.scale_layout = NVFP4_SCALES_PACKED;
+  //    rows of dY (K = output features): sign index = feature, scale RNG index = flat group id
+  q.src_kind = NVFP4_SRC_F32_ROWS;
+  q.dst_row_len = ok;
+  q.scale_seed = a->scale_seed;
+  q.col_offset = 0;
+  q.group_offset = a->token_offset * (ok / 16);
+  q.out_fp4 = a->e_h.bytes;
+  q.out_scales = a->e_h.scales_packed;
+  q.out_global_scales = a->e_h.global_scales;
+  rc = nvfp4_ms_eden_quantize(stream, &q);
+  if (rc) return rc;
+  //    rows of dY^T (K = tokens): sign index = token
+  q.src_kind = NVFP4_SRC_F32_TRANSPOSED;
+  q.dst_row_len = tk;
+  q.scale_seed = a->scale_seed ^ 0x85ebca6bu;  // gpt/linear_backward/ms_eden/quantize/pair.rs:36
+  q.col_offset = a->token_offset;
+  q.group_offset = 0;
+  q.out_fp4 = a->e_t_h.bytes;
+  q.out_scales = a->e_t_h.scales_packed;
+  q.out_global_scales = a->e_t_h.global_scales;
+  rc = nvfp4_ms_eden_quantize(stream, &q);
+  if (rc) return rc;
+
+  // 3. W^T and 4. X^T from their NVFP4 forms (quantize/transpose.rs:14-93)
+  rc = nvfp4_source_transpose(stream, NVFP4_SRC_NVFP4_TRANSPOSED, a->w_bytes, a->w_scales, a->w_global,
+                              a->weight_t_h.bytes, a->weight_t_h.scales_packed, a->weight_t_h.global_scales,
+                              a->weight_t_h.chunk_amax, a->weight_t_h.global_scale, O, I, ok, a->sign_seed,
+                              a->scale_seed ^ 0x9e3779b9u, false, NVFP4_SCALES_PACKED, 0, 0, a->w_scale_layout);
+  if (rc) return rc;
+  rc = nvfp4_source_transpose(stream, NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED, a->x_bytes, a->x_scales, a->x_globals,
+                              a->input_t_h.bytes, a->input_t_h.scales_packed, a->input_t_h.global_scales,
+                              a->input_t_h.chunk_amax, a->input_t_h.global_scale, T, I, tk, a->sign_seed,
+                              a->scale_seed ^ 0xc2b2ae35u, false, NVFP4_SCALES_PACKED, a->token_offset, 0, a->x_scale_layout);
+  if (rc) return rc;
+
+  // 5. dX = dY . W   (contraction over output features) and dW = dY^T . X (over tokens)
+  nvfp4_gemm_args g;
+  std::memset(&g, 0, sizeof(g));
+  g.global_scale_mode = NVFP4_GS_ROWWISE_A;
+  g.weight_global_scale = 1.0f;
+  g.epilogue = NVFP4_EPI_NONE;
+  g.out_dtype = a->grad_dtype;
+  g.a_bytes = a->e_h.bytes;
+  g.a_scales = a->e_h.scales_packed;
+  g.a_global = a->e_h.global_scales;
+  g.b_bytes = a->weight_t_h.bytes;
+  g.b_scales = a->weight_t_h.scales_packed;
+  g.b_global = a->weight_t_h.global_scale;
+  g.out = a->dinput;
+  g.m = T;
+  g.n = I;
+  g.k = ok;
+  g.ldo = I;
+  rc = launch_gemm(s, g);
+  if (rc) return rc;
+  g.a_bytes = a->e_t_h.bytes;
+  g.a_scales = a->e_t_h.scales_packed;
+  g.a_global = a->e_t_h.global_scales;
+  g.b_bytes = a->input_t_h.bytes;
+  g.b_scales = a->input_t_h.scales_packed;
+  g.b_global = a->input_t_h.global_scale;
+  g.out = a->dweight;
+  g.m = O;
+  g.n = I;
+  g.k = tk;
+  return launch_gemm(s, g);
+}
+
+}  // extern "C"

@@ -1,0 +1,652 @@
+// NVFP4 block-scaled projection GEMM for sm_100a.
+//
+//   out[m][n] = epilogue( (sum_k A[m][k]*sa[m][k/16] * B[n][k]*sb[n][k/16]) * weight * ga * gb )
+//
+// Semantics follow the reference's TMA GEMM and its post-op kernels
+// (crates/cuda-kernels/src/utils/nvfp4_tma_matmul/kernels.rs:310-351,538-568 and
+// gpt/projection_postop.rs:97-162); the engine is new: a persistent, warp-specialised
+// kernel in which
+//   warp 0      streams A / B nibble tiles with TMA (128-byte swizzle) and the packed
+//               scale-factor tiles with bulk copies into a shared-memory ring,
+//   warp 1      copies scale factors shared -> tensor memory (tcgen05.cp) and issues
+//               tcgen05.mma.kind::mxf4nvf4.block_scale (128 x BLOCK_N x 64 per instruction),
+//               FP32 accumulators in tensor memory,
+//   warp 2      owns the tensor-memory allocation,
+//   warps 4..7  drain accumulators (tcgen05.ld), apply global scales / bias / ReLU^2 /
+//               residual, cast and store.
+// Accumulators are double buffered when BLOCK_N = 128 so the epilogue of one tile overlaps
+// the main loop of the next.  Every mbarrier wait is bounded: on expiry the kernel records
+// a status word, drains, frees its tensor memory and returns.
+//
+// No thread-block clusters, no multicast: every load reads this GPU's own memory.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "kernels.h"
+
+namespace nvfp4 {
+
+__device__ uint32_t g_device_status = 0;
+
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockKBytes = 128;                 // 256 nibbles = one 128-byte swizzle row
+constexpr int kKAtomsPerStage = 4;                // 64-element k-atoms (one MMA each) per stage
+constexpr int kAStageBytes = kBlockM * kBlockKBytes;
+constexpr int kSfTileBytes = 512;                 // 128 rows x 4 scale bytes
+constexpr int kSfaStageBytes = kKAtomsPerStage * kSfTileBytes;
+constexpr int kTmemCols = 512;
+constexpr int kThreads = 256;
+constexpr uint64_t kWaitTimeoutNs = 2000000000ull;  // 2 s
+
+constexpr uint32_t kStatusProducerTimeout = 1u, kStatusMmaTimeout = 2u, kStatusEpilogueTimeout = 4u;
+
+template <int kBlockN>
+struct Cfg {
+  static constexpr int kNBlocks128 = kBlockN / 128;
+  static constexpr int kBStageBytes = kBlockN * kBlockKBytes;
+  static constexpr int kSfbStageBytes = kNBlocks128 * kKAtomsPerStage * kSfTileBytes;
+  static constexpr int kStages = kBlockN == 128 ? 6 : 4;
+  static constexpr int kAccStages = kBlockN == 128 ? 2 : 1;
+  static constexpr int kTmemSfa = 256;                       // column of the A scale factors
+  static constexpr int kTmemSfb = 256 + 4 * kKAtomsPerStage;  // column of the B scale factors
+  static constexpr int kSfbColsPerAtom = kBlockN / 32;
+  static constexpr int kSmemData = kStages * (kAStageBytes + kBStageBytes);
+  static constexpr int kSmemSf = kStages * (kSfaStageBytes + kSfbStageBytes);
+  static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kSmemData + kSmemSf + 256 /*barriers*/;
+  static_assert(kTmemSfb + kSfbColsPerAtom * kKAtomsPerStage <= kTmemCols, "tensor memory overflow");
+  static_assert(kAccStages * kBlockN <= 256, "accumulators overlap the scale-factor columns");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory overflow");
+};
+
+struct GemmParams {
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  const float* a_global;
+  const float* b_global;
+  const float* bias;
+  void* out;
+  void* aux;
+  uint32_t m, n, k, ldo;
+  uint32_t num_m_blocks, num_n_blocks, k_atoms, sfb_blocks128;
+  uint32_t k_splits, k_tiles_per_split, num_k_tiles;
+  int mode, epilogue, vec_store;
+  float weight;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting (this waiter timed out, or another
+// role already did); the caller then leaves its loop and goes to the common teardown.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t status_bit) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t polls = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++polls & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitTimeoutNs) {
+        *abort_flag = 1;
+        atomicOr(&g_device_status, status_bit);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_cp_sf(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_nvf4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate, uint32_t tmem_sfa, uint32_t tmem_sfb) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptors (sm_100 format: version 1 in bits 46..47).
+// A / B tiles: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart; the K offset of a
+// 64-element MMA inside the swizzle row (32 bytes) is added to the start address.
+__device__ __forceinline__ uint64_t make_ab_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1024u >> 4) << 32;  // stride byte offset
+  d |= 1ull << 46;                               // descriptor version
+  d |= 2ull << 61;                               // SWIZZLE_128B
+  return d;
+}
+// Scale-factor tiles: 32 rows x 16 bytes, no swizzle, 8-row core matrices 128 bytes apart.
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(128u >> 4) << 32;
+  d |= 1ull << 46;
+  return d;
+}
+// Instruction descriptor of kind::mxf4nvf4: E2M1 x E2M1, UE4M3 scales, K-major A and B,
+// M = 128, N = kBlockN, K = 64.
+template <int kBlockN>
+__device__ __forceinline__ constexpr uint32_t make_idesc() {
+  return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kBlockN >> 3) << 17) | (0u << 23) |
+         (static_cast<uint32_t>(kBlockM >> 4) << 24);
+}
+
+// ---- epilogue stores ------------------------------------------------------------------------
+
+template <typename OutT>
+__device__ __forceinline__ void store_row32(OutT* dst, const float (&v)[32], uint32_t valid, bool vec);
+
+template <>
+__device__ __forceinline__ void store_row32<float>(float* dst, const float (&v)[32], uint32_t valid, bool vec) {
+  if (vec && valid == 32) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (static_cast<uint32_t>(i) < valid) dst[i] = v[i];
+  }
+}
+template <>
+__device__ __forceinline__ void store_row32<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[32], uint32_t valid,
+                                                           bool vec) {
+  if (vec && valid == 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+        w[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (static_cast<uint32_t>(i) < valid) dst[i] = __float2bfloat16_rn(v[i]);
+  }
+}
+
+template <typename OutT>
+__device__ __forceinline__ float load_out(const OutT* p);
+template <>
+__device__ __forceinline__ float load_out<float>(const float* p) {
+  return *p;
+}
+template <>
+__device__ __forceinline__ float load_out<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat162float(*p);
+}
+
+// ---- the kernel -----------------------------------------------------------------------------
+
+template <int kBlockN, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+    nvfp4_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                              const GemmParams p) {
+  using C = Cfg<kBlockN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  const uint32_t smem_a = smem_base;
+  const uint32_t smem_b = smem_a + C::kStages * kAStageBytes;
+  const uint32_t smem_sfa = smem_b + C::kStages * C::kBStageBytes;
+  const uint32_t smem_sfb = smem_sfa + C::kStages * kSfaStageBytes;
+  const uint32_t smem_bar = smem_sfb + C::kStages * C::kSfbStageBytes;
+  // barrier block: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], tmem base, abort flag
+  const uint32_t bar_full = smem_bar;
+  const uint32_t bar_empty = bar_full + 8 * C::kStages;
+  const uint32_t bar_tmem_full = bar_empty + 8 * C::kStages;
+  const uint32_t bar_tmem_empty = bar_tmem_full + 16;
+  uint32_t* tmem_base_ptr = reinterpret_cast<uint32_t*>(smem_gen + (smem_bar - smem_base) + 8 * (2 * C::kStages + 4));
+  volatile uint32_t* abort_flag = tmem_base_ptr + 1;
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_a)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_b)) : "memory");
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tmem_full + 8 * a, 1);
+      mbar_init(bar_tmem_empty + 8 * a, 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_ptr)),
+                 "r"(static_cast<uint32_t>(kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tcgen05_fence_before();
+  }
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_base_ptr;
+
+  const uint32_t tiles_mn = p.num_m_blocks * p.num_n_blocks;
+  const uint32_t num_work = tiles_mn * p.k_splits;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, issued = 0;
+      bool ok = true;
+      for (uint32_t work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
+        const uint32_t tile = work % tiles_mn, split = work / tiles_mn;
+        const uint32_t m_blk = tile / p.num_n_blocks, n_blk = tile % p.num_n_blocks;
+        const uint32_t kt_begin = split * p.k_tiles_per_split;
+        const uint32_t kt_end = min(p.num_k_tiles, kt_begin + p.k_tiles_per_split);
+        for (uint32_t kt = kt_begin; kt < kt_end; ++kt) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusProducerTimeout)) {
+            ok = false;
+            break;
+          }
+          const uint32_t atoms = min(static_cast<uint32_t>(kKAtomsPerStage), p.k_atoms - kt * kKAtomsPerStage);
+          const uint32_t first_blk128 = n_blk * C::kNBlocks128;
+          const uint32_t blks128 = min(static_cast<uint32_t>(C::kNBlocks128), p.sfb_blocks128 - first_blk128);
+          const uint32_t sf_bytes = atoms * kSfTileBytes;
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_expect_tx(full, kAStageBytes + C::kBStageBytes + sf_bytes * (1u + blks128));
+          tma_load_2d(smem_a + stage * kAStageBytes, &tmap_a, full, static_cast<int32_t>(kt * kBlockKBytes),
+                      static_cast<int32_t>(m_blk * kBlockM));
+          tma_load_2d(smem_b + stage * C::kBStageBytes, &tmap_b, full, static_cast<int32_t>(kt * kBlockKBytes),
+                      static_cast<int32_t>(n_blk * kBlockN));
+          bulk_load(smem_sfa + stage * kSfaStageBytes,
+                    p.sfa + (static_cast<size_t>(m_blk) * p.k_atoms + kt * kKAtomsPerStage) * kSfTileBytes, sf_bytes,
+                    full);
+          for (uint32_t i = 0; i < blks128; ++i)
+            bulk_load(smem_sfb + stage * C::kSfbStageBytes + i * kSfaStageBytes,
+                      p.sfb + (static_cast<size_t>(first_blk128 + i) * p.k_atoms + kt * kKAtomsPerStage) * kSfTileBytes,
+                      sf_bytes, full);
+          ++issued;
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // aborting: give copies already in flight a bounded chance to land before the CTA exits
+        const uint32_t pending = min(issued, static_cast<uint32_t>(C::kStages));
+        for (uint32_t i = 0; i < pending; ++i) {
+          const uint32_t s = (stage + C::kStages - 1 - i) % C::kStages;
+          const uint32_t ph = (s < stage) ? phase : (phase ^ 1u);
+          for (int spin = 0; spin < 4096 && !mbar_try_wait(bar_full + 8 * s, ph); ++spin) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc<kBlockN>();
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (uint32_t work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
+        const uint32_t split = work / tiles_mn;
+        const uint32_t kt_begin = split * p.k_tiles_per_split;
+        const uint32_t kt_end = min(p.num_k_tiles, kt_begin + p.k_tiles_per_split);
+        if (!mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kStatusMmaTimeout)) {
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t tmem_acc = tmem_base + acc * kBlockN;
+        for (uint32_t kt = kt_begin; kt < kt_end; ++kt) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t atoms = min(static_cast<uint32_t>(kKAtomsPerStage), p.k_atoms - kt * kKAtomsPerStage);
+          const uint32_t sfa_s = smem_sfa + stage * kSfaStageBytes;
+          const uint32_t sfb_s = smem_sfb + stage * C::kSfbStageBytes;
+          for (uint32_t kb = 0; kb < atoms; ++kb) {
+            tcgen05_cp_sf(tmem_base + C::kTmemSfa + kb * 4, make_sf_desc(sfa_s + kb * kSfTileBytes));
+#pragma unroll
+            for (int i = 0; i < C::kNBlocks128; ++i)
+              tcgen05_cp_sf(tmem_base + C::kTmemSfb + kb * C::kSfbColsPerAtom + i * 4,
+                            make_sf_desc(sfb_s + i * kSfaStageBytes + kb * kSfTileBytes));
+          }
+          const uint64_t desc_a = make_ab_desc(smem_a + stage * kAStageBytes);
+          const uint64_t desc_b = make_ab_desc(smem_b + stage * C::kBStageBytes);
+          for (uint32_t kb = 0; kb < atoms; ++kb) {
+            // 64 nibbles = 32 bytes further along the swizzled row: +2 in the 16-byte start field
+            tcgen05_mma_nvf4(tmem_acc, desc_a + kb * 2, desc_b + kb * 2, idesc, (kt > kt_begin || kb > 0) ? 1u : 0u,
+                             tmem_base + C::kTmemSfa + kb * 4, tmem_base + C::kTmemSfb + kb * C::kSfbColsPerAtom);
+          }
+          tcgen05_commit(bar_empty + 8 * stage);  // frees the smem stage once these MMAs retire
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tcgen05_commit(bar_tmem_full + 8 * acc);  // accumulator complete
+        if (++acc == C::kAccStages) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ===================== epilogue =====================
+    const uint32_t ew = warp - 4;
+    OutT* out = static_cast<OutT*>(p.out);
+    OutT* aux = static_cast<OutT*>(p.aux);
+    uint32_t acc = 0, acc_phase = 0;
+    const float gb = p.mode == NVFP4_GS_NONE ? 1.0f : __ldg(p.b_global);
+    const float ga_scalar = p.mode == NVFP4_GS_TENSOR ? __ldg(p.a_global) : 1.0f;
+    for (uint32_t work = blockIdx.x; work < num_work; work += gridDim.x) {
+      const uint32_t tile = work % tiles_mn, split = work / tiles_mn;
+      const uint32_t m_blk = tile / p.num_n_blocks, n_blk = tile % p.num_n_blocks;
+      if (!mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, kStatusEpilogueTimeout)) break;
+      tcgen05_fence_after();
+      const uint32_t row = m_blk * kBlockM + ew * 32 + lane;
+      const bool row_ok = row < p.m;
+      const float ga = p.mode == NVFP4_GS_ROWWISE_A ? (row_ok ? __ldg(p.a_global + row) : 0.0f) : ga_scalar;
+      // reference order: (weight * a_scale) * b_scale, then acc * scale
+      const float scale = __fmul_rn(__fmul_rn(p.weight, ga), gb);
+      const uint32_t taddr_row = tmem_base + acc * kBlockN + ((ew * 32u) << 16);
+#pragma unroll 1
+      for (int c = 0; c < kBlockN; c += 32) {
+        uint32_t r[32];
+        tcgen05_ld_32x32b_x32(taddr_row + c, r);
+        tcgen05_wait_ld();
+        const uint32_t col0 = n_blk * kBlockN + c;
+        if (row_ok && col0 < p.n) {
+          const uint32_t valid = min(32u, p.n - col0);
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(__uint_as_float(r[i]), scale);
+          const size_t off = static_cast<size_t>(row) * p.ldo + col0;
+          if (p.k_splits > 1) {
+            // split-K partial sums: f32 reduction into a zero-initialised output; bias joins once
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (static_cast<uint32_t>(i) < valid) {
+                float t = v[i];
+                if (p.epilogue == NVFP4_EPI_BIAS && split == 0) t = __fadd_rn(t, __ldg(p.bias + col0 + i));
+                atomicAdd(reinterpret_cast<float*>(p.out) + off + i, t);
+              }
+          } else {
+            if (p.epilogue != NVFP4_EPI_NONE) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (static_cast<uint32_t>(i) < valid) v[i] = __fadd_rn(v[i], __ldg(p.bias + col0 + i));
+            }
+            if (p.epilogue == NVFP4_EPI_RELU2) {
+              if (aux) store_row32<OutT>(aux + off, v, valid, p.vec_store != 0);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float t = fmaxf(v[i], 0.0f);
+                v[i] = __fmul_rn(t, t);
+              }
+            } else if (p.epilogue == NVFP4_EPI_RESIDUAL) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (static_cast<uint32_t>(i) < valid) v[i] = __fmaf_rn(1.0f, v[i], load_out<OutT>(out + off + i));
+            }
+            store_row32<OutT>(out + off, v, valid, p.vec_store != 0);
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * acc);
+      if (++acc == C::kAccStages) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  // ===================== teardown =====================
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(kTmemCols))
+                 : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// Nibble matrix [rows][k] seen as bytes [rows][k/2]; box = 128 bytes x box_rows, 128-byte swizzle.
+int encode_operand_map(CUtensorMap* map, const uint8_t* base, uint32_t rows, uint32_t k, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) {
+    set_last_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+    return static_cast<int>(cudaErrorNotSupported);
+  }
+  const cuuint64_t dims[2] = {k / 2, rows};
+  const cuuint64_t strides[1] = {k / 2};
+  const cuuint32_t box[2] = {kBlockKBytes, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(base), dims, strides, box, elem_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled rejected the operand (base must be 16-byte aligned, k % 32 == 0)");
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  return 0;
+}
+
+int sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+    if (count <= 0) count = 148;
+  }
+  return count;
+}
+
+template <int kBlockN, typename OutT>
+int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, uint32_t grid) {
+  using C = Cfg<kBlockN>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(nvfp4_gemm_tcgen05_kernel<kBlockN, OutT>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return static_cast<int>(attr_err);
+  nvfp4_gemm_tcgen05_kernel<kBlockN, OutT><<<grid, kThreads, C::kSmemBytes, s>>>(ma, mb, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+
+uint32_t* device_status_word() {
+  uint32_t* ptr = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_device_status) != cudaSuccess) return nullptr;
+  return ptr;
+}
+
+int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
+  if (a.m == 0 || a.n == 0) return 0;
+  if (a.k == 0 || a.k % 64 != 0 || a.ldo < a.n) {
+    set_last_error("nvfp4_gemm: k must be a non-zero multiple of 64 and ldo >= n");
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if ((reinterpret_cast<uintptr_t>(a.a_bytes) | reinterpret_cast<uintptr_t>(a.b_bytes) |
+       reinterpret_cast<uintptr_t>(a.a_scales) | reinterpret_cast<uintptr_t>(a.b_scales)) & 15u) {
+    set_last_error("nvfp4_gemm: operand and scale pointers must be 16-byte aligned");
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if (a.epilogue < NVFP4_EPI_NONE || a.epilogue > NVFP4_EPI_RESIDUAL || (a.epilogue != NVFP4_EPI_NONE && !a.bias) ||
+      a.global_scale_mode < NVFP4_GS_NONE || a.global_scale_mode > NVFP4_GS_ROWWISE_A ||
+      (a.global_scale_mode != NVFP4_GS_NONE && (!a.a_global || !a.b_global)) ||
+      (a.out_dtype != NVFP4_DTYPE_F32 && a.out_dtype != NVFP4_DTYPE_BF16) || !a.out) {
+    set_last_error("nvfp4_gemm: inconsistent epilogue / scale mode / dtype arguments");
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+
+  GemmParams p;
+  p.sfa = a.a_scales;
+  p.sfb = a.b_scales;
+  p.a_global = a.a_global;
+  p.b_global = a.b_global;
+  p.bias = a.bias;
+  p.out = a.out;
+  p.aux = a.aux;
+  p.m = a.m;
+  p.n = a.n;
+  p.k = a.k;
+  p.ldo = a.ldo;
+  p.mode = a.global_scale_mode;
+  p.epilogue = a.epilogue;
+  p.weight = a.weight_global_scale;
+  p.k_atoms = a.k / 64;
+  p.num_k_tiles = (p.k_atoms + kKAtomsPerStage - 1) / kKAtomsPerStage;
+  p.num_m_blocks = (a.m + kBlockM - 1) / kBlockM;
+  p.sfb_blocks128 = (a.n + 127) / 128;
+
+  const int sms = sm_count();
+  // Tile width: 256 columns halves the shared-memory traffic per flop; 128 columns double
+  // buffers the accumulator so the (output-bound) epilogue hides behind the next main loop.
+  // Short-K GEMMs are epilogue bound, long-K GEMMs are main-loop bound.
+  const uint32_t tiles256 = p.num_m_blocks * ((a.n + 255) / 256);
+  const bool wide = (a.n % 256 == 0 || a.n > 1024) && p.num_k_tiles >= 8 && tiles256 >= static_cast<uint32_t>(sms);
+  const uint32_t block_n = wide ? 256 : 128;
+  p.num_n_blocks = (a.n + block_n - 1) / block_n;
+  const uint32_t tiles = p.num_m_blocks * p.num_n_blocks;
+
+  // split-K for long, narrow GEMMs (dW = dY^T.X): f32 output, linear epilogue only
+  p.k_splits = 1;
+  if (a.out_dtype == NVFP4_DTYPE_F32 && (a.epilogue == NVFP4_EPI_NONE || a.epilogue == NVFP4_EPI_BIAS) &&
+      tiles * 2 <= static_cast<uint32_t>(sms) && p.num_k_tiles >= 16) {
+    uint32_t splits = static_cast<uint32_t>(sms) / tiles;
+    const uint32_t max_splits = p.num_k_tiles / 8;
+    if (splits > max_splits) splits = max_splits;
+    if (splits > 1) p.k_splits = splits;
+  }
+  p.k_tiles_per_split = (p.num_k_tiles + p.k_splits - 1) / p.k_splits;
+  p.k_splits = (p.num_k_tiles + p.k_tiles_per_split - 1) / p.k_tiles_per_split;
+
+  const size_t esz = a.out_dtype == NVFP4_DTYPE_F32 ? 4 : 2;
+  const uint32_t vec_elems = 16 / static_cast<uint32_t>(esz);
+  p.vec_store = ((reinterpret_cast<uintptr_t>(a.out) & 15u) == 0 && a.ldo % vec_elems == 0 &&
+                 (!a.aux || (reinterpret_cast<uintptr_t>(a.aux) & 15u) == 0))
+                    ? 1
+                    : 0;
+
+  CUtensorMap ma, mb;
+  int rc = encode_operand_map(&ma, a.a_bytes, a.m, a.k, kBlockM);
+  if (rc) return rc;
+  rc = encode_operand_map(&mb, a.b_bytes, a.n, a.k, block_n);
+  if (rc) return rc;
+
+  if (p.k_splits > 1) {
+    cudaError_t e = cudaMemset2DAsync(a.out, static_cast<size_t>(a.ldo) * esz, 0, static_cast<size_t>(a.n) * esz, a.m, s);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+
+  const uint32_t work = tiles * p.k_splits;
+  const uint32_t grid = work < static_cast<uint32_t>(sms) ? work : static_cast<uint32_t>(sms);
+  if (block_n == 256) {
+    return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<256, float>(s, ma, mb, p, grid)
+                                          : launch_variant<256, __nv_bfloat16>(s, ma, mb, p, grid);
+  }
+  return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<128, float>(s, ma, mb, p, grid)
+                                        : launch_variant<128, __nv_bfloat16>(s, ma, mb, p, grid);
+}
+
+}  // namespace nvfp4

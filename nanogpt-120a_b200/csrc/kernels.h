@@ -1,0 +1,45 @@
+// Internal launcher declarations shared by the kernel translation units and the C ABI.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/nvfp4_b200.h"
+
+namespace nvfp4 {
+
+// quant_kernels.cu --------------------------------------------------------------------------
+int launch_row_amax(cudaStream_t s, const void* x, int dtype, float* out, uint32_t rows, uint32_t row_len);
+int launch_tensor_amax(cudaStream_t s, const void* x, int dtype, float* chunk_amax, float* out, uint64_t n);
+int launch_nvfp4_amax(cudaStream_t s, const uint8_t* bytes, const uint8_t* scales, const float* gscales, uint32_t rows,
+                      uint32_t cols, int rowwise, int packed, float* chunk_amax, float* out);
+// transform 0: out[0] = max(chunks); 1: out[0] = MS-EDEN global scale of that max
+int launch_amax_from_chunks(cudaStream_t s, const float* chunk_amax, float* out, uint32_t chunk_count, int transform);
+int launch_ms_eden_scale_from_amax(cudaStream_t s, const float* amax, float* out);
+int launch_four_six(cudaStream_t s, const void* x, int dtype, const float* amax, int rowwise, uint32_t rows,
+                    uint32_t cols, uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs);
+int launch_four_six_padded(cudaStream_t s, const float* x, const float* amax, uint8_t* out_fp4, uint8_t* out_scales,
+                           float* out_gs, uint32_t rows, uint32_t cols, uint32_t padded_rows, uint32_t padded_cols,
+                           int transposed);
+int launch_packed_scale_pad(cudaStream_t s, uint8_t* packed, uint32_t rows, uint32_t k_dim);
+int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a);
+int launch_decode(cudaStream_t s, const uint8_t* bytes, const uint8_t* scales, const float* gscales, int rowwise,
+                  int transpose, float* out, uint32_t rows, uint32_t cols);
+int launch_scale_pack(cudaStream_t s, const uint8_t* logical, uint8_t* packed, uint32_t mn, uint32_t k_dim);
+int launch_pad_u4_rows(cudaStream_t s, const uint8_t* src, uint8_t* dst, uint32_t rows, uint32_t padded_rows,
+                       uint32_t cols);
+int launch_pad_f32(cudaStream_t s, const float* src, float* dst, uint32_t rows, uint32_t cols, uint32_t padded_rows,
+                   uint32_t padded_cols, int transpose);
+int launch_crop_f32(cudaStream_t s, const float* src, float* dst, uint32_t rows, uint32_t src_cols, uint32_t dst_cols);
+int launch_postop(cudaStream_t s, float* raw, float* other, const uint8_t* bias_bytes, const uint8_t* bias_scales,
+                  const float* bias_gs, uint32_t rows, uint32_t cols, int mode);
+int launch_bias_grad(cudaStream_t s, const float* e, float* dbias, uint32_t tokens, uint32_t n);
+
+// gemm_tcgen05.cu ---------------------------------------------------------------------------
+int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a);
+// Device status word written by kernels whose bounded waits expired (0 = never).
+uint32_t* device_status_word();
+
+void set_last_error(const char* msg);
+
+}  // namespace nvfp4

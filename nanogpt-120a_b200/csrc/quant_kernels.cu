@@ -1,0 +1,808 @@
+// Bandwidth kernels of the NVFP4 projection path for sm_100a: amax reductions, the
+// four-six quantizer, the MS-EDEN quantizer (row, transposed, NVFP4-source variants),
+// decode, scale-plane packing, padding, post-ops and the bias gradient.
+//
+// Compiled with -fmad=false: the arithmetic below must round exactly like the
+// reference's device code (one rounding per operation, no contraction).
+//
+// Work decomposition differs from the reference on purpose.  The reference gives each
+// element its own lane and reduces 16-groups with shuffles; here one thread owns a whole
+// 16-group (four-six) or 32-chunk (MS-EDEN) in registers, loads it with 128-bit
+// transactions and writes nibbles as 8/16-byte words.  The reduction trees are evaluated
+// in the same order as the reference's xor butterflies, so the bytes are identical.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace nvfp4 {
+
+// ============================================================================
+// amax
+// ============================================================================
+
+template <typename T>
+struct VecTraits;
+template <>
+struct VecTraits<float> {
+  static constexpr int kPerVec = 4;
+};
+template <>
+struct VecTraits<__nv_bfloat16> {
+  static constexpr int kPerVec = 8;
+};
+
+template <typename T>
+__device__ __forceinline__ float vec_amax(const T* p);  // 16-byte aligned, kPerVec elements
+template <>
+__device__ __forceinline__ float vec_amax<float>(const float* p) {
+  float4 t = __ldg(reinterpret_cast<const float4*>(p));
+  return max_f32(max_f32(fabsf(t.x), fabsf(t.y)), max_f32(fabsf(t.z), fabsf(t.w)));
+}
+template <>
+__device__ __forceinline__ float vec_amax<__nv_bfloat16>(const __nv_bfloat16* p) {
+  uint4 t = __ldg(reinterpret_cast<const uint4*>(p));
+  uint32_t w[4] = {t.x, t.y, t.z, t.w};
+  float m = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    m = max_f32(m, fabsf(__uint_as_float(w[j] << 16)));
+    m = max_f32(m, fabsf(__uint_as_float(w[j] & 0xffff0000u)));
+  }
+  return m;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) v = max_f32(v, __shfl_xor_sync(0xffffffffu, v, s));
+  return v;
+}
+
+// One warp per row.  utils/nvfp4/quant/kernels/row_amax.rs:43-64 (max is order independent).
+template <typename T>
+__global__ void __launch_bounds__(256) row_amax_kernel(const T* __restrict__ x, float* __restrict__ out,
+                                                        uint32_t rows, uint32_t row_len) {
+  const uint32_t row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const uint32_t lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const T* p = x + static_cast<size_t>(row) * row_len;
+  constexpr int V = VecTraits<T>::kPerVec;
+  float m = 0.0f;
+  const bool aligned = (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+  uint32_t done = 0;
+  if (aligned) {
+    const uint32_t vecs = row_len / V;
+    for (uint32_t v = lane; v < vecs; v += 32) m = max_f32(m, vec_amax<T>(p + static_cast<size_t>(v) * V));
+    done = vecs * V;
+  }
+  for (uint32_t c = done + lane; c < row_len; c += 32) m = max_f32(m, fabsf(load_as_f32<T>(p, c)));
+  m = warp_max(m);
+  if (lane == 0) out[row] = m;
+}
+
+// One warp per 1024-value chunk: chunk amax plus an atomic max into out[0] (which the
+// launcher zeroes first).  utils/nvfp4/quant/kernels/row_amax.rs:67-101.
+template <typename T>
+__global__ void __launch_bounds__(256) tensor_amax_kernel(const T* __restrict__ x, float* __restrict__ chunk_amax,
+                                                           float* __restrict__ out, uint64_t n) {
+  const uint64_t chunk = static_cast<uint64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const uint32_t lane = threadIdx.x & 31;
+  const uint64_t base = chunk * 1024;
+  if (base >= n) return;
+  constexpr int V = VecTraits<T>::kPerVec;
+  float m = 0.0f;
+  const T* p = x + base;
+  if (base + 1024 <= n && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+#pragma unroll
+    for (int i = 0; i < 1024 / V / 32; ++i) m = max_f32(m, vec_amax<T>(p + (static_cast<size_t>(i) * 32 + lane) * V));
+  } else {
+    const uint32_t count = static_cast<uint32_t>(min(static_cast<uint64_t>(1024), n - base));
+    for (uint32_t i = lane; i < count; i += 32) m = max_f32(m, fabsf(load_as_f32<T>(p, i)));
+  }
+  m = warp_max(m);
+  if (lane == 0) {
+    if (chunk_amax) chunk_amax[chunk] = m;
+    atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(m));
+  }
+}
+
+// amax of a decoded NVFP4 tensor [n/cols][cols], one warp per 1024-value chunk.
+// utils/nvfp4/quant/kernels/ms_eden/amax.rs:23-64.  rowwise: one global scale per row;
+// packed: the scale bytes are in the packed tile layout.
+__global__ void __launch_bounds__(256) nvfp4_amax_kernel(const uint8_t* __restrict__ bytes,
+                                                          const uint8_t* __restrict__ scales,
+                                                          const float* __restrict__ gscales, uint64_t n, uint32_t cols,
+                                                          int rowwise, int packed, float* __restrict__ chunk_amax,
+                                                          float* __restrict__ out) {
+  const uint64_t chunk = static_cast<uint64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const uint32_t lane = threadIdx.x & 31;
+  const uint64_t base = chunk * 1024;
+  if (base >= n) return;
+  float m = 0.0f;
+  const uint64_t end = min(n, base + 1024);
+  // one 16-group (8 bytes, 1 scale) per lane per step
+  for (uint64_t g0 = base + lane * 16ull; g0 < end; g0 += 512) {
+    const uint32_t srow = static_cast<uint32_t>(g0 / cols);
+    const uint32_t skg = static_cast<uint32_t>(g0 - static_cast<uint64_t>(srow) * cols) >> 4;
+    const float gs = rowwise ? gscales[srow] : gscales[0];
+    const float sc = e4m3_value(packed ? scales[packed_scale_offset(srow, skg, cols >> 6)] : scales[g0 >> 4]);
+    const uint2 raw = *reinterpret_cast<const uint2*>(bytes + (g0 >> 1));
+    const uint32_t w[2] = {raw.x, raw.y};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float2 q = e2m1x2_values((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
+      m = max_f32(m, fabsf(q.x * sc * gs));
+      m = max_f32(m, fabsf(q.y * sc * gs));
+    }
+  }
+  m = warp_max(m);
+  if (lane == 0) {
+    if (chunk_amax) chunk_amax[chunk] = m;
+    atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(m));
+  }
+}
+
+// max over chunk values -> out[0] (transform 0) or the MS-EDEN global scale (transform 1).
+// utils/nvfp4/quant/kernels/row_amax.rs:86-101, ms_eden/amax.rs:67-104, utils/quartet.rs:6-12.
+__global__ void __launch_bounds__(256) amax_from_chunks_kernel(const float* __restrict__ chunk_amax,
+                                                                float* __restrict__ out, uint32_t chunk_count,
+                                                                int transform) {
+  __shared__ float partial[8];
+  float m = 0.0f;
+  for (uint32_t i = threadIdx.x; i < chunk_count; i += 256) m = max_f32(m, chunk_amax[i]);
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float r = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r = max_f32(r, partial[i]);
+    if (transform == 1) {
+      const float so = (17.0f / 16.0f) * 0.93f;
+      r = (r == 0.0f) ? 1.0f : r * so / (256.0f * 6.0f);
+    }
+    out[0] = r;
+  }
+}
+
+// out[0] = MS-EDEN global scale of amax[0] (single thread).
+__global__ void ms_eden_scale_from_amax_kernel(const float* __restrict__ amax, float* __restrict__ out) {
+  const float so = (17.0f / 16.0f) * 0.93f;
+  const float a = amax[0];
+  out[0] = (a == 0.0f) ? 1.0f : a * so / (256.0f * 6.0f);
+}
+
+// ============================================================================
+// four-six
+// ============================================================================
+
+__device__ __forceinline__ float four_six_global_scale(float amax) {
+  // utils/nvfp4/quant/kernels/four_six/helpers.rs:33-39 with scale_override = 1.0
+  return nz(amax == 0.0f ? 1.0f : amax * 1.0f / (256.0f * 6.0f));
+}
+
+// Sum over the group of (v - q(v*inv) * (s*gs))^2 in butterfly order (convert.rs:27-35).
+__device__ __forceinline__ float candidate_error16(const float (&v)[16], float s, float gs) {
+  const float inv = inv_scale(s, gs);
+  const float dq = s * gs;
+  float e[16];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t byte = cvt_e2m1x2(v[2 * j + 1] * inv, v[2 * j] * inv);
+    const float2 q = e2m1x2_values(byte);
+    const float d0 = v[2 * j] - q.x * dq;
+    const float d1 = v[2 * j + 1] - q.y * dq;
+    e[2 * j] = d0 * d0;
+    e[2 * j + 1] = d1 * d1;
+  }
+  return butterfly_sum16(e);
+}
+
+// v: one 16-group.  Returns the scale byte and writes the 8 nibble bytes into `packed`.
+// helpers.rs:42-76 and four_six.rs:309-344 of utils/nvfp4/quant/kernels.
+__device__ __forceinline__ uint32_t four_six_group(const float (&v)[16], float gs, uint2& packed) {
+  float ga = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) ga = max_f32(ga, fabsf(v[i]));
+  const float gsn = nz(gs);
+  const uint32_t b6 = cvt_e4m3(ga * 1.0f / (6.0f * gsn + kDenomEps));
+  const uint32_t b4 = cvt_e4m3(ga * 1.0f / (4.0f * gsn + kDenomEps));
+  const float s6 = e4m3_value(b6);
+  const float s4 = e4m3_value(b4);
+  const float err6 = candidate_error16(v, s6, gsn);
+  const float err4 = candidate_error16(v, s4, gsn);
+  const bool six = err6 <= err4;
+  const uint32_t b = six ? b6 : b4;
+  const float inv = inv_scale(six ? s6 : s4, gs);
+  uint32_t w[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t byte = cvt_e2m1x2(v[2 * j + 1] * inv, v[2 * j] * inv);
+    w[j >> 2] |= byte << (8 * (j & 3));
+  }
+  packed = make_uint2(w[0], w[1]);
+  return b;
+}
+
+// One thread per 16-group of a [rows][cols] tensor.
+template <typename T, bool kRowwise, bool kPacked>
+__global__ void __launch_bounds__(256) four_six_kernel(const T* __restrict__ x, const float* __restrict__ amax,
+                                                        uint8_t* __restrict__ out_fp4, uint8_t* __restrict__ out_scales,
+                                                        float* __restrict__ out_gs, uint64_t group_count,
+                                                        uint32_t groups_per_row) {
+  const uint64_t g = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (g >= group_count) return;
+  const uint32_t row = static_cast<uint32_t>(g / groups_per_row);
+  const uint32_t kg = static_cast<uint32_t>(g - static_cast<uint64_t>(row) * groups_per_row);
+  const float gs = four_six_global_scale(amax[kRowwise ? row : 0]);
+  float v[16];
+  Load16<T>::run(x + g * 16, v);
+  uint2 packed;
+  const uint32_t b = four_six_group(v, gs, packed);
+  *reinterpret_cast<uint2*>(out_fp4 + g * 8) = packed;
+  if (kPacked)
+    out_scales[packed_scale_offset(row, kg, groups_per_row >> 2)] = static_cast<uint8_t>(b);
+  else
+    out_scales[g] = static_cast<uint8_t>(b);
+  if (kRowwise ? (kg == 0) : (g == 0)) out_gs[kRowwise ? row : 0] = gs;
+}
+
+// Padded / transposed-padded variants: generic gather, zero outside the source extent.
+// utils/nvfp4/quant/kernels/four_six.rs:110-142,173-211,346-395.
+template <bool kTransposed>
+__global__ void __launch_bounds__(256)
+    four_six_padded_kernel(const float* __restrict__ x, const float* __restrict__ amax, uint8_t* __restrict__ out_fp4,
+                           uint8_t* __restrict__ out_scales, float* __restrict__ out_gs, uint32_t rows, uint32_t cols,
+                           uint32_t padded_cols, uint64_t group_count) {
+  const uint64_t g = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (g >= group_count) return;
+  const float gs = four_six_global_scale(amax[0]);
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const uint64_t idx = g * 16 + i;
+    const uint32_t r = static_cast<uint32_t>(idx / padded_cols);
+    const uint32_t c = static_cast<uint32_t>(idx - static_cast<uint64_t>(r) * padded_cols);
+    if (!kTransposed)
+      v[i] = (r < rows && c < cols) ? x[static_cast<size_t>(r) * cols + c] : 0.0f;
+    else
+      v[i] = (r < cols && c < rows) ? x[static_cast<size_t>(c) * cols + r] : 0.0f;
+  }
+  uint2 packed;
+  const uint32_t b = four_six_group(v, gs, packed);
+  *reinterpret_cast<uint2*>(out_fp4 + g * 8) = packed;
+  out_scales[g] = static_cast<uint8_t>(b);
+  if (g == 0) out_gs[0] = gs;
+}
+
+// Fills the pad rows [rows, padded_rows) of a packed scale plane with 0x38 (= 1.0).
+__global__ void __launch_bounds__(256) packed_scale_pad_kernel(uint8_t* __restrict__ packed, uint32_t rows,
+                                                                uint32_t padded_rows, uint32_t k_groups) {
+  const uint64_t total = static_cast<uint64_t>(padded_rows - rows) * k_groups;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
+       i += static_cast<uint64_t>(gridDim.x) * 256) {
+    const uint32_t r = rows + static_cast<uint32_t>(i / k_groups);
+    const uint32_t kg = static_cast<uint32_t>(i % k_groups);
+    packed[packed_scale_offset(r, kg, k_groups >> 2)] = 0x38;
+  }
+}
+
+// ============================================================================
+// MS-EDEN
+// ============================================================================
+
+// pack/scale.rs:7-30 of utils/nvfp4/quant/kernels/ms_eden.
+__device__ __forceinline__ uint32_t stochastic_e4m3_scale(float value, uint32_t seed, uint32_t group) {
+  const uint32_t cb = cvt_e4m3(value);
+  const float cur = e4m3_value(cb);
+  const uint32_t pb = cb == 0 ? 0u : cb - 1u;
+  const uint32_t nb = cb == 255u ? 255u : cb + 1u;
+  const float prev = e4m3_value(pb);
+  const float next = e4m3_value(nb);
+  const bool above = cur > value;
+  const float up = above ? cur : next;
+  const float down = above ? prev : cur;
+  const uint32_t up_bits = above ? cb : nb;
+  const uint32_t down_bits = above ? pb : cb;
+  const float denom = up - down;
+  const float p = denom == 0.0f ? 0.0f : (value - down) / denom;
+  return random_unit_f32(seed, group) < p ? up_bits : down_bits;
+}
+
+// In-register 32-point Walsh-Hadamard butterfly in the reference's order
+// (pack/hadamard.rs:6-19): stride 1,2,4,8,16; low lane a+b, high lane a-b; then * 1/sqrt(32).
+__device__ __forceinline__ void hadamard32(float (&u)[32]) {
+#pragma unroll
+  for (int stride = 1; stride < 32; stride <<= 1) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if ((j & stride) == 0) {
+        const float a = u[j], b = u[j | stride];
+        u[j] = a + b;
+        u[j | stride] = a - b;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 32; ++j) u[j] = u[j] * 0.17677669f;
+}
+
+// One 16-group of the rotated chunk (pack/payload.rs:15-69): returns the scale byte.
+__device__ __forceinline__ uint32_t ms_eden_group(const float* h, float safe_gs, float so_inv6_unused, float so,
+                                                  float inv6, uint32_t scale_seed, uint32_t group, uint2& packed) {
+  (void)so_inv6_unused;
+  float ga = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) ga = max_f32(ga, fabsf(h[i]));
+  const uint32_t b0 = cvt_e4m3(ga * so * inv6);
+  const float s0 = nz(e4m3_value(b0));
+  const float inv = inv_scale(s0, safe_gs);
+  float num_t[16], den_t[16];
+  uint32_t w[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float x0 = h[2 * j] * inv, x1 = h[2 * j + 1] * inv;
+    const uint32_t byte = cvt_e2m1x2(x1, x0);
+    const float2 q = e2m1x2_values(byte);
+    num_t[2 * j] = x0 * x0;
+    num_t[2 * j + 1] = x1 * x1;
+    den_t[2 * j] = x0 * q.x;
+    den_t[2 * j + 1] = x1 * q.y;
+    w[j >> 2] |= byte << (8 * (j & 3));
+  }
+  const float num = butterfly_sum16(num_t);
+  const float den = butterfly_sum16(den_t);
+  const float corr = den == 0.0f ? 1.0f : num / den;
+  const float s = nz(s0 * corr);
+  packed = make_uint2(w[0], w[1]);
+  return stochastic_e4m3_scale(s, scale_seed, group);
+}
+
+struct MsEdenParams {
+  const void* x;
+  const uint8_t* src_bytes;
+  const uint8_t* src_scales;
+  const float* src_global;
+  int src_packed;  // NVFP4 sources: scale bytes in the packed tile layout
+  uint32_t a;  // F32_ROWS: src_row_len; transposed kinds: source_rows
+  uint32_t b;  // transposed kinds: source_cols
+  uint32_t out_rows;
+  uint32_t dst_row_len;
+  const float* global_scale_dev;
+  float global_scale_host;
+  int use_host_scale;
+  float scale_override;
+  uint32_t sign_seed, scale_seed, col_offset, group_offset;
+  uint8_t* out_fp4;
+  uint8_t* out_scales;
+  float* out_global_scales;
+  float* out_chunk_amax;
+};
+
+// Finishes one chunk whose signed inputs are in u[32]: rotation, two groups, stores.
+template <bool kPacked>
+__device__ __forceinline__ void ms_eden_finish_chunk(float (&u)[32], const MsEdenParams& p, float gs, uint32_t row,
+                                                     uint32_t chunk_in_row, uint64_t chunk) {
+  hadamard32(u);
+  if (p.out_chunk_amax) {
+    float m = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) m = max_f32(m, fabsf(u[j]));
+    p.out_chunk_amax[chunk] = m;
+  }
+  const float safe_gs = nz(gs);
+  const float inv6 = inv_scale(6.0f, safe_gs);
+  const uint32_t group0 = static_cast<uint32_t>(chunk) * 2u + p.group_offset;
+  uint2 lo, hi;
+  const uint32_t sb0 = ms_eden_group(u, safe_gs, 0.0f, p.scale_override, inv6, p.scale_seed, group0, lo);
+  const uint32_t sb1 = ms_eden_group(u + 16, safe_gs, 0.0f, p.scale_override, inv6, p.scale_seed, group0 + 1, hi);
+  *reinterpret_cast<uint4*>(p.out_fp4 + chunk * 16) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+  if (kPacked) {
+    // two consecutive k-groups of the same k-atom: adjacent bytes, 2-byte aligned
+    const size_t off = packed_scale_offset(row, chunk_in_row * 2, p.dst_row_len >> 6);
+    *reinterpret_cast<uint16_t*>(p.out_scales + off) = static_cast<uint16_t>(sb0 | (sb1 << 8));
+  } else {
+    *reinterpret_cast<uint16_t*>(p.out_scales + chunk * 2) = static_cast<uint16_t>(sb0 | (sb1 << 8));
+  }
+  if (chunk_in_row == 0) p.out_global_scales[row] = gs;
+}
+
+// Generic one-thread-per-chunk kernel.  Input gathers follow
+// utils/nvfp4/quant/kernels/ms_eden/input/padded.rs:9-96.
+template <int kKind, typename T, bool kPacked>
+__global__ void __launch_bounds__(128) ms_eden_kernel(const MsEdenParams p) {
+  const uint32_t chunks_per_row = p.dst_row_len >> 5;
+  const uint64_t chunk_count = static_cast<uint64_t>(p.out_rows) * chunks_per_row;
+  const uint64_t chunk = static_cast<uint64_t>(blockIdx.x) * 128 + threadIdx.x;
+  if (chunk >= chunk_count) return;
+  const uint32_t row = static_cast<uint32_t>(chunk / chunks_per_row);
+  const uint32_t chunk_in_row = static_cast<uint32_t>(chunk - static_cast<uint64_t>(row) * chunks_per_row);
+  const uint32_t col0 = chunk_in_row * 32;
+  const float gs = p.use_host_scale ? p.global_scale_host : p.global_scale_dev[0];
+  float u[32];
+  if (kKind == 0) {
+    const T* x = static_cast<const T*>(p.x) + static_cast<size_t>(row) * p.a;
+    const bool full = col0 + 32 <= p.a && ((reinterpret_cast<uintptr_t>(x + col0) & 15u) == 0);
+    if (full) {
+      float lo[16], hi[16];
+      Load16<T>::run(x + col0, lo);
+      Load16<T>::run(x + col0 + 16, hi);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        u[j] = lo[j];
+        u[16 + j] = hi[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) u[j] = (col0 + j < p.a) ? load_as_f32<T>(x, col0 + j) : 0.0f;
+    }
+  } else if (kKind == 1) {
+    const T* x = static_cast<const T*>(p.x);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const uint32_t c = col0 + j;
+      u[j] = (c < p.a) ? load_as_f32<T>(x, static_cast<size_t>(c) * p.b + row) : 0.0f;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const uint32_t c = col0 + j;
+      if (c < p.a) {
+        const float sg = (kKind == 2) ? p.src_global[0] : p.src_global[c];
+        const size_t index = static_cast<size_t>(c) * p.b + row;
+        const uint32_t byte = p.src_bytes[index >> 1];
+        const uint32_t nib = (index & 1) ? (byte >> 4) : (byte & 0xfu);
+        const size_t sidx = p.src_packed ? packed_scale_offset(c, row >> 4, p.b >> 6) : (index >> 4);
+        u[j] = e2m1_value(nib) * e4m3_value(p.src_scales[sidx]) * sg;
+      } else {
+        u[j] = 0.0f;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    if (random_sign_negative(p.sign_seed, col0 + j + p.col_offset)) u[j] = -u[j];  // x * (-1) == -x exactly
+  ms_eden_finish_chunk<kPacked>(u, p, gs, row, chunk_in_row, chunk);
+}
+
+// ============================================================================
+// decode, scale pack, padding, post-ops, bias gradient
+// ============================================================================
+
+// utils/nvfp4/decode/kernels.rs:11-57
+__global__ void __launch_bounds__(256) decode_kernel(const uint8_t* __restrict__ bytes,
+                                                      const uint8_t* __restrict__ scales,
+                                                      const float* __restrict__ gscales, float* __restrict__ out,
+                                                      uint32_t rows, uint32_t cols, int rowwise, int transpose) {
+  const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
+  const uint64_t n = static_cast<uint64_t>(rows) * cols;
+  if (idx >= n) return;
+  const uint32_t r = static_cast<uint32_t>(idx / cols), c = static_cast<uint32_t>(idx % cols);
+  const float v = nvfp4_value(bytes, scales, rowwise ? gscales[r] : gscales[0], idx);
+  out[transpose ? static_cast<size_t>(c) * rows + r : idx] = v;
+}
+
+// utils/nvfp4_tma_matmul/scale_pack.rs:14-40
+__global__ void __launch_bounds__(256) scale_pack_kernel(const uint8_t* __restrict__ logical,
+                                                          uint8_t* __restrict__ packed, uint32_t mn, uint32_t padded_mn,
+                                                          uint32_t k_groups) {
+  const uint64_t total = static_cast<uint64_t>(padded_mn) * k_groups;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
+       i += static_cast<uint64_t>(gridDim.x) * 256) {
+    const uint32_t r = static_cast<uint32_t>(i / k_groups), kg = static_cast<uint32_t>(i % k_groups);
+    packed[packed_scale_offset(r, kg, k_groups >> 2)] = r < mn ? logical[i] : 0x38;
+  }
+}
+
+// utils/nvfp4_tma_matmul/pad.rs:115-210
+__global__ void __launch_bounds__(256) pad_u4_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                                           uint64_t src_bytes, uint64_t dst_bytes) {
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x; i < dst_bytes;
+       i += static_cast<uint64_t>(gridDim.x) * 256)
+    dst[i] = i < src_bytes ? src[i] : 0;
+}
+template <bool kTranspose>
+__global__ void __launch_bounds__(256) pad_f32_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                       uint32_t rows, uint32_t cols, uint32_t padded_rows,
+                                                       uint32_t padded_cols) {
+  const uint64_t total = static_cast<uint64_t>(padded_rows) * padded_cols;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
+       i += static_cast<uint64_t>(gridDim.x) * 256) {
+    const uint32_t r = static_cast<uint32_t>(i / padded_cols), c = static_cast<uint32_t>(i % padded_cols);
+    float v = 0.0f;
+    if (!kTranspose) {
+      if (r < rows && c < cols) v = src[static_cast<size_t>(r) * cols + c];
+    } else {
+      if (r < cols && c < rows) v = src[static_cast<size_t>(c) * cols + r];
+    }
+    dst[i] = v;
+  }
+}
+__global__ void __launch_bounds__(256) crop_f32_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                        uint32_t rows, uint32_t src_cols, uint32_t dst_cols) {
+  const uint64_t total = static_cast<uint64_t>(rows) * dst_cols;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
+       i += static_cast<uint64_t>(gridDim.x) * 256) {
+    const uint32_t r = static_cast<uint32_t>(i / dst_cols), c = static_cast<uint32_t>(i % dst_cols);
+    dst[i] = src[static_cast<size_t>(r) * src_cols + c];
+  }
+}
+
+// gpt/projection_postop.rs:97-162.  mode 0: raw += bias; 1: residual = fma(1, raw + bias, residual);
+// 2: pre = raw + bias (in place), out = max(pre, 0)^2.
+__global__ void __launch_bounds__(256) postop_kernel(float* __restrict__ raw, float* __restrict__ other,
+                                                      const uint8_t* __restrict__ bias_bytes,
+                                                      const uint8_t* __restrict__ bias_scales,
+                                                      const float* __restrict__ bias_gs, uint64_t n, uint32_t cols,
+                                                      int mode) {
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x; i < n;
+       i += static_cast<uint64_t>(gridDim.x) * 256) {
+    const uint32_t col = static_cast<uint32_t>(i % cols);
+    const float bias = nvfp4_value(bias_bytes, bias_scales, bias_gs[0], col);
+    if (mode == 0) {
+      raw[i] = raw[i] + bias;
+    } else if (mode == 1) {
+      other[i] = __fmaf_rn(1.0f, raw[i] + bias, other[i]);
+    } else {
+      const float pre = raw[i] + bias;
+      const float r = max_f32(pre, 0.0f);
+      raw[i] = pre;
+      other[i] = r * r;
+    }
+  }
+}
+
+// gpt/linear_backward/bias.rs:18-69: 8 row lanes x 32 columns per CTA; each row lane sums
+// rows lane, lane+8, ... in order; the 8 lane sums are then added left to right.
+__global__ void __launch_bounds__(256) bias_grad_kernel(const float* __restrict__ e, float* __restrict__ dbias,
+                                                         uint32_t tokens, uint32_t n) {
+  __shared__ float sums[256];
+  const uint32_t lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const uint32_t col = blockIdx.x * 32 + lane;
+  float local = 0.0f;
+  if (col < n) {
+    uint32_t row = w;
+    for (; row + 8 * 7 < tokens; row += 64) {
+      float t[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) t[i] = __ldg(e + static_cast<size_t>(row + 8 * i) * n + col);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) local += t[i];
+    }
+    for (; row < tokens; row += 8) local += __ldg(e + static_cast<size_t>(row) * n + col);
+  }
+  sums[threadIdx.x] = local;
+  __syncthreads();
+  if (w == 0 && col < n) {
+    float s = sums[lane];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) s = s + sums[lane + 32 * i];
+    dbias[col] = s;
+  }
+}
+
+// ============================================================================
+// launchers
+// ============================================================================
+
+static inline uint32_t blocks_for(uint64_t n, uint32_t per_block, uint32_t cap = 0x7fffffffu) {
+  uint64_t b = (n + per_block - 1) / per_block;
+  if (b == 0) b = 1;
+  return static_cast<uint32_t>(b > cap ? cap : b);
+}
+
+#define NVFP4_RETURN_LAST() return static_cast<int>(cudaGetLastError())
+
+int launch_row_amax(cudaStream_t s, const void* x, int dtype, float* out, uint32_t rows, uint32_t row_len) {
+  if (rows == 0) return 0;
+  if (dtype == 0)
+    row_amax_kernel<float><<<blocks_for(rows, 8), 256, 0, s>>>(static_cast<const float*>(x), out, rows, row_len);
+  else
+    row_amax_kernel<__nv_bfloat16>
+        <<<blocks_for(rows, 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), out, rows, row_len);
+  NVFP4_RETURN_LAST();
+}
+
+int launch_tensor_amax(cudaStream_t s, const void* x, int dtype, float* chunk_amax, float* out, uint64_t n) {
+  cudaError_t err = cudaMemsetAsync(out, 0, sizeof(float), s);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  if (n == 0) return 0;
+  const uint32_t grid = blocks_for((n + 1023) / 1024, 8);
+  if (dtype == 0)
+    tensor_amax_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), chunk_amax, out, n);
+  else
+    tensor_amax_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), chunk_amax, out, n);
+  NVFP4_RETURN_LAST();
+}
+
+int launch_nvfp4_amax(cudaStream_t s, const uint8_t* bytes, const uint8_t* scales, const float* gscales, uint32_t rows,
+                      uint32_t cols, int rowwise, int packed, float* chunk_amax, float* out) {
+  const uint64_t n = static_cast<uint64_t>(rows) * cols;
+  cudaError_t err = cudaMemsetAsync(out, 0, sizeof(float), s);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  if (n == 0) return 0;
+  nvfp4_amax_kernel<<<blocks_for((n + 1023) / 1024, 8), 256, 0, s>>>(bytes, scales, gscales, n, cols, rowwise, packed,
+                                                                     chunk_amax, out);
+  NVFP4_RETURN_LAST();
+}
+
+int launch_amax_from_chunks(cudaStream_t s, const float* chunk_amax, float* out, uint32_t chunk_count, int transform) {
+  amax_from_chunks_kernel<<<1, 256, 0, s>>>(chunk_amax, out, chunk_count, transform);
+  NVFP4_RETURN_LAST();
+}
+
+int launch_ms_eden_scale_from_amax(cudaStream_t s, const float* amax, float* out) {
+  ms_eden_scale_from_amax_kernel<<<1, 1, 0, s>>>(amax, out);
+  NVFP4_RETURN_LAST();
+}
+
+template <typename T>
+static int launch_four_six_t(cudaStream_t s, const T* x, const float* amax, int rowwise, uint32_t rows, uint32_t cols,
+                             uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs) {
+  const uint32_t gpr = cols / 16;
+  const uint64_t groups = static_cast<uint64_t>(rows) * gpr;
+  const uint32_t grid = blocks_for(groups, 256);
+  if (rowwise) {
+    if (packed)
+      four_six_kernel<T, true, true><<<grid, 256, 0, s>>>(x, amax, out_fp4, out_scales, out_gs, groups, gpr);
+    else
+      four_six_kernel<T, true, false><<<grid, 256, 0, s>>>(x, amax, out_fp4, out_scales, out_gs, groups, gpr);
+  } else {
+    if (packed)
+      four_six_kernel<T, false, true><<<grid, 256, 0, s>>>(x, amax, out_fp4, out_scales, out_gs, groups, gpr);
+    else
+      four_six_kernel<T, false, false><<<grid, 256, 0, s>>>(x, amax, out_fp4, out_scales, out_gs, groups, gpr);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_four_six(cudaStream_t s, const void* x, int dtype, const float* amax, int rowwise, uint32_t rows,
+                    uint32_t cols, uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs) {
+  if (rows == 0 || cols == 0) return 0;
+  int rc = dtype == 0 ? launch_four_six_t(s, static_cast<const float*>(x), amax, rowwise, rows, cols, out_fp4,
+                                          out_scales, packed, out_gs)
+                      : launch_four_six_t(s, static_cast<const __nv_bfloat16*>(x), amax, rowwise, rows, cols, out_fp4,
+                                          out_scales, packed, out_gs);
+  if (rc) return rc;
+  if (packed) return launch_packed_scale_pad(s, out_scales, rows, cols);
+  return 0;
+}
+
+int launch_packed_scale_pad(cudaStream_t s, uint8_t* packed, uint32_t rows, uint32_t k_dim) {
+  const uint32_t padded = (rows + 127u) / 128u * 128u;
+  if (padded == rows) return 0;
+  const uint32_t kg = k_dim / 16;
+  packed_scale_pad_kernel<<<blocks_for(static_cast<uint64_t>(padded - rows) * kg, 256, 1024), 256, 0, s>>>(packed, rows,
+                                                                                                         padded, kg);
+  NVFP4_RETURN_LAST();
+}
+
+int launch_four_six_padded(cudaStream_t s, const float* x, const float* amax, uint8_t* out_fp4, uint8_t* out_scales,
+                           float* out_gs, uint32_t rows, uint32_t cols, uint32_t padded_rows, uint32_t padded_cols,
+                           int transposed) {
+  const uint64_t groups = static_cast<uint64_t>(padded_rows) * padded_cols / 16;
+  if (groups == 0) return 0;
+  if (transposed)
+    four_six_padded_kernel<true>
+        <<<blocks_for(groups, 256), 256, 0, s>>>(x, amax, out_fp4, out_scales, out_gs, rows, cols, padded_cols, groups);
+  else
+    four_six_padded_kernel<false>
+        <<<blocks_for(groups, 256), 256, 0, s>>>(x, amax, out_fp4, out_scales, out_gs, rows, cols, padded_cols, groups);
+  NVFP4_RETURN_LAST();
+}
+
+template <int kKind, typename T>
+static void launch_ms_eden_t(cudaStream_t s, const MsEdenParams& p, int packed, uint32_t grid) {
+  if (packed)
+    ms_eden_kernel<kKind, T, true><<<grid, 128, 0, s>>>(p);
+  else
+    ms_eden_kernel<kKind, T, false><<<grid, 128, 0, s>>>(p);
+}
+
+int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a) {
+  MsEdenParams p;
+  p.x = a.x;
+  p.src_bytes = a.src_bytes;
+  p.src_scales = a.src_scales;
+  p.src_global = a.src_global;
+  p.src_packed = a.src_scale_layout == NVFP4_SCALES_PACKED;
+  p.a = a.src_kind == NVFP4_SRC_F32_ROWS ? a.cols : a.rows;
+  p.b = a.cols;
+  p.out_rows = a.src_kind == NVFP4_SRC_F32_ROWS ? a.rows : a.cols;
+  p.dst_row_len = a.dst_row_len;
+  p.global_scale_dev = a.global_scale;
+  p.global_scale_host = a.host_global_scale;
+  p.use_host_scale = a.host_global_scale_valid;
+  p.scale_override = a.scale_override;
+  p.sign_seed = a.sign_seed;
+  p.scale_seed = a.scale_seed;
+  p.col_offset = a.col_offset;
+  p.group_offset = a.group_offset;
+  p.out_fp4 = a.out_fp4;
+  p.out_scales = a.out_scales;
+  p.out_global_scales = a.out_global_scales;
+  p.out_chunk_amax = a.out_chunk_amax;
+  const uint64_t chunks = static_cast<uint64_t>(p.out_rows) * (p.dst_row_len / 32);
+  if (chunks == 0) return 0;
+  const uint32_t grid = blocks_for(chunks, 128);
+  const int packed = a.scale_layout == NVFP4_SCALES_PACKED;
+  const bool bf16 = a.src_dtype == NVFP4_DTYPE_BF16;
+  switch (a.src_kind) {
+    case NVFP4_SRC_F32_ROWS:
+      if (bf16) launch_ms_eden_t<0, __nv_bfloat16>(s, p, packed, grid);
+      else launch_ms_eden_t<0, float>(s, p, packed, grid);
+      break;
+    case NVFP4_SRC_F32_TRANSPOSED:
+      if (bf16) launch_ms_eden_t<1, __nv_bfloat16>(s, p, packed, grid);
+      else launch_ms_eden_t<1, float>(s, p, packed, grid);
+      break;
+    case NVFP4_SRC_NVFP4_TRANSPOSED:
+      launch_ms_eden_t<2, float>(s, p, packed, grid);
+      break;
+    case NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED:
+      launch_ms_eden_t<3, float>(s, p, packed, grid);
+      break;
+    default:
+      return 1;
+  }
+  int rc = static_cast<int>(cudaGetLastError());
+  if (rc) return rc;
+  if (packed) return launch_packed_scale_pad(s, a.out_scales, p.out_rows, p.dst_row_len);
+  return 0;
+}
+
+int launch_decode(cudaStream_t s, const uint8_t* bytes, const uint8_t* scales, const float* gscales, int rowwise,
+                  int transpose, float* out, uint32_t rows, uint32_t cols) {
+  const uint64_t n = static_cast<uint64_t>(rows) * cols;
+  if (n == 0) return 0;
+  decode_kernel<<<blocks_for(n, 256), 256, 0, s>>>(bytes, scales, gscales, out, rows, cols, rowwise, transpose);
+  NVFP4_RETURN_LAST();
+}
+
+int launch_scale_pack(cudaStream_t s, const uint8_t* logical, uint8_t* packed, uint32_t mn, uint32_t k_dim) {
+  const uint32_t padded = (mn + 127u) / 128u * 128u, kg = k_dim / 16;
+  const uint64_t total = static_cast<uint64_t>(padded) * kg;
+  if (total == 0) return 0;
+  scale_pack_kernel<<<blocks_for(total, 256, 148 * 16), 256, 0, s>>>(logical, packed, mn, padded, kg);
+  NVFP4_RETURN_LAST();
+}
+
+int launch_pad_u4_rows(cudaStream_t s, const uint8_t* src, uint8_t* dst, uint32_t rows, uint32_t padded_rows,
+                       uint32_t cols) {
+  const uint64_t sb = static_cast<uint64_t>(rows) * cols / 2, db = static_cast<uint64_t>(padded_rows) * cols / 2;
+  if (db == 0) return 0;
+  pad_u4_rows_kernel<<<blocks_for(db, 256, 148 * 16), 256, 0, s>>>(src, dst, sb, db);
+  NVFP4_RETURN_LAST();
+}
+
+int launch_pad_f32(cudaStream_t s, const float* src, float* dst, uint32_t rows, uint32_t cols, uint32_t padded_rows,
+                   uint32_t padded_cols, int transpose) {
+  const uint64_t total = static_cast<uint64_t>(padded_rows) * padded_cols;
+  if (total == 0) return 0;
+  if (transpose)
+    pad_f32_kernel<true><<<blocks_for(total, 256, 148 * 16), 256, 0, s>>>(src, dst, rows, cols, padded_rows, padded_cols);
+  else
+    pad_f32_kernel<false><<<blocks_for(total, 256, 148 * 16), 256, 0, s>>>(src, dst, rows, cols, padded_rows, padded_cols);
+  NVFP4_RETURN_LAST();
+}
+
+int launch_crop_f32(cudaStream_t s, const float* src, float* dst, uint32_t rows, uint32_t src_cols, uint32_t dst_cols) {
+  const uint64_t total = static_cast<uint64_t>(rows) * dst_cols;
+  if (total == 0) return 0;
+  crop_f32_kernel<<<blocks_for(total, 256, 148 * 16), 256, 0, s>>>(src, dst, rows, src_cols, dst_cols);
+  NVFP4_RETURN_LAST();
+}
+
+int launch_postop(cudaStream_t s, float* raw, float* other, const uint8_t* bias_bytes, const uint8_t* bias_scales,
+                  const float* bias_gs, uint32_t rows, uint32_t cols, int mode) {
+  const uint64_t n = static_cast<uint64_t>(rows) * cols;
+  if (n == 0) return 0;
+  postop_kernel<<<blocks_for(n, 256, 148 * 16), 256, 0, s>>>(raw, other, bias_bytes, bias_scales, bias_gs, n, cols, mode);
+  NVFP4_RETURN_LAST();
+}
+
+int launch_bias_grad(cudaStream_t s, const float* e, float* dbias, uint32_t tokens, uint32_t n) {
+  if (n == 0) return 0;
+  bias_grad_kernel<<<blocks_for(n, 32), 256, 0, s>>>(e, dbias, tokens, n);
+  NVFP4_RETURN_LAST();
+}
+
+}  // namespace nvfp4
