@@ -525,8 +525,10 @@ class Nvfp4GemmModule:
         if out is None:
             out = torch.empty((m, ldo), dtype=out_dtype, device=a.bytes.device)
         g = GemmArgs()
-        g.a_bytes, g.a_scales, g.a_global = _ptr(a.bytes), _ptr(_packed_scales(a)), _ptr(a.global_scales)
-        g.b_bytes, g.b_scales, g.b_global = _ptr(b.bytes), _ptr(_packed_scales(b)), _ptr(b.global_scales)
+        # keep the (possibly temporary) packed planes referenced until the launch is enqueued
+        a_packed, b_packed = _packed_scales(a), _packed_scales(b)
+        g.a_bytes, g.a_scales, g.a_global = _ptr(a.bytes), _ptr(a_packed), _ptr(a.global_scales)
+        g.b_bytes, g.b_scales, g.b_global = _ptr(b.bytes), _ptr(b_packed), _ptr(b.global_scales)
         g.out, g.aux, g.bias = _ptr(out), _ptr(aux), _ptr(bias)
         g.m, g.n, g.k, g.ldo = m, n, k, ldo
         g.global_scale_mode = mode
@@ -541,7 +543,8 @@ class Nvfp4GemmModule:
         out = torch.empty((a.rows, b.rows if not extra_dims else extra_dims[0]), dtype=torch.float32,
                           device=a.bytes.device)
         dims = [a.rows, a.cols, out.shape[1]] + ([b.rows] if extra_dims else [])
-        _call(name, _stream(), _ptr(a.bytes), _ptr(_packed_scales(a)), _ptr(b.bytes), _ptr(_packed_scales(b)),
+        a_packed, b_packed = _packed_scales(a), _packed_scales(b)
+        _call(name, _stream(), _ptr(a.bytes), _ptr(a_packed), _ptr(b.bytes), _ptr(b_packed),
               _ptr(out), *dims, _ptr(a.global_scales), _ptr(b.global_scales))
         return out
 
