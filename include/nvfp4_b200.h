@@ -64,6 +64,8 @@ extern "C" {
 
 /* Version of this ABI (bumped on incompatible change). */
 int nvfp4_abi_version(void);
+/* Number of kernels this library has launched in this process (host-side tally). */
+uint64_t nvfp4_launch_count(void);
 /* Text for the last error recorded on the calling thread (host pointer, never NULL). */
 const char* nvfp4_last_error(void);
 /* Reads and clears the device-side status word written by kernels whose bounded waits gave
@@ -312,6 +314,15 @@ int nvfp4_gemm_tma_nvfp4_rowwise_a_scale_padded_output(
     uint32_t output_dim, uint32_t padded_output_dim, const float* a_global_scales,
     const float* b_global_scale);
 
+/* Measurement aid (no reference counterpart; off by default).  Between begin and end every GEMM
+ * launch of this process is bracketed by a CUDA event pair recorded on the launch stream (up to
+ * max_records launches; the events are created by begin, once).  end waits for the recorded
+ * launches and returns their count, summed duration and summed 2*m*n*k, and optionally the
+ * per-launch values (host arrays of `capacity` entries). */
+int nvfp4_gemm_timing_begin(uint32_t max_records);
+int nvfp4_gemm_timing_end(uint32_t* count, double* total_ms, double* total_flops, float* per_launch_ms,
+                          double* per_launch_flops, uint32_t capacity);
+
 /* post-ops as separate passes (gpt/projection_postop.rs:50-162); bias is NVFP4 encoded ----- */
 int nvfp4_projection_bias_inplace(void* stream, float* raw, const uint8_t* bias_bytes,
                                   const uint8_t* bias_scales, const float* bias_global_scale,
@@ -329,6 +340,9 @@ int nvfp4_projection_relu2_inplace(void* stream, float* pre_activation, float* o
  * summed in the reference's fixed order (bit-exact). */
 int nvfp4_linear_bias_grad(void* stream, const float* e, float* dbias, uint32_t token_count,
                            uint32_t output_dim);
+/* Same sum, same order, for a bf16 dY (no reference counterpart: the reference is f32-only). */
+int nvfp4_linear_bias_grad_bf16(void* stream, const void* e, float* dbias, uint32_t token_count,
+                                uint32_t output_dim);
 
 /* Scratch of one linear backward (gpt/linear_backward/args/ms_eden/scratch.rs:11-160).  All
  * buffers are caller owned; sizes with ok = padded_k(output_dim), tk = padded_k(token_count):
@@ -360,8 +374,9 @@ typedef struct nvfp4_linear_backward_args {
   const float* x_globals;
   nvfp4_ms_eden_operand e_h, e_t_h, weight_t_h, input_t_h;
   void* dinput;                      /* [token][in]                                           */
+  int dinput_dtype;                  /* NVFP4_DTYPE_*                                         */
   void* dweight;                     /* [out][in]                                             */
-  int grad_dtype;                    /* NVFP4_DTYPE_* of dinput / dweight                     */
+  int dweight_dtype;                 /* NVFP4_DTYPE_* (f32 lets long-K GEMMs split K)         */
   float* dbias;                      /* f32[out] or NULL                                      */
   uint32_t token_count, input_dim, output_dim;
   uint32_t sign_seed, scale_seed;

@@ -74,7 +74,7 @@ class LinearBackwardArgs(Structure):
         ("w_global", c_void_p), ("x_bytes", c_void_p), ("x_scales", c_void_p), ("x_scale_layout", c_int),
         ("x_globals", c_void_p), ("e_h", MsEdenOperand),
         ("e_t_h", MsEdenOperand), ("weight_t_h", MsEdenOperand), ("input_t_h", MsEdenOperand), ("dinput", c_void_p),
-        ("dweight", c_void_p), ("grad_dtype", c_int), ("dbias", c_void_p), ("token_count", c_uint32),
+        ("dinput_dtype", c_int), ("dweight", c_void_p), ("dweight_dtype", c_int), ("dbias", c_void_p), ("token_count", c_uint32),
         ("input_dim", c_uint32), ("output_dim", c_uint32), ("sign_seed", c_uint32), ("scale_seed", c_uint32),
         ("precomputed_e_amax_chunks", c_uint32), ("token_offset", c_uint32), ("e_global_scale_override", c_void_p),
     ]
@@ -122,14 +122,19 @@ _SIGNATURES = {
     "nvfp4_gemm_tma_nvfp4_device_scales_and_global_scale_buffers": [_P] * 6 + [_U] * 3 + [_P] * 2,
     "nvfp4_gemm_tma_nvfp4_rowwise_a_scale_and_global_scale_buffer": [_P] * 6 + [_U] * 3 + [_P] * 2,
     "nvfp4_gemm_tma_nvfp4_rowwise_a_scale_padded_output": [_P] * 6 + [_U] * 4 + [_P] * 2,
+    "nvfp4_gemm_timing_begin": [_U],
+    "nvfp4_gemm_timing_end": [POINTER(c_uint32), POINTER(ctypes.c_double), POINTER(ctypes.c_double),
+                              POINTER(c_float), POINTER(ctypes.c_double), _U],
     "nvfp4_projection_bias_inplace": [_P, _P, _P, _P, _P, _U, _U],
     "nvfp4_projection_residual_add": [_P, _P, _P, _P, _P, _P, _U, _U],
     "nvfp4_projection_relu2_inplace": [_P, _P, _P, _P, _P, _P, _U, _U],
     "nvfp4_linear_bias_grad": [_P, _P, _P, _U, _U],
+    "nvfp4_linear_bias_grad_bf16": [_P, _P, _P, _U, _U],
     "nvfp4_linear_backward_ms_eden": [_P, POINTER(LinearBackwardArgs)],
 }
 _SPECIAL = {
     "nvfp4_abi_version": (c_int, []),
+    "nvfp4_launch_count": (ctypes.c_uint64, []),
     "nvfp4_last_error": (c_char_p, []),
     "nvfp4_padded_k": (c_uint32, [_U]),
     "nvfp4_scale_padded_mn_extent": (c_uint32, [_U]),
@@ -203,6 +208,26 @@ def scale_packed_len(mn: int, k: int) -> int:
 
 def tensor_amax_chunks(n: int) -> int:
     return (n + 1023) // 1024
+
+
+def launch_count() -> int:
+    """Kernels launched by the library so far in this process."""
+    return int(library().nvfp4_launch_count())
+
+
+def gemm_timing_begin(max_records: int) -> None:
+    """Start bracketing every GEMM launch with CUDA events on its stream (measurement aid)."""
+    _call("nvfp4_gemm_timing_begin", max_records)
+
+
+def gemm_timing_end(capacity: int = 0):
+    """Returns (launches, total_ms, total_flops, per_launch_ms list, per_launch_flops list)."""
+    n, ms, fl = c_uint32(0), ctypes.c_double(0), ctypes.c_double(0)
+    per_ms = (c_float * max(capacity, 1))()
+    per_fl = (ctypes.c_double * max(capacity, 1))()
+    _call("nvfp4_gemm_timing_end", ctypes.byref(n), ctypes.byref(ms), ctypes.byref(fl), per_ms, per_fl, capacity)
+    k = min(int(n.value), capacity)
+    return int(n.value), float(ms.value), float(fl.value), list(per_ms)[:k], list(per_fl)[:k]
 
 
 def read_device_status() -> int:
@@ -621,10 +646,10 @@ class LinearBackwardModule:
 
     def linear_bias_grad(self, e: torch.Tensor, dbias: Optional[torch.Tensor] = None) -> torch.Tensor:
         _require_cuda()
-        assert e.dtype == torch.float32
         tokens, n = e.shape
         dbias = torch.empty(n, dtype=torch.float32, device=e.device) if dbias is None else dbias
-        _call("nvfp4_linear_bias_grad", _stream(), _ptr(e), _ptr(dbias), tokens, n)
+        name = "nvfp4_linear_bias_grad" if _dtype_code(e) == DTYPE_F32 else "nvfp4_linear_bias_grad_bf16"
+        _call(name, _stream(), _ptr(e), _ptr(dbias), tokens, n)
         return dbias
 
     def backward_ms_eden(self, *, e: torch.Tensor, weight: Nvfp4Tensor, input: Nvfp4Tensor,
@@ -652,7 +677,8 @@ class LinearBackwardModule:
         a.x_scale_layout = SCALES_PACKED if input.packed else SCALES_LOGICAL
         a.e_h, a.e_t_h = scratch._c(scratch.e_h), scratch._c(scratch.e_t_h)
         a.weight_t_h, a.input_t_h = scratch._c(scratch.weight_t_h), scratch._c(scratch.input_t_h)
-        a.dinput, a.dweight, a.grad_dtype = _ptr(dinput), _ptr(dweight), _dtype_code(dinput)
+        a.dinput, a.dinput_dtype = _ptr(dinput), _dtype_code(dinput)
+        a.dweight, a.dweight_dtype = _ptr(dweight), _dtype_code(dweight)
         a.dbias = _ptr(dbias if want_dbias else None)
         a.token_count, a.input_dim, a.output_dim = tokens, in_dim, out_dim
         a.sign_seed, a.scale_seed = sign_seed & 0xFFFFFFFF, scale_seed & 0xFFFFFFFF

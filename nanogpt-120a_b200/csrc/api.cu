@@ -1,6 +1,7 @@
 // extern "C" boundary of the NVFP4 projection path: argument checks, composition of the
 // kernels into the reference's host-level operations, and nothing else.  Each entry cites
 // the reference method it replaces in include/nvfp4_b200.h.
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 
@@ -9,6 +10,9 @@
 namespace nvfp4 {
 
 static thread_local char g_last_error[256] = "";
+static std::atomic<uint64_t> g_launches{0};
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 void set_last_error(const char* msg) {
   std::strncpy(g_last_error, msg, sizeof(g_last_error) - 1);
@@ -33,6 +37,7 @@ using namespace nvfp4;
 extern "C" {
 
 int nvfp4_abi_version(void) { return 1; }
+uint64_t nvfp4_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 const char* nvfp4_last_error(void) { return g_last_error; }
 
 int nvfp4_read_device_status(void* stream, uint32_t* status_out) {
@@ -420,6 +425,12 @@ int nvfp4_gemm_tma_nvfp4_rowwise_a_scale_padded_output(
                     output_dim, output_dim, NVFP4_GS_ROWWISE_A, a_global_scales, b_global_scale);
 }
 
+int nvfp4_gemm_timing_begin(uint32_t max_records) { return gemm_timing_begin(max_records); }
+int nvfp4_gemm_timing_end(uint32_t* count, double* total_ms, double* total_flops, float* per_launch_ms,
+                          double* per_launch_flops, uint32_t capacity) {
+  return gemm_timing_end(count, total_ms, total_flops, per_launch_ms, per_launch_flops, capacity);
+}
+
 // ---- post-ops ---------------------------------------------------------------------------
 int nvfp4_projection_bias_inplace(void* stream, float* raw, const uint8_t* bias_bytes, const uint8_t* bias_scales,
                                   const float* bias_gs, uint32_t rows, uint32_t cols) {
@@ -437,7 +448,10 @@ int nvfp4_projection_relu2_inplace(void* stream, float* pre_activation, float* o
 
 // ---- linear backward --------------------------------------------------------------------
 int nvfp4_linear_bias_grad(void* stream, const float* e, float* dbias, uint32_t token_count, uint32_t output_dim) {
-  return launch_bias_grad(S(stream), e, dbias, token_count, output_dim);
+  return launch_bias_grad(S(stream), e, NVFP4_DTYPE_F32, dbias, token_count, output_dim);
+}
+int nvfp4_linear_bias_grad_bf16(void* stream, const void* e, float* dbias, uint32_t token_count, uint32_t output_dim) {
+  return launch_bias_grad(S(stream), e, NVFP4_DTYPE_BF16, dbias, token_count, output_dim);
 }
 
 int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args* a) {
@@ -448,10 +462,9 @@ int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args
   cudaStream_t s = S(stream);
   int rc;
 
-  // 1. dbias (reference order; f32 dY only)
+  // 1. dbias (summed in the reference's order)
   if (a->dbias) {
-    if (a->e_dtype != NVFP4_DTYPE_F32) return invalid("linear_backward: dbias needs an f32 dY");
-    rc = launch_bias_grad(s, static_cast<const float*>(a->e), a->dbias, T, O);
+    rc = launch_bias_grad(s, a->e, a->e_dtype, a->dbias, T, O);
     if (rc) return rc;
   }
 
@@ -520,7 +533,7 @@ int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args
   g.global_scale_mode = NVFP4_GS_ROWWISE_A;
   g.weight_global_scale = 1.0f;
   g.epilogue = NVFP4_EPI_NONE;
-  g.out_dtype = a->grad_dtype;
+  g.out_dtype = a->dinput_dtype;
   g.a_bytes = a->e_h.bytes;
   g.a_scales = a->e_h.scales_packed;
   g.a_global = a->e_h.global_scales;
@@ -541,6 +554,7 @@ int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args
   g.b_scales = a->input_t_h.scales_packed;
   g.b_global = a->input_t_h.global_scale;
   g.out = a->dweight;
+  g.out_dtype = a->dweight_dtype;
   g.m = O;
   g.n = I;
   g.k = tk;

@@ -24,6 +24,7 @@
 #include <cuda_runtime.h>
 
 #include <mutex>
+#include <vector>
 
 #include "kernels.h"
 
@@ -538,6 +539,18 @@ int sm_count() {
   return count;
 }
 
+// Optional event timing of GEMM launches (off by default; a measurement aid for benchmarks).
+struct GemmTimingRecord {
+  cudaEvent_t start, stop;
+  double flops;
+};
+struct GemmTiming {
+  std::mutex mu;
+  bool enabled = false;
+  std::vector<GemmTimingRecord> pool;  // events created once by timing_begin
+  size_t used = 0;
+} g_timing;
+
 template <int kBlockN, typename OutT>
 int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, uint32_t grid) {
   using C = Cfg<kBlockN>;
@@ -548,11 +561,60 @@ int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   });
   if (attr_err != cudaSuccess) return static_cast<int>(attr_err);
+  GemmTimingRecord* rec = nullptr;
+  if (g_timing.enabled) {
+    std::lock_guard<std::mutex> lock(g_timing.mu);
+    if (g_timing.enabled && g_timing.used < g_timing.pool.size()) rec = &g_timing.pool[g_timing.used++];
+  }
+  if (rec) {
+    rec->flops = 2.0 * p.m * p.n * p.k;
+    cudaEventRecord(rec->start, s);
+  }
   nvfp4_gemm_tcgen05_kernel<kBlockN, OutT><<<grid, kThreads, C::kSmemBytes, s>>>(ma, mb, p);
-  return static_cast<int>(cudaGetLastError());
+  count_launch();
+  const int rc = static_cast<int>(cudaGetLastError());
+  if (rec) cudaEventRecord(rec->stop, s);
+  return rc;
 }
 
 }  // namespace
+
+int gemm_timing_begin(uint32_t max_records) {
+  std::lock_guard<std::mutex> lock(g_timing.mu);
+  while (g_timing.pool.size() < max_records) {
+    GemmTimingRecord r;
+    r.flops = 0;
+    cudaError_t e = cudaEventCreate(&r.start);
+    if (e == cudaSuccess) e = cudaEventCreate(&r.stop);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_timing.pool.push_back(r);
+  }
+  g_timing.used = 0;
+  g_timing.enabled = true;
+  return 0;
+}
+
+int gemm_timing_end(uint32_t* count, double* total_ms, double* total_flops, float* per_launch_ms,
+                    double* per_launch_flops, uint32_t capacity) {
+  std::lock_guard<std::mutex> lock(g_timing.mu);
+  g_timing.enabled = false;
+  double ms_sum = 0, fl_sum = 0;
+  for (size_t i = 0; i < g_timing.used; ++i) {
+    float ms = 0;
+    cudaError_t e = cudaEventSynchronize(g_timing.pool[i].stop);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, g_timing.pool[i].start, g_timing.pool[i].stop);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    ms_sum += ms;
+    fl_sum += g_timing.pool[i].flops;
+    if (per_launch_ms && i < capacity) per_launch_ms[i] = ms;
+    if (per_launch_flops && i < capacity) per_launch_flops[i] = g_timing.pool[i].flops;
+  }
+  if (count) *count = static_cast<uint32_t>(g_timing.used);
+  if (total_ms) *total_ms = ms_sum;
+  if (total_flops) *total_flops = fl_sum;
+  g_timing.used = 0;
+  return 0;
+}
 
 uint32_t* device_status_word() {
   uint32_t* ptr = nullptr;

@@ -33,13 +33,18 @@ int launch_pad_f32(cudaStream_t s, const float* src, float* dst, uint32_t rows, 
 int launch_crop_f32(cudaStream_t s, const float* src, float* dst, uint32_t rows, uint32_t src_cols, uint32_t dst_cols);
 int launch_postop(cudaStream_t s, float* raw, float* other, const uint8_t* bias_bytes, const uint8_t* bias_scales,
                   const float* bias_gs, uint32_t rows, uint32_t cols, int mode);
-int launch_bias_grad(cudaStream_t s, const float* e, float* dbias, uint32_t tokens, uint32_t n);
+int launch_bias_grad(cudaStream_t s, const void* e, int dtype, float* dbias, uint32_t tokens, uint32_t n);
 
 // gemm_tcgen05.cu ---------------------------------------------------------------------------
 int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a);
+int gemm_timing_begin(uint32_t max_records);
+int gemm_timing_end(uint32_t* count, double* total_ms, double* total_flops, float* per_launch_ms,
+                    double* per_launch_flops, uint32_t capacity);
 // Device status word written by kernels whose bounded waits expired (0 = never).
 uint32_t* device_status_word();
 
 void set_last_error(const char* msg);
+// Host-side tally of kernel launches made by this library (read through nvfp4_launch_count).
+void count_launch();
 
 }  // namespace nvfp4

@@ -552,7 +552,8 @@ __global__ void __launch_bounds__(256) postop_kernel(float* __restrict__ raw, fl
 
 // gpt/linear_backward/bias.rs:18-69: 8 row lanes x 32 columns per CTA; each row lane sums
 // rows lane, lane+8, ... in order; the 8 lane sums are then added left to right.
-__global__ void __launch_bounds__(256) bias_grad_kernel(const float* __restrict__ e, float* __restrict__ dbias,
+template <typename T>
+__global__ void __launch_bounds__(256) bias_grad_kernel(const T* __restrict__ e, float* __restrict__ dbias,
                                                          uint32_t tokens, uint32_t n) {
   __shared__ float sums[256];
   const uint32_t lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -563,11 +564,11 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(const float* __restrict_
     for (; row + 8 * 7 < tokens; row += 64) {
       float t[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) t[i] = __ldg(e + static_cast<size_t>(row + 8 * i) * n + col);
+      for (int i = 0; i < 8; ++i) t[i] = load_as_f32<T>(e, static_cast<size_t>(row + 8 * i) * n + col);
 #pragma unroll
       for (int i = 0; i < 8; ++i) local += t[i];
     }
-    for (; row < tokens; row += 8) local += __ldg(e + static_cast<size_t>(row) * n + col);
+    for (; row < tokens; row += 8) local += load_as_f32<T>(e, static_cast<size_t>(row) * n + col);
   }
   sums[threadIdx.x] = local;
   __syncthreads();
@@ -589,7 +590,11 @@ static inline uint32_t blocks_for(uint64_t n, uint32_t per_block, uint32_t cap =
   return static_cast<uint32_t>(b > cap ? cap : b);
 }
 
-#define NVFP4_RETURN_LAST() return static_cast<int>(cudaGetLastError())
+#define NVFP4_RETURN_LAST() \
+  do {                       \
+    count_launch();          \
+    return static_cast<int>(cudaGetLastError()); \
+  } while (0)
 
 int launch_row_amax(cudaStream_t s, const void* x, int dtype, float* out, uint32_t rows, uint32_t row_len) {
   if (rows == 0) return 0;
@@ -651,6 +656,7 @@ static int launch_four_six_t(cudaStream_t s, const T* x, const float* amax, int 
     else
       four_six_kernel<T, false, false><<<grid, 256, 0, s>>>(x, amax, out_fp4, out_scales, out_gs, groups, gpr);
   }
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -743,6 +749,7 @@ int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a) {
     default:
       return 1;
   }
+  count_launch();
   int rc = static_cast<int>(cudaGetLastError());
   if (rc) return rc;
   if (packed) return launch_packed_scale_pad(s, a.out_scales, p.out_rows, p.dst_row_len);
@@ -799,9 +806,13 @@ int launch_postop(cudaStream_t s, float* raw, float* other, const uint8_t* bias_
   NVFP4_RETURN_LAST();
 }
 
-int launch_bias_grad(cudaStream_t s, const float* e, float* dbias, uint32_t tokens, uint32_t n) {
+int launch_bias_grad(cudaStream_t s, const void* e, int dtype, float* dbias, uint32_t tokens, uint32_t n) {
   if (n == 0) return 0;
-  bias_grad_kernel<<<blocks_for(n, 32), 256, 0, s>>>(e, dbias, tokens, n);
+  if (dtype == NVFP4_DTYPE_F32)
+    bias_grad_kernel<float><<<blocks_for(n, 32), 256, 0, s>>>(static_cast<const float*>(e), dbias, tokens, n);
+  else
+    bias_grad_kernel<__nv_bfloat16>
+        <<<blocks_for(n, 32), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(e), dbias, tokens, n);
   NVFP4_RETURN_LAST();
 }
 

@@ -1,0 +1,228 @@
+"""The training-step projection set of a GPT-2 shaped model, driven through the C ABI.
+
+One `step()` runs, for every block linear (c_attn, attention c_proj, mlp fc, mlp proj) and
+the tied LM head, the forward projection Y = X.W^T + b and the backward pass dX = dY.W,
+dW = dY^T.X (+ dbias), with every operand quantized to NVFP4 exactly as the reference's
+graph does it: four-six for activations (rowwise scale) and weights (tensor scale),
+MS-EDEN with counter-RNG stochastic scale rounding for dY, W^T and X^T.  It mirrors the
+call sequence of crates/gpt2-nvfp4/src/types/{l2_attention,l3_mlp}/forward.rs,
+types/model/final_logits.rs and backward/{linear,mlp/run,attention/*,final_head/run}.rs,
+restricted to the projections (attention core, LayerNorm, loss and optimizer are outside
+this path; their outputs are stood in for by seeded synthetic tensors).
+
+Tokens are the shardable axis: every rank holds `tokens` rows of X / dY and a full replica
+of the weights, and the per-layer dW (+dbias) buckets are summed over ranks with one NCCL
+all-reduce each, issued as soon as the layer's backward is enqueued.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from . import (EPI_BIAS, EPI_NONE, EPI_RELU2, LinearBackwardModule, LinearBackwardScratch, Nvfp4GemmModule,
+               Nvfp4QuantModule, Nvfp4Tensor, padded_k, scale_packed_len)
+
+MASK64 = (1 << 64) - 1
+
+
+class Gpt2Rng:
+    """splitmix64 stream handing out the (sign, scale) seeds of each linear
+    (crates/gpt2-nvfp4/src/random.rs:1-27)."""
+
+    def __init__(self, seed: int):
+        self.state = seed & MASK64
+
+    def next_u64(self) -> int:
+        self.state = (self.state + 0x9E3779B97F4A7C15) & MASK64
+        z = self.state
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & MASK64
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & MASK64
+        return z ^ (z >> 31)
+
+    def next_u32(self) -> int:
+        return self.next_u64() & 0xFFFFFFFF
+
+
+@dataclass(frozen=True)
+class ModelShape:
+    name: str
+    n_layer: int
+    d_model: int
+    d_mlp: int
+    vocab: int
+
+    def linears(self) -> List[Tuple[str, int, int, int]]:
+        """(name, in, out, epilogue) of one block, in forward order."""
+        d, h = self.d_model, self.d_mlp
+        return [("c_attn", d, 3 * d, EPI_BIAS), ("attn_c_proj", d, d, EPI_BIAS), ("mlp_fc", d, h, EPI_RELU2),
+                ("mlp_proj", h, d, EPI_BIAS)]
+
+    def macs_per_token(self) -> int:
+        per_layer = sum(i * o for _, i, o, _ in self.linears())
+        return self.n_layer * per_layer + self.d_model * self.vocab
+
+    def flops_per_token(self) -> int:
+        return 6 * self.macs_per_token()  # forward 2, dX 2, dW 2
+
+
+GPT2_SMALL = ModelShape("gpt2-small-proj-set", 12, 768, 3072, 32000)
+GPT2_MEDIUM = ModelShape("gpt2-medium-proj-set", 24, 1024, 4096, 32000)
+SHAPES = {"gpt2-small": GPT2_SMALL, "gpt2-medium": GPT2_MEDIUM}
+
+
+def _randn_bf16(shape, std, seed, device):
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std).to(torch.bfloat16)
+
+
+class _Linear:
+    """One projection: master weight, its per-step NVFP4 form, the saved quantized input,
+    caller-owned backward scratch and gradient views."""
+
+    def __init__(self, name, in_dim, out_dim, epilogue, tokens, device, seed, has_bias=True):
+        self.name, self.in_dim, self.out_dim, self.epilogue = name, in_dim, out_dim, epilogue
+        self.weight = _randn_bf16((out_dim, in_dim), 0.02, seed, device)
+        self.bias = _randn_bf16((out_dim,), 0.02, seed + 1, device).float() if has_bias else None
+        n = out_dim * in_dim
+        u8 = dict(dtype=torch.uint8, device=device)
+        f32 = dict(dtype=torch.float32, device=device)
+        self.wq = Nvfp4Tensor(torch.empty(n // 2, **u8), torch.empty(scale_packed_len(out_dim, in_dim), **u8),
+                              torch.empty(1, **f32), out_dim, in_dim, packed=True, rowwise=False)
+        self.w_chunk_amax = torch.empty((n + 1023) // 1024, **f32)
+        self.w_amax = torch.empty(1, **f32)
+        nx = tokens * in_dim
+        self.xq = Nvfp4Tensor(torch.empty(nx // 2, **u8), torch.empty(scale_packed_len(tokens, in_dim), **u8),
+                              torch.empty(tokens, **f32), tokens, in_dim, packed=True, rowwise=True)
+        self.x_amax = torch.empty(tokens, **f32)
+        self.dweight: Optional[torch.Tensor] = None  # views into the layer's gradient bucket
+        self.dbias: Optional[torch.Tensor] = None
+
+
+class ProjectionSet:
+    def __init__(self, shape: ModelShape, tokens: int, device, seed: int = 1234, token_offset: int = 0,
+                 process_group=None, grad_dtype: torch.dtype = torch.bfloat16):
+        assert tokens % 128 == 0, "token shards are multiples of 128 rows (scale tiles stay intact)"
+        self.shape, self.tokens, self.device = shape, tokens, device
+        self.token_offset = token_offset
+        self.pg = process_group
+        self.grad_dtype = grad_dtype
+        self.quant, self.gemm, self.bwd = Nvfp4QuantModule(), Nvfp4GemmModule(), LinearBackwardModule()
+        self.rng = Gpt2Rng(seed)
+        d, h, v = shape.d_model, shape.d_mlp, shape.vocab
+        self.layers: List[List[_Linear]] = []
+        self.buckets: List[torch.Tensor] = []
+        for l in range(shape.n_layer):
+            lin = [_Linear(n, i, o, e, tokens, device, seed * 1000 + l * 10 + j)
+                   for j, (n, i, o, e) in enumerate(shape.linears())]
+            size = sum(x.out_dim * x.in_dim + x.out_dim for x in lin)
+            bucket = torch.zeros(size, dtype=torch.float32, device=device)
+            off = 0
+            for x in lin:
+                x.dweight = bucket[off: off + x.out_dim * x.in_dim].view(x.out_dim, x.in_dim)
+                off += x.out_dim * x.in_dim
+                x.dbias = bucket[off: off + x.out_dim]
+                off += x.out_dim
+            self.layers.append(lin)
+            self.buckets.append(bucket)
+        self.lm_head = _Linear("lm_head", d, v, EPI_NONE, tokens, device, seed * 1000 + 999, has_bias=False)
+        head_bucket = torch.zeros(v * d, dtype=torch.float32, device=device)
+        self.lm_head.dweight = head_bucket.view(v, d)
+        self.buckets.append(head_bucket)
+
+        # Synthetic stand-ins for the tensors the rest of the model would produce: one activation
+        # per input width, one upstream gradient per output width (larger than L2 at bench sizes).
+        widths_in = sorted({i for _, i, _, _ in shape.linears()} | {d})
+        widths_out = sorted({o for _, _, o, _ in shape.linears()} | {v})
+        self.x: Dict[int, torch.Tensor] = {w: _randn_bf16((tokens, w), 1.0, seed + 7 * w + token_offset, device)
+                                           for w in widths_in}
+        self.dy: Dict[int, torch.Tensor] = {w: _randn_bf16((tokens, w), 1e-3, seed + 11 * w + token_offset, device)
+                                            for w in widths_out}
+        self.y: Dict[int, torch.Tensor] = {w: torch.empty((tokens, w), dtype=torch.bfloat16, device=device)
+                                           for w in widths_out}
+        self.pre: Dict[int, torch.Tensor] = {h: torch.empty((tokens, h), dtype=torch.bfloat16, device=device)}
+        self.dx: Dict[int, torch.Tensor] = {w: torch.empty((tokens, w), dtype=grad_dtype, device=device)
+                                            for w in widths_in}
+        # backward scratch is shared by all linears of the same (in, out) shape
+        self.scratch: Dict[Tuple[int, int], LinearBackwardScratch] = {}
+        for _, i, o, _ in shape.linears() + [("lm_head", d, v, EPI_NONE)]:
+            if (i, o) not in self.scratch:
+                self.scratch[(i, o)] = LinearBackwardScratch(tokens, i, o, device)
+        self.gemm_events: List[Tuple[torch.cuda.Event, torch.cuda.Event, int]] = []
+        self.record_gemm_events = False
+        self._pending = []
+
+    # ---- pieces -------------------------------------------------------------------------
+    def all_linears(self) -> List[_Linear]:
+        return [x for lin in self.layers for x in lin] + [self.lm_head]
+
+    def quantize_weights(self) -> None:
+        """Weights are re-quantized from their masters every step (four-six, tensor scale)."""
+        for lin in self.all_linears():
+            self.quant.tensor_amax(lin.weight, lin.w_chunk_amax, lin.w_amax)
+            self.quant.quantize_four_six(lin.weight, amax=lin.w_amax, rowwise=False, packed=True, out=lin.wq)
+
+    def _forward_linear(self, lin: _Linear) -> None:
+        x = self.x[lin.in_dim]
+        self.quant.row_amax(x, lin.x_amax)
+        self.quant.quantize_four_six(x, amax=lin.x_amax, rowwise=True, packed=True, out=lin.xq)  # saved for backward
+        aux = self.pre[lin.out_dim] if lin.epilogue == EPI_RELU2 else None
+        self._timed_gemm(lambda: self.gemm.gemm(lin.xq, lin.wq, bias=lin.bias, epilogue=lin.epilogue,
+                                                out=self.y[lin.out_dim], aux=aux),
+                         2 * self.tokens * lin.in_dim * lin.out_dim)
+
+    def _backward_linear(self, lin: _Linear) -> None:
+        sign_seed, scale_seed = self.rng.next_u32(), self.rng.next_u32()
+        self.bwd.backward_ms_eden(e=self.dy[lin.out_dim], weight=lin.wq, input=lin.xq,
+                                  scratch=self.scratch[(lin.in_dim, lin.out_dim)], sign_seed=sign_seed,
+                                  scale_seed=scale_seed, want_dbias=lin.dbias is not None,
+                                  dinput=self.dx[lin.in_dim], dweight=lin.dweight, dbias=lin.dbias,
+                                  token_offset=self.token_offset)
+
+    def _timed_gemm(self, fn, flops: int) -> None:
+        if self.record_gemm_events:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            self.gemm_events.append((a, b, flops))
+        else:
+            fn()
+
+    def _reduce(self, bucket: torch.Tensor) -> None:
+        if self.pg is not None:
+            import torch.distributed as dist
+
+            self._pending.append(dist.all_reduce(bucket, group=self.pg, async_op=True))
+
+    # ---- one step -----------------------------------------------------------------------
+    def forward(self) -> None:
+        for lin in self.layers:
+            for x in lin:
+                self._forward_linear(x)
+        self._forward_linear(self.lm_head)
+
+    def backward(self) -> None:
+        self._backward_linear(self.lm_head)
+        self._reduce(self.buckets[-1])
+        for l in range(self.shape.n_layer - 1, -1, -1):
+            for x in reversed(self.layers[l]):
+                self._backward_linear(x)
+            self._reduce(self.buckets[l])
+        for work in self._pending:
+            work.wait()
+        self._pending.clear()
+
+    def step(self) -> None:
+        self.quantize_weights()
+        self.forward()
+        self.backward()
+
+    def flops_per_step(self) -> int:
+        return self.shape.flops_per_token() * self.tokens
+
+    def result_digest(self) -> torch.Tensor:
+        """A small device vector summarising the step's outputs (read back by the e2e timing)."""
+        return torch.stack([b.abs().sum() for b in self.buckets])

@@ -244,3 +244,31 @@ def bias_grad(e):
     out = np.empty(n, np.float32)
     lib().oracle_bias_grad(_p(e), _p(out), c_uint32(tokens), c_uint32(n))
     return out
+
+
+def linear_forward_backward(x, w, bias, dy, sign_seed, scale_seed, epi=1):
+    """One projection, forward and backward, entirely on the CPU oracle: the composition of
+    crates/gpt2-nvfp4/src/types/l3_mlp/forward.rs:15-67 (quantize X rowwise, W tensor scale, GEMM +
+    epilogue) and crates/cuda-kernels/src/gpt/linear_backward/ms_eden.rs:15-55 (dbias, MS-EDEN of
+    dY rows / dY^T / W^T / X^T, dX and dW GEMMs).  x [T, K], w [N, K], dy [T, N] float32 arrays.
+    Returns (y, dx, dw, dbias)."""
+    x, w, dy = _f32(x), _f32(w), _f32(dy)
+    tokens, in_dim = x.shape
+    out_dim = w.shape[0]
+    xq = four_six(x, row_amax(x), rowwise=True)
+    wq = four_six(w, tensor_amax(w)[1], rowwise=False)
+    y = gemm(xq, wq, tokens, in_dim, out_dim, mode=2, bias=bias, epi=epi if bias is not None else 0)
+    dbias = bias_grad(dy)
+    ok, tk = padded_k(out_dim), padded_k(tokens)
+    gs_e = ms_eden_global_scale(float(tensor_amax(dy)[1][0]))
+    e_h = ms_eden(0, dy, tokens, ok, gs_e, sign_seed, scale_seed, want_chunk_amax=False)
+    e_t = ms_eden(1, dy, out_dim, tk, gs_e, sign_seed, scale_seed ^ 0x85EBCA6B, want_chunk_amax=False)
+    gs_w = ms_eden_global_scale(float(nvfp4_amax(*wq, out_dim, in_dim, False)[1][0]))
+    w_t = ms_eden(2, (*wq, out_dim, in_dim), in_dim, ok, gs_w, sign_seed, scale_seed ^ 0x9E3779B9,
+                  want_chunk_amax=False)
+    gs_x = ms_eden_global_scale(float(nvfp4_amax(*xq, tokens, in_dim, True)[1][0]))
+    x_t = ms_eden(3, (*xq, tokens, in_dim), in_dim, tk, gs_x, sign_seed, scale_seed ^ 0xC2B2AE35,
+                  want_chunk_amax=False)
+    dx = gemm(e_h[:3], (w_t[0], w_t[1], np.array([gs_w], np.float32)), tokens, ok, in_dim, mode=2)
+    dw = gemm(e_t[:3], (x_t[0], x_t[1], np.array([gs_x], np.float32)), out_dim, tk, in_dim, mode=2)
+    return y, dx, dw, dbias
