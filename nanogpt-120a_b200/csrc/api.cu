@@ -111,7 +111,15 @@ int nvfp4_quantize_four_six(void* stream, const void* x, int dtype, const float*
 }
 
 // ---- MS-EDEN ----------------------------------------------------------------------------
+static int validate_ms_eden(const nvfp4_ms_eden_args* a);
+
 int nvfp4_ms_eden_quantize(void* stream, const nvfp4_ms_eden_args* a) {
+  int rc = validate_ms_eden(a);
+  if (rc) return rc;
+  return launch_ms_eden(S(stream), *a);
+}
+
+static int validate_ms_eden(const nvfp4_ms_eden_args* a) {
   if (!a) return invalid("ms_eden: null args");
   if (a->dst_row_len % 32 != 0) return invalid("ms_eden: dst_row_len must be a multiple of 32");
   if (a->scale_layout == NVFP4_SCALES_PACKED && a->dst_row_len % 64 != 0)
@@ -120,7 +128,19 @@ int nvfp4_ms_eden_quantize(void* stream, const nvfp4_ms_eden_args* a) {
   const uint32_t src_len = a->src_kind == NVFP4_SRC_F32_ROWS ? a->cols : a->rows;
   if (src_len > a->dst_row_len) return invalid("ms_eden: source row longer than dst_row_len");
   if (!a->host_global_scale_valid && !a->global_scale) return invalid("ms_eden: no global scale given");
-  return launch_ms_eden(S(stream), *a);
+  return 0;
+}
+
+// Row operand + transposed operand of one matrix in a single pass (same scale, same signs).
+static int ms_eden_pair(void* stream, nvfp4_ms_eden_args rows, nvfp4_ms_eden_args transposed,
+                        float* col_sum_partials = nullptr) {
+  rows.src_kind = NVFP4_SRC_F32_ROWS;
+  transposed.src_kind = NVFP4_SRC_F32_TRANSPOSED;
+  int rc = validate_ms_eden(&rows);
+  if (rc) return rc;
+  rc = validate_ms_eden(&transposed);
+  if (rc) return rc;
+  return launch_ms_eden_pair(S(stream), rows, transposed, col_sum_partials);
 }
 
 static nvfp4_ms_eden_args rows_args(const float* x, uint8_t* out_fp4, uint8_t* out_scales, float* out_gss,
@@ -253,14 +273,14 @@ int nvfp4_fp32_pair_to_nvfp4_quartet_backward_ms_eden_derived_device_scale_no_ch
   }
   rc = launch_amax_from_chunks(S(stream), out_chunk_amax, out_global_scale, chunk_count, 1);
   if (rc) return rc;
-  rc = nvfp4_fp32_to_nvfp4_ms_eden_device_scale(stream, x, out_fp4, out_scales, out_global_scales, nullptr,
-                                                out_global_scale, row_count, src_row_len, dst_row_len, kQuartetSO,
-                                                sign_seed, scale_seed);
-  if (rc) return rc;
-  return nvfp4_fp32_transpose_to_nvfp4_ms_eden_device_scale(stream, x, transpose_out_fp4, transpose_out_scales,
-                                                            transpose_out_global_scales, nullptr, out_global_scale,
-                                                            row_count, src_row_len, transpose_dst_row_len, kQuartetSO,
-                                                            sign_seed, transpose_scale_seed);
+  nvfp4_ms_eden_args r = rows_args(x, out_fp4, out_scales, out_global_scales, nullptr, row_count, src_row_len,
+                                   dst_row_len, kQuartetSO, sign_seed, scale_seed);
+  r.global_scale = out_global_scale;
+  nvfp4_ms_eden_args t = rows_args(x, transpose_out_fp4, transpose_out_scales, transpose_out_global_scales, nullptr,
+                                   row_count, src_row_len, transpose_dst_row_len, kQuartetSO, sign_seed,
+                                   transpose_scale_seed);
+  t.global_scale = out_global_scale;
+  return ms_eden_pair(stream, r, t);
 }
 
 static int nvfp4_source_transpose(void* stream, int kind, const uint8_t* in_bytes, const uint8_t* in_scales,
@@ -462,11 +482,14 @@ int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args
   cudaStream_t s = S(stream);
   int rc;
 
-  // 1. dbias (summed in the reference's order)
-  if (a->dbias) {
-    rc = launch_bias_grad(s, a->e, a->e_dtype, a->dbias, T, O);
-    if (rc) return rc;
-  }
+  // 1. dbias.  When the dY quantization below runs tiled, the column sums ride along with it:
+  //    each row tile leaves its partial sums in the (not yet written) dinput buffer and a small
+  //    kernel adds them up in tile order -- no extra pass over dY.  Otherwise the sum is done
+  //    by the stand-alone kernel in the reference's order.
+  const size_t dx_bytes = static_cast<size_t>(T) * I * (a->dinput_dtype == NVFP4_DTYPE_F32 ? 4 : 2);
+  const size_t partial_bytes = static_cast<size_t>(ms_eden_pair_row_tiles(T)) * O * sizeof(float);
+  bool fuse_dbias = a->dbias != nullptr && partial_bytes <= dx_bytes &&
+                    (reinterpret_cast<uintptr_t>(a->dinput) & 3u) == 0;
 
   // 2. dY: tensor amax -> one global scale shared by the row and the transposed operand
   const uint64_t ne = static_cast<uint64_t>(T) * O;
@@ -501,19 +524,28 @@ int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args
   q.out_fp4 = a->e_h.bytes;
   q.out_scales = a->e_h.scales_packed;
   q.out_global_scales = a->e_h.global_scales;
-  rc = nvfp4_ms_eden_quantize(stream, &q);
-  if (rc) return rc;
   //    rows of dY^T (K = tokens): sign index = token
-  q.src_kind = NVFP4_SRC_F32_TRANSPOSED;
-  q.dst_row_len = tk;
-  q.scale_seed = a->scale_seed ^ 0x85ebca6bu;  // gpt/linear_backward/ms_eden/quantize/pair.rs:36
-  q.col_offset = a->token_offset;
-  q.group_offset = 0;
-  q.out_fp4 = a->e_t_h.bytes;
-  q.out_scales = a->e_t_h.scales_packed;
-  q.out_global_scales = a->e_t_h.global_scales;
-  rc = nvfp4_ms_eden_quantize(stream, &q);
+  nvfp4_ms_eden_args qt = q;
+  qt.src_kind = NVFP4_SRC_F32_TRANSPOSED;
+  qt.dst_row_len = tk;
+  qt.scale_seed = a->scale_seed ^ 0x85ebca6bu;  // gpt/linear_backward/ms_eden/quantize/pair.rs:36
+  qt.col_offset = a->token_offset;
+  qt.group_offset = 0;
+  qt.out_fp4 = a->e_t_h.bytes;
+  qt.out_scales = a->e_t_h.scales_packed;
+  qt.out_global_scales = a->e_t_h.global_scales;
+  fuse_dbias = fuse_dbias && ms_eden_pair_is_tiled(q, qt);
+  if (a->dbias && !fuse_dbias) {
+    rc = launch_bias_grad(s, a->e, a->e_dtype, a->dbias, T, O);
+    if (rc) return rc;
+  }
+  float* partials = fuse_dbias ? static_cast<float*>(a->dinput) : nullptr;
+  rc = ms_eden_pair(stream, q, qt, partials);  // one pass over dY for both orientations (+ column sums)
   if (rc) return rc;
+  if (fuse_dbias) {
+    rc = launch_col_sum_reduce(s, partials, a->dbias, ms_eden_pair_row_tiles(T), O);
+    if (rc) return rc;
+  }
 
   // 3. W^T and 4. X^T from their NVFP4 forms (quantize/transpose.rs:14-93)
   rc = nvfp4_source_transpose(stream, NVFP4_SRC_NVFP4_TRANSPOSED, a->w_bytes, a->w_scales, a->w_global,

@@ -40,6 +40,7 @@ constexpr int kKAtomsPerStage = 4;                // 64-element k-atoms (one MMA
 constexpr int kAStageBytes = kBlockM * kBlockKBytes;
 constexpr int kSfTileBytes = 512;                 // 128 rows x 4 scale bytes
 constexpr int kSfaStageBytes = kKAtomsPerStage * kSfTileBytes;
+constexpr int kStoreStageBytes = kBlockM * 128;   // one epilogue sub-tile: 128 rows x 128 bytes
 constexpr int kTmemCols = 512;
 constexpr int kThreads = 256;
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;  // 2 s
@@ -51,14 +52,15 @@ struct Cfg {
   static constexpr int kNBlocks128 = kBlockN / 128;
   static constexpr int kBStageBytes = kBlockN * kBlockKBytes;
   static constexpr int kSfbStageBytes = kNBlocks128 * kKAtomsPerStage * kSfTileBytes;
-  static constexpr int kStages = kBlockN == 128 ? 6 : 4;
+  static constexpr int kStages = kBlockN == 128 ? 5 : 3;
   static constexpr int kAccStages = kBlockN == 128 ? 2 : 1;
   static constexpr int kTmemSfa = 256;                       // column of the A scale factors
   static constexpr int kTmemSfb = 256 + 4 * kKAtomsPerStage;  // column of the B scale factors
   static constexpr int kSfbColsPerAtom = kBlockN / 32;
   static constexpr int kSmemData = kStages * (kAStageBytes + kBStageBytes);
   static constexpr int kSmemSf = kStages * (kSfaStageBytes + kSfbStageBytes);
-  static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kSmemData + kSmemSf + 256 /*barriers*/;
+  static constexpr int kSmemBytes =
+      1024 /*alignment slack*/ + kSmemData + kSmemSf + 2 * kStoreStageBytes + 256 /*barriers*/;
   static_assert(kTmemSfb + kSfbColsPerAtom * kKAtomsPerStage <= kTmemCols, "tensor memory overflow");
   static_assert(kAccStages * kBlockN <= 256, "accumulators overlap the scale-factor columns");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory overflow");
@@ -75,7 +77,7 @@ struct GemmParams {
   uint32_t m, n, k, ldo;
   uint32_t num_m_blocks, num_n_blocks, k_atoms, sfb_blocks128;
   uint32_t k_splits, k_tiles_per_split, num_k_tiles;
-  int mode, epilogue, vec_store;
+  int mode, epilogue, vec_store, tma_store;
   float weight;
 };
 
@@ -140,6 +142,24 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
                : "memory");
 }
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int32_t x, int32_t y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -248,12 +268,49 @@ __device__ __forceinline__ float load_out<__nv_bfloat16>(const __nv_bfloat16* p)
   return __bfloat162float(*p);
 }
 
+// One row (128 bytes) of an epilogue sub-tile into the staging buffer, 16-byte chunks XOR-swizzled
+// with the row index exactly as the SWIZZLE_128B tensor map of the output expects.
+template <typename OutT>
+struct SubTile;
+template <>
+struct SubTile<float> {
+  static constexpr int kCols = 32;
+  __device__ __forceinline__ static void stage(uint32_t row_addr, uint32_t row, const float* v) {
+#pragma unroll
+    for (uint32_t c = 0; c < 8; ++c) {
+      const uint32_t dst = row_addr + ((c ^ (row & 7u)) << 4);
+      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(v[4 * c]), "f"(v[4 * c + 1]),
+                   "f"(v[4 * c + 2]), "f"(v[4 * c + 3])
+                   : "memory");
+    }
+  }
+};
+template <>
+struct SubTile<__nv_bfloat16> {
+  static constexpr int kCols = 64;
+  __device__ __forceinline__ static void stage(uint32_t row_addr, uint32_t row, const float* v) {
+#pragma unroll
+    for (uint32_t c = 0; c < 8; ++c) {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * c + 2 * j], v[8 * c + 2 * j + 1]);
+        w[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      const uint32_t dst = row_addr + ((c ^ (row & 7u)) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                   : "memory");
+    }
+  }
+};
+
 // ---- the kernel -----------------------------------------------------------------------------
 
 template <int kBlockN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
     nvfp4_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                              const GemmParams p) {
+                              const __grid_constant__ CUtensorMap tmap_out,
+                              const __grid_constant__ CUtensorMap tmap_aux, const GemmParams p) {
   using C = Cfg<kBlockN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -263,7 +320,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t smem_b = smem_a + C::kStages * kAStageBytes;
   const uint32_t smem_sfa = smem_b + C::kStages * C::kBStageBytes;
   const uint32_t smem_sfb = smem_sfa + C::kStages * kSfaStageBytes;
-  const uint32_t smem_bar = smem_sfb + C::kStages * C::kSfbStageBytes;
+  const uint32_t smem_store = smem_sfb + C::kStages * C::kSfbStageBytes;  // 2 x 16 KB, 1024-byte aligned
+  const uint32_t smem_bar = smem_store + 2 * kStoreStageBytes;
   // barrier block: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], tmem base, abort flag
   const uint32_t bar_full = smem_bar;
   const uint32_t bar_empty = bar_full + 8 * C::kStages;
@@ -277,6 +335,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_a)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_b)) : "memory");
+    if (p.tma_store) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_out)) : "memory");
+      if (p.aux) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_aux)) : "memory");
+    }
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
@@ -410,7 +472,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t ew = warp - 4;
     OutT* out = static_cast<OutT*>(p.out);
     OutT* aux = static_cast<OutT*>(p.aux);
-    uint32_t acc = 0, acc_phase = 0;
+    uint32_t acc = 0, acc_phase = 0, store_buf = 0;
     const float gb = p.mode == NVFP4_GS_NONE ? 1.0f : __ldg(p.b_global);
     const float ga_scalar = p.mode == NVFP4_GS_TENSOR ? __ldg(p.a_global) : 1.0f;
     for (uint32_t work = blockIdx.x; work < num_work; work += gridDim.x) {
@@ -424,6 +486,70 @@ __global__ void __launch_bounds__(kThreads, 1)
       // reference order: (weight * a_scale) * b_scale, then acc * scale
       const float scale = __fmul_rn(__fmul_rn(p.weight, ga), gb);
       const uint32_t taddr_row = tmem_base + acc * kBlockN + ((ew * 32u) << 16);
+      if (p.tma_store) {
+        // Sub-tiles of 128 rows x 128 bytes go through a two-deep shared-memory ring and leave
+        // with TMA stores (TMA reduce-add for split-K partial sums); rows / columns outside the
+        // matrix are clipped by the tensor map.
+        constexpr int kSub = SubTile<OutT>::kCols;
+        const uint32_t tile_row = ew * 32 + lane;
+        const bool elected = threadIdx.x == 128;
+#pragma unroll 1
+        for (int c = 0; c < kBlockN; c += kSub) {
+          const uint32_t col0 = n_blk * kBlockN + c;
+          if (col0 >= p.n) break;  // uniform across the epilogue warps
+          float v[kSub];
+#pragma unroll
+          for (int h = 0; h < kSub / 32; ++h) {
+            uint32_t r[32];
+            tcgen05_ld_32x32b_x32(taddr_row + c + 32 * h, r);
+            tcgen05_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[32 * h + i] = __fmul_rn(__uint_as_float(r[i]), scale);
+          }
+          if (p.epilogue != NVFP4_EPI_NONE && (p.k_splits == 1 || split == 0)) {
+#pragma unroll
+            for (int i = 0; i < kSub; i += 4) {
+              float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (col0 + i + 3 < p.n) {
+                b4 = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + i));
+              } else {
+                if (col0 + i < p.n) b4.x = __ldg(p.bias + col0 + i);
+                if (col0 + i + 1 < p.n) b4.y = __ldg(p.bias + col0 + i + 1);
+                if (col0 + i + 2 < p.n) b4.z = __ldg(p.bias + col0 + i + 2);
+              }
+              v[i] = __fadd_rn(v[i], b4.x);
+              v[i + 1] = __fadd_rn(v[i + 1], b4.y);
+              v[i + 2] = __fadd_rn(v[i + 2], b4.z);
+              v[i + 3] = __fadd_rn(v[i + 3], b4.w);
+            }
+          }
+          const int passes = (p.epilogue == NVFP4_EPI_RELU2 && p.aux) ? 2 : 1;
+          for (int pass = 0; pass < passes; ++pass) {
+            const bool is_pre = passes == 2 && pass == 0;
+            if (p.epilogue == NVFP4_EPI_RELU2 && !is_pre) {
+#pragma unroll
+              for (int i = 0; i < kSub; ++i) {
+                const float t = fmaxf(v[i], 0.0f);
+                v[i] = __fmul_rn(t, t);
+              }
+            }
+            const uint32_t buf = smem_store + store_buf * kStoreStageBytes;
+            SubTile<OutT>::stage(buf + tile_row * 128, tile_row, v);
+            fence_proxy_async_smem();
+            if (elected) bulk_wait_group_read0();  // every earlier store has left shared memory
+            epilogue_barrier();
+            if (elected) {
+              const CUtensorMap* map = is_pre ? &tmap_aux : &tmap_out;
+              if (p.k_splits > 1)
+                tma_reduce_add_2d(map, buf, static_cast<int32_t>(col0), static_cast<int32_t>(m_blk * kBlockM));
+              else
+                tma_store_2d(map, buf, static_cast<int32_t>(col0), static_cast<int32_t>(m_blk * kBlockM));
+              bulk_commit_group();
+            }
+            store_buf ^= 1u;
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < kBlockN; c += 32) {
         uint32_t r[32];
@@ -467,6 +593,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
+      }  // direct-store path
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * acc);
@@ -475,6 +602,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         acc_phase ^= 1u;
       }
     }
+    if (p.tma_store && threadIdx.x == 128) bulk_wait_group0();  // stores complete before the CTA exits
   }
 
   // ===================== teardown =====================
@@ -528,6 +656,21 @@ int encode_operand_map(CUtensorMap* map, const uint8_t* base, uint32_t rows, uin
   return 0;
 }
 
+// Output matrix [rows][ld] of f32 / bf16; box = 128 bytes x 128 rows, 128-byte swizzle.
+int encode_output_map(CUtensorMap* map, void* base, int dtype, uint32_t rows, uint32_t cols, uint32_t ld) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return static_cast<int>(cudaErrorNotSupported);
+  const size_t esz = dtype == NVFP4_DTYPE_F32 ? 4 : 2;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * esz};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / esz), kBlockM};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  CUresult r = fn(map, dtype == NVFP4_DTYPE_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  base, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(cudaErrorInvalidValue);
+}
+
 int sm_count() {
   static int count = 0;
   if (count == 0) {
@@ -552,7 +695,8 @@ struct GemmTiming {
 } g_timing;
 
 template <int kBlockN, typename OutT>
-int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, uint32_t grid) {
+int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
+                   const CUtensorMap& mx, const GemmParams& p, uint32_t grid) {
   using C = Cfg<kBlockN>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
@@ -570,7 +714,7 @@ int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb,
     rec->flops = 2.0 * p.m * p.n * p.k;
     cudaEventRecord(rec->start, s);
   }
-  nvfp4_gemm_tcgen05_kernel<kBlockN, OutT><<<grid, kThreads, C::kSmemBytes, s>>>(ma, mb, p);
+  nvfp4_gemm_tcgen05_kernel<kBlockN, OutT><<<grid, kThreads, C::kSmemBytes, s>>>(ma, mb, mo, mx, p);
   count_launch();
   const int rc = static_cast<int>(cudaGetLastError());
   if (rec) cudaEventRecord(rec->stop, s);
@@ -690,11 +834,20 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
                     ? 1
                     : 0;
 
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, mo, mx;
   int rc = encode_operand_map(&ma, a.a_bytes, a.m, a.k, kBlockM);
   if (rc) return rc;
   rc = encode_operand_map(&mb, a.b_bytes, a.n, a.k, block_n);
   if (rc) return rc;
+  // TMA-store epilogue whenever the output satisfies the tensor-map rules (16-byte aligned base
+  // and row pitch); the in-place residual epilogue and odd layouts use direct stores.
+  p.tma_store = (p.vec_store && a.epilogue != NVFP4_EPI_RESIDUAL) ? 1 : 0;
+  mo = ma;
+  mx = ma;
+  if (p.tma_store) {
+    if (encode_output_map(&mo, a.out, a.out_dtype, a.m, a.n, a.ldo) != 0) p.tma_store = 0;
+    if (p.tma_store && a.aux && encode_output_map(&mx, a.aux, a.out_dtype, a.m, a.n, a.ldo) != 0) p.tma_store = 0;
+  }
 
   if (p.k_splits > 1) {
     cudaError_t e = cudaMemset2DAsync(a.out, static_cast<size_t>(a.ldo) * esz, 0, static_cast<size_t>(a.n) * esz, a.m, s);
@@ -704,11 +857,11 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   const uint32_t work = tiles * p.k_splits;
   const uint32_t grid = work < static_cast<uint32_t>(sms) ? work : static_cast<uint32_t>(sms);
   if (block_n == 256) {
-    return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<256, float>(s, ma, mb, p, grid)
-                                          : launch_variant<256, __nv_bfloat16>(s, ma, mb, p, grid);
+    return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<256, float>(s, ma, mb, mo, mx, p, grid)
+                                          : launch_variant<256, __nv_bfloat16>(s, ma, mb, mo, mx, p, grid);
   }
-  return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<128, float>(s, ma, mb, p, grid)
-                                        : launch_variant<128, __nv_bfloat16>(s, ma, mb, p, grid);
+  return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<128, float>(s, ma, mb, mo, mx, p, grid)
+                                        : launch_variant<128, __nv_bfloat16>(s, ma, mb, mo, mx, p, grid);
 }
 
 }  // namespace nvfp4

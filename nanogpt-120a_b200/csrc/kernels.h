@@ -23,6 +23,13 @@ int launch_four_six_padded(cudaStream_t s, const float* x, const float* amax, ui
                            int transposed);
 int launch_packed_scale_pad(cudaStream_t s, uint8_t* packed, uint32_t rows, uint32_t k_dim);
 int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a);
+// Pair quantization; when col_sum_partials != nullptr (and ms_eden_pair_is_tiled) it also writes the
+// per-row-tile column sums [ms_eden_pair_row_tiles(rows)][cols] for launch_col_sum_reduce.
+int launch_ms_eden_pair(cudaStream_t s, const nvfp4_ms_eden_args& rows, const nvfp4_ms_eden_args& transposed,
+                        float* col_sum_partials = nullptr);
+bool ms_eden_pair_is_tiled(const nvfp4_ms_eden_args& rows, const nvfp4_ms_eden_args& transposed);
+uint32_t ms_eden_pair_row_tiles(uint32_t rows);
+int launch_col_sum_reduce(cudaStream_t s, const float* partials, float* dbias, uint32_t tiles, uint32_t n);
 int launch_decode(cudaStream_t s, const uint8_t* bytes, const uint8_t* scales, const float* gscales, int rowwise,
                   int transpose, float* out, uint32_t rows, uint32_t cols);
 int launch_scale_pack(cudaStream_t s, const uint8_t* logical, uint8_t* packed, uint32_t mn, uint32_t k_dim);

@@ -78,33 +78,51 @@ __global__ void __launch_bounds__(256) row_amax_kernel(const T* __restrict__ x, 
   if (lane == 0) out[row] = m;
 }
 
-// One warp per 1024-value chunk: chunk amax plus an atomic max into out[0] (which the
-// launcher zeroes first).  utils/nvfp4/quant/kernels/row_amax.rs:67-101.
-template <typename T>
-__global__ void __launch_bounds__(256) tensor_amax_kernel(const T* __restrict__ x, float* __restrict__ chunk_amax,
-                                                           float* __restrict__ out, uint64_t n) {
-  const uint64_t chunk = static_cast<uint64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  const uint32_t lane = threadIdx.x & 31;
-  const uint64_t base = chunk * 1024;
-  if (base >= n) return;
-  constexpr int V = VecTraits<T>::kPerVec;
-  float m = 0.0f;
-  const T* p = x + base;
-  if (base + 1024 <= n && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+// Block max of per-warp values followed by ONE atomic max per CTA into out[0] (which the
+// launcher zeroes first; non-negative floats order like their bit patterns).
+__device__ __forceinline__ void cta_atomic_max(float warp_value, float* out) {
+  __shared__ float partial[8];
+  const uint32_t lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) partial[w] = warp_value;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float r = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 1024 / V / 32; ++i) m = max_f32(m, vec_amax<T>(p + (static_cast<size_t>(i) * 32 + lane) * V));
-  } else {
-    const uint32_t count = static_cast<uint32_t>(min(static_cast<uint64_t>(1024), n - base));
-    for (uint32_t i = lane; i < count; i += 32) m = max_f32(m, fabsf(load_as_f32<T>(p, i)));
-  }
-  m = warp_max(m);
-  if (lane == 0) {
-    if (chunk_amax) chunk_amax[chunk] = m;
-    atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(m));
+    for (int i = 0; i < 8; ++i) r = max_f32(r, partial[i]);
+    atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(r));
   }
 }
 
-// amax of a decoded NVFP4 tensor [n/cols][cols], one warp per 1024-value chunk.
+// Tensor amax: warps stride over 1024-value chunks (chunk amax written when requested).
+// utils/nvfp4/quant/kernels/row_amax.rs:67-101.
+template <typename T>
+__global__ void __launch_bounds__(256) tensor_amax_kernel(const T* __restrict__ x, float* __restrict__ chunk_amax,
+                                                           float* __restrict__ out, uint64_t n) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint64_t warps = static_cast<uint64_t>(gridDim.x) * 8;
+  const uint64_t chunks = (n + 1023) / 1024;
+  constexpr int V = VecTraits<T>::kPerVec;
+  float running = 0.0f;
+  for (uint64_t chunk = static_cast<uint64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); chunk < chunks; chunk += warps) {
+    const uint64_t base = chunk * 1024;
+    const T* p = x + base;
+    float m = 0.0f;
+    if (base + 1024 <= n && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+#pragma unroll
+      for (int i = 0; i < 1024 / V / 32; ++i)
+        m = max_f32(m, vec_amax<T>(p + (static_cast<size_t>(i) * 32 + lane) * V));
+    } else {
+      const uint32_t count = static_cast<uint32_t>(min(static_cast<uint64_t>(1024), n - base));
+      for (uint32_t i = lane; i < count; i += 32) m = max_f32(m, fabsf(load_as_f32<T>(p, i)));
+    }
+    m = warp_max(m);
+    if (lane == 0 && chunk_amax) chunk_amax[chunk] = m;
+    running = max_f32(running, m);
+  }
+  cta_atomic_max(running, out);
+}
+
+// amax of a decoded NVFP4 tensor [n/cols][cols], warps striding over 1024-value chunks.
 // utils/nvfp4/quant/kernels/ms_eden/amax.rs:23-64.  rowwise: one global scale per row;
 // packed: the scale bytes are in the packed tile layout.
 __global__ void __launch_bounds__(256) nvfp4_amax_kernel(const uint8_t* __restrict__ bytes,
@@ -112,32 +130,34 @@ __global__ void __launch_bounds__(256) nvfp4_amax_kernel(const uint8_t* __restri
                                                           const float* __restrict__ gscales, uint64_t n, uint32_t cols,
                                                           int rowwise, int packed, float* __restrict__ chunk_amax,
                                                           float* __restrict__ out) {
-  const uint64_t chunk = static_cast<uint64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   const uint32_t lane = threadIdx.x & 31;
-  const uint64_t base = chunk * 1024;
-  if (base >= n) return;
-  float m = 0.0f;
-  const uint64_t end = min(n, base + 1024);
-  // one 16-group (8 bytes, 1 scale) per lane per step
-  for (uint64_t g0 = base + lane * 16ull; g0 < end; g0 += 512) {
-    const uint32_t srow = static_cast<uint32_t>(g0 / cols);
-    const uint32_t skg = static_cast<uint32_t>(g0 - static_cast<uint64_t>(srow) * cols) >> 4;
-    const float gs = rowwise ? gscales[srow] : gscales[0];
-    const float sc = e4m3_value(packed ? scales[packed_scale_offset(srow, skg, cols >> 6)] : scales[g0 >> 4]);
-    const uint2 raw = *reinterpret_cast<const uint2*>(bytes + (g0 >> 1));
-    const uint32_t w[2] = {raw.x, raw.y};
+  const uint64_t warps = static_cast<uint64_t>(gridDim.x) * 8;
+  const uint64_t chunks = (n + 1023) / 1024;
+  float running = 0.0f;
+  for (uint64_t chunk = static_cast<uint64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); chunk < chunks; chunk += warps) {
+    const uint64_t base = chunk * 1024;
+    float m = 0.0f;
+    const uint64_t end = min(n, base + 1024);
+    // one 16-group (8 bytes, 1 scale) per lane per step
+    for (uint64_t g0 = base + lane * 16ull; g0 < end; g0 += 512) {
+      const uint32_t srow = static_cast<uint32_t>(g0 / cols);
+      const uint32_t skg = static_cast<uint32_t>(g0 - static_cast<uint64_t>(srow) * cols) >> 4;
+      const float gs = rowwise ? gscales[srow] : gscales[0];
+      const float sc = e4m3_value(packed ? scales[packed_scale_offset(srow, skg, cols >> 6)] : scales[g0 >> 4]);
+      const uint2 raw = __ldg(reinterpret_cast<const uint2*>(bytes + (g0 >> 1)));
+      const uint32_t w[2] = {raw.x, raw.y};
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float2 q = e2m1x2_values((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
-      m = max_f32(m, fabsf(q.x * sc * gs));
-      m = max_f32(m, fabsf(q.y * sc * gs));
+      for (int j = 0; j < 8; ++j) {
+        const float2 q = e2m1x2_values((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
+        m = max_f32(m, fabsf(q.x * sc * gs));
+        m = max_f32(m, fabsf(q.y * sc * gs));
+      }
     }
+    m = warp_max(m);
+    if (lane == 0 && chunk_amax) chunk_amax[chunk] = m;
+    running = max_f32(running, m);
   }
-  m = warp_max(m);
-  if (lane == 0) {
-    if (chunk_amax) chunk_amax[chunk] = m;
-    atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(m));
-  }
+  cta_atomic_max(running, out);
 }
 
 // max over chunk values -> out[0] (transform 0) or the MS-EDEN global scale (transform 1).
@@ -356,61 +376,66 @@ __device__ __forceinline__ uint32_t ms_eden_group(const float* h, float safe_gs,
   return stochastic_e4m3_scale(s, scale_seed, group);
 }
 
+// Where one orientation of an MS-EDEN result goes.
+struct MsEdenOut {
+  uint8_t* fp4;
+  uint8_t* scales;
+  float* global_scales;
+  float* chunk_amax;      // optional
+  uint32_t rows;          // valid output rows
+  uint32_t dst_row_len;   // output K (multiple of 32)
+  uint32_t scale_seed;
+  uint32_t group_offset;  // added to the flat group id of the scale RNG
+  uint32_t sign_offset;   // added to the K index of the sign hash
+  int packed;             // scale bytes in the packed tile layout
+};
+
 struct MsEdenParams {
   const void* x;
   const uint8_t* src_bytes;
   const uint8_t* src_scales;
   const float* src_global;
   int src_packed;  // NVFP4 sources: scale bytes in the packed tile layout
-  uint32_t a;  // F32_ROWS: src_row_len; transposed kinds: source_rows
-  uint32_t b;  // transposed kinds: source_cols
-  uint32_t out_rows;
-  uint32_t dst_row_len;
+  uint32_t a;      // F32_ROWS: src_row_len; transposed kinds: source_rows
+  uint32_t b;      // transposed kinds: source_cols
   const float* global_scale_dev;
   float global_scale_host;
   int use_host_scale;
   float scale_override;
-  uint32_t sign_seed, scale_seed, col_offset, group_offset;
-  uint8_t* out_fp4;
-  uint8_t* out_scales;
-  float* out_global_scales;
-  float* out_chunk_amax;
+  uint32_t sign_seed;
+  MsEdenOut out;
 };
 
 // Finishes one chunk whose signed inputs are in u[32]: rotation, two groups, stores.
-template <bool kPacked>
-__device__ __forceinline__ void ms_eden_finish_chunk(float (&u)[32], const MsEdenParams& p, float gs, uint32_t row,
-                                                     uint32_t chunk_in_row, uint64_t chunk) {
+__device__ __forceinline__ void ms_eden_emit_chunk(float (&u)[32], const MsEdenOut& o, float gs, float so, uint32_t row,
+                                                   uint32_t chunk_in_row) {
+  const uint64_t chunk = static_cast<uint64_t>(row) * (o.dst_row_len >> 5) + chunk_in_row;
   hadamard32(u);
-  if (p.out_chunk_amax) {
+  if (o.chunk_amax) {
     float m = 0.0f;
 #pragma unroll
     for (int j = 0; j < 32; ++j) m = max_f32(m, fabsf(u[j]));
-    p.out_chunk_amax[chunk] = m;
+    o.chunk_amax[chunk] = m;
   }
   const float safe_gs = nz(gs);
   const float inv6 = inv_scale(6.0f, safe_gs);
-  const uint32_t group0 = static_cast<uint32_t>(chunk) * 2u + p.group_offset;
+  const uint32_t group0 = static_cast<uint32_t>(chunk) * 2u + o.group_offset;
   uint2 lo, hi;
-  const uint32_t sb0 = ms_eden_group(u, safe_gs, 0.0f, p.scale_override, inv6, p.scale_seed, group0, lo);
-  const uint32_t sb1 = ms_eden_group(u + 16, safe_gs, 0.0f, p.scale_override, inv6, p.scale_seed, group0 + 1, hi);
-  *reinterpret_cast<uint4*>(p.out_fp4 + chunk * 16) = make_uint4(lo.x, lo.y, hi.x, hi.y);
-  if (kPacked) {
-    // two consecutive k-groups of the same k-atom: adjacent bytes, 2-byte aligned
-    const size_t off = packed_scale_offset(row, chunk_in_row * 2, p.dst_row_len >> 6);
-    *reinterpret_cast<uint16_t*>(p.out_scales + off) = static_cast<uint16_t>(sb0 | (sb1 << 8));
-  } else {
-    *reinterpret_cast<uint16_t*>(p.out_scales + chunk * 2) = static_cast<uint16_t>(sb0 | (sb1 << 8));
-  }
-  if (chunk_in_row == 0) p.out_global_scales[row] = gs;
+  const uint32_t sb0 = ms_eden_group(u, safe_gs, 0.0f, so, inv6, o.scale_seed, group0, lo);
+  const uint32_t sb1 = ms_eden_group(u + 16, safe_gs, 0.0f, so, inv6, o.scale_seed, group0 + 1, hi);
+  *reinterpret_cast<uint4*>(o.fp4 + chunk * 16) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+  // two consecutive k-groups of one k-atom: adjacent bytes in either layout, 2-byte aligned
+  const size_t off = o.packed ? packed_scale_offset(row, chunk_in_row * 2, o.dst_row_len >> 6) : chunk * 2;
+  *reinterpret_cast<uint16_t*>(o.scales + off) = static_cast<uint16_t>(sb0 | (sb1 << 8));
+  if (chunk_in_row == 0) o.global_scales[row] = gs;
 }
 
-// Generic one-thread-per-chunk kernel.  Input gathers follow
-// utils/nvfp4/quant/kernels/ms_eden/input/padded.rs:9-96.
-template <int kKind, typename T, bool kPacked>
+// Generic one-thread-per-chunk kernel (row sources, and the fallback for odd transposed
+// shapes).  Input gathers follow utils/nvfp4/quant/kernels/ms_eden/input/padded.rs:9-96.
+template <int kKind, typename T>
 __global__ void __launch_bounds__(128) ms_eden_kernel(const MsEdenParams p) {
-  const uint32_t chunks_per_row = p.dst_row_len >> 5;
-  const uint64_t chunk_count = static_cast<uint64_t>(p.out_rows) * chunks_per_row;
+  const uint32_t chunks_per_row = p.out.dst_row_len >> 5;
+  const uint64_t chunk_count = static_cast<uint64_t>(p.out.rows) * chunks_per_row;
   const uint64_t chunk = static_cast<uint64_t>(blockIdx.x) * 128 + threadIdx.x;
   if (chunk >= chunk_count) return;
   const uint32_t row = static_cast<uint32_t>(chunk / chunks_per_row);
@@ -459,8 +484,157 @@ __global__ void __launch_bounds__(128) ms_eden_kernel(const MsEdenParams p) {
   }
 #pragma unroll
   for (int j = 0; j < 32; ++j)
-    if (random_sign_negative(p.sign_seed, col0 + j + p.col_offset)) u[j] = -u[j];  // x * (-1) == -x exactly
-  ms_eden_finish_chunk<kPacked>(u, p, gs, row, chunk_in_row, chunk);
+    if (random_sign_negative(p.sign_seed, col0 + j + p.out.sign_offset)) u[j] = -u[j];  // x * (-1) == -x exactly
+  ms_eden_emit_chunk(u, p.out, gs, p.scale_override, row, chunk_in_row);
+}
+
+// Tiled kernel for the transposed operands.  A CTA stages a [128 source rows x 64 source
+// columns] tile in shared memory with coalesced 128-bit loads (decoding NVFP4 sources on the
+// way), then each thread takes one 32-chunk DOWN a column (the transposed operand, K = source
+// row) and, in pair mode, one 32-chunk ALONG a row (the row operand, K = source column): the
+// source is read from memory once for both orientations, where the reference reads it twice
+// and gathers the transposed half with a row-pitch stride
+// (utils/nvfp4/quant/kernels/ms_eden/fp32_pair/dispatch.rs:13-43, input/padded.rs:9-96).
+struct MsEdenTileParams {
+  const void* x;
+  const uint8_t* src_bytes;
+  const uint8_t* src_scales;
+  const float* src_global;
+  int src_packed;
+  uint32_t src_rows, src_cols;
+  const float* global_scale_dev;
+  float global_scale_host;
+  int use_host_scale;
+  float scale_override;
+  uint32_t sign_seed;
+  MsEdenOut t;  // transposed operand: rows = src_cols, K = src_rows (padded)
+  MsEdenOut r;  // row operand (pair mode): rows = src_rows, K = src_cols (padded)
+  float* col_sum_partials;  // pair mode, optional: [row tiles][src_cols] column sums of each tile
+};
+
+constexpr int kTileRows = 128, kTileCols = 64, kTileLd = kTileCols + 1;
+
+template <int kSrc, typename T, bool kPair>
+__global__ void __launch_bounds__(256) ms_eden_tile_kernel(const MsEdenTileParams p) {
+  __shared__ float tile[kTileRows * kTileLd];
+  __shared__ uint8_t neg_r[kTileRows];
+  __shared__ uint8_t neg_c[kTileCols];
+  const uint32_t tid = threadIdx.x;
+  const uint32_t c0 = blockIdx.x * kTileCols, r0 = blockIdx.y * kTileRows;
+  if (tid < kTileRows)
+    neg_r[tid] = random_sign_negative(p.sign_seed, r0 + tid + p.t.sign_offset) ? 1 : 0;
+  else if (kPair && tid < kTileRows + kTileCols)
+    neg_c[tid - kTileRows] = random_sign_negative(p.sign_seed, c0 + (tid - kTileRows) + p.r.sign_offset) ? 1 : 0;
+
+  if (kSrc == 0) {
+    const T* x = static_cast<const T*>(p.x);
+    constexpr int V = VecTraits<T>::kPerVec;
+    constexpr int kVecPerRow = kTileCols / V;
+    const bool vec_ok = (p.src_cols % V == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) &&
+                        (c0 + kTileCols <= p.src_cols);
+    for (uint32_t i = tid; i < kTileRows * kVecPerRow; i += 256) {
+      const uint32_t row = i / kVecPerRow, v = i % kVecPerRow;
+      const uint32_t r = r0 + row;
+      float vals[V];
+#pragma unroll
+      for (int k = 0; k < V; ++k) vals[k] = 0.0f;
+      if (r < p.src_rows) {
+        const T* src = x + static_cast<size_t>(r) * p.src_cols + c0 + v * V;
+        if (vec_ok) {
+          if (V == 4) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(src));
+            vals[0] = t.x, vals[1] = t.y, vals[2] = t.z, vals[3] = t.w;
+          } else {
+            const uint4 t = __ldg(reinterpret_cast<const uint4*>(src));
+            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              vals[(2 * k) % V] = __uint_as_float(w[k] << 16);
+              vals[(2 * k + 1) % V] = __uint_as_float(w[k] & 0xffff0000u);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < V; ++k)
+            if (c0 + v * V + k < p.src_cols) vals[k] = load_as_f32<T>(src, k);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < V; ++k) tile[row * kTileLd + v * V + k] = vals[k];
+    }
+  } else {
+    // NVFP4 source: per row of the tile 32 nibble bytes and 4 scale bytes; two threads per row
+    const uint32_t row = tid >> 1, half = tid & 1;
+    const uint32_t r = r0 + row, c = c0 + half * 32;
+    float vals[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) vals[k] = 0.0f;
+    if (r < p.src_rows) {
+      const float sg = kSrc == 2 ? p.src_global[0] : p.src_global[r];
+      const size_t index = static_cast<size_t>(r) * p.src_cols + c;
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        if (c + 16 * g < p.src_cols) {
+          const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.src_bytes + ((index + 16 * g) >> 1)));
+          const size_t sidx = p.src_packed ? packed_scale_offset(r, (c >> 4) + g, p.src_cols >> 6) : (index >> 4) + g;
+          const float sc = e4m3_value(p.src_scales[sidx]);
+          const uint32_t w[2] = {raw.x, raw.y};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float2 q = e2m1x2_values((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
+            vals[16 * g + 2 * j] = q.x * sc * sg;
+            vals[16 * g + 2 * j + 1] = q.y * sc * sg;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 32; ++k) tile[row * kTileLd + half * 32 + k] = vals[k];
+  }
+  __syncthreads();
+
+  if (kPair && p.col_sum_partials) {
+    // Column sums of this tile (the bias gradient's partial sums), in a fixed order: four
+    // sequential 32-row sums per column, then ((q0 + q1) + q2) + q3.
+    __shared__ float quarter_sum[4][kTileCols];
+    const uint32_t c = tid & 63, quarter = tid >> 6;
+    float acc = 0.0f;
+#pragma unroll 8
+    for (int j = 0; j < 32; ++j) acc += tile[(quarter * 32 + j) * kTileLd + c];
+    quarter_sum[quarter][c] = acc;
+    __syncthreads();
+    if (tid < kTileCols && c0 + tid < p.src_cols)
+      p.col_sum_partials[static_cast<size_t>(blockIdx.y) * p.src_cols + c0 + tid] =
+          ((quarter_sum[0][tid] + quarter_sum[1][tid]) + quarter_sum[2][tid]) + quarter_sum[3][tid];
+  }
+
+  const float gs = p.use_host_scale ? p.global_scale_host : p.global_scale_dev[0];
+  {
+    const uint32_t c = tid & 63, chunk = tid >> 6;
+    const uint32_t out_row = c0 + c, k0 = r0 + chunk * 32;
+    if (out_row < p.t.rows && k0 < p.t.dst_row_len) {
+      float u[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float v = tile[(chunk * 32 + j) * kTileLd + c];
+        u[j] = neg_r[chunk * 32 + j] ? -v : v;
+      }
+      ms_eden_emit_chunk(u, p.t, gs, p.scale_override, out_row, k0 >> 5);
+    }
+  }
+  if (kPair) {
+    const uint32_t row = tid >> 1, chunk = tid & 1;
+    const uint32_t out_row = r0 + row, k0 = c0 + chunk * 32;
+    if (out_row < p.r.rows && k0 < p.r.dst_row_len) {
+      float u[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float v = tile[row * kTileLd + chunk * 32 + j];
+        u[j] = neg_c[chunk * 32 + j] ? -v : v;
+      }
+      ms_eden_emit_chunk(u, p.r, gs, p.scale_override, out_row, k0 >> 5);
+    }
+  }
 }
 
 // ============================================================================
@@ -580,6 +754,24 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(const T* __restrict__ e,
   }
 }
 
+// dbias[c] = sum over row tiles of the tile column sums, tile 0 first (fixed order).
+__global__ void __launch_bounds__(256) col_sum_reduce_kernel(const float* __restrict__ partials,
+                                                              float* __restrict__ dbias, uint32_t tiles, uint32_t n) {
+  const uint32_t c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= n) return;
+  float acc = 0.0f;
+  uint32_t t = 0;
+  for (; t + 8 <= tiles; t += 8) {
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __ldg(partials + static_cast<size_t>(t + i) * n + c);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += v[i];
+  }
+  for (; t < tiles; ++t) acc += __ldg(partials + static_cast<size_t>(t) * n + c);
+  dbias[c] = acc;
+}
+
 // ============================================================================
 // launchers
 // ============================================================================
@@ -610,7 +802,7 @@ int launch_tensor_amax(cudaStream_t s, const void* x, int dtype, float* chunk_am
   cudaError_t err = cudaMemsetAsync(out, 0, sizeof(float), s);
   if (err != cudaSuccess) return static_cast<int>(err);
   if (n == 0) return 0;
-  const uint32_t grid = blocks_for((n + 1023) / 1024, 8);
+  const uint32_t grid = blocks_for((n + 1023) / 1024, 8, 148 * 8);
   if (dtype == 0)
     tensor_amax_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), chunk_amax, out, n);
   else
@@ -624,7 +816,7 @@ int launch_nvfp4_amax(cudaStream_t s, const uint8_t* bytes, const uint8_t* scale
   cudaError_t err = cudaMemsetAsync(out, 0, sizeof(float), s);
   if (err != cudaSuccess) return static_cast<int>(err);
   if (n == 0) return 0;
-  nvfp4_amax_kernel<<<blocks_for((n + 1023) / 1024, 8), 256, 0, s>>>(bytes, scales, gscales, n, cols, rowwise, packed,
+  nvfp4_amax_kernel<<<blocks_for((n + 1023) / 1024, 8, 148 * 8), 256, 0, s>>>(bytes, scales, gscales, n, cols, rowwise, packed,
                                                                      chunk_amax, out);
   NVFP4_RETURN_LAST();
 }
@@ -695,65 +887,161 @@ int launch_four_six_padded(cudaStream_t s, const float* x, const float* amax, ui
   NVFP4_RETURN_LAST();
 }
 
-template <int kKind, typename T>
-static void launch_ms_eden_t(cudaStream_t s, const MsEdenParams& p, int packed, uint32_t grid) {
-  if (packed)
-    ms_eden_kernel<kKind, T, true><<<grid, 128, 0, s>>>(p);
-  else
-    ms_eden_kernel<kKind, T, false><<<grid, 128, 0, s>>>(p);
+static MsEdenOut make_out(const nvfp4_ms_eden_args& a, uint32_t out_rows) {
+  MsEdenOut o;
+  o.fp4 = a.out_fp4;
+  o.scales = a.out_scales;
+  o.global_scales = a.out_global_scales;
+  o.chunk_amax = a.out_chunk_amax;
+  o.rows = out_rows;
+  o.dst_row_len = a.dst_row_len;
+  o.scale_seed = a.scale_seed;
+  o.group_offset = a.group_offset;
+  o.sign_offset = a.col_offset;
+  o.packed = a.scale_layout == NVFP4_SCALES_PACKED;
+  return o;
+}
+
+template <int kSrc, typename T, bool kPair>
+static void launch_tile(cudaStream_t s, const MsEdenTileParams& p) {
+  dim3 grid((p.src_cols + kTileCols - 1) / kTileCols, (p.src_rows + kTileRows - 1) / kTileRows);
+  ms_eden_tile_kernel<kSrc, T, kPair><<<grid, 256, 0, s>>>(p);
+}
+
+// The tile kernel covers K positions [0, ceil(rows/128)*128) of the transposed operand and
+// [0, ceil(cols/64)*64) of the row operand; longer destinations use the generic kernel.
+static bool tile_covers(uint32_t src_rows, uint32_t dst_row_len) {
+  return dst_row_len <= (src_rows + kTileRows - 1) / kTileRows * kTileRows;
 }
 
 int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a) {
-  MsEdenParams p;
-  p.x = a.x;
-  p.src_bytes = a.src_bytes;
-  p.src_scales = a.src_scales;
-  p.src_global = a.src_global;
-  p.src_packed = a.src_scale_layout == NVFP4_SCALES_PACKED;
-  p.a = a.src_kind == NVFP4_SRC_F32_ROWS ? a.cols : a.rows;
-  p.b = a.cols;
-  p.out_rows = a.src_kind == NVFP4_SRC_F32_ROWS ? a.rows : a.cols;
-  p.dst_row_len = a.dst_row_len;
-  p.global_scale_dev = a.global_scale;
-  p.global_scale_host = a.host_global_scale;
-  p.use_host_scale = a.host_global_scale_valid;
-  p.scale_override = a.scale_override;
-  p.sign_seed = a.sign_seed;
-  p.scale_seed = a.scale_seed;
-  p.col_offset = a.col_offset;
-  p.group_offset = a.group_offset;
-  p.out_fp4 = a.out_fp4;
-  p.out_scales = a.out_scales;
-  p.out_global_scales = a.out_global_scales;
-  p.out_chunk_amax = a.out_chunk_amax;
-  const uint64_t chunks = static_cast<uint64_t>(p.out_rows) * (p.dst_row_len / 32);
+  const bool rows_kind = a.src_kind == NVFP4_SRC_F32_ROWS;
+  const uint32_t out_rows = rows_kind ? a.rows : a.cols;
+  const uint64_t chunks = static_cast<uint64_t>(out_rows) * (a.dst_row_len / 32);
   if (chunks == 0) return 0;
-  const uint32_t grid = blocks_for(chunks, 128);
-  const int packed = a.scale_layout == NVFP4_SCALES_PACKED;
   const bool bf16 = a.src_dtype == NVFP4_DTYPE_BF16;
-  switch (a.src_kind) {
-    case NVFP4_SRC_F32_ROWS:
-      if (bf16) launch_ms_eden_t<0, __nv_bfloat16>(s, p, packed, grid);
-      else launch_ms_eden_t<0, float>(s, p, packed, grid);
-      break;
-    case NVFP4_SRC_F32_TRANSPOSED:
-      if (bf16) launch_ms_eden_t<1, __nv_bfloat16>(s, p, packed, grid);
-      else launch_ms_eden_t<1, float>(s, p, packed, grid);
-      break;
-    case NVFP4_SRC_NVFP4_TRANSPOSED:
-      launch_ms_eden_t<2, float>(s, p, packed, grid);
-      break;
-    case NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED:
-      launch_ms_eden_t<3, float>(s, p, packed, grid);
-      break;
-    default:
-      return 1;
+  const int packed = a.scale_layout == NVFP4_SCALES_PACKED;
+  if (!rows_kind && tile_covers(a.rows, a.dst_row_len)) {
+    MsEdenTileParams p;
+    p.x = a.x;
+    p.src_bytes = a.src_bytes;
+    p.src_scales = a.src_scales;
+    p.src_global = a.src_global;
+    p.src_packed = a.src_scale_layout == NVFP4_SCALES_PACKED;
+    p.src_rows = a.rows;
+    p.src_cols = a.cols;
+    p.global_scale_dev = a.global_scale;
+    p.global_scale_host = a.host_global_scale;
+    p.use_host_scale = a.host_global_scale_valid;
+    p.scale_override = a.scale_override;
+    p.sign_seed = a.sign_seed;
+    p.t = make_out(a, out_rows);
+    p.r = p.t;
+    p.col_sum_partials = nullptr;
+    switch (a.src_kind) {
+      case NVFP4_SRC_F32_TRANSPOSED:
+        if (bf16) launch_tile<0, __nv_bfloat16, false>(s, p);
+        else launch_tile<0, float, false>(s, p);
+        break;
+      case NVFP4_SRC_NVFP4_TRANSPOSED:
+        launch_tile<2, float, false>(s, p);
+        break;
+      case NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED:
+        launch_tile<3, float, false>(s, p);
+        break;
+      default:
+        return 1;
+    }
+  } else {
+    MsEdenParams p;
+    p.x = a.x;
+    p.src_bytes = a.src_bytes;
+    p.src_scales = a.src_scales;
+    p.src_global = a.src_global;
+    p.src_packed = a.src_scale_layout == NVFP4_SCALES_PACKED;
+    p.a = rows_kind ? a.cols : a.rows;
+    p.b = a.cols;
+    p.global_scale_dev = a.global_scale;
+    p.global_scale_host = a.host_global_scale;
+    p.use_host_scale = a.host_global_scale_valid;
+    p.scale_override = a.scale_override;
+    p.sign_seed = a.sign_seed;
+    p.out = make_out(a, out_rows);
+    const uint32_t grid = blocks_for(chunks, 128);
+    switch (a.src_kind) {
+      case NVFP4_SRC_F32_ROWS:
+        if (bf16) ms_eden_kernel<0, __nv_bfloat16><<<grid, 128, 0, s>>>(p);
+        else ms_eden_kernel<0, float><<<grid, 128, 0, s>>>(p);
+        break;
+      case NVFP4_SRC_F32_TRANSPOSED:
+        if (bf16) ms_eden_kernel<1, __nv_bfloat16><<<grid, 128, 0, s>>>(p);
+        else ms_eden_kernel<1, float><<<grid, 128, 0, s>>>(p);
+        break;
+      case NVFP4_SRC_NVFP4_TRANSPOSED:
+        ms_eden_kernel<2, float><<<grid, 128, 0, s>>>(p);
+        break;
+      case NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED:
+        ms_eden_kernel<3, float><<<grid, 128, 0, s>>>(p);
+        break;
+      default:
+        return 1;
+    }
   }
   count_launch();
   int rc = static_cast<int>(cudaGetLastError());
   if (rc) return rc;
-  if (packed) return launch_packed_scale_pad(s, a.out_scales, p.out_rows, p.dst_row_len);
+  if (packed) return launch_packed_scale_pad(s, a.out_scales, out_rows, a.dst_row_len);
   return 0;
+}
+
+// Row operand and transposed operand of one f32 / bf16 matrix in a single pass over it.
+// `rows_args` describes the row operand (src_kind F32_ROWS), `t_args` the transposed one
+// (src_kind F32_TRANSPOSED) of the same matrix; both use the same global scale and sign seed.
+uint32_t ms_eden_pair_row_tiles(uint32_t rows) { return (rows + kTileRows - 1) / kTileRows; }
+
+bool ms_eden_pair_is_tiled(const nvfp4_ms_eden_args& r, const nvfp4_ms_eden_args& t) {
+  return r.rows != 0 && r.cols != 0 && tile_covers(r.rows, t.dst_row_len) &&
+         r.dst_row_len <= (r.cols + kTileCols - 1) / kTileCols * kTileCols;
+}
+
+int launch_col_sum_reduce(cudaStream_t s, const float* partials, float* dbias, uint32_t tiles, uint32_t n) {
+  if (n == 0) return 0;
+  col_sum_reduce_kernel<<<blocks_for(n, 256), 256, 0, s>>>(partials, dbias, tiles, n);
+  NVFP4_RETURN_LAST();
+}
+
+int launch_ms_eden_pair(cudaStream_t s, const nvfp4_ms_eden_args& r, const nvfp4_ms_eden_args& t,
+                        float* col_sum_partials) {
+  const uint32_t rows = r.rows, cols = r.cols;
+  if (!ms_eden_pair_is_tiled(r, t)) {
+    int rc = launch_ms_eden(s, r);
+    return rc ? rc : launch_ms_eden(s, t);
+  }
+  MsEdenTileParams p;
+  p.x = r.x;
+  p.src_bytes = nullptr;
+  p.src_scales = nullptr;
+  p.src_global = nullptr;
+  p.src_packed = 0;
+  p.src_rows = rows;
+  p.src_cols = cols;
+  p.global_scale_dev = r.global_scale;
+  p.global_scale_host = r.host_global_scale;
+  p.use_host_scale = r.host_global_scale_valid;
+  p.scale_override = r.scale_override;
+  p.sign_seed = r.sign_seed;
+  p.t = make_out(t, cols);
+  p.r = make_out(r, rows);
+  p.col_sum_partials = col_sum_partials;
+  if (r.src_dtype == NVFP4_DTYPE_BF16) launch_tile<0, __nv_bfloat16, true>(s, p);
+  else launch_tile<0, float, true>(s, p);
+  count_launch();
+  int rc = static_cast<int>(cudaGetLastError());
+  if (rc) return rc;
+  if (p.r.packed) rc = launch_packed_scale_pad(s, r.out_scales, rows, r.dst_row_len);
+  if (rc) return rc;
+  if (p.t.packed) rc = launch_packed_scale_pad(s, t.out_scales, cols, t.dst_row_len);
+  return rc;
 }
 
 int launch_decode(cudaStream_t s, const uint8_t* bytes, const uint8_t* scales, const float* gscales, int rowwise,

@@ -565,4 +565,29 @@ void oracle_bias_grad(const float* e, float* dbias, uint32_t tokens, uint32_t n)
   }
 }
 
+// The same column sums in the order of the fused GPU path (no reference counterpart: the
+// reference always uses the order above): per 128-row tile four sequential 32-row sums
+// combined as ((q0 + q1) + q2) + q3, tiles then added first to last.  Same mathematical
+// value as oracle_bias_grad; differs from it by f32 rounding only.
+void oracle_bias_grad_tiled(const float* e, float* dbias, uint32_t tokens, uint32_t n) {
+  const uint32_t tiles = (tokens + 127) / 128;
+#pragma omp parallel for schedule(static)
+  for (int64_t c = 0; c < n; ++c) {
+    float acc = 0.0f;
+    for (uint32_t t = 0; t < tiles; ++t) {
+      float q[4];
+      for (int k = 0; k < 4; ++k) {
+        float a = 0.0f;
+        for (int j = 0; j < 32; ++j) {
+          uint32_t r = t * 128 + k * 32 + j;
+          a += r < tokens ? e[static_cast<size_t>(r) * n + c] : 0.0f;
+        }
+        q[k] = a;
+      }
+      acc += ((q[0] + q[1]) + q[2]) + q[3];
+    }
+    dbias[c] = acc;
+  }
+}
+
 }  // extern "C"

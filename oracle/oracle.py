@@ -246,6 +246,15 @@ def bias_grad(e):
     return out
 
 
+def bias_grad_tiled(e):
+    """Column sums in the order of the fused GPU path (128-row tiles; see nvfp4_oracle.cpp)."""
+    e = _f32(e)
+    tokens, n = e.shape
+    out = np.empty(n, np.float32)
+    lib().oracle_bias_grad_tiled(_p(e), _p(out), c_uint32(tokens), c_uint32(n))
+    return out
+
+
 def linear_forward_backward(x, w, bias, dy, sign_seed, scale_seed, epi=1):
     """One projection, forward and backward, entirely on the CPU oracle: the composition of
     crates/gpt2-nvfp4/src/types/l3_mlp/forward.rs:15-67 (quantize X rowwise, W tensor scale, GEMM +
