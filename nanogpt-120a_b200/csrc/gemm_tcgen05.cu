@@ -42,7 +42,9 @@ constexpr int kSfTileBytes = 512;                 // 128 rows x 4 scale bytes
 constexpr int kSfaStageBytes = kKAtomsPerStage * kSfTileBytes;
 constexpr int kStoreStageBytes = kBlockM * 128;   // one epilogue sub-tile: 128 rows x 128 bytes
 constexpr int kTmemCols = 512;
-constexpr int kThreads = 256;
+constexpr int kMaxStages = 8;
+constexpr int kSmemBudget = 227 * 1024;
+constexpr int kThreads = 384;
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;  // 2 s
 
 constexpr uint32_t kStatusProducerTimeout = 1u, kStatusMmaTimeout = 2u, kStatusEpilogueTimeout = 4u;
@@ -52,18 +54,23 @@ struct Cfg {
   static constexpr int kNBlocks128 = kBlockN / 128;
   static constexpr int kBStageBytes = kBlockN * kBlockKBytes;
   static constexpr int kSfbStageBytes = kNBlocks128 * kKAtomsPerStage * kSfTileBytes;
-  static constexpr int kStages = kBlockN == 128 ? 5 : 3;
   static constexpr int kAccStages = kBlockN == 128 ? 2 : 1;
-  static constexpr int kTmemSfa = 256;                       // column of the A scale factors
-  static constexpr int kTmemSfb = 256 + 4 * kKAtomsPerStage;  // column of the B scale factors
+  // Scale factors live in a 4-deep ring of column sets behind the accumulators (one set per
+  // k-tile), so the copies for the next k-tile never overwrite columns an MMA in flight reads.
   static constexpr int kSfbColsPerAtom = kBlockN / 32;
-  static constexpr int kSmemData = kStages * (kAStageBytes + kBStageBytes);
-  static constexpr int kSmemSf = kStages * (kSfaStageBytes + kSfbStageBytes);
-  static constexpr int kSmemBytes =
-      1024 /*alignment slack*/ + kSmemData + kSmemSf + 2 * kStoreStageBytes + 256 /*barriers*/;
-  static_assert(kTmemSfb + kSfbColsPerAtom * kKAtomsPerStage <= kTmemCols, "tensor memory overflow");
+  static constexpr int kSfSetCols = 4 * kKAtomsPerStage + kSfbColsPerAtom * kKAtomsPerStage;
+  static constexpr int kSfSets = 4;
+  static constexpr int kTmemSfa = 256;                       // A scale factors of set 0
+  static constexpr int kTmemSfb = 256 + 4 * kKAtomsPerStage;  // B scale factors of set 0
+  static constexpr int kStreamStageBytes = kAStageBytes + kBStageBytes + kSfaStageBytes + kSfbStageBytes;
+  static constexpr int kResidentStageBytes = kAStageBytes + kSfaStageBytes;
+  static constexpr int kPanelSlotBytes = kBStageBytes + kSfbStageBytes;
+  // epilogue staging ring: deep for the narrow tile (short-K GEMMs are epilogue bound), shallow for
+  // the wide one (long-K GEMMs need the shared memory for pipeline stages)
+  static constexpr int kStoreBufs = kBlockN == 128 ? 4 : 2;
+  static constexpr int kFixedBytes = 1024 /*alignment slack*/ + kStoreBufs * kStoreStageBytes + 512 /*barriers*/;
+  static_assert(256 + kSfSets * kSfSetCols <= kTmemCols, "tensor memory overflow");
   static_assert(kAccStages * kBlockN <= 256, "accumulators overlap the scale-factor columns");
-  static_assert(kSmemBytes <= 227 * 1024, "shared memory overflow");
 };
 
 struct GemmParams {
@@ -77,6 +84,8 @@ struct GemmParams {
   uint32_t m, n, k, ldo;
   uint32_t num_m_blocks, num_n_blocks, k_atoms, sfb_blocks128;
   uint32_t k_splits, k_tiles_per_split, num_k_tiles;
+  uint32_t stages;  // depth of the A (and, when streaming, B) ring
+  int b_resident;   // the B panel of a column block stays in shared memory (short K)
   int mode, epilogue, vec_store, tma_store;
   float weight;
 };
@@ -156,7 +165,10 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32
                : "memory");
 }
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
 __device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -165,9 +177,6 @@ __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.f
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tcgen05_cp_sf(uint32_t taddr, uint64_t desc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
 }
 __device__ __forceinline__ void tcgen05_mma_nvf4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                                  uint32_t accumulate, uint32_t tmem_sfa, uint32_t tmem_sfb) {
@@ -201,14 +210,6 @@ __device__ __forceinline__ uint64_t make_ab_desc(uint32_t smem_addr) {
   d |= static_cast<uint64_t>(1024u >> 4) << 32;  // stride byte offset
   d |= 1ull << 46;                               // descriptor version
   d |= 2ull << 61;                               // SWIZZLE_128B
-  return d;
-}
-// Scale-factor tiles: 32 rows x 16 bytes, no swizzle, 8-row core matrices 128 bytes apart.
-__device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>(128u >> 4) << 32;
-  d |= 1ull << 46;
   return d;
 }
 // Instruction descriptor of kind::mxf4nvf4: E2M1 x E2M1, UE4M3 scales, K-major A and B,
@@ -306,6 +307,11 @@ struct SubTile<__nv_bfloat16> {
 
 // ---- the kernel -----------------------------------------------------------------------------
 
+// Shared-memory plan of one launch, chosen on the host (all offsets from the 1024-byte aligned
+// base): A stages, B slots, SFA stages, SFB slots, two epilogue staging buffers, barriers.
+// Streaming mode: one B slot per pipeline stage.  Resident mode (short K): the whole
+// [kBlockN x K] B panel of the current column block stays in shared memory -- one slot per
+// k-tile -- while a CTA walks down the row blocks, so only A tiles stream through the ring.
 template <int kBlockN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
     nvfp4_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -316,18 +322,26 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
+  const uint32_t stages = p.stages;
+  const uint32_t b_slots = p.b_resident ? p.num_k_tiles : stages;
   const uint32_t smem_a = smem_base;
-  const uint32_t smem_b = smem_a + C::kStages * kAStageBytes;
-  const uint32_t smem_sfa = smem_b + C::kStages * C::kBStageBytes;
-  const uint32_t smem_sfb = smem_sfa + C::kStages * kSfaStageBytes;
-  const uint32_t smem_store = smem_sfb + C::kStages * C::kSfbStageBytes;  // 2 x 16 KB, 1024-byte aligned
-  const uint32_t smem_bar = smem_store + 2 * kStoreStageBytes;
-  // barrier block: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], tmem base, abort flag
+  const uint32_t smem_b = smem_a + stages * kAStageBytes;
+  const uint32_t smem_sfa = smem_b + b_slots * C::kBStageBytes;
+  const uint32_t smem_sfb = smem_sfa + stages * kSfaStageBytes;
+  const uint32_t smem_store = smem_sfb + b_slots * C::kSfbStageBytes;  // staging ring, 16 KB buffers, 1024-byte aligned
+  const uint32_t smem_bar = smem_store + C::kStoreBufs * kStoreStageBytes;
+  // barrier block: full[8], empty[8], tmem_full[2], tmem_empty[2], b_full, b_empty, sf_full[4], sf_empty[4],
+  // tmem base, abort flag
   const uint32_t bar_full = smem_bar;
-  const uint32_t bar_empty = bar_full + 8 * C::kStages;
-  const uint32_t bar_tmem_full = bar_empty + 8 * C::kStages;
+  const uint32_t bar_empty = bar_full + 8 * kMaxStages;
+  const uint32_t bar_tmem_full = bar_empty + 8 * kMaxStages;
   const uint32_t bar_tmem_empty = bar_tmem_full + 16;
-  uint32_t* tmem_base_ptr = reinterpret_cast<uint32_t*>(smem_gen + (smem_bar - smem_base) + 8 * (2 * C::kStages + 4));
+  const uint32_t bar_b_full = bar_tmem_empty + 16;
+  const uint32_t bar_b_empty = bar_b_full + 8;
+  const uint32_t bar_sf_full = bar_b_empty + 8;
+  const uint32_t bar_sf_empty = bar_sf_full + 8 * C::kSfSets;
+  uint32_t* tmem_base_ptr =
+      reinterpret_cast<uint32_t*>(smem_gen + (smem_bar - smem_base) + 8 * (2 * kMaxStages + 6 + 2 * C::kSfSets));
   volatile uint32_t* abort_flag = tmem_base_ptr + 1;
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -339,14 +353,20 @@ __global__ void __launch_bounds__(kThreads, 1)
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_out)) : "memory");
       if (p.aux) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_aux)) : "memory");
     }
-    for (int s = 0; s < C::kStages; ++s) {
+    for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_empty + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1 + 4);  // the MMA commit and the four scale-factor warps
+    }
+    for (int s = 0; s < C::kSfSets; ++s) {
+      mbar_init(bar_sf_full + 8 * s, 4);
+      mbar_init(bar_sf_empty + 8 * s, 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tmem_full + 8 * a, 1);
       mbar_init(bar_tmem_empty + 8 * a, 4);
     }
+    mbar_init(bar_b_full, 1);
+    mbar_init(bar_b_empty, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -361,43 +381,92 @@ __global__ void __launch_bounds__(kThreads, 1)
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_base_ptr;
 
+  // Work list, identical in every role.  Streaming: work items (tile, k-split) strided over the
+  // grid, column block fastest (neighbouring CTAs share A rows in L2).  Resident: each CTA owns a
+  // contiguous range of tiles ordered column block major, so its B panel changes at most a
+  // couple of times.
   const uint32_t tiles_mn = p.num_m_blocks * p.num_n_blocks;
-  const uint32_t num_work = tiles_mn * p.k_splits;
+  uint32_t w_begin, w_end, w_step;
+  if (p.b_resident) {
+    w_begin = static_cast<uint32_t>(static_cast<uint64_t>(tiles_mn) * blockIdx.x / gridDim.x);
+    w_end = static_cast<uint32_t>(static_cast<uint64_t>(tiles_mn) * (blockIdx.x + 1) / gridDim.x);
+    w_step = 1;
+  } else {
+    w_begin = blockIdx.x;
+    w_end = tiles_mn * p.k_splits;
+    w_step = gridDim.x;
+  }
+  auto decode = [&](uint32_t w, uint32_t& m_blk, uint32_t& n_blk, uint32_t& split) {
+    if (p.b_resident) {
+      n_blk = w / p.num_m_blocks;
+      m_blk = w - n_blk * p.num_m_blocks;
+      split = 0;
+    } else {
+      const uint32_t tile = w % tiles_mn;
+      split = w / tiles_mn;
+      m_blk = tile / p.num_n_blocks;
+      n_blk = tile - m_blk * p.num_n_blocks;
+    }
+  };
 
   if (warp == 0) {
     // ===================== TMA producer =====================
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0, issued = 0;
+      uint32_t stage = 0, phase = 0, issued = 0, runs = 0, prev_n = 0xffffffffu;
       bool ok = true;
-      for (uint32_t work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
-        const uint32_t tile = work % tiles_mn, split = work / tiles_mn;
-        const uint32_t m_blk = tile / p.num_n_blocks, n_blk = tile % p.num_n_blocks;
+      for (uint32_t w = w_begin; w < w_end && ok; w += w_step) {
+        uint32_t m_blk, n_blk, split;
+        decode(w, m_blk, n_blk, split);
         const uint32_t kt_begin = split * p.k_tiles_per_split;
         const uint32_t kt_end = min(p.num_k_tiles, kt_begin + p.k_tiles_per_split);
+        const uint32_t first_blk128 = n_blk * C::kNBlocks128;
+        const uint32_t blks128 = min(static_cast<uint32_t>(C::kNBlocks128), p.sfb_blocks128 - first_blk128);
+        if (p.b_resident && n_blk != prev_n) {
+          // new column block: wait until the MMAs of the previous run have retired, then load the panel
+          if (runs > 0 && !mbar_wait(bar_b_empty, (runs - 1) & 1u, abort_flag, kStatusProducerTimeout)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sf_total = p.k_atoms * kSfTileBytes * blks128;
+          mbar_expect_tx(bar_b_full, p.num_k_tiles * C::kBStageBytes + sf_total);
+          for (uint32_t kt = 0; kt < p.num_k_tiles; ++kt) {
+            const uint32_t atoms = min(static_cast<uint32_t>(kKAtomsPerStage), p.k_atoms - kt * kKAtomsPerStage);
+            tma_load_2d(smem_b + kt * C::kBStageBytes, &tmap_b, bar_b_full, static_cast<int32_t>(kt * kBlockKBytes),
+                        static_cast<int32_t>(n_blk * kBlockN));
+            for (uint32_t i = 0; i < blks128; ++i)
+              bulk_load(smem_sfb + kt * C::kSfbStageBytes + i * kSfaStageBytes,
+                        p.sfb + (static_cast<size_t>(first_blk128 + i) * p.k_atoms + kt * kKAtomsPerStage) * kSfTileBytes,
+                        atoms * kSfTileBytes, bar_b_full);
+          }
+          prev_n = n_blk;
+          ++runs;
+        }
         for (uint32_t kt = kt_begin; kt < kt_end; ++kt) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusProducerTimeout)) {
             ok = false;
             break;
           }
           const uint32_t atoms = min(static_cast<uint32_t>(kKAtomsPerStage), p.k_atoms - kt * kKAtomsPerStage);
-          const uint32_t first_blk128 = n_blk * C::kNBlocks128;
-          const uint32_t blks128 = min(static_cast<uint32_t>(C::kNBlocks128), p.sfb_blocks128 - first_blk128);
           const uint32_t sf_bytes = atoms * kSfTileBytes;
           const uint32_t full = bar_full + 8 * stage;
-          mbar_expect_tx(full, kAStageBytes + C::kBStageBytes + sf_bytes * (1u + blks128));
+          if (p.b_resident) {
+            mbar_expect_tx(full, kAStageBytes + sf_bytes);
+          } else {
+            mbar_expect_tx(full, kAStageBytes + C::kBStageBytes + sf_bytes * (1u + blks128));
+            tma_load_2d(smem_b + stage * C::kBStageBytes, &tmap_b, full, static_cast<int32_t>(kt * kBlockKBytes),
+                        static_cast<int32_t>(n_blk * kBlockN));
+            for (uint32_t i = 0; i < blks128; ++i)
+              bulk_load(smem_sfb + stage * C::kSfbStageBytes + i * kSfaStageBytes,
+                        p.sfb + (static_cast<size_t>(first_blk128 + i) * p.k_atoms + kt * kKAtomsPerStage) * kSfTileBytes,
+                        sf_bytes, full);
+          }
           tma_load_2d(smem_a + stage * kAStageBytes, &tmap_a, full, static_cast<int32_t>(kt * kBlockKBytes),
                       static_cast<int32_t>(m_blk * kBlockM));
-          tma_load_2d(smem_b + stage * C::kBStageBytes, &tmap_b, full, static_cast<int32_t>(kt * kBlockKBytes),
-                      static_cast<int32_t>(n_blk * kBlockN));
           bulk_load(smem_sfa + stage * kSfaStageBytes,
                     p.sfa + (static_cast<size_t>(m_blk) * p.k_atoms + kt * kKAtomsPerStage) * kSfTileBytes, sf_bytes,
                     full);
-          for (uint32_t i = 0; i < blks128; ++i)
-            bulk_load(smem_sfb + stage * C::kSfbStageBytes + i * kSfaStageBytes,
-                      p.sfb + (static_cast<size_t>(first_blk128 + i) * p.k_atoms + kt * kKAtomsPerStage) * kSfTileBytes,
-                      sf_bytes, full);
           ++issued;
-          if (++stage == C::kStages) {
+          if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -405,9 +474,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!ok) {
         // aborting: give copies already in flight a bounded chance to land before the CTA exits
-        const uint32_t pending = min(issued, static_cast<uint32_t>(C::kStages));
+        const uint32_t pending = min(issued, stages);
         for (uint32_t i = 0; i < pending; ++i) {
-          const uint32_t s = (stage + C::kStages - 1 - i) % C::kStages;
+          const uint32_t s = (stage + stages - 1 - i) % stages;
           const uint32_t ph = (s < stage) ? phase : (phase ^ 1u);
           for (int spin = 0; spin < 4096 && !mbar_try_wait(bar_full + 8 * s, ph); ++spin) {
           }
@@ -418,12 +487,21 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ===================== MMA issuer =====================
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc<kBlockN>();
-      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0, runs = 0, prev_n = 0xffffffffu, sf_set = 0, sf_phase = 0;
       bool ok = true;
-      for (uint32_t work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
-        const uint32_t split = work / tiles_mn;
+      for (uint32_t w = w_begin; w < w_end && ok; w += w_step) {
+        uint32_t m_blk, n_blk, split;
+        decode(w, m_blk, n_blk, split);
         const uint32_t kt_begin = split * p.k_tiles_per_split;
         const uint32_t kt_end = min(p.num_k_tiles, kt_begin + p.k_tiles_per_split);
+        if (p.b_resident && n_blk != prev_n) {
+          if (!mbar_wait(bar_b_full, runs & 1u, abort_flag, kStatusMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          prev_n = n_blk;
+          ++runs;
+        }
         if (!mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kStatusMmaTimeout)) {
           ok = false;
           break;
@@ -437,33 +515,118 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           tcgen05_fence_after();
           const uint32_t atoms = min(static_cast<uint32_t>(kKAtomsPerStage), p.k_atoms - kt * kKAtomsPerStage);
-          const uint32_t sfa_s = smem_sfa + stage * kSfaStageBytes;
-          const uint32_t sfb_s = smem_sfb + stage * C::kSfbStageBytes;
-          for (uint32_t kb = 0; kb < atoms; ++kb) {
-            tcgen05_cp_sf(tmem_base + C::kTmemSfa + kb * 4, make_sf_desc(sfa_s + kb * kSfTileBytes));
-#pragma unroll
-            for (int i = 0; i < C::kNBlocks128; ++i)
-              tcgen05_cp_sf(tmem_base + C::kTmemSfb + kb * C::kSfbColsPerAtom + i * 4,
-                            make_sf_desc(sfb_s + i * kSfaStageBytes + kb * kSfTileBytes));
+          const uint32_t b_slot = p.b_resident ? kt : stage;
+          // scale factors of this k-tile were put into column set `sf_set` by the scale-factor warps
+          if (!mbar_wait(bar_sf_full + 8 * sf_set, sf_phase, abort_flag, kStatusMmaTimeout)) {
+            ok = false;
+            break;
           }
+          tcgen05_fence_after();
+          const uint32_t tsfa = tmem_base + C::kTmemSfa + sf_set * C::kSfSetCols;
+          const uint32_t tsfb = tmem_base + C::kTmemSfb + sf_set * C::kSfSetCols;
           const uint64_t desc_a = make_ab_desc(smem_a + stage * kAStageBytes);
-          const uint64_t desc_b = make_ab_desc(smem_b + stage * C::kBStageBytes);
+          const uint64_t desc_b = make_ab_desc(smem_b + b_slot * C::kBStageBytes);
           for (uint32_t kb = 0; kb < atoms; ++kb) {
             // 64 nibbles = 32 bytes further along the swizzled row: +2 in the 16-byte start field
             tcgen05_mma_nvf4(tmem_acc, desc_a + kb * 2, desc_b + kb * 2, idesc, (kt > kt_begin || kb > 0) ? 1u : 0u,
-                             tmem_base + C::kTmemSfa + kb * 4, tmem_base + C::kTmemSfb + kb * C::kSfbColsPerAtom);
+                             tsfa + kb * 4, tsfb + kb * C::kSfbColsPerAtom);
           }
-          tcgen05_commit(bar_empty + 8 * stage);  // frees the smem stage once these MMAs retire
-          if (++stage == C::kStages) {
+          tcgen05_commit(bar_empty + 8 * stage);       // frees the smem stage once these MMAs retire
+          tcgen05_commit(bar_sf_empty + 8 * sf_set);   // ... and the scale-factor column set
+          if (++sf_set == C::kSfSets) {
+            sf_set = 0;
+            sf_phase ^= 1u;
+          }
+          if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
         tcgen05_commit(bar_tmem_full + 8 * acc);  // accumulator complete
+        if (p.b_resident) {
+          // last tile of this column block (or of this CTA): the panel may be replaced once
+          // everything issued so far has retired
+          uint32_t nm, nn, ns;
+          const bool last = (w + w_step >= w_end);
+          if (!last) decode(w + w_step, nm, nn, ns);
+          if (last || nn != n_blk) tcgen05_commit(bar_b_empty);
+        }
         if (++acc == C::kAccStages) {
           acc = 0;
           acc_phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp >= 8) {
+    // ===================== scale-factor warps =====================
+    // Four warps (one per 32-lane quadrant of tensor memory) read the 512-byte scale tiles of each
+    // k-tile from shared memory -- lane l takes the 16 bytes of rows l, l+32, l+64, l+96 -- and write
+    // them with tcgen05.st into the four columns per k-atom the MMA expects, replicated in every
+    // quadrant.  This keeps scale-factor transport off the tensor pipe (tcgen05.cp runs in order
+    // with the MMAs and costs about a third of a wide-tile main loop).
+    const uint32_t quad = warp & 3u;
+    uint32_t stage = 0, phase = 0, sf_set = 0, sf_phase = 0, runs = 0, prev_n = 0xffffffffu;
+    bool ok = true;
+    for (uint32_t w = w_begin; w < w_end && ok; w += w_step) {
+      uint32_t m_blk, n_blk, split;
+      decode(w, m_blk, n_blk, split);
+      const uint32_t kt_begin = split * p.k_tiles_per_split;
+      const uint32_t kt_end = min(p.num_k_tiles, kt_begin + p.k_tiles_per_split);
+      if (p.b_resident && n_blk != prev_n) {
+        if (!mbar_wait(bar_b_full, runs & 1u, abort_flag, kStatusMmaTimeout)) break;
+        prev_n = n_blk;
+        ++runs;
+      }
+      for (uint32_t kt = kt_begin; kt < kt_end; ++kt) {
+        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout) ||
+            !mbar_wait(bar_sf_empty + 8 * sf_set, sf_phase ^ 1u, abort_flag, kStatusMmaTimeout)) {
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t atoms = min(static_cast<uint32_t>(kKAtomsPerStage), p.k_atoms - kt * kKAtomsPerStage);
+        const uint32_t b_slot = p.b_resident ? kt : stage;
+        const uint32_t sfa_s = smem_sfa + stage * kSfaStageBytes + lane * 16;
+        const uint32_t sfb_s = smem_sfb + b_slot * C::kSfbStageBytes + lane * 16;
+        const uint32_t tsfa = tmem_base + C::kTmemSfa + sf_set * C::kSfSetCols + ((quad * 32u) << 16);
+        const uint32_t tsfb = tmem_base + C::kTmemSfb + sf_set * C::kSfSetCols + ((quad * 32u) << 16);
+#pragma unroll
+        for (uint32_t kb = 0; kb < kKAtomsPerStage; ++kb) {
+          if (kb < atoms) {
+            uint32_t r0, r1, r2, r3;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                         : "r"(sfa_s + kb * kSfTileBytes));
+            asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tsfa + kb * 4), "r"(r0),
+                         "r"(r1), "r"(r2), "r"(r3)
+                         : "memory");
+#pragma unroll
+            for (int i = 0; i < C::kNBlocks128; ++i) {
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                           : "r"(sfb_s + i * kSfaStageBytes + kb * kSfTileBytes));
+              asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
+                               tsfb + kb * C::kSfbColsPerAtom + i * 4),
+                           "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+                           : "memory");
+            }
+          }
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar_sf_full + 8 * sf_set);  // scale factors visible to the MMA issuer
+          mbar_arrive(bar_empty + 8 * stage);     // this warp no longer reads the smem stage
+        }
+        if (++sf_set == C::kSfSets) {
+          sf_set = 0;
+          sf_phase ^= 1u;
+        }
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1u;
         }
       }
     }
@@ -475,9 +638,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t acc = 0, acc_phase = 0, store_buf = 0;
     const float gb = p.mode == NVFP4_GS_NONE ? 1.0f : __ldg(p.b_global);
     const float ga_scalar = p.mode == NVFP4_GS_TENSOR ? __ldg(p.a_global) : 1.0f;
-    for (uint32_t work = blockIdx.x; work < num_work; work += gridDim.x) {
-      const uint32_t tile = work % tiles_mn, split = work / tiles_mn;
-      const uint32_t m_blk = tile / p.num_n_blocks, n_blk = tile % p.num_n_blocks;
+    for (uint32_t w = w_begin; w < w_end; w += w_step) {
+      uint32_t m_blk, n_blk, split;
+      decode(w, m_blk, n_blk, split);
       if (!mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, kStatusEpilogueTimeout)) break;
       tcgen05_fence_after();
       const uint32_t row = m_blk * kBlockM + ew * 32 + lane;
@@ -499,12 +662,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (col0 >= p.n) break;  // uniform across the epilogue warps
           float v[kSub];
 #pragma unroll
-          for (int h = 0; h < kSub / 32; ++h) {
-            uint32_t r[32];
-            tcgen05_ld_32x32b_x32(taddr_row + c + 32 * h, r);
+          {
+            uint32_t r[kSub / 32][32];
+#pragma unroll
+            for (int h = 0; h < kSub / 32; ++h) tcgen05_ld_32x32b_x32(taddr_row + c + 32 * h, r[h]);
             tcgen05_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[32 * h + i] = __fmul_rn(__uint_as_float(r[i]), scale);
+            for (int i = 0; i < kSub; ++i) v[i] = __fmul_rn(__uint_as_float(r[i / 32][i % 32]), scale);
           }
           if (p.epilogue != NVFP4_EPI_NONE && (p.k_splits == 1 || split == 0)) {
 #pragma unroll
@@ -536,7 +700,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint32_t buf = smem_store + store_buf * kStoreStageBytes;
             SubTile<OutT>::stage(buf + tile_row * 128, tile_row, v);
             fence_proxy_async_smem();
-            if (elected) bulk_wait_group_read0();  // every earlier store has left shared memory
+            // the buffer written next was last used kStoreBufs - 1 stores ago: allow that many in flight
+            if (elected) bulk_wait_group_read<C::kStoreBufs - 2>();
             epilogue_barrier();
             if (elected) {
               const CUtensorMap* map = is_pre ? &tmap_aux : &tmap_out;
@@ -546,7 +711,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 tma_store_2d(map, buf, static_cast<int32_t>(col0), static_cast<int32_t>(m_blk * kBlockM));
               bulk_commit_group();
             }
-            store_buf ^= 1u;
+            store_buf = (store_buf + 1) % C::kStoreBufs;
           }
         }
       } else {
@@ -696,15 +861,33 @@ struct GemmTiming {
 
 template <int kBlockN, typename OutT>
 int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
-                   const CUtensorMap& mx, const GemmParams& p, uint32_t grid) {
+                   const CUtensorMap& mx, GemmParams p, uint32_t grid, bool want_resident) {
   using C = Cfg<kBlockN>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
     attr_err = cudaFuncSetAttribute(nvfp4_gemm_tcgen05_kernel<kBlockN, OutT>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
   });
   if (attr_err != cudaSuccess) return static_cast<int>(attr_err);
+  // shared-memory plan
+  const int budget = kSmemBudget - C::kFixedBytes;
+  p.b_resident = 0;
+  if (want_resident) {
+    const int left = budget - static_cast<int>(p.num_k_tiles) * C::kPanelSlotBytes;
+    const int st = left / C::kResidentStageBytes;
+    if (st >= 4) {
+      p.b_resident = 1;
+      p.stages = static_cast<uint32_t>(st > kMaxStages ? kMaxStages : st);
+    }
+  }
+  if (!p.b_resident) {
+    const int st = budget / C::kStreamStageBytes;
+    p.stages = static_cast<uint32_t>(st > kMaxStages ? kMaxStages : st);
+  }
+  const uint32_t b_slots = p.b_resident ? p.num_k_tiles : p.stages;
+  const size_t smem_bytes = C::kFixedBytes + static_cast<size_t>(p.stages) * (kAStageBytes + kSfaStageBytes) +
+                            static_cast<size_t>(b_slots) * C::kPanelSlotBytes;
   GemmTimingRecord* rec = nullptr;
   if (g_timing.enabled) {
     std::lock_guard<std::mutex> lock(g_timing.mu);
@@ -714,7 +897,7 @@ int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb,
     rec->flops = 2.0 * p.m * p.n * p.k;
     cudaEventRecord(rec->start, s);
   }
-  nvfp4_gemm_tcgen05_kernel<kBlockN, OutT><<<grid, kThreads, C::kSmemBytes, s>>>(ma, mb, mo, mx, p);
+  nvfp4_gemm_tcgen05_kernel<kBlockN, OutT><<<grid, kThreads, smem_bytes, s>>>(ma, mb, mo, mx, p);
   count_launch();
   const int rc = static_cast<int>(cudaGetLastError());
   if (rec) cudaEventRecord(rec->stop, s);
@@ -856,12 +1039,15 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
 
   const uint32_t work = tiles * p.k_splits;
   const uint32_t grid = work < static_cast<uint32_t>(sms) ? work : static_cast<uint32_t>(sms);
+  // Short K and many row blocks: keep the B panel resident and stream only A (halves the
+  // operand traffic per tile; these shapes are otherwise bound by L2 -> SM bandwidth).
+  const bool want_resident = block_n == 128 && p.k_splits == 1 && p.num_k_tiles <= 4 && tiles >= 4 * grid;
   if (block_n == 256) {
-    return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<256, float>(s, ma, mb, mo, mx, p, grid)
-                                          : launch_variant<256, __nv_bfloat16>(s, ma, mb, mo, mx, p, grid);
+    return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<256, float>(s, ma, mb, mo, mx, p, grid, false)
+                                          : launch_variant<256, __nv_bfloat16>(s, ma, mb, mo, mx, p, grid, false);
   }
-  return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<128, float>(s, ma, mb, mo, mx, p, grid)
-                                        : launch_variant<128, __nv_bfloat16>(s, ma, mb, mo, mx, p, grid);
+  return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<128, float>(s, ma, mb, mo, mx, p, grid, want_resident)
+                                        : launch_variant<128, __nv_bfloat16>(s, ma, mb, mo, mx, p, grid, want_resident);
 }
 
 }  // namespace nvfp4

@@ -382,6 +382,24 @@ def test_gemm_split_k_and_padded_output(pkg, oracle, dev):
     assert_no_timeouts(pkg)
 
 
+def test_gemm_resident_panel_with_tails(pkg, oracle, dev):
+    """Short K with many row blocks runs with the B panel resident in shared memory; M, N and K
+    all have ragged tails here (K = 448 is seven 64-element atoms: a full k-tile and a 3-atom one)."""
+    gemm = pkg.Nvfp4GemmModule()
+    m, n, k = 10000, 1000, 448
+    rng = np.random.default_rng(5)
+    a, b = _rand_nvfp4(rng, m, k, True), _rand_nvfp4(rng, n, k, False)
+    bias = rng.normal(0, 30.0, n).astype(np.float32)
+    want = oracle.gemm(a, b, m, k, n, 2, bias=bias, epi=1)
+    A, B = _to_dev(pkg, dev, a, m, k, True), _to_dev(pkg, dev, b, n, k, False)
+    got = cpu(gemm.gemm(A, B, bias=torch.from_numpy(bias).to(dev), epilogue=pkg.EPI_BIAS))
+    assert rel_fro(got, want) <= GEMM_TOL
+    got16 = cpu(gemm.gemm(A, B, bias=torch.from_numpy(bias).to(dev), epilogue=pkg.EPI_BIAS,
+                          out_dtype=torch.bfloat16).float())
+    assert rel_fro(got16, torch.from_numpy(want).to(torch.bfloat16).float().numpy()) <= GEMM_TOL
+    assert_no_timeouts(pkg)
+
+
 def test_gemm_rejects_bad_shapes(pkg, dev):
     gemm = pkg.Nvfp4GemmModule()
     rng = np.random.default_rng(0)
