@@ -68,7 +68,8 @@ struct Cfg {
   // epilogue staging ring: deep for the narrow tile (short-K GEMMs are epilogue bound), shallow for
   // the wide one (long-K GEMMs need the shared memory for pipeline stages)
   static constexpr int kStoreBufs = kBlockN == 128 ? 4 : 2;
-  static constexpr int kFixedBytes = 1024 /*alignment slack*/ + kStoreBufs * kStoreStageBytes + 512 /*barriers*/;
+  static constexpr int kFixedBytes =
+      1024 /*alignment slack*/ + kStoreBufs * kStoreStageBytes + 512 /*barriers*/ + 1024 /*bias of the tile*/;
   static_assert(256 + kSfSets * kSfSetCols <= kTmemCols, "tensor memory overflow");
   static_assert(kAccStages * kBlockN <= 256, "accumulators overlap the scale-factor columns");
 };
@@ -197,6 +198,19 @@ __device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t (
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_st_x4(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3])
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_st_x16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -332,6 +346,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t smem_bar = smem_store + C::kStoreBufs * kStoreStageBytes;
   // barrier block: full[8], empty[8], tmem_full[2], tmem_empty[2], b_full, b_empty, sf_full[4], sf_empty[4],
   // tmem base, abort flag
+  const uint32_t smem_bias = smem_bar + 512;  // kBlockN floats
   const uint32_t bar_full = smem_bar;
   const uint32_t bar_empty = bar_full + 8 * kMaxStages;
   const uint32_t bar_tmem_full = bar_empty + 8 * kMaxStages;
@@ -591,25 +606,38 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t sfb_s = smem_sfb + b_slot * C::kSfbStageBytes + lane * 16;
         const uint32_t tsfa = tmem_base + C::kTmemSfa + sf_set * C::kSfSetCols + ((quad * 32u) << 16);
         const uint32_t tsfb = tmem_base + C::kTmemSfb + sf_set * C::kSfSetCols + ((quad * 32u) << 16);
+        // all shared-memory reads first (independent, pipelined), then the tensor-memory stores
+        uint32_t ra[kKAtomsPerStage][4];
+        uint32_t rb[kKAtomsPerStage][C::kNBlocks128][4];
 #pragma unroll
         for (uint32_t kb = 0; kb < kKAtomsPerStage; ++kb) {
           if (kb < atoms) {
-            uint32_t r0, r1, r2, r3;
             asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                         : "=r"(ra[kb][0]), "=r"(ra[kb][1]), "=r"(ra[kb][2]), "=r"(ra[kb][3])
                          : "r"(sfa_s + kb * kSfTileBytes));
-            asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tsfa + kb * 4), "r"(r0),
-                         "r"(r1), "r"(r2), "r"(r3)
-                         : "memory");
 #pragma unroll
-            for (int i = 0; i < C::kNBlocks128; ++i) {
+            for (int i = 0; i < C::kNBlocks128; ++i)
               asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                           : "=r"(rb[kb][i][0]), "=r"(rb[kb][i][1]), "=r"(rb[kb][i][2]), "=r"(rb[kb][i][3])
                            : "r"(sfb_s + i * kSfaStageBytes + kb * kSfTileBytes));
-              asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
-                               tsfb + kb * C::kSfbColsPerAtom + i * 4),
-                           "r"(r0), "r"(r1), "r"(r2), "r"(r3)
-                           : "memory");
+          }
+        }
+        if (atoms == kKAtomsPerStage) {
+          // one 16-column store for the A scales, one 16- or 32-column store for the B scales
+          tcgen05_st_x16(tsfa, &ra[0][0]);
+          if (C::kNBlocks128 == 1) {
+            tcgen05_st_x16(tsfb, &rb[0][0][0]);
+          } else {
+            tcgen05_st_x16(tsfb, &rb[0][0][0]);
+            tcgen05_st_x16(tsfb + 16, &rb[2][0][0]);
+          }
+        } else {
+#pragma unroll
+          for (uint32_t kb = 0; kb < kKAtomsPerStage; ++kb) {
+            if (kb < atoms) {
+              tcgen05_st_x4(tsfa + kb * 4, ra[kb]);
+#pragma unroll
+              for (int i = 0; i < C::kNBlocks128; ++i) tcgen05_st_x4(tsfb + kb * C::kSfbColsPerAtom + i * 4, rb[kb][i]);
             }
           }
         }
@@ -656,6 +684,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         constexpr int kSub = SubTile<OutT>::kCols;
         const uint32_t tile_row = ew * 32 + lane;
         const bool elected = threadIdx.x == 128;
+        const bool add_bias = p.epilogue != NVFP4_EPI_NONE && (p.k_splits == 1 || split == 0);
+        if (add_bias) {
+          // the tile's bias slice goes through shared memory once; every row then reads it broadcast
+          for (uint32_t i = threadIdx.x - 128; i < static_cast<uint32_t>(kBlockN); i += 128) {
+            const uint32_t col = n_blk * kBlockN + i;
+            const float bv = col < p.n ? __ldg(p.bias + col) : 0.0f;
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(smem_bias + i * 4), "f"(bv) : "memory");
+          }
+          epilogue_barrier();
+        }
 #pragma unroll 1
         for (int c = 0; c < kBlockN; c += kSub) {
           const uint32_t col0 = n_blk * kBlockN + c;
@@ -670,21 +708,17 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int i = 0; i < kSub; ++i) v[i] = __fmul_rn(__uint_as_float(r[i / 32][i % 32]), scale);
           }
-          if (p.epilogue != NVFP4_EPI_NONE && (p.k_splits == 1 || split == 0)) {
+          if (add_bias) {
 #pragma unroll
             for (int i = 0; i < kSub; i += 4) {
-              float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (col0 + i + 3 < p.n) {
-                b4 = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + i));
-              } else {
-                if (col0 + i < p.n) b4.x = __ldg(p.bias + col0 + i);
-                if (col0 + i + 1 < p.n) b4.y = __ldg(p.bias + col0 + i + 1);
-                if (col0 + i + 2 < p.n) b4.z = __ldg(p.bias + col0 + i + 2);
-              }
-              v[i] = __fadd_rn(v[i], b4.x);
-              v[i + 1] = __fadd_rn(v[i + 1], b4.y);
-              v[i + 2] = __fadd_rn(v[i + 2], b4.z);
-              v[i + 3] = __fadd_rn(v[i + 3], b4.w);
+              float b0, b1, b2, b3;
+              asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                           : "=f"(b0), "=f"(b1), "=f"(b2), "=f"(b3)
+                           : "r"(smem_bias + (c + i) * 4));
+              v[i] = __fadd_rn(v[i], b0);
+              v[i + 1] = __fadd_rn(v[i + 1], b1);
+              v[i + 2] = __fadd_rn(v[i + 2], b2);
+              v[i + 3] = __fadd_rn(v[i + 3], b3);
             }
           }
           const int passes = (p.epilogue == NVFP4_EPI_RELU2 && p.aux) ? 2 : 1;
