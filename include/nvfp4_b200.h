@@ -129,6 +129,14 @@ int nvfp4_quantize_four_six(void* stream, const void* x, int dtype, const float*
                             uint32_t rows, uint32_t cols, uint8_t* out_fp4, uint8_t* out_scales,
                             int scale_layout, float* out_global_scale);
 
+/* Row amax and rowwise four-six in one pass over the input (the caller pattern
+ * RowwiseNvfp4Scratch::quantize_row_amax, crates/gpt2-nvfp4/src/types/nvfp4_scratch/scratch.rs:35-52,
+ * issues row_amax_f32 then fp32_to_nvfp4_four_six_rowwise).  Same bytes as those two calls.
+ * out_row_amax (f32[rows]) is optional for rows of up to 4096 elements and required beyond. */
+int nvfp4_quantize_four_six_rowwise_fused(void* stream, const void* x, int dtype, uint32_t rows, uint32_t cols,
+                                          uint8_t* out_fp4, uint8_t* out_scales, int scale_layout,
+                                          float* out_global_scale, float* out_row_amax);
+
 /* MS-EDEN quantizer (random-sign Hadamard-32 rotation, RTN nibbles, EDEN-corrected block
  * scale rounded stochastically with a counter RNG) ---------------------------------------- */
 

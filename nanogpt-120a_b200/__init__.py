@@ -94,6 +94,7 @@ _SIGNATURES = {
     "nvfp4_fp32_to_nvfp4_four_six_padded": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _U],
     "nvfp4_fp32_transpose_to_nvfp4_four_six_padded": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _U],
     "nvfp4_quantize_four_six": [_P, _P, c_int, _P, c_int, _U, _U, _P, _P, c_int, _P],
+    "nvfp4_quantize_four_six_rowwise_fused": [_P, _P, c_int, _U, _U, _P, _P, c_int, _P, _P],
     "nvfp4_ms_eden_quantize": [_P, POINTER(MsEdenArgs)],
     "nvfp4_fp32_to_nvfp4_ms_eden": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _F, _F, _U, _U],
     "nvfp4_fp32_to_nvfp4_ms_eden_device_scale": [_P, _P, _P, _P, _P, _P, _P, _U, _U, _U, _F, _U, _U],
@@ -336,14 +337,21 @@ class Nvfp4QuantModule:
         """B200-native form: f32 / bf16 input, scales written in the layout the GEMM reads."""
         _require_cuda()
         rows, cols = x.shape
-        if amax is None:
-            amax = self.row_amax(x) if rowwise else self.tensor_amax(x)[1]
+        fused = amax is None and rowwise
+        if amax is None and not rowwise:
+            amax = self.tensor_amax(x)[1]
         if out is None:
             n = rows * cols
             nsc = scale_packed_len(rows, cols) if packed else n // 16
             out = Nvfp4Tensor(_empty_u8(n // 2, x.device), _empty_u8(nsc, x.device),
                               torch.empty(rows if rowwise else 1, dtype=torch.float32, device=x.device), rows, cols,
                               packed=packed, rowwise=rowwise)
+        if fused:  # row amax and quantization in one pass over x
+            row_amax = torch.empty(rows, dtype=torch.float32, device=x.device) if cols > 4096 else None
+            _call("nvfp4_quantize_four_six_rowwise_fused", _stream(), _ptr(x), _dtype_code(x), rows, cols,
+                  _ptr(out.bytes), _ptr(out.scales), SCALES_PACKED if packed else SCALES_LOGICAL,
+                  _ptr(out.global_scales), _ptr(row_amax))
+            return out
         _call("nvfp4_quantize_four_six", _stream(), _ptr(x), _dtype_code(x), _ptr(amax), 1 if rowwise else 0, rows,
               cols, _ptr(out.bytes), _ptr(out.scales), SCALES_PACKED if packed else SCALES_LOGICAL,
               _ptr(out.global_scales))

@@ -110,6 +110,26 @@ int nvfp4_quantize_four_six(void* stream, const void* x, int dtype, const float*
                          scale_layout == NVFP4_SCALES_PACKED, out_gs);
 }
 
+int nvfp4_quantize_four_six_rowwise_fused(void* stream, const void* x, int dtype, uint32_t rows, uint32_t cols,
+                                          uint8_t* out_fp4, uint8_t* out_scales, int scale_layout,
+                                          float* out_global_scale, float* out_row_amax) {
+  if (cols % 16 != 0) return invalid("quantize_four_six_rowwise_fused: cols must be a multiple of 16");
+  if (scale_layout == NVFP4_SCALES_PACKED && cols % 64 != 0)
+    return invalid("quantize_four_six_rowwise_fused: the packed scale layout needs cols % 64 == 0");
+  if (dtype != NVFP4_DTYPE_F32 && dtype != NVFP4_DTYPE_BF16) return invalid("quantize_four_six_rowwise_fused: dtype");
+  if (reinterpret_cast<uintptr_t>(x) & 15u) return invalid("quantize_four_six_rowwise_fused: input must be 16-byte aligned");
+  const int packed = scale_layout == NVFP4_SCALES_PACKED;
+  int rc = launch_four_six_rowwise_fused(S(stream), x, dtype, rows, cols, out_fp4, out_scales, packed,
+                                         out_global_scale, out_row_amax);
+  if (rc != -1) return rc;
+  // rows too long for one thread block: a row amax pass, then the rowwise quantizer
+  if (!out_row_amax) return invalid("quantize_four_six_rowwise_fused: rows longer than 4096 need out_row_amax");
+  rc = launch_row_amax(S(stream), x, dtype, out_row_amax, rows, cols);
+  if (rc) return rc;
+  return launch_four_six(S(stream), x, dtype, out_row_amax, 1, rows, cols, out_fp4, out_scales, packed,
+                         out_global_scale);
+}
+
 // ---- MS-EDEN ----------------------------------------------------------------------------
 static int validate_ms_eden(const nvfp4_ms_eden_args* a);
 
@@ -293,12 +313,14 @@ static int nvfp4_source_transpose(void* stream, int kind, const uint8_t* in_byte
   if (source_cols % 16 != 0) return invalid("nvfp4 transpose: source_cols must be a multiple of 16");
   if (src_scale_layout == NVFP4_SCALES_PACKED && source_cols % 64 != 0)
     return invalid("nvfp4 transpose: a packed source scale layout needs source_cols % 64 == 0");
+  // the amax kernel leaves max(chunk amax) in out_gs; turn it into the MS-EDEN global scale in place
   int rc = launch_nvfp4_amax(S(stream), in_bytes, in_scales, in_global, source_rows, source_cols,
                              kind == NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED, src_scale_layout == NVFP4_SCALES_PACKED,
                              out_chunk_amax, out_gs);
   if (rc) return rc;
-  rc = launch_amax_from_chunks(S(stream), out_chunk_amax, out_gs, chunks1024(n), 1);
+  rc = launch_ms_eden_scale_from_amax(S(stream), out_gs, out_gs);
   if (rc) return rc;
+  (void)n;
   nvfp4_ms_eden_args a;
   std::memset(&a, 0, sizeof(a));
   a.src_kind = kind;

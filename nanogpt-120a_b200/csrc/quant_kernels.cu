@@ -145,13 +145,13 @@ __global__ void __launch_bounds__(256) nvfp4_amax_kernel(const uint8_t* __restri
       const float gs = rowwise ? gscales[srow] : gscales[0];
       const float sc = e4m3_value(packed ? scales[packed_scale_offset(srow, skg, cols >> 6)] : scales[g0 >> 4]);
       const uint2 raw = __ldg(reinterpret_cast<const uint2*>(bytes + (g0 >> 1)));
-      const uint32_t w[2] = {raw.x, raw.y};
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float2 q = e2m1x2_values((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
-        m = max_f32(m, fabsf(q.x * sc * gs));
-        m = max_f32(m, fabsf(q.y * sc * gs));
-      }
+      // |e2m1| grows with its 3-bit magnitude code and (q * sc) * gs is monotonic in q >= 0, so
+      // the group's largest decoded magnitude is that of its largest code: one decode per group
+      uint32_t mx = __vmaxu4(__vmaxu4(raw.x & 0x07070707u, (raw.x >> 4) & 0x07070707u),
+                             __vmaxu4(raw.y & 0x07070707u, (raw.y >> 4) & 0x07070707u));
+      mx = __vmaxu4(mx, mx >> 16);
+      mx = __vmaxu4(mx, mx >> 8) & 0x7u;
+      m = max_f32(m, fabsf(e2m1_value(mx) * sc * gs));
     }
     m = warp_max(m);
     if (lane == 0 && chunk_amax) chunk_amax[chunk] = m;
@@ -263,6 +263,51 @@ __global__ void __launch_bounds__(256) four_six_kernel(const T* __restrict__ x, 
   else
     out_scales[g] = static_cast<uint8_t>(b);
   if (kRowwise ? (kg == 0) : (g == 0)) out_gs[kRowwise ? row : 0] = gs;
+}
+
+// Row amax and rowwise four-six in ONE pass over the input: a CTA owns whole rows (one thread
+// per 16-group), the row amax is the shared-memory max of the group amaxes the quantizer needs
+// anyway, and the groups are quantized from registers.  Same bytes as row_amax followed by the
+// rowwise kernel (crates/gpt2-nvfp4/src/types/nvfp4_scratch/scratch.rs:35-52 issues those two).
+template <typename T, bool kPacked>
+__global__ void __launch_bounds__(256) four_six_rowwise_fused_kernel(const T* __restrict__ x,
+                                                                      uint8_t* __restrict__ out_fp4,
+                                                                      uint8_t* __restrict__ out_scales,
+                                                                      float* __restrict__ out_gs,
+                                                                      float* __restrict__ out_amax, uint32_t rows,
+                                                                      uint32_t groups_per_row, uint32_t rows_per_cta) {
+  extern __shared__ unsigned int row_amax_bits[];
+  const uint32_t t = threadIdx.x;
+  if (t < rows_per_cta) row_amax_bits[t] = 0u;
+  __syncthreads();
+  const uint32_t local_row = t / groups_per_row;
+  const uint32_t kg = t - local_row * groups_per_row;
+  const uint32_t row = blockIdx.x * rows_per_cta + local_row;
+  const bool active = local_row < rows_per_cta && row < rows;
+  float v[16];
+  if (active) {
+    Load16<T>::run(x + (static_cast<size_t>(row) * groups_per_row + kg) * 16, v);
+    float ga = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) ga = max_f32(ga, fabsf(v[i]));
+    atomicMax(&row_amax_bits[local_row], __float_as_uint(ga));  // non-negative floats order like their bits
+  }
+  __syncthreads();
+  if (!active) return;
+  const float amax = __uint_as_float(row_amax_bits[local_row]);
+  const float gs = four_six_global_scale(amax);
+  uint2 packed;
+  const uint32_t b = four_six_group(v, gs, packed);
+  const size_t g = static_cast<size_t>(row) * groups_per_row + kg;
+  *reinterpret_cast<uint2*>(out_fp4 + g * 8) = packed;
+  if (kPacked)
+    out_scales[packed_scale_offset(row, kg, groups_per_row >> 2)] = static_cast<uint8_t>(b);
+  else
+    out_scales[g] = static_cast<uint8_t>(b);
+  if (kg == 0) {
+    out_gs[row] = gs;
+    if (out_amax) out_amax[row] = amax;
+  }
 }
 
 // Padded / transposed-padded variants: generic gather, zero outside the source extent.
@@ -754,22 +799,24 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(const T* __restrict__ e,
   }
 }
 
-// dbias[c] = sum over row tiles of the tile column sums, tile 0 first (fixed order).
+// dbias[c] = sum over row tiles of the tile column sums in a fixed order: eight lanes per
+// column each add tiles lane, lane+8, ... in sequence, then the lane sums are added 0..7.
 __global__ void __launch_bounds__(256) col_sum_reduce_kernel(const float* __restrict__ partials,
                                                               float* __restrict__ dbias, uint32_t tiles, uint32_t n) {
-  const uint32_t c = blockIdx.x * 256 + threadIdx.x;
-  if (c >= n) return;
+  __shared__ float sums[256];
+  const uint32_t lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const uint32_t c = blockIdx.x * 32 + lane;
   float acc = 0.0f;
-  uint32_t t = 0;
-  for (; t + 8 <= tiles; t += 8) {
-    float v[8];
+  if (c < n)
+    for (uint32_t t = w; t < tiles; t += 8) acc += __ldg(partials + static_cast<size_t>(t) * n + c);
+  sums[threadIdx.x] = acc;
+  __syncthreads();
+  if (w == 0 && c < n) {
+    float r = sums[lane];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __ldg(partials + static_cast<size_t>(t + i) * n + c);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc += v[i];
+    for (int i = 1; i < 8; ++i) r = r + sums[lane + 32 * i];
+    dbias[c] = r;
   }
-  for (; t < tiles; ++t) acc += __ldg(partials + static_cast<size_t>(t) * n + c);
-  dbias[c] = acc;
 }
 
 // ============================================================================
@@ -859,6 +906,33 @@ int launch_four_six(cudaStream_t s, const void* x, int dtype, const float* amax,
                                           out_scales, packed, out_gs)
                       : launch_four_six_t(s, static_cast<const __nv_bfloat16*>(x), amax, rowwise, rows, cols, out_fp4,
                                           out_scales, packed, out_gs);
+  if (rc) return rc;
+  if (packed) return launch_packed_scale_pad(s, out_scales, rows, cols);
+  return 0;
+}
+
+// Fused row amax + rowwise four-six.  Returns -1 when the row is too long for one CTA (the
+// caller then runs the two-kernel path).
+int launch_four_six_rowwise_fused(cudaStream_t s, const void* x, int dtype, uint32_t rows, uint32_t cols,
+                                  uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs, float* out_amax) {
+  const uint32_t gpr = cols / 16;
+  if (gpr == 0 || gpr > 256) return -1;
+  if (rows == 0) return 0;
+  const uint32_t rpc = 256 / gpr;
+  const uint32_t threads = (rpc * gpr + 31) / 32 * 32;
+  const uint32_t grid = (rows + rpc - 1) / rpc;
+  const size_t smem = rpc * sizeof(unsigned int);
+  if (dtype == NVFP4_DTYPE_F32) {
+    const float* p = static_cast<const float*>(x);
+    if (packed) four_six_rowwise_fused_kernel<float, true><<<grid, threads, smem, s>>>(p, out_fp4, out_scales, out_gs, out_amax, rows, gpr, rpc);
+    else four_six_rowwise_fused_kernel<float, false><<<grid, threads, smem, s>>>(p, out_fp4, out_scales, out_gs, out_amax, rows, gpr, rpc);
+  } else {
+    const __nv_bfloat16* p = static_cast<const __nv_bfloat16*>(x);
+    if (packed) four_six_rowwise_fused_kernel<__nv_bfloat16, true><<<grid, threads, smem, s>>>(p, out_fp4, out_scales, out_gs, out_amax, rows, gpr, rpc);
+    else four_six_rowwise_fused_kernel<__nv_bfloat16, false><<<grid, threads, smem, s>>>(p, out_fp4, out_scales, out_gs, out_amax, rows, gpr, rpc);
+  }
+  count_launch();
+  int rc = static_cast<int>(cudaGetLastError());
   if (rc) return rc;
   if (packed) return launch_packed_scale_pad(s, out_scales, rows, cols);
   return 0;
@@ -1006,7 +1080,7 @@ bool ms_eden_pair_is_tiled(const nvfp4_ms_eden_args& r, const nvfp4_ms_eden_args
 
 int launch_col_sum_reduce(cudaStream_t s, const float* partials, float* dbias, uint32_t tiles, uint32_t n) {
   if (n == 0) return 0;
-  col_sum_reduce_kernel<<<blocks_for(n, 256), 256, 0, s>>>(partials, dbias, tiles, n);
+  col_sum_reduce_kernel<<<blocks_for(n, 32), 256, 0, s>>>(partials, dbias, tiles, n);
   NVFP4_RETURN_LAST();
 }
 

@@ -166,8 +166,7 @@ class ProjectionSet:
 
     def _forward_linear(self, lin: _Linear) -> None:
         x = self.x[lin.in_dim]
-        self.quant.row_amax(x, lin.x_amax)
-        self.quant.quantize_four_six(x, amax=lin.x_amax, rowwise=True, packed=True, out=lin.xq)  # saved for backward
+        self.quant.quantize_four_six(x, rowwise=True, packed=True, out=lin.xq)  # amax fused; saved for backward
         aux = self.pre[lin.out_dim] if lin.epilogue == EPI_RELU2 else None
         self._timed_gemm(lambda: self.gemm.gemm(lin.xq, lin.wq, bias=lin.bias, epilogue=lin.epilogue,
                                                 out=self.y[lin.out_dim], aux=aux),

@@ -567,13 +567,14 @@ void oracle_bias_grad(const float* e, float* dbias, uint32_t tokens, uint32_t n)
 
 // The same column sums in the order of the fused GPU path (no reference counterpart: the
 // reference always uses the order above): per 128-row tile four sequential 32-row sums
-// combined as ((q0 + q1) + q2) + q3, tiles then added first to last.  Same mathematical
+// combined as ((q0 + q1) + q2) + q3; tile sums go to eight lanes (tile index mod 8), each lane
+// added in tile order, and the lanes are summed 0..7.  Same mathematical
 // value as oracle_bias_grad; differs from it by f32 rounding only.
 void oracle_bias_grad_tiled(const float* e, float* dbias, uint32_t tokens, uint32_t n) {
   const uint32_t tiles = (tokens + 127) / 128;
 #pragma omp parallel for schedule(static)
   for (int64_t c = 0; c < n; ++c) {
-    float acc = 0.0f;
+    float lanes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (uint32_t t = 0; t < tiles; ++t) {
       float q[4];
       for (int k = 0; k < 4; ++k) {
@@ -584,9 +585,11 @@ void oracle_bias_grad_tiled(const float* e, float* dbias, uint32_t tokens, uint3
         }
         q[k] = a;
       }
-      acc += ((q[0] + q[1]) + q[2]) + q[3];
+      lanes[t % 8] += ((q[0] + q[1]) + q[2]) + q[3];  // eight tile lanes, each in tile order
     }
-    dbias[c] = acc;
+    float sum = lanes[0];
+    for (int w = 1; w < 8; ++w) sum = sum + lanes[w];
+    dbias[c] = sum;
   }
 }
 

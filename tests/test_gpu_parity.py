@@ -66,6 +66,14 @@ def test_four_six_bit_exact(pkg, oracle, dev, dtype, rowwise, shape, packed):
     _check_four_six(pkg, oracle, dev, x, rowwise, packed)
 
 
+def test_four_six_rowwise_long_rows(pkg, oracle, dev):
+    """Rows longer than one thread block covers take the two-kernel path; a row that exactly fills
+    a block (4096) and ragged row counts take the fused one."""
+    for shape in [(3, 8192), (5, 4096), (7, 2048), (11, 48)]:
+        x = with_outliers(bf16_normal(23, shape), seed=9, every=53)
+        _check_four_six(pkg, oracle, dev, x, rowwise=True, packed=False)
+
+
 def test_four_six_edge_values(pkg, oracle, dev):
     """Zero rows, ties on the E2M1 grid, huge and tiny magnitudes, negative zero."""
     x = torch.zeros(8, 64)
