@@ -21,6 +21,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
+from .sharding import GradBuckets
 from . import (EPI_BIAS, EPI_NONE, EPI_RELU2, LinearBackwardModule, LinearBackwardScratch, Nvfp4GemmModule,
                Nvfp4QuantModule, Nvfp4Tensor, padded_k, scale_packed_len)
 
@@ -113,24 +114,17 @@ class ProjectionSet:
         self.rng = Gpt2Rng(seed)
         d, h, v = shape.d_model, shape.d_mlp, shape.vocab
         self.layers: List[List[_Linear]] = []
-        self.buckets: List[torch.Tensor] = []
         for l in range(shape.n_layer):
-            lin = [_Linear(n, i, o, e, tokens, device, seed * 1000 + l * 10 + j)
-                   for j, (n, i, o, e) in enumerate(shape.linears())]
-            size = sum(x.out_dim * x.in_dim + x.out_dim for x in lin)
-            bucket = torch.zeros(size, dtype=torch.float32, device=device)
-            off = 0
-            for x in lin:
-                x.dweight = bucket[off: off + x.out_dim * x.in_dim].view(x.out_dim, x.in_dim)
-                off += x.out_dim * x.in_dim
-                x.dbias = bucket[off: off + x.out_dim]
-                off += x.out_dim
-            self.layers.append(lin)
-            self.buckets.append(bucket)
+            self.layers.append([_Linear(n, i, o, e, tokens, device, seed * 1000 + l * 10 + j)
+                                for j, (n, i, o, e) in enumerate(shape.linears())])
         self.lm_head = _Linear("lm_head", d, v, EPI_NONE, tokens, device, seed * 1000 + 999, has_bias=False)
-        head_bucket = torch.zeros(v * d, dtype=torch.float32, device=device)
-        self.lm_head.dweight = head_bucket.view(v, d)
-        self.buckets.append(head_bucket)
+        # one gradient bucket per layer (dW + dbias of its four linears) and one for the LM head
+        self.grads = GradBuckets([[(x.out_dim, x.in_dim, True) for x in lin] for lin in self.layers] +
+                                 [[(v, d, False)]], device)
+        for lin, views in zip(self.layers + [[self.lm_head]], self.grads.views):
+            for x, (dw, db) in zip(lin, views):
+                x.dweight, x.dbias = dw, db
+        self.buckets = self.grads.buffers
 
         # Synthetic stand-ins for the tensors the rest of the model would produce: one activation
         # per input width, one upstream gradient per output width (larger than L2 at bench sizes).
@@ -152,7 +146,6 @@ class ProjectionSet:
                 self.scratch[(i, o)] = LinearBackwardScratch(tokens, i, o, device)
         self.gemm_events: List[Tuple[torch.cuda.Event, torch.cuda.Event, int]] = []
         self.record_gemm_events = False
-        self._pending = []
 
     # ---- pieces -------------------------------------------------------------------------
     def all_linears(self) -> List[_Linear]:
@@ -190,11 +183,9 @@ class ProjectionSet:
         else:
             fn()
 
-    def _reduce(self, bucket: torch.Tensor) -> None:
+    def _reduce(self, layer: int) -> None:
         if self.pg is not None:
-            import torch.distributed as dist
-
-            self._pending.append(dist.all_reduce(bucket, group=self.pg, async_op=True))
+            self.grads.reduce_async(layer, self.pg)
 
     # ---- one step -----------------------------------------------------------------------
     def forward(self) -> None:
@@ -205,14 +196,12 @@ class ProjectionSet:
 
     def backward(self) -> None:
         self._backward_linear(self.lm_head)
-        self._reduce(self.buckets[-1])
+        self._reduce(self.shape.n_layer)
         for l in range(self.shape.n_layer - 1, -1, -1):
             for x in reversed(self.layers[l]):
                 self._backward_linear(x)
-            self._reduce(self.buckets[l])
-        for work in self._pending:
-            work.wait()
-        self._pending.clear()
+            self._reduce(l)
+        self.grads.wait()
 
     def step(self) -> None:
         self.quantize_weights()

@@ -223,6 +223,40 @@ def test_ms_eden_reference_named_entries(pkg, oracle, dev):
     assert np.array_equal(cpu(tr.global_scales), ot[2])
 
 
+def test_kernels_match_committed_golden_vectors(pkg, dev):
+    """The CUDA path against tests/golden/*.npz (no oracle involved at run time)."""
+    import os
+
+    golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    q, gemm = pkg.Nvfp4QuantModule(), pkg.Nvfp4GemmModule()
+    g = dict(np.load(os.path.join(golden, "four_six.npz")))
+    x = torch.from_numpy(g["x"]).to(dev)
+    t = q.quantize_four_six(x.to(torch.bfloat16), rowwise=False, packed=False)
+    assert np.array_equal(cpu(t.bytes), g["fs_tensor_bytes"]) and np.array_equal(cpu(t.scales), g["fs_tensor_scales"])
+    t = q.quantize_four_six(x, rowwise=True, packed=True)
+    assert np.array_equal(cpu(t.bytes), g["fs_row_bytes"]) and np.array_equal(cpu(t.scales), g["fs_row_packed"])
+    assert np.array_equal(cpu(t.global_scales), g["fs_row_gs"])
+    src = q.quantize_four_six(x, rowwise=True, packed=False)
+    m = dict(np.load(os.path.join(golden, "ms_eden.npz")))
+    e = torch.from_numpy(m["e"]).to(dev)
+    r, tr, gs = q.fp32_pair_to_nvfp4_quartet_backward_ms_eden_derived_device_scale_no_chunk_amax(
+        e, 128, 64, SIGN, SCALE, SCALE ^ 0x85EBCA6B)
+    assert cpu(gs)[0] == m["gs"]
+    assert np.array_equal(cpu(r.bytes), m["rows_bytes"]) and np.array_equal(cpu(r.scales), m["rows_scales"])
+    assert np.array_equal(cpu(tr.bytes), m["t_bytes"]) and np.array_equal(cpu(tr.scales), m["t_scales"])
+    xt, xgs, _ = q.rowwise_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale(src, 64, SIGN,
+                                                                                             SCALE ^ 0xC2B2AE35)
+    assert cpu(xgs)[0] == m["xt_gs_scalar"]
+    assert np.array_equal(cpu(xt.bytes), m["xt_bytes"]) and np.array_equal(cpu(xt.scales), m["xt_scales"])
+    k = dict(np.load(os.path.join(golden, "gemm.npz")))
+    A = _to_dev(pkg, dev, (k["a_bytes"], k["a_scales"], k["a_gs"]), 48, 128, True)
+    W = _to_dev(pkg, dev, (k["w_bytes"], k["w_scales"], k["w_gs"]), 40, 128, False)
+    assert rel_fro(cpu(gemm.gemm(A, W)), k["raw"]) <= GEMM_TOL
+    aux = torch.empty((48, 40), dtype=torch.float32, device=dev)
+    out = gemm.gemm(A, W, bias=torch.from_numpy(k["bias"]).to(dev), epilogue=pkg.EPI_RELU2, aux=aux)
+    assert rel_fro(cpu(out), k["relu2"]) <= GEMM_TOL and rel_fro(cpu(aux), k["pre"]) <= GEMM_TOL
+
+
 # ------------------------------------------------------------------------------------------ layout / decode / post-ops
 
 def test_scale_pack_decode_pad(pkg, oracle, dev):
