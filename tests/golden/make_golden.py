@@ -29,9 +29,10 @@ def bf16_round(a):
 
 
 def main():
-    x = bf16_round(normal(1, (24, 128)))
+    x = normal(1, (24, 128))
     x[3, 5] *= 50.0
     x[7] = 0.0
+    x = bf16_round(x)  # every fixture input is exactly representable in bf16
     out = {"x": x}
     b, s, g = oracle.four_six(x, oracle.tensor_amax(x)[1], rowwise=False)
     out.update(fs_tensor_bytes=b, fs_tensor_scales=s, fs_tensor_gs=g)
