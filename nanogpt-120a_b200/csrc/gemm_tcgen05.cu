@@ -174,6 +174,15 @@ __device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
@@ -500,7 +509,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
-    if (lane == 0) {
+    // The whole warp walks the loops so that tile / stage bookkeeping and the descriptors stay warp
+    // uniform (uniform registers); one elected lane issues the tensor-core instructions.  Issuing
+    // from inside a single-lane branch instead costs ~140 cycles per tcgen05.mma.
+    {
       constexpr uint32_t idesc = make_idesc<kBlockN>();
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0, runs = 0, prev_n = 0xffffffffu, sf_set = 0, sf_phase = 0;
       bool ok = true;
@@ -510,44 +522,46 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t kt_begin = split * p.k_tiles_per_split;
         const uint32_t kt_end = min(p.num_k_tiles, kt_begin + p.k_tiles_per_split);
         if (p.b_resident && n_blk != prev_n) {
-          if (!mbar_wait(bar_b_full, runs & 1u, abort_flag, kStatusMmaTimeout)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_b_full, runs & 1u, abort_flag, kStatusMmaTimeout))) {
             ok = false;
             break;
           }
           prev_n = n_blk;
           ++runs;
         }
-        if (!mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kStatusMmaTimeout)) {
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kStatusMmaTimeout))) {
           ok = false;
           break;
         }
         tcgen05_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * kBlockN;
         for (uint32_t kt = kt_begin; kt < kt_end; ++kt) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout)) {
+          // operands landed in shared memory, and the scale-factor warps filled column set `sf_set`
+          bool ready = mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout);
+          ready = ready && mbar_wait(bar_sf_full + 8 * sf_set, sf_phase, abort_flag, kStatusMmaTimeout);
+          if (!__all_sync(0xffffffffu, ready)) {
             ok = false;
             break;
           }
           tcgen05_fence_after();
           const uint32_t atoms = min(static_cast<uint32_t>(kKAtomsPerStage), p.k_atoms - kt * kKAtomsPerStage);
           const uint32_t b_slot = p.b_resident ? kt : stage;
-          // scale factors of this k-tile were put into column set `sf_set` by the scale-factor warps
-          if (!mbar_wait(bar_sf_full + 8 * sf_set, sf_phase, abort_flag, kStatusMmaTimeout)) {
-            ok = false;
-            break;
-          }
-          tcgen05_fence_after();
           const uint32_t tsfa = tmem_base + C::kTmemSfa + sf_set * C::kSfSetCols;
           const uint32_t tsfb = tmem_base + C::kTmemSfb + sf_set * C::kSfSetCols;
           const uint64_t desc_a = make_ab_desc(smem_a + stage * kAStageBytes);
           const uint64_t desc_b = make_ab_desc(smem_b + b_slot * C::kBStageBytes);
-          for (uint32_t kb = 0; kb < atoms; ++kb) {
-            // 64 nibbles = 32 bytes further along the swizzled row: +2 in the 16-byte start field
-            tcgen05_mma_nvf4(tmem_acc, desc_a + kb * 2, desc_b + kb * 2, idesc, (kt > kt_begin || kb > 0) ? 1u : 0u,
-                             tsfa + kb * 4, tsfb + kb * C::kSfbColsPerAtom);
+          if (elect_one()) {
+#pragma unroll
+            for (uint32_t kb = 0; kb < kKAtomsPerStage; ++kb) {
+              // 64 nibbles = 32 bytes further along the swizzled row: +2 in the 16-byte start field
+              if (kb < atoms)
+                tcgen05_mma_nvf4(tmem_acc, desc_a + kb * 2, desc_b + kb * 2, idesc, (kt > kt_begin || kb > 0) ? 1u : 0u,
+                                 tsfa + kb * 4, tsfb + kb * C::kSfbColsPerAtom);
+            }
+            tcgen05_commit(bar_empty + 8 * stage);       // frees the smem stage once these MMAs retire
+            tcgen05_commit(bar_sf_empty + 8 * sf_set);   // ... and the scale-factor column set
           }
-          tcgen05_commit(bar_empty + 8 * stage);       // frees the smem stage once these MMAs retire
-          tcgen05_commit(bar_sf_empty + 8 * sf_set);   // ... and the scale-factor column set
+          __syncwarp();
           if (++sf_set == C::kSfSets) {
             sf_set = 0;
             sf_phase ^= 1u;
@@ -558,15 +572,20 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         if (!ok) break;
-        tcgen05_commit(bar_tmem_full + 8 * acc);  // accumulator complete
+        // last tile of this column block (or of this CTA): the resident panel may be replaced once
+        // everything issued so far has retired
+        bool release_panel = false;
         if (p.b_resident) {
-          // last tile of this column block (or of this CTA): the panel may be replaced once
-          // everything issued so far has retired
-          uint32_t nm, nn, ns;
+          uint32_t nm, nn = n_blk, ns;
           const bool last = (w + w_step >= w_end);
           if (!last) decode(w + w_step, nm, nn, ns);
-          if (last || nn != n_blk) tcgen05_commit(bar_b_empty);
+          release_panel = last || nn != n_blk;
         }
+        if (elect_one()) {
+          tcgen05_commit(bar_tmem_full + 8 * acc);  // accumulator complete
+          if (release_panel) tcgen05_commit(bar_b_empty);
+        }
+        __syncwarp();
         if (++acc == C::kAccStages) {
           acc = 0;
           acc_phase ^= 1u;
