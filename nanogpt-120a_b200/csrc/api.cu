@@ -32,12 +32,10 @@ static const float kQuartetSO = (17.0f / 16.0f) * 0.93f;  // utils/quartet.rs:1
 
 }  // namespace nvfp4
 
-namespace nvfp4 { void debug_read(unsigned long long* out); }
 using namespace nvfp4;
 
 extern "C" {
 
-void nvfp4_debug_read(unsigned long long* out) { nvfp4::debug_read(out); }
 int nvfp4_abi_version(void) { return 1; }
 uint64_t nvfp4_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 const char* nvfp4_last_error(void) { return g_last_error; }

@@ -74,6 +74,61 @@ __device__ __forceinline__ float butterfly_sum16(const float (&e)[16]) {
   return c0 + c1;
 }
 
+// ---- packed f32x2 arithmetic (sm_100): two independent IEEE f32 operations per instruction.
+// Each lane rounds exactly like the scalar add / sub / mul, so results stay bit-exact; the
+// quantizers are instruction-issue bound and this halves their FP32 instruction count.
+typedef unsigned long long f32x2_t;
+__device__ __forceinline__ f32x2_t pack2(float lo, float hi) {
+  f32x2_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2_t add2(f32x2_t a, f32x2_t b) {
+  f32x2_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2_t sub2(f32x2_t a, f32x2_t b) {
+  f32x2_t r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2_t mul2(f32x2_t a, f32x2_t b) {
+  f32x2_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// A packed product that is going to feed a packed add / sub.  The assembler contracts
+// mul.rn.f32x2 followed by add.rn.f32x2 into one fused multiply-add even with contraction
+// switched off (measured: the scalar forms are left alone), which would skip the rounding of
+// the product.  Written as fma(a, b, -0) with the -0 pair read from constant memory, the
+// product is rounded once, exactly like a multiply (x + -0 == x for every x, signed zeros
+// included), and a fused multiply-add cannot be contracted any further.
+static __constant__ unsigned long long kNegZeroPair = 0x8000000080000000ull;
+__device__ __forceinline__ f32x2_t mul2_rounded(f32x2_t a, f32x2_t b) {
+  f32x2_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(kNegZeroPair));
+  return r;
+}
+// Packed form of butterfly_sum16: both lanes in the xor-8,4,2,1 order.
+__device__ __forceinline__ f32x2_t butterfly_sum16_x2(const f32x2_t (&e)[16]) {
+  f32x2_t a0 = add2(e[0], e[8]), a1 = add2(e[1], e[9]), a2 = add2(e[2], e[10]), a3 = add2(e[3], e[11]);
+  f32x2_t a4 = add2(e[4], e[12]), a5 = add2(e[5], e[13]), a6 = add2(e[6], e[14]), a7 = add2(e[7], e[15]);
+  f32x2_t b0 = add2(a0, a4), b1 = add2(a1, a5), b2 = add2(a2, a6), b3 = add2(a3, a7);
+  return add2(add2(b0, b2), add2(b1, b3));
+}
+// max(m, |a|, |b|) with max.f32 semantics (NaN operands dropped).
+__device__ __forceinline__ float max3_abs(float m, float a, float b) {
+  float r;
+  asm("{\n\t.reg .f32 x, y;\n\tabs.f32 x, %2;\n\tabs.f32 y, %3;\n\tmax.f32 %0, %1, x, y;\n\t}"
+      : "=f"(r)
+      : "f"(m), "f"(a), "f"(b));
+  return r;
+}
+
 // NVFP4 element: (e2m1 * e4m3) * global_scale, even index = low nibble
 // (utils/nvfp4/tensor.rs:48-57).
 __device__ __forceinline__ float nvfp4_value(const uint8_t* __restrict__ bytes, const uint8_t* __restrict__ scales,

@@ -31,7 +31,6 @@
 namespace nvfp4 {
 
 __device__ uint32_t g_device_status = 0;
-__device__ unsigned long long g_debug[32];
 
 namespace {
 
@@ -516,7 +515,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     {
       constexpr uint32_t idesc = make_idesc<kBlockN>();
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0, runs = 0, prev_n = 0xffffffffu, sf_set = 0, sf_phase = 0;
-      long long t_full = 0, t_sf = 0, t_issue = 0, t_acc = 0, t_cnt = 0, t_start = clock64(), t_tile = 0;
       bool ok = true;
       for (uint32_t w = w_begin; w < w_end && ok; w += w_step) {
         uint32_t m_blk, n_blk, split;
@@ -531,21 +529,16 @@ __global__ void __launch_bounds__(kThreads, 1)
           prev_n = n_blk;
           ++runs;
         }
-        long long a0 = clock64();
         if (!__all_sync(0xffffffffu, mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kStatusMmaTimeout))) {
           ok = false;
           break;
         }
-        t_acc += clock64() - a0;
         tcgen05_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * kBlockN;
         for (uint32_t kt = kt_begin; kt < kt_end; ++kt) {
           // operands landed in shared memory, and the scale-factor warps filled column set `sf_set`
-          long long b0 = clock64();
           bool ready = mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout);
-          long long b1 = clock64();
           ready = ready && mbar_wait(bar_sf_full + 8 * sf_set, sf_phase, abort_flag, kStatusMmaTimeout);
-          long long b2 = clock64(); t_full += b1 - b0; t_sf += b2 - b1;
           if (!__all_sync(0xffffffffu, ready)) {
             ok = false;
             break;
@@ -569,7 +562,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             tcgen05_commit(bar_sf_empty + 8 * sf_set);   // ... and the scale-factor column set
           }
           __syncwarp();
-          t_issue += clock64() - b2; t_cnt++;
           if (++sf_set == C::kSfSets) {
             sf_set = 0;
             sf_phase ^= 1u;
@@ -599,7 +591,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           acc_phase ^= 1u;
         }
       }
-      if (blockIdx.x == 0 && lane == 0) { g_debug[8] = t_full; g_debug[9] = t_sf; g_debug[10] = t_issue; g_debug[11] = t_acc; g_debug[12] = t_cnt; g_debug[13] = clock64() - t_start; }
     }
   } else if (warp >= 8) {
     // ===================== scale-factor warps =====================
@@ -1004,8 +995,6 @@ int gemm_timing_end(uint32_t* count, double* total_ms, double* total_flops, floa
   g_timing.used = 0;
   return 0;
 }
-
-void debug_read(unsigned long long* out) { cudaMemcpyFromSymbol(out, g_debug, sizeof(unsigned long long) * 32); }
 
 uint32_t* device_status_word() {
   uint32_t* ptr = nullptr;

@@ -199,21 +199,27 @@ __device__ __forceinline__ float four_six_global_scale(float amax) {
   return nz(amax == 0.0f ? 1.0f : amax * 1.0f / (256.0f * 6.0f));
 }
 
-// Sum over the group of (v - q(v*inv) * (s*gs))^2 in butterfly order (convert.rs:27-35).
-__device__ __forceinline__ float candidate_error16(const float (&v)[16], float s, float gs) {
-  const float inv = inv_scale(s, gs);
-  const float dq = s * gs;
-  float e[16];
+// Squared quantization error of the group for the 6-anchored (low lane) and the 4-anchored
+// (high lane) candidate scale at once: sum of (v - q(v*inv) * (s*gs))^2 in butterfly order
+// (utils/nvfp4/quant/kernels/convert.rs:27-35), each lane with its own inv / dequant scale.
+__device__ __forceinline__ f32x2_t candidate_errors16(const float (&v)[16], float s6, float s4, float gs) {
+  const f32x2_t inv = pack2(inv_scale(s6, gs), inv_scale(s4, gs));
+  const f32x2_t dq = pack2(s6 * gs, s4 * gs);
+  f32x2_t e[16];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const uint32_t byte = cvt_e2m1x2(v[2 * j + 1] * inv, v[2 * j] * inv);
-    const float2 q = e2m1x2_values(byte);
-    const float d0 = v[2 * j] - q.x * dq;
-    const float d1 = v[2 * j + 1] - q.y * dq;
-    e[2 * j] = d0 * d0;
-    e[2 * j + 1] = d1 * d1;
+    const f32x2_t v0 = pack2(v[2 * j], v[2 * j]), v1 = pack2(v[2 * j + 1], v[2 * j + 1]);
+    float x0a, x0b, x1a, x1b;
+    unpack2(mul2(v0, inv), x0a, x0b);
+    unpack2(mul2(v1, inv), x1a, x1b);
+    const float2 qa = e2m1x2_values(cvt_e2m1x2(x1a, x0a));  // candidate six: elements 2j, 2j+1
+    const float2 qb = e2m1x2_values(cvt_e2m1x2(x1b, x0b));  // candidate four
+    const f32x2_t d0 = sub2(v0, mul2_rounded(pack2(qa.x, qb.x), dq));
+    const f32x2_t d1 = sub2(v1, mul2_rounded(pack2(qa.y, qb.y), dq));
+    e[2 * j] = mul2_rounded(d0, d0);
+    e[2 * j + 1] = mul2_rounded(d1, d1);
   }
-  return butterfly_sum16(e);
+  return butterfly_sum16_x2(e);
 }
 
 // v: one 16-group.  Returns the scale byte and writes the 8 nibble bytes into `packed`.
@@ -221,22 +227,24 @@ __device__ __forceinline__ float candidate_error16(const float (&v)[16], float s
 __device__ __forceinline__ uint32_t four_six_group(const float (&v)[16], float gs, uint2& packed) {
   float ga = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) ga = max_f32(ga, fabsf(v[i]));
+  for (int i = 0; i < 16; i += 2) ga = max3_abs(ga, v[i], v[i + 1]);
   const float gsn = nz(gs);
   const uint32_t b6 = cvt_e4m3(ga * 1.0f / (6.0f * gsn + kDenomEps));
   const uint32_t b4 = cvt_e4m3(ga * 1.0f / (4.0f * gsn + kDenomEps));
   const float s6 = e4m3_value(b6);
   const float s4 = e4m3_value(b4);
-  const float err6 = candidate_error16(v, s6, gsn);
-  const float err4 = candidate_error16(v, s4, gsn);
+  float err6, err4;
+  unpack2(candidate_errors16(v, s6, s4, gsn), err6, err4);
   const bool six = err6 <= err4;
   const uint32_t b = six ? b6 : b4;
   const float inv = inv_scale(six ? s6 : s4, gs);
+  const f32x2_t inv2 = pack2(inv, inv);
   uint32_t w[2] = {0u, 0u};
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const uint32_t byte = cvt_e2m1x2(v[2 * j + 1] * inv, v[2 * j] * inv);
-    w[j >> 2] |= byte << (8 * (j & 3));
+    float x0, x1;
+    unpack2(mul2(pack2(v[2 * j], v[2 * j + 1]), inv2), x0, x1);
+    w[j >> 2] |= cvt_e2m1x2(x1, x0) << (8 * (j & 3));
   }
   packed = make_uint2(w[0], w[1]);
   return b;
@@ -374,51 +382,70 @@ __device__ __forceinline__ uint32_t stochastic_e4m3_scale(float value, uint32_t 
 
 // In-register 32-point Walsh-Hadamard butterfly in the reference's order
 // (pack/hadamard.rs:6-19): stride 1,2,4,8,16; low lane a+b, high lane a-b; then * 1/sqrt(32).
-__device__ __forceinline__ void hadamard32(float (&u)[32]) {
+// The chunk is held as 16 packed pairs P[i] = (u[i], u[i+16]): strides 1..8 act between
+// registers on both halves at once (packed add / sub), stride 16 inside each register.
+__device__ __forceinline__ void hadamard32_x2(f32x2_t (&P)[16]) {
 #pragma unroll
-  for (int stride = 1; stride < 32; stride <<= 1) {
+  for (int stride = 1; stride < 16; stride <<= 1) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if ((j & stride) == 0) {
-        const float a = u[j], b = u[j | stride];
-        u[j] = a + b;
-        u[j | stride] = a - b;
+    for (int i = 0; i < 16; ++i) {
+      if ((i & stride) == 0) {
+        const f32x2_t a = P[i], b = P[i | stride];
+        P[i] = add2(a, b);
+        P[i | stride] = sub2(a, b);
       }
     }
   }
+  const f32x2_t c = pack2(0.17677669f, 0.17677669f);
 #pragma unroll
-  for (int j = 0; j < 32; ++j) u[j] = u[j] * 0.17677669f;
+  for (int i = 0; i < 16; ++i) {
+    float lo, hi;
+    unpack2(P[i], lo, hi);
+    P[i] = mul2(pack2(lo + hi, lo - hi), c);  // after this: low lane = group 0, high lane = group 1
+  }
 }
 
-// One 16-group of the rotated chunk (pack/payload.rs:15-69): returns the scale byte.
-__device__ __forceinline__ uint32_t ms_eden_group(const float* h, float safe_gs, float so_inv6_unused, float so,
-                                                  float inv6, uint32_t scale_seed, uint32_t group, uint2& packed) {
-  (void)so_inv6_unused;
-  float ga = 0.0f;
+// Both 16-groups of a rotated chunk at once (low lane = group 0, high lane = group 1):
+// block scale, RTN nibbles, EDEN correction and the stochastic scale byte of each
+// (pack/payload.rs:15-69).  Returns the two scale bytes (group 0 in bits 0..7).
+__device__ __forceinline__ uint32_t ms_eden_groups_x2(const f32x2_t (&H)[16], float safe_gs, float so, float inv6,
+                                                      uint32_t scale_seed, uint32_t group0, uint4& packed) {
+  float ga0 = 0.0f, ga1 = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) ga = max_f32(ga, fabsf(h[i]));
-  const uint32_t b0 = cvt_e4m3(ga * so * inv6);
-  const float s0 = nz(e4m3_value(b0));
-  const float inv = inv_scale(s0, safe_gs);
-  float num_t[16], den_t[16];
-  uint32_t w[2] = {0u, 0u};
+  for (int i = 0; i < 16; i += 2) {
+    float a0, a1, b0, b1;
+    unpack2(H[i], a0, a1);
+    unpack2(H[i + 1], b0, b1);
+    ga0 = max3_abs(ga0, a0, b0);
+    ga1 = max3_abs(ga1, a1, b1);
+  }
+  const float s0a = nz(e4m3_value(cvt_e4m3(ga0 * so * inv6)));
+  const float s0b = nz(e4m3_value(cvt_e4m3(ga1 * so * inv6)));
+  const f32x2_t inv = pack2(inv_scale(s0a, safe_gs), inv_scale(s0b, safe_gs));
+  f32x2_t num_t[16], den_t[16];
+  uint32_t wa[2] = {0u, 0u}, wb[2] = {0u, 0u};
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const float x0 = h[2 * j] * inv, x1 = h[2 * j + 1] * inv;
-    const uint32_t byte = cvt_e2m1x2(x1, x0);
-    const float2 q = e2m1x2_values(byte);
-    num_t[2 * j] = x0 * x0;
-    num_t[2 * j + 1] = x1 * x1;
-    den_t[2 * j] = x0 * q.x;
-    den_t[2 * j + 1] = x1 * q.y;
-    w[j >> 2] |= byte << (8 * (j & 3));
+    const f32x2_t x0 = mul2(H[2 * j], inv), x1 = mul2(H[2 * j + 1], inv);
+    float x0a, x0b, x1a, x1b;
+    unpack2(x0, x0a, x0b);
+    unpack2(x1, x1a, x1b);
+    const uint32_t byte_a = cvt_e2m1x2(x1a, x0a), byte_b = cvt_e2m1x2(x1b, x0b);
+    const float2 qa = e2m1x2_values(byte_a), qb = e2m1x2_values(byte_b);
+    num_t[2 * j] = mul2_rounded(x0, x0);
+    num_t[2 * j + 1] = mul2_rounded(x1, x1);
+    den_t[2 * j] = mul2_rounded(x0, pack2(qa.x, qb.x));
+    den_t[2 * j + 1] = mul2_rounded(x1, pack2(qa.y, qb.y));
+    wa[j >> 2] |= byte_a << (8 * (j & 3));
+    wb[j >> 2] |= byte_b << (8 * (j & 3));
   }
-  const float num = butterfly_sum16(num_t);
-  const float den = butterfly_sum16(den_t);
-  const float corr = den == 0.0f ? 1.0f : num / den;
-  const float s = nz(s0 * corr);
-  packed = make_uint2(w[0], w[1]);
-  return stochastic_e4m3_scale(s, scale_seed, group);
+  float num_a, num_b, den_a, den_b;
+  unpack2(butterfly_sum16_x2(num_t), num_a, num_b);
+  unpack2(butterfly_sum16_x2(den_t), den_a, den_b);
+  const float sa = nz(s0a * (den_a == 0.0f ? 1.0f : num_a / den_a));
+  const float sb = nz(s0b * (den_b == 0.0f ? 1.0f : num_b / den_b));
+  packed = make_uint4(wa[0], wa[1], wb[0], wb[1]);
+  return stochastic_e4m3_scale(sa, scale_seed, group0) | (stochastic_e4m3_scale(sb, scale_seed, group0 + 1) << 8);
 }
 
 // Where one orientation of an MS-EDEN result goes.
@@ -451,28 +478,39 @@ struct MsEdenParams {
   MsEdenOut out;
 };
 
-// Finishes one chunk whose signed inputs are in u[32]: rotation, two groups, stores.
-__device__ __forceinline__ void ms_eden_emit_chunk(float (&u)[32], const MsEdenOut& o, float gs, float so, uint32_t row,
-                                                   uint32_t chunk_in_row) {
+// Finishes one chunk whose signed inputs are in P (P[i] = (u[i], u[i+16])): rotation, two
+// groups, stores.
+__device__ __forceinline__ void ms_eden_emit_chunk(f32x2_t (&P)[16], const MsEdenOut& o, float gs, float so,
+                                                   uint32_t row, uint32_t chunk_in_row) {
   const uint64_t chunk = static_cast<uint64_t>(row) * (o.dst_row_len >> 5) + chunk_in_row;
-  hadamard32(u);
+  hadamard32_x2(P);
   if (o.chunk_amax) {
     float m = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) m = max_f32(m, fabsf(u[j]));
+    for (int i = 0; i < 16; ++i) {
+      float lo, hi;
+      unpack2(P[i], lo, hi);
+      m = max3_abs(m, lo, hi);
+    }
     o.chunk_amax[chunk] = m;
   }
   const float safe_gs = nz(gs);
   const float inv6 = inv_scale(6.0f, safe_gs);
   const uint32_t group0 = static_cast<uint32_t>(chunk) * 2u + o.group_offset;
-  uint2 lo, hi;
-  const uint32_t sb0 = ms_eden_group(u, safe_gs, 0.0f, so, inv6, o.scale_seed, group0, lo);
-  const uint32_t sb1 = ms_eden_group(u + 16, safe_gs, 0.0f, so, inv6, o.scale_seed, group0 + 1, hi);
-  *reinterpret_cast<uint4*>(o.fp4 + chunk * 16) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+  uint4 nibbles;
+  const uint32_t sb = ms_eden_groups_x2(P, safe_gs, so, inv6, o.scale_seed, group0, nibbles);
+  *reinterpret_cast<uint4*>(o.fp4 + chunk * 16) = nibbles;
   // two consecutive k-groups of one k-atom: adjacent bytes in either layout, 2-byte aligned
   const size_t off = o.packed ? packed_scale_offset(row, chunk_in_row * 2, o.dst_row_len >> 6) : chunk * 2;
-  *reinterpret_cast<uint16_t*>(o.scales + off) = static_cast<uint16_t>(sb0 | (sb1 << 8));
+  *reinterpret_cast<uint16_t*>(o.scales + off) = static_cast<uint16_t>(sb);
   if (chunk_in_row == 0) o.global_scales[row] = gs;
+}
+
+// Signed input pair (u[i], u[i+16]) from two values and the chunk's 32 sign bits.
+__device__ __forceinline__ f32x2_t signed_pair(float lo, float hi, uint32_t neg_mask, int i) {
+  const uint32_t a = __float_as_uint(lo) ^ ((neg_mask << (31 - i)) & 0x80000000u);
+  const uint32_t b = __float_as_uint(hi) ^ ((neg_mask << (15 - i)) & 0x80000000u);
+  return pack2(__uint_as_float(a), __uint_as_float(b));
 }
 
 // Generic one-thread-per-chunk kernel (row sources, and the fallback for odd transposed
@@ -527,10 +565,14 @@ __global__ void __launch_bounds__(128) ms_eden_kernel(const MsEdenParams p) {
       }
     }
   }
+  uint32_t neg_mask = 0;  // x * (-1) == -x exactly: the random signs are applied as sign-bit flips
 #pragma unroll
   for (int j = 0; j < 32; ++j)
-    if (random_sign_negative(p.sign_seed, col0 + j + p.out.sign_offset)) u[j] = -u[j];  // x * (-1) == -x exactly
-  ms_eden_emit_chunk(u, p.out, gs, p.scale_override, row, chunk_in_row);
+    neg_mask |= (random_sign_negative(p.sign_seed, col0 + j + p.out.sign_offset) ? 1u : 0u) << j;
+  f32x2_t P[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) P[i] = signed_pair(u[i], u[i + 16], neg_mask, i);
+  ms_eden_emit_chunk(P, p.out, gs, p.scale_override, row, chunk_in_row);
 }
 
 // Tiled kernel for the transposed operands.  A CTA stages a [128 source rows x 64 source
@@ -562,14 +604,18 @@ constexpr int kTileRows = 128, kTileCols = 64, kTileLd = kTileCols + 1;
 template <int kSrc, typename T, bool kPair>
 __global__ void __launch_bounds__(256) ms_eden_tile_kernel(const MsEdenTileParams p) {
   __shared__ float tile[kTileRows * kTileLd];
-  __shared__ uint8_t neg_r[kTileRows];
-  __shared__ uint8_t neg_c[kTileCols];
+  __shared__ uint32_t neg_r[kTileRows / 32];  // sign bits of the tile's rows (K of the transposed operand)
+  __shared__ uint32_t neg_c[kTileCols / 32];  // sign bits of the tile's columns (K of the row operand)
   const uint32_t tid = threadIdx.x;
   const uint32_t c0 = blockIdx.x * kTileCols, r0 = blockIdx.y * kTileRows;
-  if (tid < kTileRows)
-    neg_r[tid] = random_sign_negative(p.sign_seed, r0 + tid + p.t.sign_offset) ? 1 : 0;
-  else if (kPair && tid < kTileRows + kTileCols)
-    neg_c[tid - kTileRows] = random_sign_negative(p.sign_seed, c0 + (tid - kTileRows) + p.r.sign_offset) ? 1 : 0;
+  if (tid < kTileRows) {
+    const uint32_t bits = __ballot_sync(0xffffffffu, random_sign_negative(p.sign_seed, r0 + tid + p.t.sign_offset));
+    if ((tid & 31) == 0) neg_r[tid >> 5] = bits;
+  } else if (kPair && tid < kTileRows + kTileCols) {
+    const uint32_t bits =
+        __ballot_sync(0xffffffffu, random_sign_negative(p.sign_seed, c0 + (tid - kTileRows) + p.r.sign_offset));
+    if ((tid & 31) == 0) neg_c[(tid - kTileRows) >> 5] = bits;
+  }
 
   if (kSrc == 0) {
     const T* x = static_cast<const T*>(p.x);
@@ -658,26 +704,24 @@ __global__ void __launch_bounds__(256) ms_eden_tile_kernel(const MsEdenTileParam
     const uint32_t c = tid & 63, chunk = tid >> 6;
     const uint32_t out_row = c0 + c, k0 = r0 + chunk * 32;
     if (out_row < p.t.rows && k0 < p.t.dst_row_len) {
-      float u[32];
+      const uint32_t mask = neg_r[chunk];
+      f32x2_t P[16];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float v = tile[(chunk * 32 + j) * kTileLd + c];
-        u[j] = neg_r[chunk * 32 + j] ? -v : v;
-      }
-      ms_eden_emit_chunk(u, p.t, gs, p.scale_override, out_row, k0 >> 5);
+      for (int i = 0; i < 16; ++i)
+        P[i] = signed_pair(tile[(chunk * 32 + i) * kTileLd + c], tile[(chunk * 32 + i + 16) * kTileLd + c], mask, i);
+      ms_eden_emit_chunk(P, p.t, gs, p.scale_override, out_row, k0 >> 5);
     }
   }
   if (kPair) {
     const uint32_t row = tid >> 1, chunk = tid & 1;
     const uint32_t out_row = r0 + row, k0 = c0 + chunk * 32;
     if (out_row < p.r.rows && k0 < p.r.dst_row_len) {
-      float u[32];
+      const uint32_t mask = neg_c[chunk];
+      f32x2_t P[16];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float v = tile[row * kTileLd + chunk * 32 + j];
-        u[j] = neg_c[chunk * 32 + j] ? -v : v;
-      }
-      ms_eden_emit_chunk(u, p.r, gs, p.scale_override, out_row, k0 >> 5);
+      for (int i = 0; i < 16; ++i)
+        P[i] = signed_pair(tile[row * kTileLd + chunk * 32 + i], tile[row * kTileLd + chunk * 32 + i + 16], mask, i);
+      ms_eden_emit_chunk(P, p.r, gs, p.scale_override, out_row, k0 >> 5);
     }
   }
 }
