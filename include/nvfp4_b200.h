@@ -94,6 +94,15 @@ int nvfp4_row_amax_bf16(void* stream, const void* x, float* out, uint32_t row_co
  * chunk_amax[ceil(n/1024)] and out[1] are both written. */
 int nvfp4_tensor_amax_f32(void* stream, const float* x, float* chunk_amax, float* out, uint32_t element_count);
 int nvfp4_tensor_amax_bf16(void* stream, const void* x, float* chunk_amax, float* out, uint32_t element_count);
+/* No counterpart in the reference.  Same out[0] as nvfp4_tensor_amax_f32, for callers that cannot
+ * supply the chunk_amax scratch because they cannot allocate at the point of the call (device
+ * handed to an arena sized earlier, a loop where an allocation would synchronise the device, a
+ * full GPU).  Allocates nothing: the per-chunk scratch is a fixed 256 KiB array inside the
+ * library, one per device.  Limits: element_count <= 67108864 (2^26), larger returns 1 with a
+ * message; calls that overlap in time on one device race on the array (order them on a stream);
+ * the first call on a device does one-time set-up (address look-up), so make it during
+ * initialisation and before any stream capture. */
+int nvfp4_tensor_amax_f32_static_scratch(void* stream, const float* x, float* out, uint64_t element_count);
 /* utils/nvfp4/quant/amax.rs:25-39  Nvfp4QuantModule::tensor_amax_from_chunks_f32 */
 int nvfp4_tensor_amax_from_chunks_f32(void* stream, const float* chunk_amax, float* out, uint32_t chunk_count);
 

@@ -89,6 +89,7 @@ _SIGNATURES = {
     "nvfp4_tensor_amax_f32": [_P, _P, _P, _P, _U],
     "nvfp4_tensor_amax_bf16": [_P, _P, _P, _P, _U],
     "nvfp4_tensor_amax_from_chunks_f32": [_P, _P, _P, _U],
+    "nvfp4_tensor_amax_f32_static_scratch": [_P, _P, _P, ctypes.c_uint64],
     "nvfp4_fp32_to_nvfp4_four_six": [_P, _P, _P, _P, _P, _P, _U],
     "nvfp4_fp32_to_nvfp4_four_six_rowwise": [_P, _P, _P, _P, _P, _P, _U, _U],
     "nvfp4_fp32_to_nvfp4_four_six_padded": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _U],
@@ -287,6 +288,15 @@ class Nvfp4QuantModule:
         return chunk_amax, out
 
     tensor_amax_f32 = tensor_amax
+
+    def tensor_amax_f32_static_scratch(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """Tensor amax of an f32 tensor into the caller's `out[0]`, with the chunk scratch held
+        inside the library (no allocation anywhere; at most 2**26 values; calls on one device
+        must not overlap in time; make the first call before any stream capture)."""
+        _require_cuda()
+        assert x.dtype == torch.float32 and out.dtype == torch.float32 and out.numel() >= 1
+        _call("nvfp4_tensor_amax_f32_static_scratch", _stream(), _ptr(x), _ptr(out), x.numel())
+        return out
 
     def tensor_amax_from_chunks_f32(self, chunk_amax: torch.Tensor, chunk_count: int,
                                     out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -25,6 +25,7 @@ UNITS = [
     ("quant_kernels.cu", ["-fmad=false"]),
     ("gemm_tcgen05.cu", []),
     ("api.cu", []),
+    ("tensor_amax_static.cu", []),
 ]
 
 
