@@ -40,6 +40,34 @@ __device__ __forceinline__ float2 e2m1x2_values(uint32_t byte) {
   return __half22float2(h);
 }
 
+// Eight values to four E2M1x2 bytes in one word (byte k holds elements 2k and 2k+1, the even
+// element in the low nibble).  The bytes are packed in PTX so that no separate mask or shift
+// instruction is needed after the conversions.
+__device__ __forceinline__ uint32_t cvt_e2m1x8(float x0, float x1, float x2, float x3, float x4, float x5, float x6,
+                                               float x7) {
+  uint32_t r;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+      : "=r"(r)
+      : "f"(x0), "f"(x1), "f"(x2), "f"(x3), "f"(x4), "f"(x5), "f"(x6), "f"(x7));
+  return r;
+}
+// Decoding goes byte by byte through an explicit byte extract: unpacking the word with
+// mov.b32 {b0,b1,b2,b3} right after the pack above was measured to return zeros for some bytes
+// (the assembler forwards the 8-bit temporaries without their masking).
+__device__ __forceinline__ void e2m1x8_values(uint32_t word, float (&q)[8]) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = e2m1x2_values(__byte_perm(word, 0u, 0x4440u | k));
+    q[2 * k] = f.x;
+    q[2 * k + 1] = f.y;
+  }
+}
+
 __device__ __forceinline__ float e2m1_value(uint32_t nibble) { return e2m1x2_values(nibble & 0xfu).x; }
 
 __device__ __forceinline__ float e4m3_value(uint32_t bits) {

@@ -202,28 +202,36 @@ __device__ __forceinline__ float four_six_global_scale(float amax) {
 // Squared quantization error of the group for the 6-anchored (low lane) and the 4-anchored
 // (high lane) candidate scale at once: sum of (v - q(v*inv) * (s*gs))^2 in butterfly order
 // (utils/nvfp4/quant/kernels/convert.rs:27-35), each lane with its own inv / dequant scale.
-__device__ __forceinline__ f32x2_t candidate_errors16(const float (&v)[16], float s6, float s4, float gs) {
+// The nibble bytes of both candidates come back too: the winner's bytes are the output.
+__device__ __forceinline__ f32x2_t candidate_errors16(const float (&v)[16], float s6, float s4, float gs, uint2& nib6,
+                                                      uint2& nib4) {
   const f32x2_t inv = pack2(inv_scale(s6, gs), inv_scale(s4, gs));
   const f32x2_t dq = pack2(s6 * gs, s4 * gs);
-  f32x2_t e[16];
+  float x6[16], x4[16];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const f32x2_t v0 = pack2(v[2 * j], v[2 * j]), v1 = pack2(v[2 * j + 1], v[2 * j + 1]);
-    float x0a, x0b, x1a, x1b;
-    unpack2(mul2(v0, inv), x0a, x0b);
-    unpack2(mul2(v1, inv), x1a, x1b);
-    const float2 qa = e2m1x2_values(cvt_e2m1x2(x1a, x0a));  // candidate six: elements 2j, 2j+1
-    const float2 qb = e2m1x2_values(cvt_e2m1x2(x1b, x0b));  // candidate four
-    const f32x2_t d0 = sub2(v0, mul2_rounded(pack2(qa.x, qb.x), dq));
-    const f32x2_t d1 = sub2(v1, mul2_rounded(pack2(qa.y, qb.y), dq));
-    e[2 * j] = mul2_rounded(d0, d0);
-    e[2 * j + 1] = mul2_rounded(d1, d1);
+  for (int i = 0; i < 16; ++i) unpack2(mul2(pack2(v[i], v[i]), inv), x6[i], x4[i]);
+  nib6 = make_uint2(cvt_e2m1x8(x6[0], x6[1], x6[2], x6[3], x6[4], x6[5], x6[6], x6[7]),
+                    cvt_e2m1x8(x6[8], x6[9], x6[10], x6[11], x6[12], x6[13], x6[14], x6[15]));
+  nib4 = make_uint2(cvt_e2m1x8(x4[0], x4[1], x4[2], x4[3], x4[4], x4[5], x4[6], x4[7]),
+                    cvt_e2m1x8(x4[8], x4[9], x4[10], x4[11], x4[12], x4[13], x4[14], x4[15]));
+  float q6a[8], q6b[8], q4a[8], q4b[8];
+  e2m1x8_values(nib6.x, q6a);
+  e2m1x8_values(nib6.y, q6b);
+  e2m1x8_values(nib4.x, q4a);
+  e2m1x8_values(nib4.y, q4b);
+  f32x2_t a8[8];  // first butterfly level: a8[i] = e[i] + e[i + 8]
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const f32x2_t d0 = sub2(pack2(v[i], v[i]), mul2_rounded(pack2(q6a[i], q4a[i]), dq));
+    const f32x2_t d8 = sub2(pack2(v[i + 8], v[i + 8]), mul2_rounded(pack2(q6b[i], q4b[i]), dq));
+    a8[i] = add2(mul2_rounded(d0, d0), mul2_rounded(d8, d8));
   }
-  return butterfly_sum16_x2(e);
+  return add2(add2(add2(a8[0], a8[4]), add2(a8[2], a8[6])), add2(add2(a8[1], a8[5]), add2(a8[3], a8[7])));
 }
 
 // v: one 16-group.  Returns the scale byte and writes the 8 nibble bytes into `packed`.
-// helpers.rs:42-76 and four_six.rs:309-344 of utils/nvfp4/quant/kernels.
+// helpers.rs:42-76 and four_six.rs:309-344 of utils/nvfp4/quant/kernels.  The output nibbles
+// are cvt(v * inv) with the chosen candidate's inv, i.e. exactly that candidate's trial bytes.
 __device__ __forceinline__ uint32_t four_six_group(const float (&v)[16], float gs, uint2& packed) {
   float ga = 0.0f;
 #pragma unroll
@@ -234,20 +242,11 @@ __device__ __forceinline__ uint32_t four_six_group(const float (&v)[16], float g
   const float s6 = e4m3_value(b6);
   const float s4 = e4m3_value(b4);
   float err6, err4;
-  unpack2(candidate_errors16(v, s6, s4, gsn), err6, err4);
+  uint2 nib6, nib4;
+  unpack2(candidate_errors16(v, s6, s4, gsn, nib6, nib4), err6, err4);
   const bool six = err6 <= err4;
-  const uint32_t b = six ? b6 : b4;
-  const float inv = inv_scale(six ? s6 : s4, gs);
-  const f32x2_t inv2 = pack2(inv, inv);
-  uint32_t w[2] = {0u, 0u};
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    float x0, x1;
-    unpack2(mul2(pack2(v[2 * j], v[2 * j + 1]), inv2), x0, x1);
-    w[j >> 2] |= cvt_e2m1x2(x1, x0) << (8 * (j & 3));
-  }
-  packed = make_uint2(w[0], w[1]);
-  return b;
+  packed = six ? nib6 : nib4;
+  return six ? b6 : b4;
 }
 
 // One thread per 16-group of a [rows][cols] tensor.
@@ -366,17 +365,25 @@ __global__ void __launch_bounds__(256) packed_scale_pad_kernel(uint8_t* __restri
 __device__ __forceinline__ uint32_t stochastic_e4m3_scale(float value, uint32_t seed, uint32_t group) {
   const uint32_t cb = cvt_e4m3(value);
   const float cur = e4m3_value(cb);
-  const uint32_t pb = cb == 0 ? 0u : cb - 1u;
-  const uint32_t nb = cb == 255u ? 255u : cb + 1u;
-  const float prev = e4m3_value(pb);
-  const float next = e4m3_value(nb);
   const bool above = cur > value;
-  const float up = above ? cur : next;
-  const float down = above ? prev : cur;
-  const uint32_t up_bits = above ? cb : nb;
-  const uint32_t down_bits = above ? pb : cb;
+  // Only the neighbour on the far side of `value` is needed: the code below when the nearest
+  // code lies above the value, the code above otherwise (clamped like the reference's prev / next).
+  const uint32_t ob = above ? (cb == 0 ? 0u : cb - 1u) : (cb == 255u ? 255u : cb + 1u);
+  const float other = e4m3_value(ob);
+  const float up = above ? cur : other;
+  const float down = above ? other : cur;
+  const uint32_t up_bits = above ? cb : ob;
+  const uint32_t down_bits = above ? ob : cb;
   const float denom = up - down;
-  const float p = denom == 0.0f ? 0.0f : (value - down) / denom;
+  const uint32_t dbits = __float_as_uint(denom);
+  float p;
+  if ((dbits & 0x807fffffu) == 0u && dbits - 0x00800000u <= 0x7e000000u - 0x00800000u) {
+    // Neighbouring E4M3 values differ by a power of two, 2^e with a normal reciprocal: dividing
+    // by it and multiplying by 2^-e round the same real number, so the product is the quotient.
+    p = (value - down) * __uint_as_float(0x7f000000u - dbits);
+  } else {
+    p = denom == 0.0f ? 0.0f : (value - down) / denom;
+  }
   return random_unit_f32(seed, group) < p ? up_bits : down_bits;
 }
 
@@ -405,11 +412,13 @@ __device__ __forceinline__ void hadamard32_x2(f32x2_t (&P)[16]) {
   }
 }
 
-// Both 16-groups of a rotated chunk at once (low lane = group 0, high lane = group 1):
-// block scale, RTN nibbles, EDEN correction and the stochastic scale byte of each
-// (pack/payload.rs:15-69).  Returns the two scale bytes (group 0 in bits 0..7).
-__device__ __forceinline__ uint32_t ms_eden_groups_x2(const f32x2_t (&H)[16], float safe_gs, float so, float inv6,
-                                                      uint32_t scale_seed, uint32_t group0, uint4& packed) {
+// Two rotated 16-groups at once, one per packed lane (they may belong to one chunk or to two
+// different chunks): block scale, RTN nibbles, EDEN correction and the stochastic scale byte
+// of each (pack/payload.rs:15-69).  H points at the 16 packed values.  Returns the two scale
+// bytes (low lane in bits 0..7) and the 8 nibble bytes of each lane.
+__device__ __forceinline__ uint32_t ms_eden_group_lanes(const f32x2_t* H, float safe_gs, float so, float inv6,
+                                                        uint32_t scale_seed, uint32_t group_lo, uint32_t group_hi,
+                                                        uint2& nib_lo, uint2& nib_hi) {
   float ga0 = 0.0f, ga1 = 0.0f;
 #pragma unroll
   for (int i = 0; i < 16; i += 2) {
@@ -422,30 +431,46 @@ __device__ __forceinline__ uint32_t ms_eden_groups_x2(const f32x2_t (&H)[16], fl
   const float s0a = nz(e4m3_value(cvt_e4m3(ga0 * so * inv6)));
   const float s0b = nz(e4m3_value(cvt_e4m3(ga1 * so * inv6)));
   const f32x2_t inv = pack2(inv_scale(s0a, safe_gs), inv_scale(s0b, safe_gs));
-  f32x2_t num_t[16], den_t[16];
-  uint32_t wa[2] = {0u, 0u}, wb[2] = {0u, 0u};
+  f32x2_t x[16];
+  float xa[16], xb[16];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const f32x2_t x0 = mul2(H[2 * j], inv), x1 = mul2(H[2 * j + 1], inv);
-    float x0a, x0b, x1a, x1b;
-    unpack2(x0, x0a, x0b);
-    unpack2(x1, x1a, x1b);
-    const uint32_t byte_a = cvt_e2m1x2(x1a, x0a), byte_b = cvt_e2m1x2(x1b, x0b);
-    const float2 qa = e2m1x2_values(byte_a), qb = e2m1x2_values(byte_b);
-    num_t[2 * j] = mul2_rounded(x0, x0);
-    num_t[2 * j + 1] = mul2_rounded(x1, x1);
-    den_t[2 * j] = mul2_rounded(x0, pack2(qa.x, qb.x));
-    den_t[2 * j + 1] = mul2_rounded(x1, pack2(qa.y, qb.y));
-    wa[j >> 2] |= byte_a << (8 * (j & 3));
-    wb[j >> 2] |= byte_b << (8 * (j & 3));
+  for (int i = 0; i < 16; ++i) {
+    x[i] = mul2(H[i], inv);
+    unpack2(x[i], xa[i], xb[i]);
+  }
+  nib_lo = make_uint2(cvt_e2m1x8(xa[0], xa[1], xa[2], xa[3], xa[4], xa[5], xa[6], xa[7]),
+                      cvt_e2m1x8(xa[8], xa[9], xa[10], xa[11], xa[12], xa[13], xa[14], xa[15]));
+  nib_hi = make_uint2(cvt_e2m1x8(xb[0], xb[1], xb[2], xb[3], xb[4], xb[5], xb[6], xb[7]),
+                      cvt_e2m1x8(xb[8], xb[9], xb[10], xb[11], xb[12], xb[13], xb[14], xb[15]));
+  float qa0[8], qa1[8], qb0[8], qb1[8];  // decoded nibbles: lane a / b, elements 0..7 / 8..15
+  e2m1x8_values(nib_lo.x, qa0);
+  e2m1x8_values(nib_lo.y, qa1);
+  e2m1x8_values(nib_hi.x, qb0);
+  e2m1x8_values(nib_hi.y, qb1);
+  // first level of the xor-8 butterfly sums formed on the spot: entry i = e[i] + e[i + 8]
+  f32x2_t num8[8], den8[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    num8[i] = add2(mul2_rounded(x[i], x[i]), mul2_rounded(x[i + 8], x[i + 8]));
+    den8[i] = add2(mul2_rounded(x[i], pack2(qa0[i], qb0[i])), mul2_rounded(x[i + 8], pack2(qa1[i], qb1[i])));
   }
   float num_a, num_b, den_a, den_b;
-  unpack2(butterfly_sum16_x2(num_t), num_a, num_b);
-  unpack2(butterfly_sum16_x2(den_t), den_a, den_b);
+  unpack2(add2(add2(add2(num8[0], num8[4]), add2(num8[2], num8[6])), add2(add2(num8[1], num8[5]), add2(num8[3], num8[7]))),
+          num_a, num_b);
+  unpack2(add2(add2(add2(den8[0], den8[4]), add2(den8[2], den8[6])), add2(add2(den8[1], den8[5]), add2(den8[3], den8[7]))),
+          den_a, den_b);
   const float sa = nz(s0a * (den_a == 0.0f ? 1.0f : num_a / den_a));
   const float sb = nz(s0b * (den_b == 0.0f ? 1.0f : num_b / den_b));
-  packed = make_uint4(wa[0], wa[1], wb[0], wb[1]);
-  return stochastic_e4m3_scale(sa, scale_seed, group0) | (stochastic_e4m3_scale(sb, scale_seed, group0 + 1) << 8);
+  return stochastic_e4m3_scale(sa, scale_seed, group_lo) | (stochastic_e4m3_scale(sb, scale_seed, group_hi) << 8);
+}
+
+// Both 16-groups of one rotated chunk (low lane = group 0, high lane = group 1).
+__device__ __forceinline__ uint32_t ms_eden_groups_x2(const f32x2_t (&H)[16], float safe_gs, float so, float inv6,
+                                                      uint32_t scale_seed, uint32_t group0, uint4& packed) {
+  uint2 lo, hi;
+  const uint32_t sb = ms_eden_group_lanes(&H[0], safe_gs, so, inv6, scale_seed, group0, group0 + 1, lo, hi);
+  packed = make_uint4(lo.x, lo.y, hi.x, hi.y);
+  return sb;
 }
 
 // Where one orientation of an MS-EDEN result goes.
@@ -504,6 +529,61 @@ __device__ __forceinline__ void ms_eden_emit_chunk(f32x2_t (&P)[16], const MsEde
   const size_t off = o.packed ? packed_scale_offset(row, chunk_in_row * 2, o.dst_row_len >> 6) : chunk * 2;
   *reinterpret_cast<uint16_t*>(o.scales + off) = static_cast<uint16_t>(sb);
   if (chunk_in_row == 0) o.global_scales[row] = gs;
+}
+
+// Two chunks at once, one per packed lane (low lane = chunk of row_lo, high lane = chunk of
+// row_hi, both at chunk_in_row): P[k] holds the signed inputs of K position k of both, so all
+// five butterfly strides act between registers.
+__device__ __forceinline__ void ms_eden_emit_chunk_lanes(f32x2_t (&P)[32], const MsEdenOut& o, float gs, float so,
+                                                         uint32_t row_lo, uint32_t row_hi, uint32_t chunk_in_row) {
+  const uint32_t chunks_per_row = o.dst_row_len >> 5;
+  const uint64_t chunk_lo = static_cast<uint64_t>(row_lo) * chunks_per_row + chunk_in_row;
+  const uint64_t chunk_hi = static_cast<uint64_t>(row_hi) * chunks_per_row + chunk_in_row;
+#pragma unroll
+  for (int stride = 1; stride < 32; stride <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if ((i & stride) == 0) {
+        const f32x2_t a = P[i], b = P[i | stride];
+        P[i] = add2(a, b);
+        P[i | stride] = sub2(a, b);
+      }
+    }
+  }
+  const f32x2_t c = pack2(0.17677669f, 0.17677669f);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) P[i] = mul2(P[i], c);
+  if (o.chunk_amax) {
+    float m_lo = 0.0f, m_hi = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float a0, a1, b0, b1;
+      unpack2(P[i], a0, a1);
+      unpack2(P[i + 1], b0, b1);
+      m_lo = max3_abs(m_lo, a0, b0);
+      m_hi = max3_abs(m_hi, a1, b1);
+    }
+    o.chunk_amax[chunk_lo] = m_lo;
+    o.chunk_amax[chunk_hi] = m_hi;
+  }
+  const float safe_gs = nz(gs);
+  const float inv6 = inv_scale(6.0f, safe_gs);
+  const uint32_t g_lo = static_cast<uint32_t>(chunk_lo) * 2u + o.group_offset;
+  const uint32_t g_hi = static_cast<uint32_t>(chunk_hi) * 2u + o.group_offset;
+  uint2 lo0, hi0, lo1, hi1;
+  const uint32_t sb0 = ms_eden_group_lanes(&P[0], safe_gs, so, inv6, o.scale_seed, g_lo, g_hi, lo0, hi0);
+  const uint32_t sb1 = ms_eden_group_lanes(&P[16], safe_gs, so, inv6, o.scale_seed, g_lo + 1, g_hi + 1, lo1, hi1);
+  *reinterpret_cast<uint4*>(o.fp4 + chunk_lo * 16) = make_uint4(lo0.x, lo0.y, lo1.x, lo1.y);
+  *reinterpret_cast<uint4*>(o.fp4 + chunk_hi * 16) = make_uint4(hi0.x, hi0.y, hi1.x, hi1.y);
+  const uint32_t k_atoms = o.dst_row_len >> 6;
+  const size_t off_lo = o.packed ? packed_scale_offset(row_lo, chunk_in_row * 2, k_atoms) : chunk_lo * 2;
+  const size_t off_hi = o.packed ? packed_scale_offset(row_hi, chunk_in_row * 2, k_atoms) : chunk_hi * 2;
+  *reinterpret_cast<uint16_t*>(o.scales + off_lo) = static_cast<uint16_t>((sb0 & 0xffu) | ((sb1 & 0xffu) << 8));
+  *reinterpret_cast<uint16_t*>(o.scales + off_hi) = static_cast<uint16_t>(((sb0 >> 8) & 0xffu) | (sb1 & 0xff00u));
+  if (chunk_in_row == 0) {
+    o.global_scales[row_lo] = gs;
+    o.global_scales[row_hi] = gs;
+  }
 }
 
 // Signed input pair (u[i], u[i+16]) from two values and the chunk's 32 sign bits.
@@ -723,6 +803,126 @@ __global__ void __launch_bounds__(256) ms_eden_tile_kernel(const MsEdenTileParam
         P[i] = signed_pair(tile[row * kTileLd + chunk * 32 + i], tile[row * kTileLd + chunk * 32 + i + 16], mask, i);
       ms_eden_emit_chunk(P, p.r, gs, p.scale_override, out_row, k0 >> 5);
     }
+  }
+}
+
+// Pair kernel for bf16 sources whose extents are whole tiles (rows % 128 == 0, cols % 64 == 0):
+// the same outputs as ms_eden_tile_kernel<0, bf16, true>, organised for instruction count.
+//  * Persistent CTAs walk the tiles; the next tile's 128 x 128-byte rows arrive through
+//    cp.async into the other shared-memory stage while the current one is being quantized.
+//    The tile stays bf16; the 144-byte row pitch makes all three access patterns conflict-free.
+//  * Every thread quantizes TWO chunks at once, one per f32x2 lane, chosen so that both lanes
+//    share their K positions: warps 0-3 take two adjacent source columns down 32 rows (the
+//    transposed operand), warps 4-7 take rows r and r+32 along 32 columns (the row operand).
+//    One 32-bit shared load then feeds both lanes, the random signs are one xor on the raw
+//    bf16 pair, and all five Hadamard strides are packed register-to-register operations.
+constexpr int kPairPitch = 144;                          // bytes per staged row
+constexpr int kPairStageBytes = kTileRows * kPairPitch;  // 18432
+
+__device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+__global__ void __launch_bounds__(256, 2) ms_eden_pair_bf16_kernel(const MsEdenTileParams p, uint32_t tiles_x,
+                                                                    uint32_t tile_count) {
+  __shared__ __align__(16) uint8_t stage[2][kPairStageBytes];
+  __shared__ __align__(16) uint32_t flip_row[kTileRows];      // 0x80008000 where the row's sign is negative
+  __shared__ __align__(16) uint32_t flip_col[kTileCols / 2];  // sign bits of a column pair, bf16-pair positions
+  __shared__ __align__(8) float quarter_sum[4][kTileCols];
+  const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.x);
+  const float gs = p.use_host_scale ? p.global_scale_host : p.global_scale_dev[0];
+  const uint32_t stage_base = static_cast<uint32_t>(__cvta_generic_to_shared(&stage[0][0]));
+
+  // 1024 16-byte pieces per tile, four per thread: piece i = row i/8, 16-byte column i%8
+  auto issue_tile = [&](uint32_t tile, uint32_t buf) {
+    const uint32_t r0 = (tile / tiles_x) * kTileRows, c0 = (tile % tiles_x) * kTileCols;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t i = tid + 256 * k, row = i >> 3, piece = i & 7;
+      cp_async_16(stage_base + buf * kPairStageBytes + row * kPairPitch + piece * 16,
+                  x + static_cast<size_t>(r0 + row) * p.src_cols + c0 + piece * 8);
+    }
+  };
+
+  uint32_t tile = blockIdx.x, buf = 0;
+  if (tile < tile_count) issue_tile(tile, 0);
+  cp_async_commit();
+  for (; tile < tile_count; tile += gridDim.x, buf ^= 1) {
+    const uint32_t next = tile + gridDim.x;
+    if (next < tile_count) issue_tile(next, buf ^ 1);
+    cp_async_commit();
+    const uint32_t ty = tile / tiles_x, r0 = ty * kTileRows, c0 = (tile % tiles_x) * kTileCols;
+    if (tid < kTileRows) {
+      flip_row[tid] = random_sign_negative(p.sign_seed, r0 + tid + p.t.sign_offset) ? 0x80008000u : 0u;
+    } else if (tid < kTileRows + kTileCols / 2) {
+      const uint32_t col = c0 + 2 * (tid - kTileRows) + p.r.sign_offset;
+      flip_col[tid - kTileRows] = (random_sign_negative(p.sign_seed, col) ? 0x00008000u : 0u) |
+                                  (random_sign_negative(p.sign_seed, col + 1) ? 0x80000000u : 0u);
+    }
+    cp_async_wait_all_but_one();
+    __syncthreads();
+    const uint8_t* t = stage[buf];
+
+    if (p.col_sum_partials && warp >= 4) {
+      // Column sums of this tile in the fixed order of the bias gradient: per column four
+      // sequential 32-row sums, combined below as ((q0 + q1) + q2) + q3.  Two columns per thread
+      // (done by the row-operand warps, whose tile loads are the cheaper ones).
+      const uint32_t quarter = warp - 4;
+      f32x2_t acc = pack2(0.0f, 0.0f);
+#pragma unroll 8
+      for (int j = 0; j < 32; ++j) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(t + (quarter * 32 + j) * kPairPitch + lane * 4);
+        acc = add2(acc, pack2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u)));
+      }
+      float a0, a1;
+      unpack2(acc, a0, a1);
+      *reinterpret_cast<float2*>(&quarter_sum[quarter][2 * lane]) = make_float2(a0, a1);
+    }
+
+    f32x2_t P[32];
+    uint32_t row_lo, row_hi, chunk_in_row;
+    if (warp < 4) {
+      // transposed operand: source columns c0 + 2*lane (+1), K = source rows r0 + 32*warp ..
+      const uint8_t* src = t + warp * 32 * kPairPitch + lane * 4;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(src + i * kPairPitch) ^ flip_row[warp * 32 + i];
+        P[i] = pack2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+      }
+      row_lo = c0 + 2 * lane;
+      row_hi = row_lo + 1;
+      chunk_in_row = (r0 >> 5) + warp;
+    } else {
+      // row operand: rows r0 + base + lane and + 32 more, K = source columns c0 + 32*chunk ..
+      const uint32_t chunk = warp & 1, row = ((warp - 4) >> 1) * 64 + lane;
+      const uint8_t* src_lo = t + row * kPairPitch + chunk * 64;
+      const uint8_t* src_hi = src_lo + 32 * kPairPitch;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 a = *reinterpret_cast<const uint4*>(src_lo + 16 * j);
+        const uint4 b = *reinterpret_cast<const uint4*>(src_hi + 16 * j);
+        const uint4 f = *reinterpret_cast<const uint4*>(&flip_col[chunk * 16 + 4 * j]);
+        const uint32_t wa[4] = {a.x ^ f.x, a.y ^ f.y, a.z ^ f.z, a.w ^ f.w};
+        const uint32_t wb[4] = {b.x ^ f.x, b.y ^ f.y, b.z ^ f.z, b.w ^ f.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          P[8 * j + 2 * k] = pack2(__uint_as_float(wa[k] << 16), __uint_as_float(wb[k] << 16));
+          P[8 * j + 2 * k + 1] = pack2(__uint_as_float(wa[k] & 0xffff0000u), __uint_as_float(wb[k] & 0xffff0000u));
+        }
+      }
+      row_lo = r0 + row;
+      row_hi = row_lo + 32;
+      chunk_in_row = (c0 >> 5) + chunk;
+    }
+    // one copy of the quantizer body for both roles (the role is warp-uniform)
+    ms_eden_emit_chunk_lanes(P, warp < 4 ? p.t : p.r, gs, p.scale_override, row_lo, row_hi, chunk_in_row);
+    __syncthreads();
+    if (p.col_sum_partials && tid < kTileCols)
+      p.col_sum_partials[static_cast<size_t>(ty) * p.src_cols + c0 + tid] =
+          ((quarter_sum[0][tid] + quarter_sum[1][tid]) + quarter_sum[2][tid]) + quarter_sum[3][tid];
   }
 }
 
@@ -1151,8 +1351,16 @@ int launch_ms_eden_pair(cudaStream_t s, const nvfp4_ms_eden_args& r, const nvfp4
   p.t = make_out(t, cols);
   p.r = make_out(r, rows);
   p.col_sum_partials = col_sum_partials;
-  if (r.src_dtype == NVFP4_DTYPE_BF16) launch_tile<0, __nv_bfloat16, true>(s, p);
-  else launch_tile<0, float, true>(s, p);
+  const bool whole_tiles = rows % kTileRows == 0 && cols % kTileCols == 0 && t.dst_row_len == rows &&
+                           r.dst_row_len == cols && (reinterpret_cast<uintptr_t>(r.x) & 15u) == 0;
+  if (r.src_dtype == NVFP4_DTYPE_BF16 && whole_tiles) {
+    const uint32_t tiles_x = cols / kTileCols, tile_count = tiles_x * (rows / kTileRows);
+    ms_eden_pair_bf16_kernel<<<min(tile_count, 148u * 2u), 256, 0, s>>>(p, tiles_x, tile_count);
+  } else if (r.src_dtype == NVFP4_DTYPE_BF16) {
+    launch_tile<0, __nv_bfloat16, true>(s, p);
+  } else {
+    launch_tile<0, float, true>(s, p);
+  }
   count_launch();
   int rc = static_cast<int>(cudaGetLastError());
   if (rc) return rc;
