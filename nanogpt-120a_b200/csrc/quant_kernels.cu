@@ -374,17 +374,25 @@ __device__ __forceinline__ uint32_t stochastic_e4m3_scale(float value, uint32_t 
   const float down = above ? other : cur;
   const uint32_t up_bits = above ? cb : ob;
   const uint32_t down_bits = above ? ob : cb;
-  const float denom = up - down;
-  const uint32_t dbits = __float_as_uint(denom);
-  float p;
-  if ((dbits & 0x807fffffu) == 0u && dbits - 0x00800000u <= 0x7e000000u - 0x00800000u) {
-    // Neighbouring E4M3 values differ by a power of two, 2^e with a normal reciprocal: dividing
-    // by it and multiplying by 2^-e round the same real number, so the product is the quotient.
-    p = (value - down) * __uint_as_float(0x7f000000u - dbits);
-  } else {
-    p = denom == 0.0f ? 0.0f : (value - down) / denom;
-  }
-  return random_unit_f32(seed, group) < p ? up_bits : down_bits;
+  // p = (value - down) / (up - down).  Two E4M3 codes one step apart differ by +-2^e with
+  // -9 <= e <= 5 unless one of them is the NaN code or the step was clamped, so the difference is
+  // a power of two, zero or NaN.  For a power of two the quotient equals the product with the
+  // exact reciprocal (both round the same real number); for zero the reference takes p = 0 and
+  // for NaN the quotient is NaN: either way the draw is not below p and the lower code is kept.
+  const uint32_t dbits = __float_as_uint(up - down);
+  const uint32_t mag = dbits & 0x7fffffffu;
+  const bool pow2 = (mag & 0x007fffffu) == 0u && mag - 0x00800000u <= 0x7e000000u - 0x00800000u;
+  const float p = (value - down) * __uint_as_float((0x7f000000u - mag) | (dbits & 0x80000000u));
+  return (pow2 && random_unit_f32(seed, group) < p) ? up_bits : down_bits;
+}
+
+// a / b by the IEEE division instruction, issued unconditionally (the compiler would otherwise
+// wrap it in a branch where its result is selected away, and a branch per group costs more
+// than the quotient).
+__device__ __forceinline__ float div_rn_always(float a, float b) {
+  float r;
+  asm volatile("div.rn.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
 }
 
 // In-register 32-point Walsh-Hadamard butterfly in the reference's order
@@ -459,8 +467,9 @@ __device__ __forceinline__ uint32_t ms_eden_group_lanes(const f32x2_t* H, float 
           num_a, num_b);
   unpack2(add2(add2(add2(den8[0], den8[4]), add2(den8[2], den8[6])), add2(add2(den8[1], den8[5]), add2(den8[3], den8[7]))),
           den_a, den_b);
-  const float sa = nz(s0a * (den_a == 0.0f ? 1.0f : num_a / den_a));
-  const float sb = nz(s0b * (den_b == 0.0f ? 1.0f : num_b / den_b));
+  const float qa = div_rn_always(num_a, den_a), qb = div_rn_always(num_b, den_b);
+  const float sa = nz(s0a * (den_a == 0.0f ? 1.0f : qa));
+  const float sb = nz(s0b * (den_b == 0.0f ? 1.0f : qb));
   return stochastic_e4m3_scale(sa, scale_seed, group_lo) | (stochastic_e4m3_scale(sb, scale_seed, group_hi) << 8);
 }
 
