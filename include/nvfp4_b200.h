@@ -141,10 +141,13 @@ int nvfp4_quantize_four_six(void* stream, const void* x, int dtype, const float*
 /* Row amax and rowwise four-six in one pass over the input (the caller pattern
  * RowwiseNvfp4Scratch::quantize_row_amax, crates/gpt2-nvfp4/src/types/nvfp4_scratch/scratch.rs:35-52,
  * issues row_amax_f32 then fp32_to_nvfp4_four_six_rowwise).  Same bytes as those two calls.
- * out_row_amax (f32[rows]) is optional for rows of up to 4096 elements and required beyond. */
+ * out_row_amax (f32[rows]) is optional for rows of up to 4096 elements and required beyond.
+ * out_decoded_amax (f32[1], optional): max |decoded value| of the quantized tensor, the number
+ * rowwise_nvfp4_chunk_amax + its reduction (utils/nvfp4/quant/kernels/ms_eden/amax.rs:23-104) derive
+ * from the stored tensor in the backward pass; pass it on as x_decoded_amax to skip that pass. */
 int nvfp4_quantize_four_six_rowwise_fused(void* stream, const void* x, int dtype, uint32_t rows, uint32_t cols,
                                           uint8_t* out_fp4, uint8_t* out_scales, int scale_layout,
-                                          float* out_global_scale, float* out_row_amax);
+                                          float* out_global_scale, float* out_row_amax, float* out_decoded_amax);
 
 /* MS-EDEN quantizer (random-sign Hadamard-32 rotation, RTN nibbles, EDEN-corrected block
  * scale rounded stochastically with a counter RNG) ---------------------------------------- */
@@ -400,6 +403,8 @@ typedef struct nvfp4_linear_backward_args {
   uint32_t precomputed_e_amax_chunks; /* 0 = compute the dY chunk amax here                   */
   uint32_t token_offset;             /* first token of this shard (sign / RNG index spaces)   */
   const float* e_global_scale_override; /* device f32[1] shared across shards, or NULL        */
+  const float* x_decoded_amax;       /* device f32[1]: max |decoded X| (from the forward quantizer),
+                                        or NULL = compute it here with a pass over X             */
 } nvfp4_linear_backward_args;
 
 /* gpt/linear_backward/ms_eden.rs:15-55  LinearBackwardModule::backward_ms_eden :

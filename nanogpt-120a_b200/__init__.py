@@ -77,6 +77,7 @@ class LinearBackwardArgs(Structure):
         ("dinput_dtype", c_int), ("dweight", c_void_p), ("dweight_dtype", c_int), ("dbias", c_void_p), ("token_count", c_uint32),
         ("input_dim", c_uint32), ("output_dim", c_uint32), ("sign_seed", c_uint32), ("scale_seed", c_uint32),
         ("precomputed_e_amax_chunks", c_uint32), ("token_offset", c_uint32), ("e_global_scale_override", c_void_p),
+        ("x_decoded_amax", c_void_p),
     ]
 
 
@@ -95,7 +96,7 @@ _SIGNATURES = {
     "nvfp4_fp32_to_nvfp4_four_six_padded": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _U],
     "nvfp4_fp32_transpose_to_nvfp4_four_six_padded": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _U],
     "nvfp4_quantize_four_six": [_P, _P, c_int, _P, c_int, _U, _U, _P, _P, c_int, _P],
-    "nvfp4_quantize_four_six_rowwise_fused": [_P, _P, c_int, _U, _U, _P, _P, c_int, _P, _P],
+    "nvfp4_quantize_four_six_rowwise_fused": [_P, _P, c_int, _U, _U, _P, _P, c_int, _P, _P, _P],
     "nvfp4_ms_eden_quantize": [_P, POINTER(MsEdenArgs)],
     "nvfp4_fp32_to_nvfp4_ms_eden": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _F, _F, _U, _U],
     "nvfp4_fp32_to_nvfp4_ms_eden_device_scale": [_P, _P, _P, _P, _P, _P, _P, _U, _U, _U, _F, _U, _U],
@@ -250,6 +251,7 @@ class Nvfp4Tensor:
     cols: int
     packed: bool = False
     rowwise: bool = False
+    decoded_amax: Optional[torch.Tensor] = None  # f32 [1]: max |decoded value|, when the quantizer emitted it
 
 
 def _empty_u8(n: int, device) -> torch.Tensor:
@@ -343,8 +345,11 @@ class Nvfp4QuantModule:
         return self.fp32_to_nvfp4_four_six_padded(x, amax, padded_rows, padded_cols, transposed=True)
 
     def quantize_four_six(self, x: torch.Tensor, amax: Optional[torch.Tensor] = None, rowwise: bool = False,
-                          packed: bool = True, out: Optional[Nvfp4Tensor] = None) -> Nvfp4Tensor:
-        """B200-native form: f32 / bf16 input, scales written in the layout the GEMM reads."""
+                          packed: bool = True, out: Optional[Nvfp4Tensor] = None,
+                          decoded_amax: bool = False) -> Nvfp4Tensor:
+        """B200-native form: f32 / bf16 input, scales written in the layout the GEMM reads.
+        decoded_amax (fused rowwise path only): also emit max |decoded value| of the result, which
+        LinearBackwardModule.backward_ms_eden then uses instead of a pass over the saved tensor."""
         _require_cuda()
         rows, cols = x.shape
         fused = amax is None and rowwise
@@ -358,9 +363,13 @@ class Nvfp4QuantModule:
                               packed=packed, rowwise=rowwise)
         if fused:  # row amax and quantization in one pass over x
             row_amax = torch.empty(rows, dtype=torch.float32, device=x.device) if cols > 4096 else None
+            if decoded_amax and out.decoded_amax is None:
+                out.decoded_amax = torch.empty(1, dtype=torch.float32, device=x.device)
+            elif not decoded_amax:
+                out.decoded_amax = None
             _call("nvfp4_quantize_four_six_rowwise_fused", _stream(), _ptr(x), _dtype_code(x), rows, cols,
                   _ptr(out.bytes), _ptr(out.scales), SCALES_PACKED if packed else SCALES_LOGICAL,
-                  _ptr(out.global_scales), _ptr(row_amax))
+                  _ptr(out.global_scales), _ptr(row_amax), _ptr(out.decoded_amax))
             return out
         _call("nvfp4_quantize_four_six", _stream(), _ptr(x), _dtype_code(x), _ptr(amax), 1 if rowwise else 0, rows,
               cols, _ptr(out.bytes), _ptr(out.scales), SCALES_PACKED if packed else SCALES_LOGICAL,
@@ -703,6 +712,7 @@ class LinearBackwardModule:
         a.precomputed_e_amax_chunks = precomputed_e_amax_chunks
         a.token_offset = token_offset
         a.e_global_scale_override = _ptr(e_global_scale)
+        a.x_decoded_amax = _ptr(input.decoded_amax)
         _call("nvfp4_linear_backward_ms_eden", _stream(), ctypes.byref(a))
         return dinput, dweight, (dbias if want_dbias else None)
 

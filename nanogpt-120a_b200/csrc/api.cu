@@ -112,7 +112,8 @@ int nvfp4_quantize_four_six(void* stream, const void* x, int dtype, const float*
 
 int nvfp4_quantize_four_six_rowwise_fused(void* stream, const void* x, int dtype, uint32_t rows, uint32_t cols,
                                           uint8_t* out_fp4, uint8_t* out_scales, int scale_layout,
-                                          float* out_global_scale, float* out_row_amax) {
+                                          float* out_global_scale, float* out_row_amax,
+                                          float* out_decoded_amax) {
   if (cols % 16 != 0) return invalid("quantize_four_six_rowwise_fused: cols must be a multiple of 16");
   if (scale_layout == NVFP4_SCALES_PACKED && cols % 64 != 0)
     return invalid("quantize_four_six_rowwise_fused: the packed scale layout needs cols % 64 == 0");
@@ -120,14 +121,17 @@ int nvfp4_quantize_four_six_rowwise_fused(void* stream, const void* x, int dtype
   if (reinterpret_cast<uintptr_t>(x) & 15u) return invalid("quantize_four_six_rowwise_fused: input must be 16-byte aligned");
   const int packed = scale_layout == NVFP4_SCALES_PACKED;
   int rc = launch_four_six_rowwise_fused(S(stream), x, dtype, rows, cols, out_fp4, out_scales, packed,
-                                         out_global_scale, out_row_amax);
+                                         out_global_scale, out_row_amax, out_decoded_amax);
   if (rc != -1) return rc;
   // rows too long for one thread block: a row amax pass, then the rowwise quantizer
   if (!out_row_amax) return invalid("quantize_four_six_rowwise_fused: rows longer than 4096 need out_row_amax");
   rc = launch_row_amax(S(stream), x, dtype, out_row_amax, rows, cols);
   if (rc) return rc;
-  return launch_four_six(S(stream), x, dtype, out_row_amax, 1, rows, cols, out_fp4, out_scales, packed,
-                         out_global_scale);
+  rc = launch_four_six(S(stream), x, dtype, out_row_amax, 1, rows, cols, out_fp4, out_scales, packed,
+                       out_global_scale);
+  if (rc || !out_decoded_amax) return rc;
+  return launch_nvfp4_amax(S(stream), out_fp4, out_scales, out_global_scale, rows, cols, 1, packed, nullptr,
+                           out_decoded_amax);
 }
 
 // ---- MS-EDEN ----------------------------------------------------------------------------
@@ -308,17 +312,22 @@ static int nvfp4_source_transpose(void* stream, int kind, const uint8_t* in_byte
                                   float* out_chunk_amax, float* out_gs, uint32_t source_rows, uint32_t source_cols,
                                   uint32_t dst_row_len, uint32_t sign_seed, uint32_t scale_seed, bool chunk_amax_out,
                                   int scale_layout, uint32_t col_offset, uint32_t group_offset,
-                                  int src_scale_layout = NVFP4_SCALES_LOGICAL) {
+                                  int src_scale_layout = NVFP4_SCALES_LOGICAL,
+                                  const float* precomputed_amax = nullptr) {
   const uint64_t n = static_cast<uint64_t>(source_rows) * source_cols;
   if (source_cols % 16 != 0) return invalid("nvfp4 transpose: source_cols must be a multiple of 16");
   if (src_scale_layout == NVFP4_SCALES_PACKED && source_cols % 64 != 0)
     return invalid("nvfp4 transpose: a packed source scale layout needs source_cols % 64 == 0");
-  // the amax kernel leaves max(chunk amax) in out_gs; turn it into the MS-EDEN global scale in place
-  int rc = launch_nvfp4_amax(S(stream), in_bytes, in_scales, in_global, source_rows, source_cols,
-                             kind == NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED, src_scale_layout == NVFP4_SCALES_PACKED,
-                             out_chunk_amax, out_gs);
+  // the amax kernel leaves max(chunk amax) in out_gs; turn it into the MS-EDEN global scale in place.
+  // A caller that already holds the decoded amax of the source (the forward quantizer can emit it)
+  // skips the pass over the source.
+  int rc = 0;
+  if (!precomputed_amax)
+    rc = launch_nvfp4_amax(S(stream), in_bytes, in_scales, in_global, source_rows, source_cols,
+                           kind == NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED, src_scale_layout == NVFP4_SCALES_PACKED,
+                           out_chunk_amax, out_gs);
   if (rc) return rc;
-  rc = launch_ms_eden_scale_from_amax(S(stream), out_gs, out_gs);
+  rc = launch_ms_eden_scale_from_amax(S(stream), precomputed_amax ? precomputed_amax : out_gs, out_gs);
   if (rc) return rc;
   (void)n;
   nvfp4_ms_eden_args a;
@@ -578,7 +587,8 @@ int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args
   rc = nvfp4_source_transpose(stream, NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED, a->x_bytes, a->x_scales, a->x_globals,
                               a->input_t_h.bytes, a->input_t_h.scales_packed, a->input_t_h.global_scales,
                               a->input_t_h.chunk_amax, a->input_t_h.global_scale, T, I, tk, a->sign_seed,
-                              a->scale_seed ^ 0xc2b2ae35u, false, NVFP4_SCALES_PACKED, a->token_offset, 0, a->x_scale_layout);
+                              a->scale_seed ^ 0xc2b2ae35u, false, NVFP4_SCALES_PACKED, a->token_offset, 0, a->x_scale_layout,
+                              a->x_decoded_amax);
   if (rc) return rc;
 
   // 5. dX = dY . W   (contraction over output features) and dW = dY^T . X (over tokens)

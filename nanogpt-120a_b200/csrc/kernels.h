@@ -19,7 +19,8 @@ int launch_ms_eden_scale_from_amax(cudaStream_t s, const float* amax, float* out
 int launch_four_six(cudaStream_t s, const void* x, int dtype, const float* amax, int rowwise, uint32_t rows,
                     uint32_t cols, uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs);
 int launch_four_six_rowwise_fused(cudaStream_t s, const void* x, int dtype, uint32_t rows, uint32_t cols,
-                                  uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs, float* out_amax);
+                                  uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs, float* out_amax,
+                                  float* decoded_amax);
 int launch_four_six_padded(cudaStream_t s, const float* x, const float* amax, uint8_t* out_fp4, uint8_t* out_scales,
                            float* out_gs, uint32_t rows, uint32_t cols, uint32_t padded_rows, uint32_t padded_cols,
                            int transposed);

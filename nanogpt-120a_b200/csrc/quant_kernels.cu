@@ -272,20 +272,35 @@ __global__ void __launch_bounds__(256) four_six_kernel(const T* __restrict__ x, 
   if (kRowwise ? (kg == 0) : (g == 0)) out_gs[kRowwise ? row : 0] = gs;
 }
 
+// Largest decoded magnitude of one quantized 16-group: |e2m1| grows with its 3-bit magnitude
+// code and (q * scale) * gs is monotonic in q >= 0, so it is the decode of the largest code
+// (the same expression the stand-alone NVFP4 amax kernel evaluates per group).
+__device__ __forceinline__ float decoded_group_amax(uint2 nibbles, uint32_t scale_byte, float gs) {
+  uint32_t mx = __vmaxu4(__vmaxu4(nibbles.x & 0x07070707u, (nibbles.x >> 4) & 0x07070707u),
+                         __vmaxu4(nibbles.y & 0x07070707u, (nibbles.y >> 4) & 0x07070707u));
+  mx = __vmaxu4(mx, mx >> 16);
+  mx = __vmaxu4(mx, mx >> 8) & 0x7u;
+  return fabsf(e2m1_value(mx) * e4m3_value(scale_byte) * gs);
+}
+
 // Row amax and rowwise four-six in ONE pass over the input: a CTA owns whole rows (one thread
 // per 16-group), the row amax is the shared-memory max of the group amaxes the quantizer needs
 // anyway, and the groups are quantized from registers.  Same bytes as row_amax followed by the
 // rowwise kernel (crates/gpt2-nvfp4/src/types/nvfp4_scratch/scratch.rs:35-52 issues those two).
+// decoded_amax (optional, zeroed by the launcher): max |decoded value| of the whole quantized
+// tensor, i.e. what utils/nvfp4/quant/kernels/ms_eden/amax.rs:23-64 computes from the stored
+// tensor before the backward transposer -- handed over so that pass can be skipped.
 template <typename T, bool kPacked>
 __global__ void __launch_bounds__(256) four_six_rowwise_fused_kernel(const T* __restrict__ x,
                                                                       uint8_t* __restrict__ out_fp4,
                                                                       uint8_t* __restrict__ out_scales,
                                                                       float* __restrict__ out_gs,
-                                                                      float* __restrict__ out_amax, uint32_t rows,
+                                                                      float* __restrict__ out_amax,
+                                                                      float* __restrict__ decoded_amax, uint32_t rows,
                                                                       uint32_t groups_per_row, uint32_t rows_per_cta) {
-  extern __shared__ unsigned int row_amax_bits[];
+  extern __shared__ unsigned int row_amax_bits[];  // [rows_per_cta] row amax, then one word for the CTA's decoded amax
   const uint32_t t = threadIdx.x;
-  if (t < rows_per_cta) row_amax_bits[t] = 0u;
+  for (uint32_t i = t; i <= rows_per_cta; i += blockDim.x) row_amax_bits[i] = 0u;
   __syncthreads();
   const uint32_t local_row = t / groups_per_row;
   const uint32_t kg = t - local_row * groups_per_row;
@@ -296,24 +311,33 @@ __global__ void __launch_bounds__(256) four_six_rowwise_fused_kernel(const T* __
     Load16<T>::run(x + (static_cast<size_t>(row) * groups_per_row + kg) * 16, v);
     float ga = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) ga = max_f32(ga, fabsf(v[i]));
+    for (int i = 0; i < 16; i += 2) ga = max3_abs(ga, v[i], v[i + 1]);
     atomicMax(&row_amax_bits[local_row], __float_as_uint(ga));  // non-negative floats order like their bits
   }
   __syncthreads();
-  if (!active) return;
-  const float amax = __uint_as_float(row_amax_bits[local_row]);
-  const float gs = four_six_global_scale(amax);
-  uint2 packed;
-  const uint32_t b = four_six_group(v, gs, packed);
-  const size_t g = static_cast<size_t>(row) * groups_per_row + kg;
-  *reinterpret_cast<uint2*>(out_fp4 + g * 8) = packed;
-  if (kPacked)
-    out_scales[packed_scale_offset(row, kg, groups_per_row >> 2)] = static_cast<uint8_t>(b);
-  else
-    out_scales[g] = static_cast<uint8_t>(b);
-  if (kg == 0) {
-    out_gs[row] = gs;
-    if (out_amax) out_amax[row] = amax;
+  uint32_t dec_bits = 0u;
+  if (active) {
+    const float amax = __uint_as_float(row_amax_bits[local_row]);
+    const float gs = four_six_global_scale(amax);
+    uint2 packed;
+    const uint32_t b = four_six_group(v, gs, packed);
+    const size_t g = static_cast<size_t>(row) * groups_per_row + kg;
+    *reinterpret_cast<uint2*>(out_fp4 + g * 8) = packed;
+    if (kPacked)
+      out_scales[packed_scale_offset(row, kg, groups_per_row >> 2)] = static_cast<uint8_t>(b);
+    else
+      out_scales[g] = static_cast<uint8_t>(b);
+    if (kg == 0) {
+      out_gs[row] = gs;
+      if (out_amax) out_amax[row] = amax;
+    }
+    if (decoded_amax) dec_bits = __float_as_uint(decoded_group_amax(packed, b, gs));
+  }
+  if (decoded_amax) {  // uniform across the CTA
+    dec_bits = __reduce_max_sync(0xffffffffu, dec_bits);
+    if ((t & 31) == 0) atomicMax(&row_amax_bits[rows_per_cta], dec_bits);
+    __syncthreads();
+    if (t == 0) atomicMax(reinterpret_cast<unsigned int*>(decoded_amax), row_amax_bits[rows_per_cta]);
   }
 }
 
@@ -1167,23 +1191,30 @@ int launch_four_six(cudaStream_t s, const void* x, int dtype, const float* amax,
 // Fused row amax + rowwise four-six.  Returns -1 when the row is too long for one CTA (the
 // caller then runs the two-kernel path).
 int launch_four_six_rowwise_fused(cudaStream_t s, const void* x, int dtype, uint32_t rows, uint32_t cols,
-                                  uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs, float* out_amax) {
+                                  uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs, float* out_amax,
+                                  float* decoded_amax) {
   const uint32_t gpr = cols / 16;
   if (gpr == 0 || gpr > 256) return -1;
+  if (decoded_amax) {
+    const cudaError_t err = cudaMemsetAsync(decoded_amax, 0, sizeof(float), s);
+    if (err != cudaSuccess) return static_cast<int>(err);
+  }
   if (rows == 0) return 0;
   const uint32_t rpc = 256 / gpr;
   const uint32_t threads = (rpc * gpr + 31) / 32 * 32;
   const uint32_t grid = (rows + rpc - 1) / rpc;
-  const size_t smem = rpc * sizeof(unsigned int);
+  const size_t smem = (rpc + 1) * sizeof(unsigned int);
+#define NVFP4_LAUNCH_FUSED(T, P) \
+  four_six_rowwise_fused_kernel<T, P><<<grid, threads, smem, s>>>(static_cast<const T*>(x), out_fp4, out_scales, \
+                                                                  out_gs, out_amax, decoded_amax, rows, gpr, rpc)
   if (dtype == NVFP4_DTYPE_F32) {
-    const float* p = static_cast<const float*>(x);
-    if (packed) four_six_rowwise_fused_kernel<float, true><<<grid, threads, smem, s>>>(p, out_fp4, out_scales, out_gs, out_amax, rows, gpr, rpc);
-    else four_six_rowwise_fused_kernel<float, false><<<grid, threads, smem, s>>>(p, out_fp4, out_scales, out_gs, out_amax, rows, gpr, rpc);
+    if (packed) NVFP4_LAUNCH_FUSED(float, true);
+    else NVFP4_LAUNCH_FUSED(float, false);
   } else {
-    const __nv_bfloat16* p = static_cast<const __nv_bfloat16*>(x);
-    if (packed) four_six_rowwise_fused_kernel<__nv_bfloat16, true><<<grid, threads, smem, s>>>(p, out_fp4, out_scales, out_gs, out_amax, rows, gpr, rpc);
-    else four_six_rowwise_fused_kernel<__nv_bfloat16, false><<<grid, threads, smem, s>>>(p, out_fp4, out_scales, out_gs, out_amax, rows, gpr, rpc);
+    if (packed) NVFP4_LAUNCH_FUSED(__nv_bfloat16, true);
+    else NVFP4_LAUNCH_FUSED(__nv_bfloat16, false);
   }
+#undef NVFP4_LAUNCH_FUSED
   count_launch();
   int rc = static_cast<int>(cudaGetLastError());
   if (rc) return rc;

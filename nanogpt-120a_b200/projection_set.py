@@ -159,7 +159,8 @@ class ProjectionSet:
 
     def _forward_linear(self, lin: _Linear) -> None:
         x = self.x[lin.in_dim]
-        self.quant.quantize_four_six(x, rowwise=True, packed=True, out=lin.xq)  # amax fused; saved for backward
+        # row amax fused; the decoded amax rides along so that backward need not re-read X for it
+        self.quant.quantize_four_six(x, rowwise=True, packed=True, out=lin.xq, decoded_amax=True)
         aux = self.pre[lin.out_dim] if lin.epilogue == EPI_RELU2 else None
         self._timed_gemm(lambda: self.gemm.gemm(lin.xq, lin.wq, bias=lin.bias, epilogue=lin.epilogue,
                                                 out=self.y[lin.out_dim], aux=aux),

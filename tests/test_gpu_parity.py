@@ -523,6 +523,42 @@ def test_linear_backward_vs_oracle(pkg, oracle, dev, tokens, in_dim, out_dim):
     assert rel_fro(cpu(dw), ef.T @ xf) < 0.3
 
 
+@pytest.mark.parametrize("shape,packed", [((130, 192), True), ((64, 48), False), ((5, 4096), False), ((3, 8192), False)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_four_six_fused_decoded_amax(pkg, oracle, dev, shape, packed, dtype):
+    """The fused rowwise quantizer's by-product equals the amax of the decoded tensor
+    (utils/nvfp4/quant/kernels/ms_eden/amax.rs:23-64), on the one- and the two-kernel path."""
+    q = pkg.Nvfp4QuantModule()
+    x = with_outliers(bf16_normal(77, shape), seed=3, every=61).to(dtype)
+    t = q.quantize_four_six(x.to(dev), rowwise=True, packed=packed, decoded_amax=True)
+    xf = x.float().numpy()
+    ob, os_, og = oracle.four_six(xf, oracle.row_amax(xf), True)
+    assert np.array_equal(cpu(t.bytes), ob)
+    want = oracle.nvfp4_amax(ob, os_, og, shape[0], shape[1], True)[1]
+    assert cpu(t.decoded_amax).tobytes() == np.asarray(want, np.float32).tobytes()
+    assert float(want[0]) == np.abs(oracle.decode(ob, os_, og, shape[0], shape[1], True, False)).max()
+
+
+def test_linear_backward_precomputed_x_amax(pkg, oracle, dev):
+    """Handing the forward quantizer's decoded amax to the backward changes no output byte."""
+    q, bwd = pkg.Nvfp4QuantModule(), pkg.LinearBackwardModule()
+    tokens, in_dim, out_dim = 256, 192, 128
+    x, w = bf16_normal(401, (tokens, in_dim)), bf16_normal(402, (out_dim, in_dim), 0.02)
+    dy = bf16_normal(403, (tokens, out_dim), 1e-3).to(dev)
+    wq = q.quantize_four_six(w.to(dev), rowwise=False, packed=True)
+    outs = []
+    for hand_over in (False, True):
+        xq = q.quantize_four_six(x.to(dev), rowwise=True, packed=True, decoded_amax=hand_over)
+        assert (xq.decoded_amax is not None) == hand_over
+        sc = pkg.LinearBackwardScratch(tokens, in_dim, out_dim, dev)
+        dx, dw, db = bwd.backward_ms_eden(e=dy, weight=wq, input=xq, scratch=sc, sign_seed=SIGN, scale_seed=SCALE)
+        outs.append((cpu(sc.input_t_h["bytes"]), cpu(sc.input_t_h["scales_packed"]), cpu(sc.input_t_h["global_scale"]),
+                     cpu(dx), cpu(dw), cpu(db)))
+    for a, b in zip(*outs):
+        assert a.tobytes() == b.tobytes()
+    assert_no_timeouts(pkg)
+
+
 def test_linear_backward_sharded_equals_whole(pkg, oracle, dev):
     """Token sharding (two shards run back to back on one GPU): with the shared dY scale and the
     token offsets, shard dX rows equal the unsharded rows and the shard dW sum matches."""
