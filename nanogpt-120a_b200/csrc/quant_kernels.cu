@@ -959,6 +959,98 @@ __global__ void __launch_bounds__(256, 2) ms_eden_pair_bf16_kernel(const MsEdenT
   }
 }
 
+// Transposer for NVFP4 sources whose extents are whole 128 x 128 tiles and whose scale bytes are
+// in the packed layout: the same outputs as ms_eden_tile_kernel<2 | 3, float, false>, organised
+// like the pair kernel above.  One nibble byte holds two adjacent source columns of one row,
+// which are exactly the two f32x2 lanes of a thread (two output rows, the same K position):
+// per K position a thread does one byte load, one E2M1x2 decode and two packed multiplies,
+// (q * scale) * global_scale as utils/nvfp4/tensor.rs:48-57 decodes.  The random sign of the K
+// position (the source row) is folded into that row's global scale, (q*s) * (-g) == -((q*s) * g).
+constexpr int kNvTileCols = 128;                          // source columns per tile
+constexpr int kNvBytePitch = kNvTileCols / 2 + 16;        // staged bytes per source row
+constexpr int kNvStageBytes = kTileRows * kNvBytePitch;   // 10240
+
+template <bool kRowwise>
+__global__ void __launch_bounds__(256, 2) ms_eden_nvfp4_transpose_kernel(const MsEdenTileParams p, uint32_t tiles_x,
+                                                                          uint32_t tile_count) {
+  __shared__ __align__(16) uint8_t stage[2][kNvStageBytes];
+  __shared__ __align__(16) float2 scale2[kTileRows][kNvTileCols / 16];  // block scale of (row, group), duplicated
+  __shared__ __align__(16) float2 sgs2[kTileRows];                      // signed global scale of the row, duplicated
+  const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float gs = p.use_host_scale ? p.global_scale_host : p.global_scale_dev[0];
+  const uint32_t stage_base = static_cast<uint32_t>(__cvta_generic_to_shared(&stage[0][0]));
+  const uint32_t k_atoms = p.src_cols >> 6;
+
+  // 512 16-byte pieces per tile, two per thread: piece i = row i/4, 16-byte column i%4
+  auto issue_tile = [&](uint32_t tile, uint32_t buf) {
+    const uint32_t r0 = (tile / tiles_x) * kTileRows, c0 = (tile % tiles_x) * kNvTileCols;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const uint32_t i = tid + 256 * k, row = i >> 2, piece = i & 3;
+      cp_async_16(stage_base + buf * kNvStageBytes + row * kNvBytePitch + piece * 16,
+                  p.src_bytes + ((static_cast<size_t>(r0 + row) * p.src_cols + c0) >> 1) + piece * 16);
+    }
+  };
+  // The tile's 1024 scale bytes are two adjacent 512-byte blocks of the packed plane; thread t
+  // takes word t: block t/128, and inside it the four groups of row (w%4)*32 + w/4, w = t%128.
+  auto scale_word = [&](uint32_t tile) {
+    const uint32_t rb = tile / tiles_x, atom0 = (tile % tiles_x) * 2;
+    return __ldg(reinterpret_cast<const uint32_t*>(p.src_scales + (static_cast<size_t>(rb) * k_atoms + atom0) * 512u) + tid);
+  };
+
+  uint32_t tile = blockIdx.x, buf = 0;
+  uint32_t sw = 0;
+  if (tile < tile_count) {
+    issue_tile(tile, 0);
+    sw = scale_word(tile);
+  }
+  cp_async_commit();
+  for (; tile < tile_count; tile += gridDim.x, buf ^= 1) {
+    const uint32_t next = tile + gridDim.x;
+    uint32_t sw_next = 0;
+    if (next < tile_count) {
+      issue_tile(next, buf ^ 1);
+      sw_next = scale_word(next);
+    }
+    cp_async_commit();
+    const uint32_t r0 = (tile / tiles_x) * kTileRows, c0 = (tile % tiles_x) * kNvTileCols;
+    {
+      const uint32_t w = tid & 127, row = (w & 3) * 32 + (w >> 2), g0 = (tid >> 7) * 4;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float sc = e4m3_value((sw >> (8 * j)) & 0xffu);
+        scale2[row][g0 + j] = make_float2(sc, sc);
+      }
+    }
+    if (tid < kTileRows) {
+      const float g = kRowwise ? p.src_global[r0 + tid] : p.src_global[0];
+      const float sg = random_sign_negative(p.sign_seed, r0 + tid + p.t.sign_offset) ? -g : g;
+      sgs2[tid] = make_float2(sg, sg);
+    }
+    cp_async_wait_all_but_one();
+    __syncthreads();
+
+    // thread: source columns c0 + 2*cp (+1), K = source rows r0 + 32*q ..
+    const uint32_t cp = tid & 63, q = tid >> 6;
+    const uint8_t* src = stage[buf] + q * 32 * kNvBytePitch + cp;
+    f32x2_t P[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float2 qv = e2m1x2_values(src[i * kNvBytePitch]);
+      const float2 sc = scale2[q * 32 + i][cp >> 3];
+      const float2 sg = sgs2[q * 32 + i];
+      // the last product feeds the butterfly's packed adds: it has to be the rounded form
+      P[i] = mul2_rounded(mul2(pack2(qv.x, qv.y), pack2(sc.x, sc.y)), pack2(sg.x, sg.y));
+    }
+    const uint32_t out_row = c0 + 2 * cp;
+    ms_eden_emit_chunk_lanes(P, p.t, gs, p.scale_override, out_row, out_row + 1, (r0 >> 5) + q);
+    __syncthreads();
+    sw = sw_next;
+  }
+  (void)lane;
+  (void)warp;
+}
+
 // ============================================================================
 // decode, scale pack, padding, post-ops, bias gradient
 // ============================================================================
@@ -1296,16 +1388,26 @@ int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a) {
     p.t = make_out(a, out_rows);
     p.r = p.t;
     p.col_sum_partials = nullptr;
+    const bool nv_whole_tiles = p.src_packed && a.rows % kTileRows == 0 && a.cols % kNvTileCols == 0 &&
+                                a.dst_row_len == a.rows && (reinterpret_cast<uintptr_t>(a.src_bytes) & 15u) == 0 &&
+                                (reinterpret_cast<uintptr_t>(a.src_scales) & 3u) == 0;
+    const uint32_t nv_tiles_x = a.cols / kNvTileCols, nv_tiles = nv_tiles_x * (a.rows / kTileRows);
     switch (a.src_kind) {
       case NVFP4_SRC_F32_TRANSPOSED:
         if (bf16) launch_tile<0, __nv_bfloat16, false>(s, p);
         else launch_tile<0, float, false>(s, p);
         break;
       case NVFP4_SRC_NVFP4_TRANSPOSED:
-        launch_tile<2, float, false>(s, p);
+        if (nv_whole_tiles)
+          ms_eden_nvfp4_transpose_kernel<false><<<min(nv_tiles, 148u * 2u), 256, 0, s>>>(p, nv_tiles_x, nv_tiles);
+        else
+          launch_tile<2, float, false>(s, p);
         break;
       case NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED:
-        launch_tile<3, float, false>(s, p);
+        if (nv_whole_tiles)
+          ms_eden_nvfp4_transpose_kernel<true><<<min(nv_tiles, 148u * 2u), 256, 0, s>>>(p, nv_tiles_x, nv_tiles);
+        else
+          launch_tile<3, float, false>(s, p);
         break;
       default:
         return 1;

@@ -479,17 +479,27 @@ def test_config2_c_attn_forward(pkg, oracle, dev):
 
 # ------------------------------------------------------------------------------------------ linear backward
 
-@pytest.mark.parametrize("tokens,in_dim,out_dim", [(64, 64, 64), (256, 128, 192), (200, 64, 100), (1024, 768, 2304)])
-def test_linear_backward_vs_oracle(pkg, oracle, dev, tokens, in_dim, out_dim):
+@pytest.mark.parametrize("native", [False, True])
+@pytest.mark.parametrize("tokens,in_dim,out_dim", [(64, 64, 64), (256, 128, 192), (200, 64, 100), (1024, 768, 2304),
+                                                   (384, 256, 128)])
+def test_linear_backward_vs_oracle(pkg, oracle, dev, tokens, in_dim, out_dim, native):
     """gpt/linear_backward/ms_eden.rs:15-55 composition: every quantized operand bit-exact, the two
-    GEMMs within tolerance of the oracle GEMM over the same operands."""
+    GEMMs within tolerance of the oracle GEMM over the same operands.  native=False is the
+    reference's data flow (f32 dY, logical scale planes); native=True the B200 one (bf16 dY, packed
+    scale planes, decoded amax handed over), which takes the whole-tile kernels where shapes allow."""
     q, bwd = pkg.Nvfp4QuantModule(), pkg.LinearBackwardModule()
     x, w = bf16_normal(201, (tokens, in_dim)), bf16_normal(202, (out_dim, in_dim), 0.02)
-    dy = torch.from_numpy(normal(203, (tokens, out_dim), 1e-3).astype(np.float32))
-    xq = q.quantize_four_six(x.to(dev), rowwise=True, packed=False)
-    wq = q.quantize_four_six(w.to(dev), rowwise=False, packed=False)
+    if native:
+        dy = bf16_normal(203, (tokens, out_dim), 1e-3)
+        e_dev, dy = dy.to(dev), dy.float()
+    else:
+        dy = torch.from_numpy(normal(203, (tokens, out_dim), 1e-3).astype(np.float32))
+        e_dev = dy.to(dev)
+    xq = q.quantize_four_six(x.to(dev), rowwise=True, packed=native, decoded_amax=native)
+    wq = q.quantize_four_six(w.to(dev), rowwise=False, packed=native)
     scratch = pkg.LinearBackwardScratch(tokens, in_dim, out_dim, dev)
-    dx, dw, db = bwd.backward_ms_eden(e=dy.to(dev), weight=wq, input=xq, scratch=scratch, sign_seed=SIGN, scale_seed=SCALE)
+    dx, dw, db = bwd.backward_ms_eden(e=e_dev, weight=wq, input=xq, scratch=scratch, sign_seed=SIGN, scale_seed=SCALE)
+    dx, dw = dx.float(), dw.float()
     assert_no_timeouts(pkg)
 
     xf, wf, ef = x.float().numpy(), w.float().numpy(), dy.numpy()
