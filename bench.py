@@ -111,6 +111,8 @@ def cpu_sample(tokens: int, steps: int, warmup: int):
 
     from oracle import oracle
 
+    # launchers such as torchrun export OMP_NUM_THREADS=1; the CPU leg is meant to use every host core
+    oracle.set_threads(os.cpu_count() or 1)
     rng = np.random.default_rng(0)
     d, h = 768, 3072
     shapes = [(d, 3 * d), (d, d), (d, h), (h, d)]
@@ -181,6 +183,42 @@ def quantize_bandwidth(pkg, torch, dev, peak_gbs):
     return {"workload": "four-six quantize [8192x768] bf16 -> NVFP4, rowwise scale, packed scale layout "
                         "(amax precomputed), 16 rotating buffers", "us": us, "achieved_gbs": gbs,
             "algorithmic_bytes": algo_bytes, "frac_of_hbm_peak": gbs / peak_gbs}
+
+
+def run_small_case(args):
+    """A small case of one kernel family on cuda:0, for profiler captures of single launches (a few
+    hundred MB on the device, two iterations): `quantizers` = one forward quantization of
+    X bf16 [32768 x 768] plus one linear backward with dY bf16 [32768 x 2304] (MS-EDEN pair, W^T and X^T
+    transposers, both gradient GEMMs); `gemm` = the forward and the two backward GEMM shapes of c_attn
+    at 32768 tokens.  Prints no benchmark line."""
+    import torch
+
+    import __graft_entry__ as entry
+
+    pkg = entry.load_package()
+    dev = torch.device("cuda:0")
+    q, g, bwd = pkg.Nvfp4QuantModule(), pkg.Nvfp4GemmModule(), pkg.LinearBackwardModule()
+    tokens, in_dim, out_dim = 32768, 768, 2304
+    x = torch.randn(tokens, in_dim, device=dev).to(torch.bfloat16)
+    w = (torch.randn(out_dim, in_dim, device=dev) * 0.02).to(torch.bfloat16)
+    dy = (torch.randn(tokens, out_dim, device=dev) * 1e-3).to(torch.bfloat16)
+    bias = torch.zeros(out_dim, device=dev)
+    wq = q.quantize_four_six(w, rowwise=False, packed=True)
+    scratch = pkg.LinearBackwardScratch(tokens, in_dim, out_dim, dev)
+    y = torch.empty(tokens, out_dim, dtype=torch.bfloat16, device=dev)
+    dx = torch.empty(tokens, in_dim, dtype=torch.bfloat16, device=dev)
+    dw = torch.empty(out_dim, in_dim, dtype=torch.float32, device=dev)
+    for _ in range(2):
+        xq = q.quantize_four_six(x, rowwise=True, packed=True, decoded_amax=True)
+        if args.small_case == "gemm":
+            g.gemm(xq, wq, bias=bias, epilogue=pkg.EPI_BIAS, out=y)
+        bwd.backward_ms_eden(e=dy, weight=wq, input=xq, scratch=scratch, sign_seed=1, scale_seed=2,
+                             dinput=dx, dweight=dw)
+    torch.cuda.synchronize()
+    status = pkg.read_device_status()
+    print(f"small case '{args.small_case}' done, device status {status}", flush=True)
+    if status != 0:
+        raise SystemExit(1)
 
 
 def run_gpu(args):
@@ -335,9 +373,13 @@ def main():
                     help="tokens per GPU (weak scaling) or in total (strong scaling)")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--small-case", default=None, choices=["quantizers", "gemm"],
+                    help="run a small single-GPU case of one kernel family (for profiler captures) and exit")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.small_case:
+        run_small_case(args)
     else:
         run_gpu(args)
 

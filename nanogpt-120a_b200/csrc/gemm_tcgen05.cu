@@ -12,8 +12,11 @@
 //               tcgen05.mma.kind::mxf4nvf4.block_scale (128 x BLOCK_N x 64 per instruction),
 //               FP32 accumulators in tensor memory,
 //   warp 2      owns the tensor-memory allocation,
-//   warps 4..7  drain accumulators (tcgen05.ld), apply global scales / bias / ReLU^2 /
-//               residual, cast and store.
+//   warps 4..7 and 12..15  two epilogue groups: drain accumulators (tcgen05.ld), apply global
+//               scales / bias / ReLU^2 / residual, cast and store; the groups take alternate
+//               128-byte column sub-tiles of a tile (a warp reaches the tensor-memory lanes of
+//               its index modulo four, so warps w and w + 8 share a lane quadrant),
+//   warps 8..11 move the scale factors shared -> tensor memory (tcgen05.st).
 // Accumulators are double buffered when BLOCK_N = 128 so the epilogue of one tile overlaps
 // the main loop of the next.  Every mbarrier wait is bounded: on expiry the kernel records
 // a status word, drains, frees its tensor memory and returns.
@@ -44,7 +47,7 @@ constexpr int kStoreStageBytes = kBlockM * 128;   // one epilogue sub-tile: 128 
 constexpr int kTmemCols = 512;
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 227 * 1024;
-constexpr int kThreads = 384;
+constexpr int kThreads = 512;
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;  // 2 s
 
 constexpr uint32_t kStatusProducerTimeout = 1u, kStatusMmaTimeout = 2u, kStatusEpilogueTimeout = 4u;
@@ -69,7 +72,8 @@ struct Cfg {
   // the wide one (long-K GEMMs need the shared memory for pipeline stages)
   static constexpr int kStoreBufs = kBlockN == 128 ? 4 : 2;
   static constexpr int kFixedBytes =
-      1024 /*alignment slack*/ + kStoreBufs * kStoreStageBytes + 512 /*barriers*/ + 1024 /*bias of the tile*/;
+      1024 /*alignment slack*/ + kStoreBufs * kStoreStageBytes + 512 /*barriers*/ +
+      2 * kBlockN * 4 /*bias of the tile, one copy per epilogue group*/;
   static_assert(256 + kSfSets * kSfSetCols <= kTmemCols, "tensor memory overflow");
   static_assert(kAccStages * kBlockN <= 256, "accumulators overlap the scale-factor columns");
 };
@@ -172,7 +176,10 @@ __device__ __forceinline__ void bulk_wait_group_read() {
 }
 __device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// one named barrier per epilogue warp group (ids 1 and 2), 128 threads each
+__device__ __forceinline__ void epilogue_barrier(uint32_t group) {
+  asm volatile("bar.sync %0, 128;" ::"r"(group + 1u) : "memory");
+}
 
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
@@ -387,7 +394,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tmem_full + 8 * a, 1);
-      mbar_init(bar_tmem_empty + 8 * a, 4);
+      mbar_init(bar_tmem_empty + 8 * a, 8);
     }
     mbar_init(bar_b_full, 1);
     mbar_init(bar_b_empty, 1);
@@ -592,7 +599,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
-  } else if (warp >= 8) {
+  } else if (warp >= 8 && warp < 12) {
     // ===================== scale-factor warps =====================
     // Four warps (one per 32-lane quadrant of tensor memory) read the 512-byte scale tiles of each
     // k-tile from shared memory -- lane l takes the 16 bytes of rows l, l+32, l+64, l+96 -- and write
@@ -678,66 +685,81 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else if (warp >= 4) {
-    // ===================== epilogue =====================
-    const uint32_t ew = warp - 4;
+    // ===================== epilogue (two groups of four warps) =====================
+    const uint32_t ew = warp & 3u;               // lane quadrant of tensor memory this warp reaches
+    const uint32_t eg = warp >= 12 ? 1u : 0u;    // epilogue group
+    const uint32_t gtid = ew * 32 + lane;        // thread index inside the group, also the tile row
+    const bool elected = gtid == 0;
+    constexpr uint32_t kRing = C::kStoreBufs / 2;  // staging buffers per group
     OutT* out = static_cast<OutT*>(p.out);
     OutT* aux = static_cast<OutT*>(p.aux);
     uint32_t acc = 0, acc_phase = 0, store_buf = 0;
+    const uint32_t my_bias = smem_bias + eg * kBlockN * 4;
+    const float* my_bias_gen = reinterpret_cast<const float*>(smem_gen + (my_bias - smem_base));
+    const uint32_t my_store = smem_store + eg * kRing * kStoreStageBytes;
     const float gb = p.mode == NVFP4_GS_NONE ? 1.0f : __ldg(p.b_global);
     const float ga_scalar = p.mode == NVFP4_GS_TENSOR ? __ldg(p.a_global) : 1.0f;
+    // the row's global scale of a tile is fetched one tile ahead: its load latency would
+    // otherwise sit between the accumulator becoming ready and the first store
+    auto row_scale = [&](uint32_t w) {
+      uint32_t mb, nb, sp;
+      decode(w, mb, nb, sp);
+      const uint32_t r = mb * kBlockM + gtid;
+      return (p.mode == NVFP4_GS_ROWWISE_A && r < p.m) ? __ldg(p.a_global + r) : 0.0f;
+    };
+    float ga_next = w_begin < w_end ? row_scale(w_begin) : 0.0f;
     for (uint32_t w = w_begin; w < w_end; w += w_step) {
       uint32_t m_blk, n_blk, split;
       decode(w, m_blk, n_blk, split);
+      const float ga_row = ga_next;
+      if (w + w_step < w_end) ga_next = row_scale(w + w_step);
       if (!mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, kStatusEpilogueTimeout)) break;
       tcgen05_fence_after();
-      const uint32_t row = m_blk * kBlockM + ew * 32 + lane;
+      const uint32_t row = m_blk * kBlockM + gtid;
       const bool row_ok = row < p.m;
-      const float ga = p.mode == NVFP4_GS_ROWWISE_A ? (row_ok ? __ldg(p.a_global + row) : 0.0f) : ga_scalar;
+      const float ga = p.mode == NVFP4_GS_ROWWISE_A ? ga_row : ga_scalar;
       // reference order: (weight * a_scale) * b_scale, then acc * scale
       const float scale = __fmul_rn(__fmul_rn(p.weight, ga), gb);
       const uint32_t taddr_row = tmem_base + acc * kBlockN + ((ew * 32u) << 16);
       if (p.tma_store) {
-        // Sub-tiles of 128 rows x 128 bytes go through a two-deep shared-memory ring and leave
+        // Sub-tiles of 128 rows x 128 bytes go through the group's shared-memory ring and leave
         // with TMA stores (TMA reduce-add for split-K partial sums); rows / columns outside the
         // matrix are clipped by the tensor map.
         constexpr int kSub = SubTile<OutT>::kCols;
-        const uint32_t tile_row = ew * 32 + lane;
-        const bool elected = threadIdx.x == 128;
         const bool add_bias = p.epilogue != NVFP4_EPI_NONE && (p.k_splits == 1 || split == 0);
         if (add_bias) {
           // the tile's bias slice goes through shared memory once; every row then reads it broadcast
-          for (uint32_t i = threadIdx.x - 128; i < static_cast<uint32_t>(kBlockN); i += 128) {
+          for (uint32_t i = gtid; i < static_cast<uint32_t>(kBlockN); i += 128) {
             const uint32_t col = n_blk * kBlockN + i;
             const float bv = col < p.n ? __ldg(p.bias + col) : 0.0f;
-            asm volatile("st.shared.f32 [%0], %1;" ::"r"(smem_bias + i * 4), "f"(bv) : "memory");
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(my_bias + i * 4), "f"(bv) : "memory");
           }
-          epilogue_barrier();
+          epilogue_barrier(eg);
         }
 #pragma unroll 1
-        for (int c = 0; c < kBlockN; c += kSub) {
+        for (int c = eg * kSub; c < kBlockN; c += 2 * kSub) {
           const uint32_t col0 = n_blk * kBlockN + c;
-          if (col0 >= p.n) break;  // uniform across the epilogue warps
+          if (col0 >= p.n) break;  // uniform across the group
           float v[kSub];
-#pragma unroll
           {
             uint32_t r[kSub / 32][32];
 #pragma unroll
             for (int h = 0; h < kSub / 32; ++h) tcgen05_ld_32x32b_x32(taddr_row + c + 32 * h, r[h]);
             tcgen05_wait_ld();
+            if (add_bias) {
+              // acc * scale + bias in one rounding (the reference rounds the product first; the
+              // difference is below the f32 ulp and far inside the GEMM tolerance)
 #pragma unroll
-            for (int i = 0; i < kSub; ++i) v[i] = __fmul_rn(__uint_as_float(r[i / 32][i % 32]), scale);
-          }
-          if (add_bias) {
+              for (int i = 0; i < kSub; i += 4) {
+                const float4 b = *reinterpret_cast<const float4*>(my_bias_gen + c + i);
+                v[i] = __fmaf_rn(__uint_as_float(r[i / 32][i % 32]), scale, b.x);
+                v[i + 1] = __fmaf_rn(__uint_as_float(r[(i + 1) / 32][(i + 1) % 32]), scale, b.y);
+                v[i + 2] = __fmaf_rn(__uint_as_float(r[(i + 2) / 32][(i + 2) % 32]), scale, b.z);
+                v[i + 3] = __fmaf_rn(__uint_as_float(r[(i + 3) / 32][(i + 3) % 32]), scale, b.w);
+              }
+            } else {
 #pragma unroll
-            for (int i = 0; i < kSub; i += 4) {
-              float b0, b1, b2, b3;
-              asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                           : "=f"(b0), "=f"(b1), "=f"(b2), "=f"(b3)
-                           : "r"(smem_bias + (c + i) * 4));
-              v[i] = __fadd_rn(v[i], b0);
-              v[i + 1] = __fadd_rn(v[i + 1], b1);
-              v[i + 2] = __fadd_rn(v[i + 2], b2);
-              v[i + 3] = __fadd_rn(v[i + 3], b3);
+              for (int i = 0; i < kSub; ++i) v[i] = __fmul_rn(__uint_as_float(r[i / 32][i % 32]), scale);
             }
           }
           const int passes = (p.epilogue == NVFP4_EPI_RELU2 && p.aux) ? 2 : 1;
@@ -750,12 +772,17 @@ __global__ void __launch_bounds__(kThreads, 1)
                 v[i] = __fmul_rn(t, t);
               }
             }
-            const uint32_t buf = smem_store + store_buf * kStoreStageBytes;
-            SubTile<OutT>::stage(buf + tile_row * 128, tile_row, v);
+            const uint32_t buf = my_store + store_buf * kStoreStageBytes;
+            if (kRing == 1) {
+              // single staging buffer: the previous store must have read it before it is rewritten
+              if (elected) bulk_wait_group_read<0>();
+              epilogue_barrier(eg);
+            }
+            SubTile<OutT>::stage(buf + gtid * 128, gtid, v);
             fence_proxy_async_smem();
-            // the buffer written next was last used kStoreBufs - 1 stores ago: allow that many in flight
-            if (elected) bulk_wait_group_read<C::kStoreBufs - 2>();
-            epilogue_barrier();
+            // deeper rings: the buffer written next was last used kRing - 1 stores ago
+            if (kRing > 1 && elected) bulk_wait_group_read<(kRing > 1 ? kRing - 2 : 0)>();
+            epilogue_barrier(eg);
             if (elected) {
               const CUtensorMap* map = is_pre ? &tmap_aux : &tmap_out;
               if (p.k_splits > 1)
@@ -764,12 +791,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                 tma_store_2d(map, buf, static_cast<int32_t>(col0), static_cast<int32_t>(m_blk * kBlockM));
               bulk_commit_group();
             }
-            store_buf = (store_buf + 1) % C::kStoreBufs;
+            store_buf = (store_buf + 1) % kRing;
           }
         }
       } else {
 #pragma unroll 1
-      for (int c = 0; c < kBlockN; c += 32) {
+      for (int c = eg * 32; c < kBlockN; c += 64) {
         uint32_t r[32];
         tcgen05_ld_32x32b_x32(taddr_row + c, r);
         tcgen05_wait_ld();
@@ -820,7 +847,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         acc_phase ^= 1u;
       }
     }
-    if (p.tma_store && threadIdx.x == 128) bulk_wait_group0();  // stores complete before the CTA exits
+    if (p.tma_store && elected) bulk_wait_group0();  // stores complete before the CTA exits
   }
 
   // ===================== teardown =====================
@@ -1046,7 +1073,13 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   // buffers the accumulator so the (output-bound) epilogue hides behind the next main loop.
   // Short-K GEMMs are epilogue bound, long-K GEMMs are main-loop bound.
   const uint32_t tiles256 = p.num_m_blocks * ((a.n + 255) / 256);
-  const bool wide = (a.n % 256 == 0 || a.n > 1024) && p.num_k_tiles >= 8 && tiles256 >= static_cast<uint32_t>(sms);
+  const bool wide_long_k = (a.n % 256 == 0 || a.n > 1024) && p.num_k_tiles >= 8 && tiles256 >= static_cast<uint32_t>(sms);
+  // Short K with many row blocks: a block-scaled FP4 tcgen05.mma occupies the tensor pipe for about
+  // as long at N = 128 as at N = 256 (measured ~140 cycles per instruction either way), so the wide
+  // tile with its whole B panel resident does twice the work per instruction; the next tile's
+  // A stages fill while the single-buffered accumulator drains.
+  const bool wide_short_k = a.n % 256 == 0 && p.num_k_tiles <= 3 && tiles256 >= 4u * static_cast<uint32_t>(sms);
+  const bool wide = wide_long_k || wide_short_k;
   const uint32_t block_n = wide ? 256 : 128;
   p.num_n_blocks = (a.n + block_n - 1) / block_n;
   const uint32_t tiles = p.num_m_blocks * p.num_n_blocks;
@@ -1094,10 +1127,11 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   const uint32_t grid = work < static_cast<uint32_t>(sms) ? work : static_cast<uint32_t>(sms);
   // Short K and many row blocks: keep the B panel resident and stream only A (halves the
   // operand traffic per tile; these shapes are otherwise bound by L2 -> SM bandwidth).
-  const bool want_resident = block_n == 128 && p.k_splits == 1 && p.num_k_tiles <= 4 && tiles >= 4 * grid;
+  const bool want_resident =
+      p.k_splits == 1 && p.num_k_tiles <= (block_n == 128 ? 4u : 3u) && tiles >= 4 * grid;
   if (block_n == 256) {
-    return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<256, float>(s, ma, mb, mo, mx, p, grid, false)
-                                          : launch_variant<256, __nv_bfloat16>(s, ma, mb, mo, mx, p, grid, false);
+    return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<256, float>(s, ma, mb, mo, mx, p, grid, want_resident)
+                                          : launch_variant<256, __nv_bfloat16>(s, ma, mb, mo, mx, p, grid, want_resident);
   }
   return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<128, float>(s, ma, mb, mo, mx, p, grid, want_resident)
                                         : launch_variant<128, __nv_bfloat16>(s, ma, mb, mo, mx, p, grid, want_resident);
