@@ -1072,22 +1072,27 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   // Tile width: 256 columns halves the shared-memory traffic per flop; 128 columns double
   // buffers the accumulator so the (output-bound) epilogue hides behind the next main loop.
   // Short-K GEMMs are epilogue bound, long-K GEMMs are main-loop bound.
+  // Tile width.  A block-scaled FP4 tcgen05.mma occupies the tensor pipe for about as long at
+  // N = 128 as at N = 256 (measured ~140 cycles per instruction either way), so the wide tile does
+  // twice the work per instruction and is preferred whenever the shape can still fill the SMs:
+  //  * long K: enough wide tiles, or (f32 output, linear epilogue) enough tiles x K splits;
+  //  * short K with many row blocks: wide tile with its whole B panel resident -- the next tile's
+  //    A stages fill while the single-buffered accumulator drains.
+  // The narrow tile double buffers its accumulator and remains for everything else.
   const uint32_t tiles256 = p.num_m_blocks * ((a.n + 255) / 256);
-  const bool wide_long_k = (a.n % 256 == 0 || a.n > 1024) && p.num_k_tiles >= 8 && tiles256 >= static_cast<uint32_t>(sms);
-  // Short K with many row blocks: a block-scaled FP4 tcgen05.mma occupies the tensor pipe for about
-  // as long at N = 128 as at N = 256 (measured ~140 cycles per instruction either way), so the wide
-  // tile with its whole B panel resident does twice the work per instruction; the next tile's
-  // A stages fill while the single-buffered accumulator drains.
+  const bool can_split = a.out_dtype == NVFP4_DTYPE_F32 &&
+                         (a.epilogue == NVFP4_EPI_NONE || a.epilogue == NVFP4_EPI_BIAS) && p.num_k_tiles >= 16;
+  const bool wide_shape = a.n % 256 == 0 || a.n > 1024;
+  const bool wide_long_k = wide_shape && p.num_k_tiles >= 8 && (tiles256 >= static_cast<uint32_t>(sms) || can_split);
   const bool wide_short_k = a.n % 256 == 0 && p.num_k_tiles <= 3 && tiles256 >= 4u * static_cast<uint32_t>(sms);
   const bool wide = wide_long_k || wide_short_k;
   const uint32_t block_n = wide ? 256 : 128;
   p.num_n_blocks = (a.n + block_n - 1) / block_n;
   const uint32_t tiles = p.num_m_blocks * p.num_n_blocks;
 
-  // split-K for long, narrow GEMMs (dW = dY^T.X): f32 output, linear epilogue only
+  // split-K for long GEMMs with few tiles (dW = dY^T.X): f32 output, linear epilogue only
   p.k_splits = 1;
-  if (a.out_dtype == NVFP4_DTYPE_F32 && (a.epilogue == NVFP4_EPI_NONE || a.epilogue == NVFP4_EPI_BIAS) &&
-      tiles * 2 <= static_cast<uint32_t>(sms) && p.num_k_tiles >= 16) {
+  if (can_split && tiles * 2 <= static_cast<uint32_t>(sms)) {
     uint32_t splits = static_cast<uint32_t>(sms) / tiles;
     const uint32_t max_splits = p.num_k_tiles / 8;
     if (splits > max_splits) splits = max_splits;
