@@ -48,6 +48,13 @@ def measured_peaks():
 # clocks
 # --------------------------------------------------------------------------------------------
 
+# dram__bytes_read.sum + dram__bytes_write.sum over the 147 GEMM launches of one step of the default
+# workload (GPT-2-small projection set, 65536 tokens, 1 GPU): 17.15 GB read + 23.36 GB written.
+GEMM_DRAM_BYTES_PER_STEP_65536 = 17.154715e9 + 23.360743e9
+GEMM_TRAFFIC_SOURCE = ("ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum over one step's 147 GEMM launches "
+                       "(profiles/gemm_tcgen05_ncu.md); algorithmic bytes of the same launches: 37.5 GB")
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -71,9 +78,10 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
-    def stop(self):
+    def stop(self, t_begin: float = 0.0, t_end: float = float("inf")):
+        """Summary of the samples that arrived inside [t_begin, t_end] (host clock)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -83,7 +91,9 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for stamp, line in self.lines:
+            if stamp < t_begin or stamp > t_end:
+                continue
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -268,51 +278,80 @@ def run_gpu(args):
         return float(t.item())
 
     # ---- device-resident timing -----------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()  # nvidia-smi needs a moment to come up: started ahead of the warm-up steps
     for _ in range(max(args.warmup, 3)):
         ps.step()
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     launches_before = pkg.launch_count()
     gemm_per_step = 3 * (4 * shape.n_layer + 1)
     pkg.gemm_timing_begin(gemm_per_step * args.steps)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t_begin = time.time()
     start.record()
     for _ in range(args.steps):
         ps.step()
     stop.record()
     barrier()
+    t_end = time.time()
     ms_total = max_over_ranks(start.elapsed_time(stop))
     n_gemm, gemm_ms, gemm_flops, _, _ = pkg.gemm_timing_end(0)
     launches = pkg.launch_count() - launches_before
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     status = pkg.read_device_status()
     ms_step = ms_total / args.steps
     value = flops_step_total / (ms_step * 1e-3) / 1e12
 
     # ---- end to end: host buffers, H2D + step + D2H every step ------------------------------
+    # Every step's activations and output gradients start in pinned host memory.  They are copied
+    # into one of two device input sets on a copy stream while the previous step computes on the
+    # other set (what a prefetching loader does); each step ends with a device -> host read of the
+    # gradient digest.  All copies of all timed steps lie inside the timed region.
     host_in = {}
     for name, group in (("x", ps.x), ("dy", ps.dy)):
         for w, t in group.items():
-            host_in[(name, w)] = (torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t), t)
-    h2d_bytes = sum(h.numel() * h.element_size() for h, _ in host_in.values())
+            host_in[(name, w)] = torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
+    h2d_bytes = sum(h.numel() * h.element_size() for h in host_in.values())
     digest_host = torch.empty(len(ps.buckets), dtype=torch.float32, pin_memory=True)
     d2h_bytes = digest_host.numel() * 4
+    input_sets = [(ps.x, ps.dy),
+                  ({w: torch.empty_like(t) for w, t in ps.x.items()}, {w: torch.empty_like(t) for w, t in ps.dy.items()})]
+    copy_stream = torch.cuda.Stream()
+    main_stream = torch.cuda.current_stream()
 
-    def e2e_step():
-        for h, d in host_in.values():
-            d.copy_(h, non_blocking=True)
-        ps.step()
-        digest_host.copy_(ps.result_digest(), non_blocking=True)
+    def e2e_run(steps: int):
+        ready = [torch.cuda.Event(), torch.cuda.Event()]
+        done = [torch.cuda.Event(), torch.cuda.Event()]
 
-    e2e_step()
+        def stage(step_index: int):
+            which = step_index % 2
+            with torch.cuda.stream(copy_stream):
+                if step_index >= 2:
+                    copy_stream.wait_event(done[which])  # the step that last read this set has finished
+                xs, dys = input_sets[which]
+                for (name, w), h in host_in.items():
+                    (xs if name == "x" else dys)[w].copy_(h, non_blocking=True)
+                ready[which].record(copy_stream)
+
+        stage(0)
+        for i in range(steps):
+            if i + 1 < steps:
+                stage(i + 1)
+            which = i % 2
+            main_stream.wait_event(ready[which])
+            ps.x, ps.dy = input_sets[which]
+            ps.step()
+            digest_host.copy_(ps.result_digest(), non_blocking=True)
+            done[which].record(main_stream)
+        ps.x, ps.dy = input_sets[0]
+
+    e2e_run(2)
     barrier()
-    e2e_steps = max(1, min(args.steps, 3))
+    e2e_steps = max(2, min(args.steps, 4))
     start.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    e2e_run(e2e_steps)
     stop.record()
     barrier()
     e2e_ms = max_over_ranks(start.elapsed_time(stop)) / e2e_steps
@@ -330,6 +369,11 @@ def run_gpu(args):
 
     if rank == 0:
         achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+        # DRAM bytes per GEMM launch (average over the launches of a step): profiler capture of one full
+        # step of this workload at 65536 tokens per GPU; operand and output bytes grow with the tokens
+        gemm_traffic = None
+        if args.model == "gpt2-small" and n_gemm > 0:
+            gemm_traffic = GEMM_DRAM_BYTES_PER_STEP_65536 * (tokens_rank / 65536.0) / gemm_per_step
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
@@ -348,7 +392,8 @@ def run_gpu(args):
                                         f"bf16 burst would be {4 * peaks['bf16_tflops']:.0f})",
                          "frac_of_4x_measured_bf16_burst": achieved / (4 * peaks["bf16_tflops"]),
                          "launches": n_gemm, "avg_launch_ms": gemm_ms / max(n_gemm, 1),
-                         "gemm_share_of_step": gemm_ms / ms_total if ms_total > 0 else None, "traffic": None,
+                         "gemm_share_of_step": gemm_ms / ms_total if ms_total > 0 else None,
+                         "traffic": gemm_traffic, "traffic_source": GEMM_TRAFFIC_SOURCE if gemm_traffic else None,
                          "peaks_file": peak_kind},
             "quantize": quant,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d_bytes,
@@ -365,7 +410,7 @@ def run_gpu(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="gpt2-small", choices=["gpt2-small", "gpt2-medium"])
