@@ -149,6 +149,21 @@ int nvfp4_quantize_four_six_rowwise_fused(void* stream, const void* x, int dtype
                                           uint8_t* out_fp4, uint8_t* out_scales, int scale_layout,
                                           float* out_global_scale, float* out_row_amax, float* out_decoded_amax);
 
+/* gpt/optimizer/launcher/update.rs:11-58  OptimizerModule::materialize_schedule_free
+ * (kernels gpt/optimizer/schedule_free/{value,amax,four_six}.rs): the weight a schedule-free optimizer
+ * evaluates with, y = z + beta * (x - z) of the two f32 masters, quantized four-six with a tensor scale
+ * without ever being written in f32.  amax[1] receives max|y|; chunk_amax[ceil(len/1024)] is optional.
+ * len % 16 == 0; scales in the logical layout. */
+int nvfp4_materialize_schedule_free(void* stream, const float* z_master, const float* x_master, float* chunk_amax,
+                                    float* amax, uint8_t* bytes, uint8_t* scales, float* global_scale, float beta,
+                                    uint32_t len);
+/* Same for a [rows x cols] weight with the scale bytes written in either layout (NVFP4_SCALES_PACKED is what
+ * nvfp4_gemm reads; no reference counterpart for that layout choice). */
+int nvfp4_materialize_schedule_free_matrix(void* stream, const float* z_master, const float* x_master,
+                                           float* chunk_amax, float* amax, uint8_t* bytes, uint8_t* scales,
+                                           int scale_layout, float* global_scale, float beta, uint32_t rows,
+                                           uint32_t cols);
+
 /* MS-EDEN quantizer (random-sign Hadamard-32 rotation, RTN nibbles, EDEN-corrected block
  * scale rounded stochastically with a counter RNG) ---------------------------------------- */
 

@@ -97,6 +97,8 @@ _SIGNATURES = {
     "nvfp4_fp32_transpose_to_nvfp4_four_six_padded": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _U],
     "nvfp4_quantize_four_six": [_P, _P, c_int, _P, c_int, _U, _U, _P, _P, c_int, _P],
     "nvfp4_quantize_four_six_rowwise_fused": [_P, _P, c_int, _U, _U, _P, _P, c_int, _P, _P, _P],
+    "nvfp4_materialize_schedule_free": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _U],
+    "nvfp4_materialize_schedule_free_matrix": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, _F, _U, _U],
     "nvfp4_ms_eden_quantize": [_P, POINTER(MsEdenArgs)],
     "nvfp4_fp32_to_nvfp4_ms_eden": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _F, _F, _U, _U],
     "nvfp4_fp32_to_nvfp4_ms_eden_device_scale": [_P, _P, _P, _P, _P, _P, _P, _U, _U, _U, _F, _U, _U],
@@ -491,6 +493,32 @@ class Nvfp4QuantModule:
                                                                                   scale_seed):
         return self._named_transpose("nvfp4_rowwise_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale",
                                      src, dst_row_len, sign_seed, scale_seed)
+
+
+class OptimizerModule:
+    """The part of gpt/optimizer/launcher that feeds the projection path: weight materialisation."""
+
+    def materialize_schedule_free(self, z_master: torch.Tensor, x_master: torch.Tensor, beta: float,
+                                  packed: bool = False, out: Optional[Nvfp4Tensor] = None):
+        """gpt/optimizer/launcher/update.rs:11-58.  z / x: f32 masters of one [rows, cols] weight.
+        Returns (Nvfp4Tensor with a tensor scale, amax[1])."""
+        _require_cuda()
+        assert z_master.dtype == torch.float32 and x_master.dtype == torch.float32 and z_master.shape == x_master.shape
+        rows, cols = z_master.shape
+        dev, n = z_master.device, rows * cols
+        if out is None:
+            nsc = scale_packed_len(rows, cols) if packed else n // 16
+            out = Nvfp4Tensor(_empty_u8(n // 2, dev), _empty_u8(nsc, dev),
+                              torch.empty(1, dtype=torch.float32, device=dev), rows, cols, packed=packed, rowwise=False)
+        amax = torch.empty(1, dtype=torch.float32, device=dev)
+        chunk = torch.empty(max(1, tensor_amax_chunks(n)), dtype=torch.float32, device=dev)
+        if packed:
+            _call("nvfp4_materialize_schedule_free_matrix", _stream(), _ptr(z_master), _ptr(x_master), _ptr(chunk),
+                  _ptr(amax), _ptr(out.bytes), _ptr(out.scales), SCALES_PACKED, _ptr(out.global_scales), beta, rows, cols)
+        else:
+            _call("nvfp4_materialize_schedule_free", _stream(), _ptr(z_master), _ptr(x_master), _ptr(chunk), _ptr(amax),
+                  _ptr(out.bytes), _ptr(out.scales), _ptr(out.global_scales), beta, n)
+        return out, amax
 
 
 class Nvfp4DecodeModule:

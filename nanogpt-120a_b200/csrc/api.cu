@@ -134,6 +134,33 @@ int nvfp4_quantize_four_six_rowwise_fused(void* stream, const void* x, int dtype
                            out_decoded_amax);
 }
 
+// ---- schedule-free weight materialisation ---------------------------------------------------
+int nvfp4_materialize_schedule_free(void* stream, const float* z_master, const float* x_master, float* chunk_amax,
+                                    float* amax, uint8_t* bytes, uint8_t* scales, float* global_scale, float beta,
+                                    uint32_t len) {
+  if (len % 16 != 0) return invalid("materialize_schedule_free: len must be a multiple of 16");
+  if (!amax || !bytes || !scales || !global_scale || (len && (!z_master || !x_master)))
+    return invalid("materialize_schedule_free: null pointer");
+  if ((reinterpret_cast<uintptr_t>(z_master) | reinterpret_cast<uintptr_t>(x_master)) & 15u)
+    return invalid("materialize_schedule_free: the masters must be 16-byte aligned");
+  return launch_schedule_free_materialize(S(stream), z_master, x_master, beta, chunk_amax, amax, bytes, scales, 0,
+                                          global_scale, 1, len);
+}
+int nvfp4_materialize_schedule_free_matrix(void* stream, const float* z_master, const float* x_master,
+                                           float* chunk_amax, float* amax, uint8_t* bytes, uint8_t* scales,
+                                           int scale_layout, float* global_scale, float beta, uint32_t rows,
+                                           uint32_t cols) {
+  if (cols % 16 != 0) return invalid("materialize_schedule_free_matrix: cols must be a multiple of 16");
+  if (scale_layout == NVFP4_SCALES_PACKED && cols % 64 != 0)
+    return invalid("materialize_schedule_free_matrix: the packed scale layout needs cols % 64 == 0");
+  if (!amax || !bytes || !scales || !global_scale || (rows && cols && (!z_master || !x_master)))
+    return invalid("materialize_schedule_free_matrix: null pointer");
+  if ((reinterpret_cast<uintptr_t>(z_master) | reinterpret_cast<uintptr_t>(x_master)) & 15u)
+    return invalid("materialize_schedule_free_matrix: the masters must be 16-byte aligned");
+  return launch_schedule_free_materialize(S(stream), z_master, x_master, beta, chunk_amax, amax, bytes, scales,
+                                          scale_layout == NVFP4_SCALES_PACKED, global_scale, rows, cols);
+}
+
 // ---- MS-EDEN ----------------------------------------------------------------------------
 static int validate_ms_eden(const nvfp4_ms_eden_args* a);
 

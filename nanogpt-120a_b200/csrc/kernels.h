@@ -25,6 +25,10 @@ int launch_four_six_padded(cudaStream_t s, const float* x, const float* amax, ui
                            float* out_gs, uint32_t rows, uint32_t cols, uint32_t padded_rows, uint32_t padded_cols,
                            int transposed);
 int launch_packed_scale_pad(cudaStream_t s, uint8_t* packed, uint32_t rows, uint32_t k_dim);
+// y = z + beta * (x - z) -> tensor amax -> four-six (tensor scale); chunk_amax optional
+int launch_schedule_free_materialize(cudaStream_t s, const float* z, const float* x, float beta, float* chunk_amax,
+                                     float* amax, uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs,
+                                     uint32_t rows, uint32_t cols);
 int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a);
 // Pair quantization; when col_sum_partials != nullptr (and ms_eden_pair_is_tiled) it also writes the
 // per-row-tile column sums [ms_eden_pair_row_tiles(rows)][cols] for launch_col_sum_reduce.

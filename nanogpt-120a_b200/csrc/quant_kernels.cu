@@ -341,6 +341,72 @@ __global__ void __launch_bounds__(256) four_six_rowwise_fused_kernel(const T* __
   }
 }
 
+// Schedule-free weight materialisation (gpt/optimizer/schedule_free/{value,amax,four_six}.rs):
+// the weight quantized every step is y = z + beta * (x - z) of the two f32 masters; it is never
+// written out in f32.  Kernel 1: tensor amax of y (1024-value chunks per warp, chunk amax kept for
+// callers that want it); kernel 2: four-six of y with the tensor scale, one thread per 16-group.
+__device__ __forceinline__ float schedule_free_value(float z, float x, float beta) { return z + beta * (x - z); }
+
+__global__ void __launch_bounds__(256) schedule_free_amax_kernel(const float* __restrict__ z,
+                                                                  const float* __restrict__ x,
+                                                                  float* __restrict__ chunk_amax,
+                                                                  float* __restrict__ out, float beta, uint64_t n) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint64_t warps = static_cast<uint64_t>(gridDim.x) * 8;
+  const uint64_t chunks = (n + 1023) / 1024;
+  float running = 0.0f;
+  for (uint64_t chunk = static_cast<uint64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); chunk < chunks; chunk += warps) {
+    const uint64_t base = chunk * 1024;
+    float m = 0.0f;
+    if (base + 1024 <= n && ((reinterpret_cast<uintptr_t>(z + base) | reinterpret_cast<uintptr_t>(x + base)) & 15u) == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(z + base) + i * 32 + lane);
+        const float4 b = __ldg(reinterpret_cast<const float4*>(x + base) + i * 32 + lane);
+        m = max3_abs(m, schedule_free_value(a.x, b.x, beta), schedule_free_value(a.y, b.y, beta));
+        m = max3_abs(m, schedule_free_value(a.z, b.z, beta), schedule_free_value(a.w, b.w, beta));
+      }
+    } else {
+      const uint32_t count = static_cast<uint32_t>(min(static_cast<uint64_t>(1024), n - base));
+      for (uint32_t i = lane; i < count; i += 32)
+        m = max_f32(m, fabsf(schedule_free_value(__ldg(z + base + i), __ldg(x + base + i), beta)));
+    }
+    m = warp_max(m);
+    if (lane == 0 && chunk_amax) chunk_amax[chunk] = m;
+    running = max_f32(running, m);
+  }
+  cta_atomic_max(running, out);
+}
+
+template <bool kPacked>
+__global__ void __launch_bounds__(256) schedule_free_four_six_kernel(const float* __restrict__ z,
+                                                                      const float* __restrict__ x,
+                                                                      const float* __restrict__ amax,
+                                                                      uint8_t* __restrict__ out_fp4,
+                                                                      uint8_t* __restrict__ out_scales,
+                                                                      float* __restrict__ out_gs, float beta,
+                                                                      uint64_t group_count, uint32_t groups_per_row) {
+  const uint64_t g = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (g >= group_count) return;
+  const float gs = four_six_global_scale(amax[0]);
+  float zv[16], xv[16], v[16];
+  Load16<float>::run(z + g * 16, zv);
+  Load16<float>::run(x + g * 16, xv);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = schedule_free_value(zv[i], xv[i], beta);
+  uint2 packed;
+  const uint32_t b = four_six_group(v, gs, packed);
+  *reinterpret_cast<uint2*>(out_fp4 + g * 8) = packed;
+  if (kPacked) {
+    const uint32_t row = static_cast<uint32_t>(g / groups_per_row);
+    const uint32_t kg = static_cast<uint32_t>(g - static_cast<uint64_t>(row) * groups_per_row);
+    out_scales[packed_scale_offset(row, kg, groups_per_row >> 2)] = static_cast<uint8_t>(b);
+  } else {
+    out_scales[g] = static_cast<uint8_t>(b);
+  }
+  if (g == 0) out_gs[0] = gs;
+}
+
 // Padded / transposed-padded variants: generic gather, zero outside the source extent.
 // utils/nvfp4/quant/kernels/four_six.rs:110-142,173-211,346-395.
 template <bool kTransposed>
@@ -1307,6 +1373,30 @@ int launch_four_six_rowwise_fused(cudaStream_t s, const void* x, int dtype, uint
     else NVFP4_LAUNCH_FUSED(__nv_bfloat16, false);
   }
 #undef NVFP4_LAUNCH_FUSED
+  count_launch();
+  int rc = static_cast<int>(cudaGetLastError());
+  if (rc) return rc;
+  if (packed) return launch_packed_scale_pad(s, out_scales, rows, cols);
+  return 0;
+}
+
+int launch_schedule_free_materialize(cudaStream_t s, const float* z, const float* x, float beta, float* chunk_amax,
+                                     float* amax, uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs,
+                                     uint32_t rows, uint32_t cols) {
+  const uint64_t n = static_cast<uint64_t>(rows) * cols;
+  cudaError_t err = cudaMemsetAsync(amax, 0, sizeof(float), s);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  if (n == 0) return 0;
+  schedule_free_amax_kernel<<<blocks_for((n + 1023) / 1024, 8, 148 * 8), 256, 0, s>>>(z, x, chunk_amax, amax, beta, n);
+  count_launch();
+  const uint64_t groups = n / 16;
+  const uint32_t gpr = cols / 16;
+  if (packed)
+    schedule_free_four_six_kernel<true><<<blocks_for(groups, 256), 256, 0, s>>>(z, x, amax, out_fp4, out_scales, out_gs,
+                                                                               beta, groups, gpr);
+  else
+    schedule_free_four_six_kernel<false><<<blocks_for(groups, 256), 256, 0, s>>>(z, x, amax, out_fp4, out_scales, out_gs,
+                                                                                beta, groups, gpr);
   count_launch();
   int rc = static_cast<int>(cudaGetLastError());
   if (rc) return rc;

@@ -375,6 +375,16 @@ void oracle_row_amax_f32(const float* x, float* out, uint32_t rows, uint32_t row
 }
 
 // quant/kernels/row_amax.rs:67-101: 1024-value chunk amax, then the max of the chunks.
+// crates/cuda-kernels/src/gpt/optimizer/schedule_free/value.rs:4-9: the weight a schedule-free
+// optimizer evaluates with, y = z + beta * (x - z), every operation rounded to f32 on its own.
+void oracle_schedule_free_value(const float* z_master, const float* x_master, float beta, uint64_t n, float* out) {
+  for (uint64_t i = 0; i < n; ++i) {
+    const float d = x_master[i] - z_master[i];
+    const float m = beta * d;
+    out[i] = z_master[i] + m;
+  }
+}
+
 void oracle_tensor_amax_f32(const float* x, float* chunk_amax, float* out, uint64_t n) {
   uint64_t chunks = (n + 1023) / 1024;
   float total = 0.0f;

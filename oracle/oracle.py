@@ -122,6 +122,14 @@ def row_amax(x):
     return out
 
 
+def schedule_free_value(z_master, x_master, beta: float):
+    """gpt/optimizer/schedule_free/value.rs:4-9: y = z + beta * (x - z) in f32."""
+    z, x = _f32(z_master).reshape(-1), _f32(x_master).reshape(-1)
+    out = np.empty(z.size, np.float32)
+    lib().oracle_schedule_free_value(_p(z), _p(x), c_float(beta), c_uint64(z.size), _p(out))
+    return out
+
+
 def tensor_amax(x):
     """Returns (chunk_amax[ceil(n/1024)], amax[1])."""
     x = _f32(x).reshape(-1)

@@ -66,6 +66,27 @@ def test_four_six_bit_exact(pkg, oracle, dev, dtype, rowwise, shape, packed):
     _check_four_six(pkg, oracle, dev, x, rowwise, packed)
 
 
+@pytest.mark.parametrize("shape,packed", [((1, 16), False), ((3, 48), False), ((37, 1040), False), ((200, 192), True),
+                                          ((768, 768), True)])
+@pytest.mark.parametrize("beta", [0.0, 0.9, 1.0])
+def test_materialize_schedule_free(pkg, oracle, dev, shape, packed, beta):
+    """gpt/optimizer/launcher/update.rs:11-58: amax and four-six of y = z + beta (x - z), bit-exact."""
+    opt = pkg.OptimizerModule()
+    z = torch.from_numpy(normal(61, shape, 0.02).astype(np.float32))
+    x = z + torch.from_numpy(normal(62, shape, 0.003).astype(np.float32))
+    x[0, 3] = 1.5  # an outlier decides the tensor scale
+    t, amax = opt.materialize_schedule_free(z.to(dev), x.to(dev), beta, packed=packed)
+    y = oracle.schedule_free_value(z.numpy(), x.numpy(), beta).reshape(shape)
+    if beta == 0.0:
+        assert np.array_equal(y, z.numpy())
+    want_amax = oracle.tensor_amax(y)[1]
+    assert cpu(amax).tobytes() == want_amax.tobytes()
+    ob, os_, og = oracle.four_six(y, want_amax, False)
+    assert np.array_equal(cpu(t.bytes), ob)
+    assert np.array_equal(cpu(t.scales), oracle.scale_pack(os_, *shape) if packed else os_)
+    assert np.array_equal(cpu(t.global_scales), og)
+
+
 def test_four_six_rowwise_long_rows(pkg, oracle, dev):
     """Rows longer than one thread block covers take the two-kernel path; a row that exactly fills
     a block (4096) and ragged row counts take the fused one."""

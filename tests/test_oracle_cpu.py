@@ -328,3 +328,15 @@ def test_tensor_amax_chunks(oracle):
     chunks, amax = oracle.tensor_amax(x)
     assert chunks.size == 5 and amax[0] == np.abs(x).max()
     assert chunks[4] == np.abs(x[4096:]).max()
+
+
+def test_schedule_free_value(oracle):
+    """gpt/optimizer/schedule_free/value.rs:4-9: each operation rounds to f32 on its own."""
+    rng = np.random.default_rng(4)
+    z = rng.normal(0, 0.02, 4096).astype(np.float32)
+    x = (z + rng.normal(0, 0.003, 4096)).astype(np.float32)
+    for beta in (0.0, 0.5, 0.9, 1.0):
+        b = np.float32(beta)
+        want = (z + (b * (x - z)).astype(np.float32)).astype(np.float32)
+        assert np.array_equal(oracle.schedule_free_value(z, x, beta), want)
+    assert np.array_equal(oracle.schedule_free_value(z, x, 0.0), z)
