@@ -149,6 +149,16 @@ int nvfp4_quantize_four_six_rowwise_fused(void* stream, const void* x, int dtype
                                           uint8_t* out_fp4, uint8_t* out_scales, int scale_layout,
                                           float* out_global_scale, float* out_row_amax, float* out_decoded_amax);
 
+/* gpt/mlp/launcher.rs:66-76  MlpModule::relu2_backward / relu2_backward_f16 (kernels gpt/mlp/kernels.rs:72-104):
+ * d_pre = (d_out * 2) * max(pre, 0) between the two MLP linears of the backward pass. */
+int nvfp4_relu2_backward(void* stream, const float* pre_activation, const float* d_out, float* d_pre_activation,
+                         uint32_t len);
+int nvfp4_relu2_backward_f16(void* stream, const uint16_t* pre_activation /* IEEE f16 bits */, const float* d_out,
+                             float* d_pre_activation, uint32_t len);
+/* all three tensors bf16 (the B200 data flow; no reference counterpart): f32 arithmetic, one rounding to bf16 */
+int nvfp4_relu2_backward_bf16(void* stream, const void* pre_activation, const void* d_out, void* d_pre_activation,
+                              uint64_t len);
+
 /* gpt/optimizer/launcher/update.rs:11-58  OptimizerModule::materialize_schedule_free
  * (kernels gpt/optimizer/schedule_free/{value,amax,four_six}.rs): the weight a schedule-free optimizer
  * evaluates with, y = z + beta * (x - z) of the two f32 masters, quantized four-six with a tensor scale

@@ -97,6 +97,9 @@ _SIGNATURES = {
     "nvfp4_fp32_transpose_to_nvfp4_four_six_padded": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _U],
     "nvfp4_quantize_four_six": [_P, _P, c_int, _P, c_int, _U, _U, _P, _P, c_int, _P],
     "nvfp4_quantize_four_six_rowwise_fused": [_P, _P, c_int, _U, _U, _P, _P, c_int, _P, _P, _P],
+    "nvfp4_relu2_backward": [_P, _P, _P, _P, _U],
+    "nvfp4_relu2_backward_f16": [_P, _P, _P, _P, _U],
+    "nvfp4_relu2_backward_bf16": [_P, _P, _P, _P, ctypes.c_uint64],
     "nvfp4_materialize_schedule_free": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _U],
     "nvfp4_materialize_schedule_free_matrix": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, _F, _U, _U],
     "nvfp4_ms_eden_quantize": [_P, POINTER(MsEdenArgs)],
@@ -493,6 +496,31 @@ class Nvfp4QuantModule:
                                                                                   scale_seed):
         return self._named_transpose("nvfp4_rowwise_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale",
                                      src, dst_row_len, sign_seed, scale_seed)
+
+
+class MlpModule:
+    """gpt/mlp/launcher.rs:66-76: the element-wise step between the two MLP linears of the backward pass
+    (the forward projections of that module are `projection_forward` with the ReLU^2 epilogue)."""
+
+    def relu2_backward(self, pre_activation: torch.Tensor, d_out: torch.Tensor,
+                       d_pre_activation: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """d_pre = d_out * 2 * relu(pre).  (pre f32 | f16, gradients f32) as in the reference, or all bf16."""
+        _require_cuda()
+        n = pre_activation.numel()
+        assert d_out.numel() == n
+        if pre_activation.dtype == torch.bfloat16:
+            assert d_out.dtype == torch.bfloat16
+            out = torch.empty_like(d_out) if d_pre_activation is None else d_pre_activation
+            _call("nvfp4_relu2_backward_bf16", _stream(), _ptr(pre_activation), _ptr(d_out), _ptr(out), n)
+            return out
+        assert d_out.dtype == torch.float32
+        out = torch.empty_like(d_out) if d_pre_activation is None else d_pre_activation
+        name = "nvfp4_relu2_backward" if pre_activation.dtype == torch.float32 else "nvfp4_relu2_backward_f16"
+        assert pre_activation.dtype in (torch.float32, torch.float16)
+        _call(name, _stream(), _ptr(pre_activation), _ptr(d_out), _ptr(out), n)
+        return out
+
+    relu2_backward_f16 = relu2_backward
 
 
 class OptimizerModule:

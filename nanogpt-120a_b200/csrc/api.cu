@@ -134,6 +134,20 @@ int nvfp4_quantize_four_six_rowwise_fused(void* stream, const void* x, int dtype
                            out_decoded_amax);
 }
 
+// ---- ReLU^2 backward -------------------------------------------------------------------------
+int nvfp4_relu2_backward(void* stream, const float* pre_activation, const float* d_out, float* d_pre_activation,
+                         uint32_t len) {
+  return launch_relu2_backward(S(stream), pre_activation, 0, d_out, d_pre_activation, 0, len);
+}
+int nvfp4_relu2_backward_f16(void* stream, const uint16_t* pre_activation, const float* d_out, float* d_pre_activation,
+                             uint32_t len) {
+  return launch_relu2_backward(S(stream), pre_activation, 2, d_out, d_pre_activation, 0, len);
+}
+int nvfp4_relu2_backward_bf16(void* stream, const void* pre_activation, const void* d_out, void* d_pre_activation,
+                              uint64_t len) {
+  return launch_relu2_backward(S(stream), pre_activation, 1, d_out, d_pre_activation, 1, len);
+}
+
 // ---- schedule-free weight materialisation ---------------------------------------------------
 int nvfp4_materialize_schedule_free(void* stream, const float* z_master, const float* x_master, float* chunk_amax,
                                     float* amax, uint8_t* bytes, uint8_t* scales, float* global_scale, float beta,

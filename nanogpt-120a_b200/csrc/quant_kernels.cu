@@ -10,6 +10,8 @@
 // 16-group (four-six) or 32-chunk (MS-EDEN) in registers, loads it with 128-bit
 // transactions and writes nibbles as 8/16-byte words.  The reduction trees are evaluated
 // in the same order as the reference's xor butterflies, so the bytes are identical.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -1117,6 +1119,82 @@ __global__ void __launch_bounds__(256, 2) ms_eden_nvfp4_transpose_kernel(const M
   (void)warp;
 }
 
+// ReLU^2 backward between the two MLP linears (gpt/mlp/kernels.rs:72-104):
+// d_pre = (d_out * 2) * max(pre, 0).  Element types: pre f32 / f16 / bf16, d_out and d_pre f32 / bf16
+// (the reference has pre f32 | f16 with f32 gradients).  Eight elements per thread and step.
+enum { kPreF32 = 0, kPreBf16 = 1, kPreF16 = 2 };
+
+template <int kPre>
+__device__ __forceinline__ void load8_pre(const void* p, size_t i, float (&v)[8]) {
+  if (kPre == kPreF32) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(p) + i));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(p) + i) + 1);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+  } else {
+    const uint4 t = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p) + i));
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (kPre == kPreBf16) {
+        v[2 * k] = __uint_as_float(w[k] << 16);
+        v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+      } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+        v[2 * k] = f.x;
+        v[2 * k + 1] = f.y;
+      }
+    }
+  }
+}
+template <int kPre>
+__device__ __forceinline__ float load1_pre(const void* p, size_t i) {
+  if (kPre == kPreF32) return __ldg(static_cast<const float*>(p) + i);
+  const uint16_t h = __ldg(static_cast<const uint16_t*>(p) + i);
+  if (kPre == kPreBf16) return __uint_as_float(static_cast<uint32_t>(h) << 16);
+  return __half2float(__ushort_as_half(h));
+}
+template <bool kBf16>
+__device__ __forceinline__ void store8_grad(void* p, size_t i, const float (&v)[8]) {
+  if (!kBf16) {
+    float4* q = reinterpret_cast<float4*>(static_cast<float*>(p) + i);
+    q[0] = make_float4(v[0], v[1], v[2], v[3]);
+    q[1] = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+      w[k] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p) + i) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+template <int kPre, bool kGradBf16>
+__global__ void __launch_bounds__(256) relu2_backward_kernel(const void* __restrict__ pre, const void* __restrict__ d_out,
+                                                              void* __restrict__ d_pre, uint64_t n, int vectorized) {
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * 256;
+  const uint64_t tid = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
+  const uint64_t vec_n = vectorized ? n / 8 : 0;
+  for (uint64_t i = tid; i < vec_n; i += stride) {
+    float p[8], d[8], r[8];
+    load8_pre<kPre>(pre, i * 8, p);
+    load8_pre<kGradBf16 ? kPreBf16 : kPreF32>(d_out, i * 8, d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) r[k] = (d[k] * 2.0f) * max_f32(p[k], 0.0f);
+    store8_grad<kGradBf16>(d_pre, i * 8, r);
+  }
+  for (uint64_t i = vec_n * 8 + tid; i < n; i += stride) {
+    const float p = load1_pre<kPre>(pre, i);
+    const float d = load1_pre<kGradBf16 ? kPreBf16 : kPreF32>(d_out, i);
+    const float r = (d * 2.0f) * max_f32(p, 0.0f);
+    if (kGradBf16)
+      static_cast<__nv_bfloat16*>(d_pre)[i] = __float2bfloat16_rn(r);
+    else
+      static_cast<float*>(d_pre)[i] = r;
+  }
+}
+
 // ============================================================================
 // decode, scale pack, padding, post-ops, bias gradient
 // ============================================================================
@@ -1600,6 +1678,26 @@ int launch_ms_eden_pair(cudaStream_t s, const nvfp4_ms_eden_args& r, const nvfp4
   if (rc) return rc;
   if (p.t.packed) rc = launch_packed_scale_pad(s, t.out_scales, cols, t.dst_row_len);
   return rc;
+}
+
+int launch_relu2_backward(cudaStream_t s, const void* pre, int pre_kind, const void* d_out, void* d_pre, int grad_bf16,
+                          uint64_t n) {
+  if (n == 0) return 0;
+  const int vectorized = ((reinterpret_cast<uintptr_t>(pre) | reinterpret_cast<uintptr_t>(d_out) |
+                           reinterpret_cast<uintptr_t>(d_pre)) & 15u) == 0;
+  const uint32_t grid = blocks_for((n + 7) / 8, 256, 148 * 8);
+#define NVFP4_RELU2_BWD(K, G) relu2_backward_kernel<K, G><<<grid, 256, 0, s>>>(pre, d_out, d_pre, n, vectorized)
+  if (grad_bf16) {
+    if (pre_kind == kPreF32) NVFP4_RELU2_BWD(kPreF32, true);
+    else if (pre_kind == kPreBf16) NVFP4_RELU2_BWD(kPreBf16, true);
+    else NVFP4_RELU2_BWD(kPreF16, true);
+  } else {
+    if (pre_kind == kPreF32) NVFP4_RELU2_BWD(kPreF32, false);
+    else if (pre_kind == kPreBf16) NVFP4_RELU2_BWD(kPreBf16, false);
+    else NVFP4_RELU2_BWD(kPreF16, false);
+  }
+#undef NVFP4_RELU2_BWD
+  NVFP4_RETURN_LAST();
 }
 
 int launch_decode(cudaStream_t s, const uint8_t* bytes, const uint8_t* scales, const float* gscales, int rowwise,

@@ -375,6 +375,17 @@ void oracle_row_amax_f32(const float* x, float* out, uint32_t rows, uint32_t row
 }
 
 // quant/kernels/row_amax.rs:67-101: 1024-value chunk amax, then the max of the chunks.
+// crates/cuda-kernels/src/gpt/mlp/kernels.rs:72-104: d_pre = (d_out * 2) * max(pre, 0), elementwise
+// (max.f32 semantics: a NaN pre-activation gives relu = 0).
+void oracle_relu2_backward(const float* pre_activation, const float* d_out, float* d_pre, uint64_t n) {
+  for (uint64_t i = 0; i < n; ++i) {
+    const float p = pre_activation[i];
+    const float relu = (p > 0.0f) ? p : 0.0f;  // NaN compares false
+    const float t = d_out[i] * 2.0f;
+    d_pre[i] = t * relu;
+  }
+}
+
 // crates/cuda-kernels/src/gpt/optimizer/schedule_free/value.rs:4-9: the weight a schedule-free
 // optimizer evaluates with, y = z + beta * (x - z), every operation rounded to f32 on its own.
 void oracle_schedule_free_value(const float* z_master, const float* x_master, float beta, uint64_t n, float* out) {

@@ -122,6 +122,14 @@ def row_amax(x):
     return out
 
 
+def relu2_backward(pre_activation, d_out):
+    """gpt/mlp/kernels.rs:72-104: d_pre = d_out * 2 * relu(pre), f32."""
+    p, d = _f32(pre_activation).reshape(-1), _f32(d_out).reshape(-1)
+    out = np.empty(p.size, np.float32)
+    lib().oracle_relu2_backward(_p(p), _p(d), _p(out), c_uint64(p.size))
+    return out
+
+
 def schedule_free_value(z_master, x_master, beta: float):
     """gpt/optimizer/schedule_free/value.rs:4-9: y = z + beta * (x - z) in f32."""
     z, x = _f32(z_master).reshape(-1), _f32(x_master).reshape(-1)

@@ -87,6 +87,29 @@ def test_materialize_schedule_free(pkg, oracle, dev, shape, packed, beta):
     assert np.array_equal(cpu(t.global_scales), og)
 
 
+@pytest.mark.parametrize("n", [1, 8, 1000, 8 * 4096 + 5])
+@pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
+def test_relu2_backward(pkg, oracle, dev, n, kind):
+    """gpt/mlp/kernels.rs:72-104, including -0, NaN and unaligned views."""
+    mlp = pkg.MlpModule()
+    pre = torch.from_numpy(normal(71, (n + 1,), 1.0).astype(np.float32))
+    d = torch.from_numpy(normal(72, (n + 1,), 1e-3).astype(np.float32))
+    pre[0] = -0.0
+    if n > 4:
+        pre[3] = float("nan")
+    for off in (0, 1):  # offset 1: not 16-byte aligned
+        p, g = pre[off:off + n], d[off:off + n]
+        if kind == "bf16":
+            p, g = p.bfloat16(), g.bfloat16()
+            got = mlp.relu2_backward(p.to(dev)[:], g.to(dev)[:]).float()
+            want = torch.from_numpy(oracle.relu2_backward(p.float().numpy(), g.float().numpy())).bfloat16().float()
+        else:
+            p = p.half() if kind == "f16" else p
+            got = mlp.relu2_backward(p.to(dev), g.to(dev))
+            want = torch.from_numpy(oracle.relu2_backward(p.float().numpy(), g.numpy()))
+        assert cpu(got).tobytes() == want.numpy().tobytes()
+
+
 def test_four_six_rowwise_long_rows(pkg, oracle, dev):
     """Rows longer than one thread block covers take the two-kernel path; a row that exactly fills
     a block (4096) and ragged row counts take the fused one."""

@@ -340,3 +340,10 @@ def test_schedule_free_value(oracle):
         want = (z + (b * (x - z)).astype(np.float32)).astype(np.float32)
         assert np.array_equal(oracle.schedule_free_value(z, x, beta), want)
     assert np.array_equal(oracle.schedule_free_value(z, x, 0.0), z)
+
+
+def test_relu2_backward(oracle):
+    """gpt/mlp/kernels.rs:72-104."""
+    pre = np.array([-1.0, -0.0, 0.0, 0.5, 2.0, np.nan], np.float32)
+    d = np.array([3.0, 3.0, 3.0, 3.0, -0.25, 1.0], np.float32)
+    assert np.array_equal(oracle.relu2_backward(pre, d), np.array([0, 0, 0, 3.0, -1.0, 0], np.float32))
