@@ -91,6 +91,7 @@ struct GemmParams {
   uint32_t k_splits, k_tiles_per_split, num_k_tiles;
   uint32_t stages;  // depth of the A (and, when streaming, B) ring
   int b_resident;   // the B panel of a column block stays in shared memory (short K)
+  uint32_t resident_cpn;  // resident mode: CTAs per column block (0 = contiguous tile ranges instead)
   int mode, epilogue, vec_store, tma_store;
   float weight;
 };
@@ -418,7 +419,15 @@ __global__ void __launch_bounds__(kThreads, 1)
   // couple of times.
   const uint32_t tiles_mn = p.num_m_blocks * p.num_n_blocks;
   uint32_t w_begin, w_end, w_step;
-  if (p.b_resident) {
+  if (p.b_resident && p.resident_cpn) {
+    // Column block c / cpn, row blocks j, j + cpn, j + 2 cpn, ...: at any moment the CTAs of all
+    // column blocks work on the same band of cpn row blocks, so whole output rows are written at
+    // about the same time (full DRAM pages when L2 writes them back).
+    const bool has_work = blockIdx.x < p.resident_cpn * p.num_n_blocks;
+    w_begin = blockIdx.x % p.resident_cpn;
+    w_end = has_work ? p.num_m_blocks : 0;
+    w_step = p.resident_cpn;
+  } else if (p.b_resident) {
     w_begin = static_cast<uint32_t>(static_cast<uint64_t>(tiles_mn) * blockIdx.x / gridDim.x);
     w_end = static_cast<uint32_t>(static_cast<uint64_t>(tiles_mn) * (blockIdx.x + 1) / gridDim.x);
     w_step = 1;
@@ -428,7 +437,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     w_step = gridDim.x;
   }
   auto decode = [&](uint32_t w, uint32_t& m_blk, uint32_t& n_blk, uint32_t& split) {
-    if (p.b_resident) {
+    if (p.b_resident && p.resident_cpn) {
+      n_blk = blockIdx.x / p.resident_cpn;
+      m_blk = w;
+      split = 0;
+    } else if (p.b_resident) {
       n_blk = w / p.num_m_blocks;
       m_blk = w - n_blk * p.num_m_blocks;
       split = 0;
@@ -953,12 +966,16 @@ int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb,
   // shared-memory plan
   const int budget = kSmemBudget - C::kFixedBytes;
   p.b_resident = 0;
+  p.resident_cpn = 0;
   if (want_resident) {
     const int left = budget - static_cast<int>(p.num_k_tiles) * C::kPanelSlotBytes;
     const int st = left / C::kResidentStageBytes;
     if (st >= 4) {
       p.b_resident = 1;
       p.stages = static_cast<uint32_t>(st > kMaxStages ? kMaxStages : st);
+      // banded schedule when the column blocks divide the grid almost evenly
+      const uint32_t cpn = grid / p.num_n_blocks;
+      if (cpn >= 1 && cpn * p.num_n_blocks * 20 >= grid * 19 && p.num_m_blocks >= 4 * cpn) p.resident_cpn = cpn;
     }
   }
   if (!p.b_resident) {
