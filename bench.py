@@ -147,8 +147,11 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    tokens = 4096
-    tflops, ms, cores = cpu_sample(tokens, max(1, args.steps), min(args.warmup, 1))
+    # bounded sample: about 4096 tokens per step for up to 16 steps, fewer tokens per step beyond that, so
+    # that K steps end within a few minutes on a 16-core host
+    steps = max(1, args.steps)
+    tokens = max(512, min(4096, (4096 * 16 // steps) // 256 * 256))
+    tflops, ms, cores = cpu_sample(tokens, steps, min(args.warmup, 1))
     sample = f"one GPT-2-small layer (c_attn, c_proj, fc, proj) fwd+bwd at {tokens} tokens per step"
     line = {
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
