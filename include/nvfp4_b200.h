@@ -62,7 +62,8 @@ extern "C" {
 
 /* Library / device ------------------------------------------------------------------------ */
 
-/* Version of this ABI (bumped on incompatible change). */
+/* Version of this ABI (bumped on incompatible change).  2: nvfp4_linear_backward_args gained
+ * x_decoded_amax, nvfp4_quantize_four_six_rowwise_fused gained out_decoded_amax. */
 int nvfp4_abi_version(void);
 /* Number of kernels this library has launched in this process (host-side tally). */
 uint64_t nvfp4_launch_count(void);

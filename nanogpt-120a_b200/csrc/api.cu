@@ -36,7 +36,7 @@ using namespace nvfp4;
 
 extern "C" {
 
-int nvfp4_abi_version(void) { return 1; }
+int nvfp4_abi_version(void) { return 2; }
 uint64_t nvfp4_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 const char* nvfp4_last_error(void) { return g_last_error; }
 

@@ -309,12 +309,28 @@ __global__ void __launch_bounds__(256) four_six_rowwise_fused_kernel(const T* __
   const uint32_t row = blockIdx.x * rows_per_cta + local_row;
   const bool active = local_row < rows_per_cta && row < rows;
   float v[16];
+  float ga = 0.0f;
   if (active) {
     Load16<T>::run(x + (static_cast<size_t>(row) * groups_per_row + kg) * 16, v);
-    float ga = 0.0f;
 #pragma unroll
     for (int i = 0; i < 16; i += 2) ga = max3_abs(ga, v[i], v[i + 1]);
-    atomicMax(&row_amax_bits[local_row], __float_as_uint(ga));  // non-negative floats order like their bits
+  }
+  // Row max: non-negative floats order like their bit patterns.  With at least 32 groups per row a
+  // warp touches at most two rows, so two warp-wide integer maxima and two shared-memory atomics
+  // replace up to 32 atomics on the same word.
+  const uint32_t ga_bits = active ? __float_as_uint(ga) : 0u;
+  if (groups_per_row >= 32) {
+    const uint32_t first_row = __shfl_sync(0xffffffffu, local_row, 0);
+    const bool in_first = local_row == first_row;
+    const uint32_t m_first = __reduce_max_sync(0xffffffffu, in_first ? ga_bits : 0u);
+    const uint32_t m_other = __reduce_max_sync(0xffffffffu, in_first ? 0u : ga_bits);
+    const uint32_t other_lanes = __ballot_sync(0xffffffffu, !in_first && active);
+    const uint32_t lane_id = t & 31u;
+    if (lane_id == 0 && active) atomicMax(&row_amax_bits[local_row], m_first);
+    if (other_lanes != 0u && lane_id == static_cast<uint32_t>(__ffs(other_lanes) - 1))
+      atomicMax(&row_amax_bits[local_row], m_other);
+  } else if (active) {
+    atomicMax(&row_amax_bits[local_row], ga_bits);
   }
   __syncthreads();
   uint32_t dec_bits = 0u;

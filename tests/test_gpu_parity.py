@@ -242,6 +242,29 @@ def test_ms_eden_nvfp4_sources_bit_exact(pkg, oracle, dev, rowwise, src_packed):
     assert np.array_equal(cpu(t.global_scales), og)
 
 
+@pytest.mark.parametrize("rowwise", [False, True])
+@pytest.mark.parametrize("rows,cols", [(128, 128), (256, 384)])
+def test_ms_eden_nvfp4_whole_tile_sources(pkg, oracle, dev, rowwise, rows, cols):
+    """Whole 128 x 128 tiles with packed source scales take the two-rows-per-thread transposer;
+    chunk amax, sign / group offsets and a packed destination included."""
+    q = pkg.Nvfp4QuantModule()
+    x = with_outliers(bf16_normal(46, (rows, cols)), seed=8, every=211)
+    src = q.quantize_four_six(x.to(dev), rowwise=rowwise, packed=True)
+    xf = x.float().numpy()
+    sb, ss, sg = oracle.four_six(xf, oracle.row_amax(xf) if rowwise else oracle.tensor_amax(xf)[1], rowwise)
+    kind = 3 if rowwise else 2
+    gs = oracle.ms_eden_global_scale(float(oracle.nvfp4_amax(sb, ss, sg, rows, cols, rowwise)[1][0]))
+    for packed_dst in (False, True):
+        ob, os_, og, oc = oracle.ms_eden(kind, (sb, ss, sg, rows, cols), cols, rows, gs, SIGN, SCALE, col_offset=5,
+                                         group_offset=10)
+        t, ca = q.ms_eden_quantize(src_kind=kind, src=src, rows=rows, cols=cols, dst_row_len=rows, global_scale=gs,
+                                   sign_seed=SIGN, scale_seed=SCALE, packed=packed_dst, want_chunk_amax=True,
+                                   col_offset=5, group_offset=10)
+        assert np.array_equal(cpu(t.bytes), ob)
+        assert np.array_equal(cpu(t.scales), oracle.scale_pack(os_, cols, rows) if packed_dst else os_)
+        assert np.array_equal(cpu(t.global_scales), og) and np.array_equal(cpu(ca), oc)
+
+
 def test_ms_eden_reference_named_entries(pkg, oracle, dev):
     """derived-device-scale rows, the pair entry and the reference's 64-value ramp case."""
     q = pkg.Nvfp4QuantModule()
