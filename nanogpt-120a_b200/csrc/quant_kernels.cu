@@ -206,8 +206,10 @@ __device__ __forceinline__ float four_six_global_scale(float amax) {
 // (utils/nvfp4/quant/kernels/convert.rs:27-35), each lane with its own inv / dequant scale.
 // The nibble bytes of both candidates come back too: the winner's bytes are the output.
 __device__ __forceinline__ f32x2_t candidate_errors16(const float (&v)[16], float s6, float s4, float gs, uint2& nib6,
-                                                      uint2& nib4) {
-  const f32x2_t inv = pack2(inv_scale(s6, gs), inv_scale(s4, gs));
+                                                      uint2& nib4, float& inv6, float& inv4) {
+  inv6 = inv_scale(s6, gs);
+  inv4 = inv_scale(s4, gs);
+  const f32x2_t inv = pack2(inv6, inv4);
   const f32x2_t dq = pack2(s6 * gs, s4 * gs);
   float x6[16], x4[16];
 #pragma unroll
@@ -234,7 +236,8 @@ __device__ __forceinline__ f32x2_t candidate_errors16(const float (&v)[16], floa
 // v: one 16-group.  Returns the scale byte and writes the 8 nibble bytes into `packed`.
 // helpers.rs:42-76 and four_six.rs:309-344 of utils/nvfp4/quant/kernels.  The output nibbles
 // are cvt(v * inv) with the chosen candidate's inv, i.e. exactly that candidate's trial bytes.
-__device__ __forceinline__ uint32_t four_six_group(const float (&v)[16], float gs, uint2& packed) {
+__device__ __forceinline__ uint32_t four_six_group(const float (&v)[16], float gs, uint2& packed,
+                                                   float* decoded_amax = nullptr) {
   float ga = 0.0f;
 #pragma unroll
   for (int i = 0; i < 16; i += 2) ga = max3_abs(ga, v[i], v[i + 1]);
@@ -243,11 +246,18 @@ __device__ __forceinline__ uint32_t four_six_group(const float (&v)[16], float g
   const uint32_t b4 = cvt_e4m3(ga * 1.0f / (4.0f * gsn + kDenomEps));
   const float s6 = e4m3_value(b6);
   const float s4 = e4m3_value(b4);
-  float err6, err4;
+  float err6, err4, inv6, inv4;
   uint2 nib6, nib4;
-  unpack2(candidate_errors16(v, s6, s4, gsn, nib6, nib4), err6, err4);
+  unpack2(candidate_errors16(v, s6, s4, gsn, nib6, nib4, inv6, inv4), err6, err4);
   const bool six = err6 <= err4;
   packed = six ? nib6 : nib4;
+  if (decoded_amax) {
+    // Largest decoded magnitude of the group, (q * scale) * gs as the stand-alone NVFP4 amax kernel
+    // evaluates it (utils/nvfp4/quant/kernels/ms_eden/amax.rs:23-64): rounding to E2M1 is monotonic
+    // in |x|, so the largest nibble is the one of the element with the largest magnitude, ga.
+    const float q = e2m1x2_values(cvt_e2m1x2(0.0f, ga * (six ? inv6 : inv4))).x;
+    *decoded_amax = fabsf(q * (six ? s6 : s4) * gs);
+  }
   return six ? b6 : b4;
 }
 
@@ -272,17 +282,6 @@ __global__ void __launch_bounds__(256) four_six_kernel(const T* __restrict__ x, 
   else
     out_scales[g] = static_cast<uint8_t>(b);
   if (kRowwise ? (kg == 0) : (g == 0)) out_gs[kRowwise ? row : 0] = gs;
-}
-
-// Largest decoded magnitude of one quantized 16-group: |e2m1| grows with its 3-bit magnitude
-// code and (q * scale) * gs is monotonic in q >= 0, so it is the decode of the largest code
-// (the same expression the stand-alone NVFP4 amax kernel evaluates per group).
-__device__ __forceinline__ float decoded_group_amax(uint2 nibbles, uint32_t scale_byte, float gs) {
-  uint32_t mx = __vmaxu4(__vmaxu4(nibbles.x & 0x07070707u, (nibbles.x >> 4) & 0x07070707u),
-                         __vmaxu4(nibbles.y & 0x07070707u, (nibbles.y >> 4) & 0x07070707u));
-  mx = __vmaxu4(mx, mx >> 16);
-  mx = __vmaxu4(mx, mx >> 8) & 0x7u;
-  return fabsf(e2m1_value(mx) * e4m3_value(scale_byte) * gs);
 }
 
 // Row amax and rowwise four-six in ONE pass over the input: a CTA owns whole rows (one thread
@@ -338,7 +337,8 @@ __global__ void __launch_bounds__(256) four_six_rowwise_fused_kernel(const T* __
     const float amax = __uint_as_float(row_amax_bits[local_row]);
     const float gs = four_six_global_scale(amax);
     uint2 packed;
-    const uint32_t b = four_six_group(v, gs, packed);
+    float dec = 0.0f;
+    const uint32_t b = four_six_group(v, gs, packed, decoded_amax ? &dec : nullptr);
     const size_t g = static_cast<size_t>(row) * groups_per_row + kg;
     *reinterpret_cast<uint2*>(out_fp4 + g * 8) = packed;
     if (kPacked)
@@ -349,7 +349,7 @@ __global__ void __launch_bounds__(256) four_six_rowwise_fused_kernel(const T* __
       out_gs[row] = gs;
       if (out_amax) out_amax[row] = amax;
     }
-    if (decoded_amax) dec_bits = __float_as_uint(decoded_group_amax(packed, b, gs));
+    dec_bits = __float_as_uint(dec);
   }
   if (decoded_amax) {  // uniform across the CTA
     dec_bits = __reduce_max_sync(0xffffffffu, dec_bits);
