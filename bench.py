@@ -362,6 +362,25 @@ def run_gpu(args):
 
     quant = quantize_bandwidth(pkg, torch, dev, peaks["hbm_gbs"]) if rank == 0 else None
 
+    # ---- the same step replayed from a CUDA graph (launch-overhead-free figure, single rank) ------
+    graph_info = None
+    if world == 1:
+        try:
+            graph = ps.capture_step()
+            for _ in range(2):
+                graph.replay()
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(args.steps):
+                graph.replay()
+            stop.record()
+            torch.cuda.synchronize()
+            g_ms = start.elapsed_time(stop) / args.steps
+            graph_info = {"ms_per_step": g_ms, "value": flops_step_total / (g_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                          "device_status": pkg.read_device_status()}
+        except Exception as exc:  # the eager figures above stand on their own
+            graph_info = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         tokens = 2048
@@ -398,7 +417,7 @@ def run_gpu(args):
                          "gemm_share_of_step": gemm_ms / ms_total if ms_total > 0 else None,
                          "traffic": gemm_traffic, "traffic_source": GEMM_TRAFFIC_SOURCE if gemm_traffic else None,
                          "peaks_file": peak_kind},
-            "quantize": quant,
+            "quantize": quant, "cuda_graph_replay": graph_info,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
             "gpu_launches": launches, "clocks": clocks, "device_status": status,

@@ -141,6 +141,11 @@ __device__ __forceinline__ f32x2_t mul2_rounded(f32x2_t a, f32x2_t b) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(kNegZeroPair));
   return r;
 }
+__device__ __forceinline__ f32x2_t fma2(f32x2_t a, f32x2_t b, f32x2_t c) {
+  f32x2_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
 // Packed form of butterfly_sum16: both lanes in the xor-8,4,2,1 order.
 __device__ __forceinline__ f32x2_t butterfly_sum16_x2(const f32x2_t (&e)[16]) {
   f32x2_t a0 = add2(e[0], e[8]), a1 = add2(e[1], e[9]), a2 = add2(e[2], e[10]), a3 = add2(e[3], e[11]);

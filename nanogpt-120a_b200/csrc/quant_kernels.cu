@@ -947,6 +947,7 @@ __global__ void __launch_bounds__(256, 2) ms_eden_pair_bf16_kernel(const MsEdenT
   __shared__ __align__(16) uint8_t stage[2][kPairStageBytes];
   __shared__ __align__(16) uint32_t flip_row[kTileRows];      // 0x80008000 where the row's sign is negative
   __shared__ __align__(16) uint32_t flip_col[kTileCols / 2];  // sign bits of a column pair, bf16-pair positions
+  __shared__ __align__(16) float2 unflip_row[kTileRows];      // (-1, -1) where the row's sign is negative, else (1, 1)
   __shared__ __align__(8) float quarter_sum[4][kTileCols];
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.x);
@@ -973,7 +974,9 @@ __global__ void __launch_bounds__(256, 2) ms_eden_pair_bf16_kernel(const MsEdenT
     cp_async_commit();
     const uint32_t ty = tile / tiles_x, r0 = ty * kTileRows, c0 = (tile % tiles_x) * kTileCols;
     if (tid < kTileRows) {
-      flip_row[tid] = random_sign_negative(p.sign_seed, r0 + tid + p.t.sign_offset) ? 0x80008000u : 0u;
+      const bool neg = random_sign_negative(p.sign_seed, r0 + tid + p.t.sign_offset);
+      flip_row[tid] = neg ? 0x80008000u : 0u;
+      unflip_row[tid] = neg ? make_float2(-1.0f, -1.0f) : make_float2(1.0f, 1.0f);
     } else if (tid < kTileRows + kTileCols / 2) {
       const uint32_t col = c0 + 2 * (tid - kTileRows) + p.r.sign_offset;
       flip_col[tid - kTileRows] = (random_sign_negative(p.sign_seed, col) ? 0x00008000u : 0u) |
@@ -982,22 +985,6 @@ __global__ void __launch_bounds__(256, 2) ms_eden_pair_bf16_kernel(const MsEdenT
     cp_async_wait_all_but_one();
     __syncthreads();
     const uint8_t* t = stage[buf];
-
-    if (p.col_sum_partials && warp >= 4) {
-      // Column sums of this tile in the fixed order of the bias gradient: per column four
-      // sequential 32-row sums, combined below as ((q0 + q1) + q2) + q3.  Two columns per thread
-      // (done by the row-operand warps, whose tile loads are the cheaper ones).
-      const uint32_t quarter = warp - 4;
-      f32x2_t acc = pack2(0.0f, 0.0f);
-#pragma unroll 8
-      for (int j = 0; j < 32; ++j) {
-        const uint32_t w = *reinterpret_cast<const uint32_t*>(t + (quarter * 32 + j) * kPairPitch + lane * 4);
-        acc = add2(acc, pack2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u)));
-      }
-      float a0, a1;
-      unpack2(acc, a0, a1);
-      *reinterpret_cast<float2*>(&quarter_sum[quarter][2 * lane]) = make_float2(a0, a1);
-    }
 
     f32x2_t P[32];
     uint32_t row_lo, row_hi, chunk_in_row;
@@ -1008,6 +995,20 @@ __global__ void __launch_bounds__(256, 2) ms_eden_pair_bf16_kernel(const MsEdenT
       for (int i = 0; i < 32; ++i) {
         const uint32_t w = *reinterpret_cast<const uint32_t*>(src + i * kPairPitch) ^ flip_row[warp * 32 + i];
         P[i] = pack2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+      }
+      if (p.col_sum_partials) {
+        // Column sums of this tile (dbias partials) in their fixed order -- per column four
+        // sequential 32-row sums, combined below as ((q0 + q1) + q2) + q3 -- from the values this
+        // thread already holds: x = P * (+-1) exactly, so acc + x is one fused multiply-add.
+        f32x2_t acc = pack2(0.0f, 0.0f);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float2 u = unflip_row[warp * 32 + i];
+          acc = fma2(P[i], pack2(u.x, u.y), acc);
+        }
+        float a0, a1;
+        unpack2(acc, a0, a1);
+        *reinterpret_cast<float2*>(&quarter_sum[warp][2 * lane]) = make_float2(a0, a1);
       }
       row_lo = c0 + 2 * lane;
       row_hi = row_lo + 1;

@@ -209,6 +209,17 @@ class ProjectionSet:
         self.forward()
         self.backward()
 
+    def capture_step(self) -> "torch.cuda.CUDAGraph":
+        """One step captured in a CUDA graph (single rank; call after at least one eager step so that
+        one-time set-up is done).  The library allocates nothing and never synchronises inside a step,
+        and tensor maps travel as kernel parameters, so the whole step is capturable; the MS-EDEN seeds
+        drawn during capture are baked into the graph."""
+        assert self.pg is None, "graph capture is offered for the single-rank step only"
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.step()
+        return graph
+
     def flops_per_step(self) -> int:
         return self.shape.flops_per_token() * self.tokens
 
