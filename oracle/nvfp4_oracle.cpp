@@ -344,6 +344,9 @@ float oracle_e4m3_decode(uint8_t bits) { return e4m3_decode(bits); }
 uint8_t oracle_e2m1_encode(float x) { return e2m1_encode(x); }
 uint8_t oracle_e4m3_encode(float x) { return e4m3_encode(x); }
 uint32_t oracle_hash_u32(uint32_t v) { return hash_u32(v); }
+uint8_t oracle_stochastic_e4m3_scale(float value, uint32_t seed, uint32_t group) {
+  return stochastic_e4m3_scale(value, seed, group);
+}
 float oracle_quartet_scale_override() { return kQuartetSO; }
 float oracle_four_six_global_scale(float amax) { return four_six_global_scale(amax); }
 float oracle_ms_eden_global_scale(float amax) { return ms_eden_global_scale(amax); }

@@ -122,6 +122,19 @@ def row_amax(x):
     return out
 
 
+def stochastic_e4m3_scale(value: float, seed: int, group: int) -> int:
+    """utils/nvfp4/quant/kernels/ms_eden/pack/scale.rs:7-30: E4M3 code of `value`, rounded stochastically."""
+    fn = lib().oracle_stochastic_e4m3_scale
+    fn.restype = ctypes.c_uint8
+    return int(fn(c_float(value), c_uint32(seed & 0xFFFFFFFF), c_uint32(group & 0xFFFFFFFF)))
+
+
+def hash_u32(v: int) -> int:
+    fn = lib().oracle_hash_u32
+    fn.restype = c_uint32
+    return int(fn(c_uint32(v & 0xFFFFFFFF)))
+
+
 def relu2_backward(pre_activation, d_out):
     """gpt/mlp/kernels.rs:72-104: d_pre = d_out * 2 * relu(pre), f32."""
     p, d = _f32(pre_activation).reshape(-1), _f32(d_out).reshape(-1)

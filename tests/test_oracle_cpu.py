@@ -347,3 +347,20 @@ def test_relu2_backward(oracle):
     pre = np.array([-1.0, -0.0, 0.0, 0.5, 2.0, np.nan], np.float32)
     d = np.array([3.0, 3.0, 3.0, 3.0, -0.25, 1.0], np.float32)
     assert np.array_equal(oracle.relu2_backward(pre, d), np.array([0, 0, 0, 3.0, -1.0, 0], np.float32))
+
+
+def test_stochastic_scale_integer_identity(oracle):
+    """Inside the normal E4M3 range the stochastic rounding of pack/scale.rs:7-30 reduces to integers:
+    lower code = (f32 bits >> 20) - 960, p = low 20 mantissa bits / 2^20, draw = 24 hash bits / 2^24.
+    The CUDA quantizers use this form; here it is pinned against the restatement of the reference."""
+    rng = np.random.default_rng(11)
+    values = np.concatenate([rng.uniform(2.0 ** -6, 448.0, 3000), 2.0 ** rng.uniform(-6, 8.8, 3000),
+                             [2.0 ** -6, 1.0, 1.125, 447.99, 0.015625 * 1.875]]).astype(np.float32)
+    for i, v in enumerate(values):
+        if not (np.float32(2.0 ** -6) <= v < np.float32(448.0)):
+            continue
+        bits = int(v.view(np.uint32))
+        seed, group = 0x9ABCDEF0, i * 2654435761 & 0xFFFFFFFF
+        draw = oracle.hash_u32(seed ^ group) & 0xFFFFFF
+        fast = (bits >> 20) - 960 + (1 if draw < ((bits & 0xFFFFF) << 4) else 0)
+        assert fast == oracle.stochastic_e4m3_scale(float(v), seed, group)
