@@ -4,6 +4,7 @@
 #include <atomic>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "kernels.h"
 
@@ -25,6 +26,33 @@ static int invalid(const char* msg) {
 }
 
 static inline cudaStream_t S(void* stream) { return static_cast<cudaStream_t>(stream); }
+
+// A second stream per device for the one place where two independent kernel chains of a call use
+// different resources (the backward's NVFP4 transposers are ALU bound, its dY amax pass is HBM
+// bound).  Created on first use, never destroyed; fork / join are event waits, so it also works
+// while the caller's stream is being captured into a graph.
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+static std::mutex g_side_mutex;
+static SideStream g_side[64];
+
+static SideStream* side_stream() {
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_side_mutex);
+  SideStream& ss = g_side[device];
+  if (!ss.stream) {
+    if (cudaStreamCreateWithFlags(&ss.stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ss.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ss.join, cudaEventDisableTiming) != cudaSuccess) {
+      ss = SideStream();
+      return nullptr;
+    }
+  }
+  return &ss;
+}
 
 static inline uint32_t padded_k(uint32_t k) { return (k + 63u) / 64u * 64u; }
 static inline uint32_t chunks1024(uint64_t n) { return static_cast<uint32_t>((n + 1023) / 1024); }
@@ -554,6 +582,31 @@ int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args
   cudaStream_t s = S(stream);
   int rc;
 
+  // 3. W^T and 4. X^T from their NVFP4 forms (quantize/transpose.rs:14-93).  Enqueued first and on
+  //    the side stream: they depend on nothing computed below, are ALU bound, and so run beside the
+  //    HBM-bound dY amax pass of step 2.  Without a side stream they simply run first on `s`.
+  SideStream* side = side_stream();
+  // the fork / join events are per device: keep concurrent host threads from interleaving their use
+  static std::mutex enqueue_mutex;
+  std::unique_lock<std::mutex> enqueue_lock(enqueue_mutex, std::defer_lock);
+  if (side) enqueue_lock.lock();
+  if (side) {
+    if (cudaEventRecord(side->fork, s) != cudaSuccess || cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess)
+      side = nullptr;
+  }
+  void* ts = side ? static_cast<void*>(side->stream) : stream;
+  rc = nvfp4_source_transpose(ts, NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED, a->x_bytes, a->x_scales, a->x_globals,
+                              a->input_t_h.bytes, a->input_t_h.scales_packed, a->input_t_h.global_scales,
+                              a->input_t_h.chunk_amax, a->input_t_h.global_scale, T, I, tk, a->sign_seed,
+                              a->scale_seed ^ 0xc2b2ae35u, false, NVFP4_SCALES_PACKED, a->token_offset, 0, a->x_scale_layout,
+                              a->x_decoded_amax);
+  if (rc) return rc;
+  rc = nvfp4_source_transpose(ts, NVFP4_SRC_NVFP4_TRANSPOSED, a->w_bytes, a->w_scales, a->w_global,
+                              a->weight_t_h.bytes, a->weight_t_h.scales_packed, a->weight_t_h.global_scales,
+                              a->weight_t_h.chunk_amax, a->weight_t_h.global_scale, O, I, ok, a->sign_seed,
+                              a->scale_seed ^ 0x9e3779b9u, false, NVFP4_SCALES_PACKED, 0, 0, a->w_scale_layout);
+  if (rc) return rc;
+
   // 1. dbias.  When the dY quantization below runs tiled, the column sums ride along with it:
   //    each row tile leaves its partial sums in the (not yet written) dinput buffer and a small
   //    kernel adds them up in tile order -- no extra pass over dY.  Otherwise the sum is done
@@ -619,18 +672,11 @@ int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args
     if (rc) return rc;
   }
 
-  // 3. W^T and 4. X^T from their NVFP4 forms (quantize/transpose.rs:14-93)
-  rc = nvfp4_source_transpose(stream, NVFP4_SRC_NVFP4_TRANSPOSED, a->w_bytes, a->w_scales, a->w_global,
-                              a->weight_t_h.bytes, a->weight_t_h.scales_packed, a->weight_t_h.global_scales,
-                              a->weight_t_h.chunk_amax, a->weight_t_h.global_scale, O, I, ok, a->sign_seed,
-                              a->scale_seed ^ 0x9e3779b9u, false, NVFP4_SCALES_PACKED, 0, 0, a->w_scale_layout);
-  if (rc) return rc;
-  rc = nvfp4_source_transpose(stream, NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED, a->x_bytes, a->x_scales, a->x_globals,
-                              a->input_t_h.bytes, a->input_t_h.scales_packed, a->input_t_h.global_scales,
-                              a->input_t_h.chunk_amax, a->input_t_h.global_scale, T, I, tk, a->sign_seed,
-                              a->scale_seed ^ 0xc2b2ae35u, false, NVFP4_SCALES_PACKED, a->token_offset, 0, a->x_scale_layout,
-                              a->x_decoded_amax);
-  if (rc) return rc;
+  // join: the GEMMs need W^T and X^T
+  if (side) {
+    if (cudaEventRecord(side->join, side->stream) != cudaSuccess || cudaStreamWaitEvent(s, side->join, 0) != cudaSuccess)
+      return invalid("linear_backward: could not join the side stream");
+  }
 
   // 5. dX = dY . W   (contraction over output features) and dW = dY^T . X (over tokens)
   nvfp4_gemm_args g;

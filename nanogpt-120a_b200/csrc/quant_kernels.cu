@@ -1078,8 +1078,11 @@ constexpr int kNvTileCols = 128;                          // source columns per 
 constexpr int kNvBytePitch = kNvTileCols / 2 + 16;        // staged bytes per source row
 constexpr int kNvStageBytes = kTileRows * kNvBytePitch;   // 10240
 
+// Register budget of three CTAs per SM (80 registers, a few spilled words, same speed as the
+// unconstrained 113), launched two per SM: the free third of the register file lets the
+// bandwidth-bound dY amax kernel of the same backward call run beside it on another stream.
 template <bool kRowwise>
-__global__ void __launch_bounds__(256, 2) ms_eden_nvfp4_transpose_kernel(const MsEdenTileParams p, uint32_t tiles_x,
+__global__ void __launch_bounds__(256, 3) ms_eden_nvfp4_transpose_kernel(const MsEdenTileParams p, uint32_t tiles_x,
                                                                           uint32_t tile_count) {
   __shared__ __align__(16) uint8_t stage[2][kNvStageBytes];
   __shared__ __align__(16) float2 scale2[kTileRows][kNvTileCols / 16];  // block scale of (row, group), duplicated
