@@ -12,6 +12,8 @@
 // in the same order as the reference's xor butterflies, so the bytes are identical.
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -946,8 +948,8 @@ __global__ void __launch_bounds__(256) ms_eden_tile_kernel(const MsEdenTileParam
   }
 }
 
-// Pair kernel for bf16 sources whose extents are whole tiles (rows % 128 == 0, cols % 64 == 0):
-// the same outputs as ms_eden_tile_kernel<0, bf16, true>, organised for instruction count.
+// Pair kernel for sources whose extents are whole tiles (rows % 128 == 0, cols % 64 == 0):
+// the same outputs as ms_eden_tile_kernel<0, T, true>, organised for instruction count.
 //  * Persistent CTAs walk the tiles; the next tile's 128 x 128-byte rows arrive through
 //    cp.async into the other shared-memory stage while the current one is being quantized.
 //    The tile stays bf16; the 144-byte row pitch makes all three access patterns conflict-free.
@@ -965,26 +967,41 @@ __device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* gmem
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
-__global__ void __launch_bounds__(256, 2) ms_eden_pair_bf16_kernel(const MsEdenTileParams p, uint32_t tiles_x,
-                                                                    uint32_t tile_count) {
-  __shared__ __align__(16) uint8_t stage[2][kPairStageBytes];
-  __shared__ __align__(16) uint32_t flip_row[kTileRows];      // 0x80008000 where the row's sign is negative
-  __shared__ __align__(16) uint32_t flip_col[kTileCols / 2];  // sign bits of a column pair, bf16-pair positions
+// f32 sources use the same kernel with a [128 x 64] f32 tile (272-byte pitch, dynamic shared
+// memory): a 64-bit load is the two lanes of the transposed role, two 32-bit values of rows r and
+// r + 32 those of the row role, and the signs are xors on the f32 sign bits.
+template <typename T>
+struct PairTile {
+  static constexpr bool kBf16 = sizeof(T) == 2;
+  static constexpr int kPitch = kBf16 ? kPairPitch : kTileCols * 4 + 16;  // bytes per staged row
+  static constexpr int kStageBytes = kTileRows * kPitch;
+  static constexpr int kPiecesPerRow = kTileCols * static_cast<int>(sizeof(T)) / 16;
+  static constexpr int kPiecesPerThread = kTileRows * kPiecesPerRow / 256;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256, 2) ms_eden_pair_kernel(const MsEdenTileParams p, uint32_t tiles_x,
+                                                               uint32_t tile_count) {
+  using PT = PairTile<T>;
+  constexpr bool kBf16 = PT::kBf16;
+  extern __shared__ __align__(16) uint8_t pair_stage[];       // [2][PT::kStageBytes]
+  __shared__ __align__(16) uint32_t flip_row[kTileRows];      // sign-bit mask of the row (both bf16 halves)
+  __shared__ __align__(16) uint32_t flip_col[kTileCols];      // bf16: per column pair; f32: per column
   __shared__ __align__(16) float2 unflip_row[kTileRows];      // (-1, -1) where the row's sign is negative, else (1, 1)
   __shared__ __align__(8) float quarter_sum[4][kTileCols];
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.x);
+  const T* x = static_cast<const T*>(p.x);
   const float gs = p.use_host_scale ? p.global_scale_host : p.global_scale_dev[0];
-  const uint32_t stage_base = static_cast<uint32_t>(__cvta_generic_to_shared(&stage[0][0]));
+  const uint32_t stage_base = static_cast<uint32_t>(__cvta_generic_to_shared(pair_stage));
 
-  // 1024 16-byte pieces per tile, four per thread: piece i = row i/8, 16-byte column i%8
+  // 16-byte pieces of the tile, row-major, PT::kPiecesPerThread per thread
   auto issue_tile = [&](uint32_t tile, uint32_t buf) {
     const uint32_t r0 = (tile / tiles_x) * kTileRows, c0 = (tile % tiles_x) * kTileCols;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const uint32_t i = tid + 256 * k, row = i >> 3, piece = i & 7;
-      cp_async_16(stage_base + buf * kPairStageBytes + row * kPairPitch + piece * 16,
-                  x + static_cast<size_t>(r0 + row) * p.src_cols + c0 + piece * 8);
+    for (int k = 0; k < PT::kPiecesPerThread; ++k) {
+      const uint32_t i = tid + 256 * k, row = i / PT::kPiecesPerRow, piece = i % PT::kPiecesPerRow;
+      cp_async_16(stage_base + buf * PT::kStageBytes + row * PT::kPitch + piece * 16,
+                  x + static_cast<size_t>(r0 + row) * p.src_cols + c0 + piece * (16 / sizeof(T)));
     }
   };
 
@@ -998,26 +1015,35 @@ __global__ void __launch_bounds__(256, 2) ms_eden_pair_bf16_kernel(const MsEdenT
     const uint32_t ty = tile / tiles_x, r0 = ty * kTileRows, c0 = (tile % tiles_x) * kTileCols;
     if (tid < kTileRows) {
       const bool neg = random_sign_negative(p.sign_seed, r0 + tid + p.t.sign_offset);
-      flip_row[tid] = neg ? 0x80008000u : 0u;
+      flip_row[tid] = neg ? (kBf16 ? 0x80008000u : 0x80000000u) : 0u;
       unflip_row[tid] = neg ? make_float2(-1.0f, -1.0f) : make_float2(1.0f, 1.0f);
-    } else if (tid < kTileRows + kTileCols / 2) {
+    } else if (kBf16 && tid < kTileRows + kTileCols / 2) {
       const uint32_t col = c0 + 2 * (tid - kTileRows) + p.r.sign_offset;
       flip_col[tid - kTileRows] = (random_sign_negative(p.sign_seed, col) ? 0x00008000u : 0u) |
                                   (random_sign_negative(p.sign_seed, col + 1) ? 0x80000000u : 0u);
+    } else if (!kBf16 && tid < kTileRows + kTileCols) {
+      const uint32_t col = c0 + (tid - kTileRows) + p.r.sign_offset;
+      flip_col[tid - kTileRows] = random_sign_negative(p.sign_seed, col) ? 0x80000000u : 0u;
     }
     cp_async_wait_all_but_one();
     __syncthreads();
-    const uint8_t* t = stage[buf];
+    const uint8_t* t = pair_stage + buf * PT::kStageBytes;
 
     f32x2_t P[32];
     uint32_t row_lo, row_hi, chunk_in_row;
     if (warp < 4) {
       // transposed operand: source columns c0 + 2*lane (+1), K = source rows r0 + 32*warp ..
-      const uint8_t* src = t + warp * 32 * kPairPitch + lane * 4;
+      const uint8_t* src = t + warp * 32 * PT::kPitch + lane * 2 * sizeof(T);
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const uint32_t w = *reinterpret_cast<const uint32_t*>(src + i * kPairPitch) ^ flip_row[warp * 32 + i];
-        P[i] = pack2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+        const uint32_t f = flip_row[warp * 32 + i];
+        if (kBf16) {
+          const uint32_t w = *reinterpret_cast<const uint32_t*>(src + i * PT::kPitch) ^ f;
+          P[i] = pack2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+        } else {
+          const uint2 w = *reinterpret_cast<const uint2*>(src + i * PT::kPitch);
+          P[i] = pack2(__uint_as_float(w.x ^ f), __uint_as_float(w.y ^ f));
+        }
       }
       if (p.col_sum_partials) {
         // Column sums of this tile (dbias partials) in their fixed order -- per column four
@@ -1039,19 +1065,32 @@ __global__ void __launch_bounds__(256, 2) ms_eden_pair_bf16_kernel(const MsEdenT
     } else {
       // row operand: rows r0 + base + lane and + 32 more, K = source columns c0 + 32*chunk ..
       const uint32_t chunk = warp & 1, row = ((warp - 4) >> 1) * 64 + lane;
-      const uint8_t* src_lo = t + row * kPairPitch + chunk * 64;
-      const uint8_t* src_hi = src_lo + 32 * kPairPitch;
+      const uint8_t* src_lo = t + row * PT::kPitch + chunk * 32 * sizeof(T);
+      const uint8_t* src_hi = src_lo + 32 * PT::kPitch;
+      if (kBf16) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint4 a = *reinterpret_cast<const uint4*>(src_lo + 16 * j);
-        const uint4 b = *reinterpret_cast<const uint4*>(src_hi + 16 * j);
-        const uint4 f = *reinterpret_cast<const uint4*>(&flip_col[chunk * 16 + 4 * j]);
-        const uint32_t wa[4] = {a.x ^ f.x, a.y ^ f.y, a.z ^ f.z, a.w ^ f.w};
-        const uint32_t wb[4] = {b.x ^ f.x, b.y ^ f.y, b.z ^ f.z, b.w ^ f.w};
+        for (int j = 0; j < 4; ++j) {
+          const uint4 a = *reinterpret_cast<const uint4*>(src_lo + 16 * j);
+          const uint4 b = *reinterpret_cast<const uint4*>(src_hi + 16 * j);
+          const uint4 f = *reinterpret_cast<const uint4*>(&flip_col[chunk * 16 + 4 * j]);
+          const uint32_t wa[4] = {a.x ^ f.x, a.y ^ f.y, a.z ^ f.z, a.w ^ f.w};
+          const uint32_t wb[4] = {b.x ^ f.x, b.y ^ f.y, b.z ^ f.z, b.w ^ f.w};
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          P[8 * j + 2 * k] = pack2(__uint_as_float(wa[k] << 16), __uint_as_float(wb[k] << 16));
-          P[8 * j + 2 * k + 1] = pack2(__uint_as_float(wa[k] & 0xffff0000u), __uint_as_float(wb[k] & 0xffff0000u));
+          for (int k = 0; k < 4; ++k) {
+            P[8 * j + 2 * k] = pack2(__uint_as_float(wa[k] << 16), __uint_as_float(wb[k] << 16));
+            P[8 * j + 2 * k + 1] = pack2(__uint_as_float(wa[k] & 0xffff0000u), __uint_as_float(wb[k] & 0xffff0000u));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint4 a = *reinterpret_cast<const uint4*>(src_lo + 16 * j);
+          const uint4 b = *reinterpret_cast<const uint4*>(src_hi + 16 * j);
+          const uint4 f = *reinterpret_cast<const uint4*>(&flip_col[chunk * 32 + 4 * j]);
+          P[4 * j] = pack2(__uint_as_float(a.x ^ f.x), __uint_as_float(b.x ^ f.x));
+          P[4 * j + 1] = pack2(__uint_as_float(a.y ^ f.y), __uint_as_float(b.y ^ f.y));
+          P[4 * j + 2] = pack2(__uint_as_float(a.z ^ f.z), __uint_as_float(b.z ^ f.z));
+          P[4 * j + 3] = pack2(__uint_as_float(a.w ^ f.w), __uint_as_float(b.w ^ f.w));
         }
       }
       row_lo = r0 + row;
@@ -1706,9 +1745,22 @@ int launch_ms_eden_pair(cudaStream_t s, const nvfp4_ms_eden_args& r, const nvfp4
   p.col_sum_partials = col_sum_partials;
   const bool whole_tiles = rows % kTileRows == 0 && cols % kTileCols == 0 && t.dst_row_len == rows &&
                            r.dst_row_len == cols && (reinterpret_cast<uintptr_t>(r.x) & 15u) == 0;
-  if (r.src_dtype == NVFP4_DTYPE_BF16 && whole_tiles) {
+  if (whole_tiles) {
     const uint32_t tiles_x = cols / kTileCols, tile_count = tiles_x * (rows / kTileRows);
-    ms_eden_pair_bf16_kernel<<<min(tile_count, 148u * 2u), 256, 0, s>>>(p, tiles_x, tile_count);
+    const uint32_t grid = min(tile_count, 148u * 2u);
+    if (r.src_dtype == NVFP4_DTYPE_BF16) {
+      ms_eden_pair_kernel<__nv_bfloat16>
+          <<<grid, 256, 2 * PairTile<__nv_bfloat16>::kStageBytes, s>>>(p, tiles_x, tile_count);
+    } else {
+      static std::once_flag once;
+      static cudaError_t attr_err = cudaSuccess;
+      std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(ms_eden_pair_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        2 * PairTile<float>::kStageBytes);
+      });
+      if (attr_err != cudaSuccess) return static_cast<int>(attr_err);
+      ms_eden_pair_kernel<float><<<grid, 256, 2 * PairTile<float>::kStageBytes, s>>>(p, tiles_x, tile_count);
+    }
   } else if (r.src_dtype == NVFP4_DTYPE_BF16) {
     launch_tile<0, __nv_bfloat16, true>(s, p);
   } else {
