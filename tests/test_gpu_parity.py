@@ -636,6 +636,50 @@ def test_linear_backward_precomputed_x_amax(pkg, oracle, dev):
     assert_no_timeouts(pkg)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_linear_backward_edge_values_whole_tiles(pkg, oracle, dev, dtype):
+    """The whole-tile quantizers (two chunks per thread, integer scale rounding with its range
+    checks) on the values that leave their fast paths: zero rows and columns, groups 2^20 below the
+    tensor amax (sub-normal block scales), one huge outlier (saturating scales), negative zeros."""
+    q, bwd = pkg.Nvfp4QuantModule(), pkg.LinearBackwardModule()
+    tokens, in_dim, out_dim = 256, 128, 128
+    dy = bf16_normal(501, (tokens, out_dim), 1e-3)
+    dy[3] = 0.0
+    dy[:, 7] = 0.0
+    dy[16:48] *= 2.0 ** -20
+    dy[100, 100] = 3.0e4
+    dy[5, ::2] = -0.0
+    x = bf16_normal(502, (tokens, in_dim))
+    x[9] = 0.0
+    x[64:96] *= 2.0 ** -18
+    x[200, 5] = 1.0e4
+    w = bf16_normal(503, (out_dim, in_dim), 0.02)
+    w[:, 3] = 0.0
+    xq = q.quantize_four_six(x.to(dev), rowwise=True, packed=True, decoded_amax=True)
+    wq = q.quantize_four_six(w.to(dev), rowwise=False, packed=True)
+    scratch = pkg.LinearBackwardScratch(tokens, in_dim, out_dim, dev)
+    e_dev = dy.to(dev) if dtype == torch.bfloat16 else dy.float().to(dev)
+    bwd.backward_ms_eden(e=e_dev, weight=wq, input=xq, scratch=scratch, sign_seed=SIGN, scale_seed=SCALE)
+    assert_no_timeouts(pkg)
+    xf, wf, ef = x.float().numpy(), w.float().numpy(), dy.float().numpy()
+    oxq = oracle.four_six(xf, oracle.row_amax(xf), True)
+    owq = oracle.four_six(wf, oracle.tensor_amax(wf)[1], False)
+    assert np.array_equal(cpu(xq.bytes), oxq[0])
+    gs_e = oracle.ms_eden_global_scale(float(np.abs(ef).max()))
+    e_h = oracle.ms_eden(0, ef, tokens, out_dim, gs_e, SIGN, SCALE, want_chunk_amax=False)
+    e_t = oracle.ms_eden(1, ef, out_dim, tokens, gs_e, SIGN, SCALE ^ 0x85EBCA6B, want_chunk_amax=False)
+    gs_w = oracle.ms_eden_global_scale(float(oracle.nvfp4_amax(*owq, out_dim, in_dim, False)[1][0]))
+    w_t = oracle.ms_eden(2, (*owq, out_dim, in_dim), in_dim, out_dim, gs_w, SIGN, SCALE ^ 0x9E3779B9, want_chunk_amax=False)
+    gs_x = oracle.ms_eden_global_scale(float(oracle.nvfp4_amax(*oxq, tokens, in_dim, True)[1][0]))
+    x_t = oracle.ms_eden(3, (*oxq, tokens, in_dim), in_dim, tokens, gs_x, SIGN, SCALE ^ 0xC2B2AE35, want_chunk_amax=False)
+    for name, ref, rows, kk in (("e_h", e_h, tokens, out_dim), ("e_t_h", e_t, out_dim, tokens),
+                                ("weight_t_h", w_t, in_dim, out_dim), ("input_t_h", x_t, in_dim, tokens)):
+        op = getattr(scratch, name)
+        assert np.array_equal(cpu(op["bytes"]), ref[0]), name
+        assert np.array_equal(cpu(op["scales_packed"]), oracle.scale_pack(ref[1], rows, kk)), name
+        assert np.array_equal(cpu(op["global_scales"]), ref[2]), name
+
+
 def test_linear_backward_sharded_equals_whole(pkg, oracle, dev):
     """Token sharding (two shards run back to back on one GPU): with the shared dY scale and the
     token offsets, shard dX rows equal the unsharded rows and the shard dW sum matches."""
