@@ -98,13 +98,14 @@ class _Linear:
         self.xq = Nvfp4Tensor(torch.empty(nx // 2, **u8), torch.empty(scale_packed_len(tokens, in_dim), **u8),
                               torch.empty(tokens, **f32), tokens, in_dim, packed=True, rowwise=True)
         self.x_amax = torch.empty(tokens, **f32)
+        self.wq_ready: Optional[torch.cuda.Event] = None  # set when this step's NVFP4 weight is ready
         self.dweight: Optional[torch.Tensor] = None  # views into the layer's gradient bucket
         self.dbias: Optional[torch.Tensor] = None
 
 
 class ProjectionSet:
     def __init__(self, shape: ModelShape, tokens: int, device, seed: int = 1234, token_offset: int = 0,
-                 process_group=None, grad_dtype: torch.dtype = torch.bfloat16):
+                 process_group=None, grad_dtype: torch.dtype = torch.bfloat16, overlap_weight_quantization: bool = True):
         assert tokens % 128 == 0, "token shards are multiples of 128 rows (scale tiles stay intact)"
         self.shape, self.tokens, self.device = shape, tokens, device
         self.token_offset = token_offset
@@ -144,6 +145,8 @@ class ProjectionSet:
         for _, i, o, _ in shape.linears() + [("lm_head", d, v, EPI_NONE)]:
             if (i, o) not in self.scratch:
                 self.scratch[(i, o)] = LinearBackwardScratch(tokens, i, o, device)
+        self._weight_stream: Optional[torch.cuda.Stream] = None
+        self.overlap_weight_quantization = overlap_weight_quantization
         self.gemm_events: List[Tuple[torch.cuda.Event, torch.cuda.Event, int]] = []
         self.record_gemm_events = False
 
@@ -152,15 +155,33 @@ class ProjectionSet:
         return [x for lin in self.layers for x in lin] + [self.lm_head]
 
     def quantize_weights(self) -> None:
-        """Weights are re-quantized from their masters every step (four-six, tensor scale)."""
-        for lin in self.all_linears():
-            self.quant.tensor_amax(lin.weight, lin.w_chunk_amax, lin.w_amax)
-            self.quant.quantize_four_six(lin.weight, amax=lin.w_amax, rowwise=False, packed=True, out=lin.wq)
+        """Weights are re-quantized from their masters every step (four-six, tensor scale).  The 2 x 49
+        launches are tiny (a few microseconds each, a fraction of the SMs), so they go to a side stream in
+        the order the forward pass needs them and run in the shadow of the activation quantizers; each
+        forward GEMM waits for its own weight's event."""
+        if not self.overlap_weight_quantization:
+            for lin in self.all_linears():
+                self.quant.tensor_amax(lin.weight, lin.w_chunk_amax, lin.w_amax)
+                self.quant.quantize_four_six(lin.weight, amax=lin.w_amax, rowwise=False, packed=True, out=lin.wq)
+            return
+        main = torch.cuda.current_stream()
+        if self._weight_stream is None:
+            self._weight_stream = torch.cuda.Stream(device=self.device)
+            for lin in self.all_linears():
+                lin.wq_ready = torch.cuda.Event()
+        self._weight_stream.wait_stream(main)  # the previous step has finished with the old NVFP4 weights
+        with torch.cuda.stream(self._weight_stream):
+            for lin in self.all_linears():
+                self.quant.tensor_amax(lin.weight, lin.w_chunk_amax, lin.w_amax)
+                self.quant.quantize_four_six(lin.weight, amax=lin.w_amax, rowwise=False, packed=True, out=lin.wq)
+                lin.wq_ready.record(self._weight_stream)
 
     def _forward_linear(self, lin: _Linear) -> None:
         x = self.x[lin.in_dim]
         # row amax fused; the decoded amax rides along so that backward need not re-read X for it
         self.quant.quantize_four_six(x, rowwise=True, packed=True, out=lin.xq, decoded_amax=True)
+        if lin.wq_ready is not None:
+            torch.cuda.current_stream().wait_event(lin.wq_ready)
         aux = self.pre[lin.out_dim] if lin.epilogue == EPI_RELU2 else None
         self._timed_gemm(lambda: self.gemm.gemm(lin.xq, lin.wq, bias=lin.bias, epilogue=lin.epilogue,
                                                 out=self.y[lin.out_dim], aux=aux),

@@ -708,3 +708,32 @@ def test_linear_backward_sharded_equals_whole(pkg, oracle, dev):
     true_dw = cpu(dy).T @ x.float().numpy()
     assert rel_fro(cpu(dws[0] + dws[1]), true_dw) < 0.3 and rel_fro(cpu(dw), true_dw) < 0.3
     assert_no_timeouts(pkg)
+
+
+# ------------------------------------------------------------------------------------------ projection set
+
+def test_projection_set_step_streams_and_graph(pkg, dev):
+    """The training-step projection set: the side-stream weight quantization changes no output, and a
+    step replayed from a CUDA graph equals the eager step drawn with the same seeds."""
+    from nanogpt_120a_b200.projection_set import ModelShape, ProjectionSet
+
+    shape = ModelShape("tiny-proj-set", 2, 128, 256, 512)
+
+    def buckets(ps):
+        torch.cuda.synchronize()
+        return [b.clone() for b in ps.buckets] + [ps.dx[w].clone() for w in sorted(ps.dx)]
+
+    a = ProjectionSet(shape, 256, dev, seed=5)
+    b = ProjectionSet(shape, 256, dev, seed=5, overlap_weight_quantization=False)
+    a.step(), b.step()
+    first_a, first_b = buckets(a), buckets(b)
+    for x, y in zip(first_a, first_b):
+        assert torch.equal(x, y)
+    a.step()  # second eager step: the second pair of seeds per linear
+    second_a = buckets(a)
+    assert any(not torch.equal(x, y) for x, y in zip(first_a, second_a))  # the seeds did change the gradients
+    graph = b.capture_step()  # capture draws the same second seeds
+    graph.replay()
+    for x, y in zip(second_a, buckets(b)):
+        assert torch.equal(x, y)
+    assert_no_timeouts(pkg)
