@@ -438,6 +438,17 @@ typedef struct nvfp4_linear_backward_args {
  * dX = dY.W and dW = dY^T.X on the tcgen05 GEMM. */
 int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args* args /* host */);
 
+/* utils/nvfp4_tc_matmul/launcher.rs:23-87  Nvfp4TcMatmulModule::matmul_ms_eden : out[m][n] (f32) = a[m][k] . b_t[n][k]^T
+ * with both operands MS-EDEN quantized (caller-given global scales, the second with scale_seed ^ 0x9e3779b9) and K
+ * zero-padded to a multiple of 64.  The operand structs are caller scratch: bytes [rows * padded_k / 2], scales_packed
+ * [nvfp4_scale_packed_len(rows, padded_k)], global_scales [rows], chunk_amax [rows * padded_k / 32]; their global_scale
+ * member is not used.  The reference's padded f32 copies of the operands are not needed. */
+int nvfp4_tc_matmul_ms_eden(void* stream, const float* a, const float* b_t, float* out,
+                            const nvfp4_ms_eden_operand* a_q, float a_global_scale,
+                            const nvfp4_ms_eden_operand* b_q, float b_global_scale, uint32_t m, uint32_t n, uint32_t k,
+                            uint32_t sign_seed, uint32_t scale_seed);
+
+
 #ifdef __cplusplus
 }
 #endif

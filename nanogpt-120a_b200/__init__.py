@@ -97,6 +97,7 @@ _SIGNATURES = {
     "nvfp4_fp32_transpose_to_nvfp4_four_six_padded": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _U],
     "nvfp4_quantize_four_six": [_P, _P, c_int, _P, c_int, _U, _U, _P, _P, c_int, _P],
     "nvfp4_quantize_four_six_rowwise_fused": [_P, _P, c_int, _U, _U, _P, _P, c_int, _P, _P, _P],
+    "nvfp4_tc_matmul_ms_eden": [_P, _P, _P, _P, POINTER(MsEdenOperand), _F, POINTER(MsEdenOperand), _F, _U, _U, _U, _U, _U],
     "nvfp4_relu2_backward": [_P, _P, _P, _P, _U],
     "nvfp4_relu2_backward_f16": [_P, _P, _P, _P, _U],
     "nvfp4_relu2_backward_bf16": [_P, _P, _P, _P, ctypes.c_uint64],
@@ -496,6 +497,32 @@ class Nvfp4QuantModule:
                                                                                   scale_seed):
         return self._named_transpose("nvfp4_rowwise_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale",
                                      src, dst_row_len, sign_seed, scale_seed)
+
+
+class Nvfp4TcMatmulModule:
+    """utils/nvfp4_tc_matmul/launcher.rs:23-87."""
+
+    def matmul_ms_eden(self, a: torch.Tensor, b_t: torch.Tensor, sign_seed: int, scale_seed: int,
+                       a_global_scale: float = 1.0, b_global_scale: float = 1.0):
+        """out[m, n] = a[m, k] . b_t[n, k]^T, both operands MS-EDEN quantized with the given global scales.
+        Returns (out f32, a_quantized, b_quantized) with the operands as Nvfp4Tensor (packed scales)."""
+        _require_cuda()
+        assert a.dtype == torch.float32 and b_t.dtype == torch.float32 and a.shape[1] == b_t.shape[1]
+        (m, k), n, dev = a.shape, b_t.shape[0], a.device
+        pk = padded_k(k)
+
+        def operand(rows):
+            t = Nvfp4Tensor(_empty_u8(rows * pk // 2, dev), _empty_u8(scale_packed_len(rows, pk), dev),
+                            torch.empty(rows, dtype=torch.float32, device=dev), rows, pk, packed=True, rowwise=True)
+            chunk = torch.empty(max(1, rows * pk // 32), dtype=torch.float32, device=dev)
+            return t, chunk, MsEdenOperand(_ptr(t.bytes), _ptr(t.scales), _ptr(t.global_scales), c_void_p(None), _ptr(chunk))
+
+        ta, ca, oa = operand(m)
+        tb, cb, ob = operand(n)
+        out = torch.empty((m, n), dtype=torch.float32, device=dev)
+        _call("nvfp4_tc_matmul_ms_eden", _stream(), _ptr(a), _ptr(b_t), _ptr(out), ctypes.byref(oa), a_global_scale,
+              ctypes.byref(ob), b_global_scale, m, n, k, sign_seed & 0xFFFFFFFF, scale_seed & 0xFFFFFFFF)
+        return out, ta, tb
 
 
 class MlpModule:

@@ -574,6 +574,52 @@ int nvfp4_linear_bias_grad_bf16(void* stream, const void* e, float* dbias, uint3
   return launch_bias_grad(S(stream), e, NVFP4_DTYPE_BF16, dbias, token_count, output_dim);
 }
 
+// ---- generic MS-EDEN matmul ---------------------------------------------------------------------
+int nvfp4_tc_matmul_ms_eden(void* stream, const float* a, const float* b_t, float* out,
+                            const nvfp4_ms_eden_operand* a_q, float a_global_scale,
+                            const nvfp4_ms_eden_operand* b_q, float b_global_scale, uint32_t m, uint32_t n, uint32_t k,
+                            uint32_t sign_seed, uint32_t scale_seed) {
+  if (!a_q || !b_q || !out || (m && k && !a) || (n && k && !b_t)) return invalid("tc_matmul_ms_eden: null pointer");
+  if (m == 0 || n == 0) return 0;
+  if (k == 0) return invalid("tc_matmul_ms_eden: k must be non-zero");
+  const uint32_t pk = padded_k(k);
+  // both operands: MS-EDEN rows with the caller's global scale, K zero-padded to a multiple of 64 on the
+  // fly (utils/nvfp4_tc_matmul/{launcher.rs:23-69,quantize.rs:6-32}; no padded f32 copies are made)
+  nvfp4_ms_eden_args qa = rows_args(a, a_q->bytes, a_q->scales_packed, a_q->global_scales, a_q->chunk_amax, m, k, pk,
+                                    kQuartetSO, sign_seed, scale_seed);
+  qa.scale_layout = NVFP4_SCALES_PACKED;
+  qa.host_global_scale = a_global_scale;
+  qa.host_global_scale_valid = 1;
+  int rc = nvfp4_ms_eden_quantize(stream, &qa);
+  if (rc) return rc;
+  nvfp4_ms_eden_args qb = rows_args(b_t, b_q->bytes, b_q->scales_packed, b_q->global_scales, b_q->chunk_amax, n, k, pk,
+                                    kQuartetSO, sign_seed, scale_seed ^ 0x9e3779b9u);
+  qb.scale_layout = NVFP4_SCALES_PACKED;
+  qb.host_global_scale = b_global_scale;
+  qb.host_global_scale_valid = 1;
+  rc = nvfp4_ms_eden_quantize(stream, &qb);
+  if (rc) return rc;
+  // out = acc * a_scale[row] * b_scale (launcher.rs:71-86); every row of b carries the same scale
+  nvfp4_gemm_args g;
+  std::memset(&g, 0, sizeof(g));
+  g.a_bytes = a_q->bytes;
+  g.a_scales = a_q->scales_packed;
+  g.a_global = a_q->global_scales;
+  g.b_bytes = b_q->bytes;
+  g.b_scales = b_q->scales_packed;
+  g.b_global = b_q->global_scales;
+  g.out = out;
+  g.m = m;
+  g.n = n;
+  g.k = pk;
+  g.ldo = n;
+  g.global_scale_mode = NVFP4_GS_ROWWISE_A;
+  g.weight_global_scale = 1.0f;
+  g.epilogue = NVFP4_EPI_NONE;
+  g.out_dtype = NVFP4_DTYPE_F32;
+  return nvfp4_gemm(stream, &g);
+}
+
 int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args* a) {
   if (!a) return invalid("linear_backward: null args");
   const uint32_t T = a->token_count, I = a->input_dim, O = a->output_dim;

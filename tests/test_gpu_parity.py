@@ -710,6 +710,35 @@ def test_linear_backward_sharded_equals_whole(pkg, oracle, dev):
     assert_no_timeouts(pkg)
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 1, 65), (48, 40, 200), (256, 192, 1024)])
+def test_tc_matmul_ms_eden(pkg, oracle, dev, m, n, k):
+    """utils/nvfp4_tc_matmul/launcher.rs:23-87 (the (1, 1, 65) all-ones case is the reference's own test,
+    tests/nvfp4_tc_matmul.rs:20-49): both quantized operands bit-exact, the product within the GEMM tolerance
+    of the dequantized dot products."""
+    mod = pkg.Nvfp4TcMatmulModule()
+    if (m, n, k) == (1, 1, 65):
+        a, b = torch.ones(m, k), torch.full((n, k), 0.5)
+        ga = gb = 1.0
+    else:
+        a = torch.from_numpy(normal(81, (m, k)).astype(np.float32))
+        b = torch.from_numpy(normal(82, (n, k), 0.02).astype(np.float32))
+        ga = oracle.ms_eden_global_scale(float(a.abs().max()))
+        gb = oracle.ms_eden_global_scale(float(b.abs().max()))
+    out, ta, tb = mod.matmul_ms_eden(a.to(dev), b.to(dev), SIGN, SCALE, ga, gb)
+    pk = oracle.padded_k(k)
+    oa = oracle.ms_eden(0, a.numpy(), m, pk, ga, SIGN, SCALE, want_chunk_amax=False)
+    ob = oracle.ms_eden(0, b.numpy(), n, pk, gb, SIGN, SCALE ^ 0x9E3779B9, want_chunk_amax=False)
+    for t, o, rows in ((ta, oa, m), (tb, ob, n)):
+        assert np.array_equal(cpu(t.bytes), o[0])
+        assert np.array_equal(cpu(t.scales), oracle.scale_pack(o[1], rows, pk))
+        assert np.array_equal(cpu(t.global_scales), o[2])
+    want = oracle.gemm(oa[:3], (ob[0], ob[1], np.array([gb], np.float32)), m, pk, n, 2)
+    assert rel_fro(cpu(out), want) <= GEMM_TOL
+    if k == 65:
+        assert abs(float(cpu(out)[0, 0]) - float(want[0, 0])) <= 1.0e-5 * max(1.0, abs(float(want[0, 0])))
+    assert_no_timeouts(pkg)
+
+
 # ------------------------------------------------------------------------------------------ projection set
 
 def test_projection_set_step_streams_and_graph(pkg, dev):
