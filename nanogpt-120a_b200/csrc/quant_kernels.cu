@@ -1426,8 +1426,18 @@ __global__ void __launch_bounds__(256) col_sum_reduce_kernel(const float* __rest
   const uint32_t lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const uint32_t c = blockIdx.x * 32 + lane;
   float acc = 0.0f;
-  if (c < n)
-    for (uint32_t t = w; t < tiles; t += 8) acc += __ldg(partials + static_cast<size_t>(t) * n + c);
+  if (c < n) {
+    // sixteen loads in flight per thread, added in tile order (the loads dominate: few CTAs, long latency)
+    uint32_t t = w;
+    for (; t + 8 * 15 < tiles; t += 8 * 16) {
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = __ldg(partials + static_cast<size_t>(t + 8 * j) * n + c);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc += v[j];
+    }
+    for (; t < tiles; t += 8) acc += __ldg(partials + static_cast<size_t>(t) * n + c);
+  }
   sums[threadIdx.x] = acc;
   __syncthreads();
   if (w == 0 && c < n) {
