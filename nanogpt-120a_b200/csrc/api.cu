@@ -226,14 +226,14 @@ static int validate_ms_eden(const nvfp4_ms_eden_args* a) {
 
 // Row operand + transposed operand of one matrix in a single pass (same scale, same signs).
 static int ms_eden_pair(void* stream, nvfp4_ms_eden_args rows, nvfp4_ms_eden_args transposed,
-                        float* col_sum_partials = nullptr) {
+                        float* col_sum_partials = nullptr, const float* amax_in = nullptr, float* gs_out = nullptr) {
   rows.src_kind = NVFP4_SRC_F32_ROWS;
   transposed.src_kind = NVFP4_SRC_F32_TRANSPOSED;
   int rc = validate_ms_eden(&rows);
   if (rc) return rc;
   rc = validate_ms_eden(&transposed);
   if (rc) return rc;
-  return launch_ms_eden_pair(S(stream), rows, transposed, col_sum_partials);
+  return launch_ms_eden_pair(S(stream), rows, transposed, col_sum_partials, amax_in, gs_out);
 }
 
 static nvfp4_ms_eden_args rows_args(const float* x, uint8_t* out_fp4, uint8_t* out_scales, float* out_gss,
@@ -662,20 +662,11 @@ int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args
   bool fuse_dbias = a->dbias != nullptr && partial_bytes <= dx_bytes &&
                     (reinterpret_cast<uintptr_t>(a->dinput) & 3u) == 0;
 
-  // 2. dY: tensor amax -> one global scale shared by the row and the transposed operand
+  // 2. dY: tensor amax -> one global scale shared by the row and the transposed operand.  The amax
+  //    pass is enqueued further down, once it is known whether the pair kernel can turn the amax into
+  //    the scale by itself (whole tiles) or a one-thread kernel has to do it.
   const uint64_t ne = static_cast<uint64_t>(T) * O;
-  const float* e_gs = a->e_global_scale_override;
-  if (!e_gs) {
-    if (a->precomputed_e_amax_chunks == 0) {
-      rc = launch_tensor_amax(s, a->e, a->e_dtype, a->e_h.chunk_amax, a->e_h.global_scale, ne);
-      if (rc) return rc;
-      rc = launch_ms_eden_scale_from_amax(s, a->e_h.global_scale, a->e_h.global_scale);
-    } else {
-      rc = launch_amax_from_chunks(s, a->e_h.chunk_amax, a->e_h.global_scale, a->precomputed_e_amax_chunks, 1);
-    }
-    if (rc) return rc;
-    e_gs = a->e_h.global_scale;
-  }
+  const float* e_gs = a->e_global_scale_override ? a->e_global_scale_override : a->e_h.global_scale;
   nvfp4_ms_eden_args q;
   std::memset(&q, 0, sizeof(q));
   q.src_dtype = a->e_dtype;
@@ -710,8 +701,25 @@ int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args
     rc = launch_bias_grad(s, a->e, a->e_dtype, a->dbias, T, O);
     if (rc) return rc;
   }
+  const float* amax_in = nullptr;
+  if (!a->e_global_scale_override) {
+    if (a->precomputed_e_amax_chunks != 0) {
+      rc = launch_amax_from_chunks(s, a->e_h.chunk_amax, a->e_h.global_scale, a->precomputed_e_amax_chunks, 1);
+    } else if (ms_eden_pair_takes_amax(q, qt)) {
+      // the amax accumulates in word 0 of the (otherwise unused) chunk scratch; the pair kernel derives the
+      // scale from it and publishes it in e_h.global_scale
+      rc = launch_tensor_amax(s, a->e, a->e_dtype, nullptr, a->e_h.chunk_amax, ne);
+      amax_in = a->e_h.chunk_amax;
+    } else {
+      rc = launch_tensor_amax(s, a->e, a->e_dtype, a->e_h.chunk_amax, a->e_h.global_scale, ne);
+      if (rc) return rc;
+      rc = launch_ms_eden_scale_from_amax(s, a->e_h.global_scale, a->e_h.global_scale);
+    }
+    if (rc) return rc;
+  }
   float* partials = fuse_dbias ? static_cast<float*>(a->dinput) : nullptr;
-  rc = ms_eden_pair(stream, q, qt, partials);  // one pass over dY for both orientations (+ column sums)
+  // one pass over dY for both orientations (+ column sums)
+  rc = ms_eden_pair(stream, q, qt, partials, amax_in, amax_in ? a->e_h.global_scale : nullptr);
   if (rc) return rc;
   if (fuse_dbias) {
     rc = launch_col_sum_reduce(s, partials, a->dbias, ms_eden_pair_row_tiles(T), O);

@@ -32,8 +32,11 @@ int launch_schedule_free_materialize(cudaStream_t s, const float* z, const float
 int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a);
 // Pair quantization; when col_sum_partials != nullptr (and ms_eden_pair_is_tiled) it also writes the
 // per-row-tile column sums [ms_eden_pair_row_tiles(rows)][cols] for launch_col_sum_reduce.
+// amax_in / gs_out (only when ms_eden_pair_takes_amax): the kernel derives the global scale from amax_in[0]
+// itself and writes it to gs_out[0]; rows.global_scale / transposed.global_scale are then not read.
 int launch_ms_eden_pair(cudaStream_t s, const nvfp4_ms_eden_args& rows, const nvfp4_ms_eden_args& transposed,
-                        float* col_sum_partials = nullptr);
+                        float* col_sum_partials = nullptr, const float* amax_in = nullptr, float* gs_out = nullptr);
+bool ms_eden_pair_takes_amax(const nvfp4_ms_eden_args& rows, const nvfp4_ms_eden_args& transposed);
 bool ms_eden_pair_is_tiled(const nvfp4_ms_eden_args& rows, const nvfp4_ms_eden_args& transposed);
 uint32_t ms_eden_pair_row_tiles(uint32_t rows);
 int launch_col_sum_reduce(cudaStream_t s, const float* partials, float* dbias, uint32_t tiles, uint32_t n);

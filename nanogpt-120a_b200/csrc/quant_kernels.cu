@@ -212,10 +212,13 @@ __global__ void __launch_bounds__(256) amax_from_chunks_kernel(const float* __re
 }
 
 // out[0] = MS-EDEN global scale of amax[0] (single thread).
-__global__ void ms_eden_scale_from_amax_kernel(const float* __restrict__ amax, float* __restrict__ out) {
+// utils/quartet.rs:1-12: global scale of an MS-EDEN operand from the amax of its source.
+__device__ __forceinline__ float ms_eden_scale_of_amax(float a) {
   const float so = (17.0f / 16.0f) * 0.93f;
-  const float a = amax[0];
-  out[0] = (a == 0.0f) ? 1.0f : a * so / (256.0f * 6.0f);
+  return (a == 0.0f) ? 1.0f : a * so / (256.0f * 6.0f);
+}
+__global__ void ms_eden_scale_from_amax_kernel(const float* __restrict__ amax, float* __restrict__ out) {
+  out[0] = ms_eden_scale_of_amax(amax[0]);
 }
 
 // ============================================================================
@@ -843,6 +846,10 @@ struct MsEdenTileParams {
   MsEdenOut t;  // transposed operand: rows = src_cols, K = src_rows (padded)
   MsEdenOut r;  // row operand (pair mode): rows = src_rows, K = src_cols (padded)
   float* col_sum_partials;  // pair mode, optional: [row tiles][src_cols] column sums of each tile
+  // whole-tile pair kernel, optional: take the global scale from the source amax (every thread
+  // evaluates the same two operations) and publish it, instead of a one-thread kernel in between
+  const float* amax_in;
+  float* gs_out;
 };
 
 constexpr int kTileRows = 128, kTileCols = 64, kTileLd = kTileCols + 1;
@@ -1015,7 +1022,13 @@ __global__ void __launch_bounds__(256, 2) ms_eden_pair_kernel(const MsEdenTilePa
   __shared__ __align__(8) float quarter_sum[4][kTileCols];
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const T* x = static_cast<const T*>(p.x);
-  const float gs = p.use_host_scale ? p.global_scale_host : p.global_scale_dev[0];
+  float gs;
+  if (p.amax_in) {
+    gs = ms_eden_scale_of_amax(p.amax_in[0]);
+    if (blockIdx.x == 0 && tid == 0) p.gs_out[0] = gs;
+  } else {
+    gs = p.use_host_scale ? p.global_scale_host : p.global_scale_dev[0];
+  }
   const uint32_t stage_base = static_cast<uint32_t>(__cvta_generic_to_shared(pair_stage));
 
   // 16-byte pieces of the tile, row-major, PT::kPiecesPerThread per thread
@@ -1754,9 +1767,19 @@ int launch_col_sum_reduce(cudaStream_t s, const float* partials, float* dbias, u
   NVFP4_RETURN_LAST();
 }
 
+static bool pair_whole_tiles(const nvfp4_ms_eden_args& r, const nvfp4_ms_eden_args& t) {
+  return r.rows % kTileRows == 0 && r.cols % kTileCols == 0 && t.dst_row_len == r.rows && r.dst_row_len == r.cols &&
+         (reinterpret_cast<uintptr_t>(r.x) & 15u) == 0;
+}
+
+bool ms_eden_pair_takes_amax(const nvfp4_ms_eden_args& r, const nvfp4_ms_eden_args& t) {
+  return ms_eden_pair_is_tiled(r, t) && pair_whole_tiles(r, t);
+}
+
 int launch_ms_eden_pair(cudaStream_t s, const nvfp4_ms_eden_args& r, const nvfp4_ms_eden_args& t,
-                        float* col_sum_partials) {
+                        float* col_sum_partials, const float* amax_in, float* gs_out) {
   const uint32_t rows = r.rows, cols = r.cols;
+  if (amax_in && !ms_eden_pair_takes_amax(r, t)) return static_cast<int>(cudaErrorInvalidValue);
   if (!ms_eden_pair_is_tiled(r, t)) {
     int rc = launch_ms_eden(s, r);
     return rc ? rc : launch_ms_eden(s, t);
@@ -1777,8 +1800,9 @@ int launch_ms_eden_pair(cudaStream_t s, const nvfp4_ms_eden_args& r, const nvfp4
   p.t = make_out(t, cols);
   p.r = make_out(r, rows);
   p.col_sum_partials = col_sum_partials;
-  const bool whole_tiles = rows % kTileRows == 0 && cols % kTileCols == 0 && t.dst_row_len == rows &&
-                           r.dst_row_len == cols && (reinterpret_cast<uintptr_t>(r.x) & 15u) == 0;
+  p.amax_in = amax_in;
+  p.gs_out = gs_out;
+  const bool whole_tiles = pair_whole_tiles(r, t);
   if (whole_tiles) {
     const uint32_t tiles_x = cols / kTileCols, tile_count = tiles_x * (rows / kTileRows);
     const uint32_t grid = min(tile_count, 148u * 2u);
