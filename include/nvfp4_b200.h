@@ -160,6 +160,18 @@ int nvfp4_relu2_backward_f16(void* stream, const uint16_t* pre_activation /* IEE
 int nvfp4_relu2_backward_bf16(void* stream, const void* pre_activation, const void* d_out, void* d_pre_activation,
                               uint64_t len);
 
+/* The same element-wise pass that also emits the amax of what it stores, as a chunk list (one value per
+ * CTA, nvfp4_relu2_backward_amax_chunks(len) of them, written to chunk_amax and counted in *out_chunks).
+ * Point chunk_amax at nvfp4_linear_backward_args.e_h.chunk_amax of the MLP fc backward and pass *out_chunks
+ * as precomputed_e_amax_chunks: the linear backward then skips its own amax pass over dY, the hand-over the
+ * reference makes for the loss gradient (gpt/loss/kernels.rs:67-88 -> backward/final_head/run.rs:34,54).
+ * Outputs of the linear backward are bit-identical either way.  pre_kind: 0 f32, 1 bf16, 2 IEEE f16;
+ * grad_dtype (d_out and d_pre_activation): NVFP4_DTYPE_F32 or NVFP4_DTYPE_BF16. */
+uint32_t nvfp4_relu2_backward_amax_chunks(uint64_t len);
+int nvfp4_relu2_backward_amax(void* stream, const void* pre_activation, int pre_kind, const void* d_out,
+                              void* d_pre_activation, int grad_dtype, uint64_t len, float* chunk_amax,
+                              uint32_t chunk_capacity, uint32_t* out_chunks);
+
 /* gpt/optimizer/launcher/update.rs:11-58  OptimizerModule::materialize_schedule_free
  * (kernels gpt/optimizer/schedule_free/{value,amax,four_six}.rs): the weight a schedule-free optimizer
  * evaluates with, y = z + beta * (x - z) of the two f32 masters, quantized four-six with a tensor scale

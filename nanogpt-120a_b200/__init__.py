@@ -101,6 +101,7 @@ _SIGNATURES = {
     "nvfp4_relu2_backward": [_P, _P, _P, _P, _U],
     "nvfp4_relu2_backward_f16": [_P, _P, _P, _P, _U],
     "nvfp4_relu2_backward_bf16": [_P, _P, _P, _P, ctypes.c_uint64],
+    "nvfp4_relu2_backward_amax": [_P, _P, c_int, _P, _P, c_int, ctypes.c_uint64, _P, _U, POINTER(c_uint32)],
     "nvfp4_materialize_schedule_free": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _U],
     "nvfp4_materialize_schedule_free_matrix": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, _F, _U, _U],
     "nvfp4_ms_eden_quantize": [_P, POINTER(MsEdenArgs)],
@@ -149,6 +150,7 @@ _SPECIAL = {
     "nvfp4_scale_padded_mn_extent": (c_uint32, [_U]),
     "nvfp4_scale_packed_len": (c_size_t, [_U, _U]),
     "nvfp4_tensor_amax_chunks": (c_uint32, [_U]),
+    "nvfp4_relu2_backward_amax_chunks": (c_uint32, [ctypes.c_uint64]),
 }
 EXPORTED_SYMBOLS = sorted(list(_SIGNATURES) + list(_SPECIAL))
 
@@ -548,6 +550,24 @@ class MlpModule:
         return out
 
     relu2_backward_f16 = relu2_backward
+
+    def relu2_backward_amax(self, pre_activation: torch.Tensor, d_out: torch.Tensor, chunk_amax: torch.Tensor,
+                            d_pre_activation: Optional[torch.Tensor] = None) -> tuple:
+        """`relu2_backward` that also writes the amax of the gradient it stores as a chunk list into
+        `chunk_amax` (normally `LinearBackwardScratch.e_h["chunk_amax"]` of the fc linear's backward).  Returns
+        (d_pre, chunk_count); pass chunk_count as `precomputed_e_amax_chunks` to `backward_ms_eden`, which then
+        skips its own amax pass over the gradient (gpt/loss/kernels.rs:67-88 hands the loss gradient over the
+        same way)."""
+        _require_cuda()
+        n = pre_activation.numel()
+        assert d_out.numel() == n and d_out.dtype in (torch.float32, torch.bfloat16)
+        pre_kind = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[pre_activation.dtype]
+        out = torch.empty_like(d_out) if d_pre_activation is None else d_pre_activation
+        assert out.dtype == d_out.dtype and chunk_amax.dtype == torch.float32
+        chunks = c_uint32(0)
+        _call("nvfp4_relu2_backward_amax", _stream(), _ptr(pre_activation), pre_kind, _ptr(d_out), _ptr(out),
+              _dtype_code(d_out), n, _ptr(chunk_amax), chunk_amax.numel(), ctypes.byref(chunks))
+        return out, chunks.value
 
 
 class OptimizerModule:

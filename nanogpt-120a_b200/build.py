@@ -67,5 +67,22 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_cpp_driver(force: bool = False) -> str:
+    """Compiles tests/cpp/mlp_layer_driver.cpp (a C++ caller of include/nvfp4_b200.hpp that walks one MLP
+    block forward and backward) against the in-tree library; returns the binary's path."""
+    root = os.path.abspath(os.path.join(HERE, ".."))
+    src = os.path.join(root, "tests", "cpp", "mlp_layer_driver.cpp")
+    out_dir = os.path.join(root, "tests", "cpp", "build")
+    exe = os.path.join(out_dir, "mlp_layer_driver")
+    include = os.path.join(root, "include")
+    deps = [src, os.path.join(include, "nvfp4_b200.hpp"), os.path.join(include, "nvfp4_b200.h"), build()]
+    if force or _stale(exe, deps):
+        os.makedirs(out_dir, exist_ok=True)
+        subprocess.check_call([_nvcc(), "-O2", "-std=c++17", "-I", include, src, "-o", exe, "-L", HERE,
+                               "-lnvfp4_b200", "-Xlinker", "-rpath", "-Xlinker", HERE])
+    return exe
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_cpp_driver(force="--force" in sys.argv))

@@ -176,6 +176,22 @@ int nvfp4_relu2_backward_bf16(void* stream, const void* pre_activation, const vo
   return launch_relu2_backward(S(stream), pre_activation, 1, d_out, d_pre_activation, 1, len);
 }
 
+uint32_t nvfp4_relu2_backward_amax_chunks(uint64_t len) { return len ? relu2_backward_grid(len) : 0; }
+int nvfp4_relu2_backward_amax(void* stream, const void* pre_activation, int pre_kind, const void* d_out,
+                              void* d_pre_activation, int grad_dtype, uint64_t len, float* chunk_amax,
+                              uint32_t chunk_capacity, uint32_t* out_chunks) {
+  if (pre_kind < 0 || pre_kind > 2) return invalid("relu2_backward_amax: pre_kind must be 0 (f32), 1 (bf16) or 2 (f16)");
+  if (grad_dtype != NVFP4_DTYPE_F32 && grad_dtype != NVFP4_DTYPE_BF16)
+    return invalid("relu2_backward_amax: grad_dtype must be NVFP4_DTYPE_F32 or NVFP4_DTYPE_BF16");
+  if (!chunk_amax || !out_chunks) return invalid("relu2_backward_amax: null chunk_amax / out_chunks");
+  if (len && (!pre_activation || !d_out || !d_pre_activation)) return invalid("relu2_backward_amax: null pointer");
+  const uint32_t chunks = nvfp4_relu2_backward_amax_chunks(len);
+  if (chunks > chunk_capacity) return invalid("relu2_backward_amax: chunk_amax holds fewer than the chunks of len");
+  *out_chunks = chunks;
+  return launch_relu2_backward(S(stream), pre_activation, pre_kind, d_out, d_pre_activation,
+                               grad_dtype == NVFP4_DTYPE_BF16, len, chunk_amax);
+}
+
 // ---- schedule-free weight materialisation ---------------------------------------------------
 int nvfp4_materialize_schedule_free(void* stream, const float* z_master, const float* x_master, float* chunk_amax,
                                     float* amax, uint8_t* bytes, uint8_t* scales, float* global_scale, float beta,

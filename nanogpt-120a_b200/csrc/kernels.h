@@ -51,9 +51,11 @@ int launch_crop_f32(cudaStream_t s, const float* src, float* dst, uint32_t rows,
 int launch_postop(cudaStream_t s, float* raw, float* other, const uint8_t* bias_bytes, const uint8_t* bias_scales,
                   const float* bias_gs, uint32_t rows, uint32_t cols, int mode);
 int launch_bias_grad(cudaStream_t s, const void* e, int dtype, float* dbias, uint32_t tokens, uint32_t n);
-// d_pre = (d_out * 2) * max(pre, 0); pre_kind 0 f32, 1 bf16, 2 f16; gradients f32 or (grad_bf16) bf16
+// d_pre = (d_out * 2) * max(pre, 0); pre_kind 0 f32, 1 bf16, 2 f16; gradients f32 or (grad_bf16) bf16.
+// chunk_amax (optional, relu2_backward_grid(n) floats): per-CTA amax of the stored gradient.
 int launch_relu2_backward(cudaStream_t s, const void* pre, int pre_kind, const void* d_out, void* d_pre, int grad_bf16,
-                          uint64_t n);
+                          uint64_t n, float* chunk_amax = nullptr);
+uint32_t relu2_backward_grid(uint64_t n);
 
 // gemm_tcgen05.cu ---------------------------------------------------------------------------
 int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a);

@@ -1289,12 +1289,17 @@ __device__ __forceinline__ void store8_grad(void* p, size_t i, const float (&v)[
   }
 }
 
-template <int kPre, bool kGradBf16>
+// With chunk_amax set the kernel also emits, per CTA, the amax of the values it stored (after their rounding to
+// the gradient type): the chunk list nvfp4_linear_backward_ms_eden accepts in place of its own amax pass over dY
+// (the hand-over gpt/loss/kernels.rs:67-88 -> backward/final_head/run.rs:34,54 makes for the loss gradient).
+template <int kPre, bool kGradBf16, bool kAmax>
 __global__ void __launch_bounds__(256) relu2_backward_kernel(const void* __restrict__ pre, const void* __restrict__ d_out,
-                                                              void* __restrict__ d_pre, uint64_t n, int vectorized) {
+                                                              void* __restrict__ d_pre, uint64_t n, int vectorized,
+                                                              float* __restrict__ chunk_amax) {
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * 256;
   const uint64_t tid = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
   const uint64_t vec_n = vectorized ? n / 8 : 0;
+  float m = 0.0f;
   for (uint64_t i = tid; i < vec_n; i += stride) {
     float p[8], d[8], r[8];
     load8_pre<kPre>(pre, i * 8, p);
@@ -1302,15 +1307,39 @@ __global__ void __launch_bounds__(256) relu2_backward_kernel(const void* __restr
 #pragma unroll
     for (int k = 0; k < 8; ++k) r[k] = (d[k] * 2.0f) * max_f32(p[k], 0.0f);
     store8_grad<kGradBf16>(d_pre, i * 8, r);
+    if (kAmax) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float stored = kGradBf16 ? __bfloat162float(__float2bfloat16_rn(r[k])) : r[k];
+        m = max_f32(m, fabsf(stored));
+      }
+    }
   }
   for (uint64_t i = vec_n * 8 + tid; i < n; i += stride) {
     const float p = load1_pre<kPre>(pre, i);
     const float d = load1_pre<kGradBf16 ? kPreBf16 : kPreF32>(d_out, i);
     const float r = (d * 2.0f) * max_f32(p, 0.0f);
-    if (kGradBf16)
-      static_cast<__nv_bfloat16*>(d_pre)[i] = __float2bfloat16_rn(r);
-    else
+    float stored = r;
+    if (kGradBf16) {
+      const __nv_bfloat16 h = __float2bfloat16_rn(r);
+      static_cast<__nv_bfloat16*>(d_pre)[i] = h;
+      stored = __bfloat162float(h);
+    } else {
       static_cast<float*>(d_pre)[i] = r;
+    }
+    if (kAmax) m = max_f32(m, fabsf(stored));
+  }
+  if (kAmax) {
+    __shared__ float partial[8];
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float r = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) r = max_f32(r, partial[i]);
+      chunk_amax[blockIdx.x] = r;
+    }
   }
 }
 
@@ -1833,13 +1862,21 @@ int launch_ms_eden_pair(cudaStream_t s, const nvfp4_ms_eden_args& r, const nvfp4
   return rc;
 }
 
+uint32_t relu2_backward_grid(uint64_t n) { return blocks_for((n + 7) / 8, 256, 148 * 8); }
+
 int launch_relu2_backward(cudaStream_t s, const void* pre, int pre_kind, const void* d_out, void* d_pre, int grad_bf16,
-                          uint64_t n) {
+                          uint64_t n, float* chunk_amax) {
   if (n == 0) return 0;
   const int vectorized = ((reinterpret_cast<uintptr_t>(pre) | reinterpret_cast<uintptr_t>(d_out) |
                            reinterpret_cast<uintptr_t>(d_pre)) & 15u) == 0;
-  const uint32_t grid = blocks_for((n + 7) / 8, 256, 148 * 8);
-#define NVFP4_RELU2_BWD(K, G) relu2_backward_kernel<K, G><<<grid, 256, 0, s>>>(pre, d_out, d_pre, n, vectorized)
+  const uint32_t grid = relu2_backward_grid(n);
+#define NVFP4_RELU2_BWD_A(K, G, A) \
+  relu2_backward_kernel<K, G, A><<<grid, 256, 0, s>>>(pre, d_out, d_pre, n, vectorized, chunk_amax)
+#define NVFP4_RELU2_BWD(K, G)                     \
+  do {                                            \
+    if (chunk_amax) NVFP4_RELU2_BWD_A(K, G, true); \
+    else NVFP4_RELU2_BWD_A(K, G, false);          \
+  } while (0)
   if (grad_bf16) {
     if (pre_kind == kPreF32) NVFP4_RELU2_BWD(kPreF32, true);
     else if (pre_kind == kPreBf16) NVFP4_RELU2_BWD(kPreBf16, true);
@@ -1850,6 +1887,7 @@ int launch_relu2_backward(cudaStream_t s, const void* pre, int pre_kind, const v
     else NVFP4_RELU2_BWD(kPreF16, false);
   }
 #undef NVFP4_RELU2_BWD
+#undef NVFP4_RELU2_BWD_A
   NVFP4_RETURN_LAST();
 }
 

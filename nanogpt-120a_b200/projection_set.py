@@ -146,6 +146,7 @@ class ProjectionSet:
             if (i, o) not in self.scratch:
                 self.scratch[(i, o)] = LinearBackwardScratch(tokens, i, o, device)
         self._weight_stream: Optional[torch.cuda.Stream] = None
+        self._weights_quantized = False
         self.overlap_weight_quantization = overlap_weight_quantization
         self.gemm_events: List[Tuple[torch.cuda.Event, torch.cuda.Event, int]] = []
         self.record_gemm_events = False
@@ -225,8 +226,14 @@ class ProjectionSet:
             self._reduce(l)
         self.grads.wait()
 
-    def step(self) -> None:
-        self.quantize_weights()
+    def step(self, weights_changed: bool = True) -> None:
+        """One forward + backward pass over this rank's tokens.  `weights_changed=False` (the second and later
+        micro-steps of a gradient accumulation, where no optimizer update happened in between) reuses the
+        packed NVFP4 weights of the previous step instead of re-quantizing the masters; W^T cannot be reused
+        the same way because its MS-EDEN form is drawn with fresh seeds in every linear backward."""
+        if weights_changed or not self._weights_quantized:
+            self.quantize_weights()
+            self._weights_quantized = True
         self.forward()
         self.backward()
 

@@ -636,6 +636,55 @@ def test_linear_backward_precomputed_x_amax(pkg, oracle, dev):
     assert_no_timeouts(pkg)
 
 
+@pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("shape", [(256, 128), (384, 192), (200, 100)])
+def test_relu2_backward_amax_hand_over(pkg, oracle, dev, kind, shape):
+    """The ReLU^2 backward that emits the amax of its own output: same gradient bytes as the plain entry
+    (and as the oracle, gpt/mlp/kernels.rs:72-104), chunk maxima whose max is the tensor amax, and a linear
+    backward fed with them (precomputed_e_amax_chunks) that differs in no output byte from one that reads dY."""
+    q, bwd, mlp = pkg.Nvfp4QuantModule(), pkg.LinearBackwardModule(), pkg.MlpModule()
+    tokens, out_dim = shape
+    in_dim = 128
+    pre = torch.from_numpy(normal(601, (tokens, out_dim), 1.0).astype(np.float32))
+    d = torch.from_numpy(normal(602, (tokens, out_dim), 1e-3).astype(np.float32))
+    pre[0, 0], pre[1, 2] = -0.0, float("nan")
+    if kind == "bf16":
+        pre, d = pre.bfloat16(), d.bfloat16()
+    elif kind == "f16":
+        pre = pre.half()
+    want = torch.from_numpy(oracle.relu2_backward(pre.float().numpy(), d.float().numpy()))
+    want = want.bfloat16() if kind == "bf16" else want
+    sc = pkg.LinearBackwardScratch(tokens, in_dim, out_dim, dev)
+    sc.e_h["chunk_amax"].fill_(float("inf"))  # stale content must not leak into the scale
+    got, chunks = mlp.relu2_backward_amax(pre.to(dev), d.to(dev), sc.e_h["chunk_amax"])
+    assert cpu(got.float()).tobytes() == want.float().numpy().tobytes()
+    assert 0 < chunks <= sc.e_h["chunk_amax"].numel()
+    finite = torch.nan_to_num(want.float(), nan=0.0).abs().max()
+    assert float(sc.e_h["chunk_amax"][:chunks].max()) == float(finite)
+    plain = mlp.relu2_backward(pre.to(dev), d.to(dev))
+    assert cpu(plain.float()).tobytes() == cpu(got.float()).tobytes()
+
+    x, w = bf16_normal(603, (tokens, in_dim)), bf16_normal(604, (out_dim, in_dim), 0.02)
+    # the NaN the element-wise check carried would poison every GEMM output: drop it for the hand-over check
+    pre_clean = torch.nan_to_num(pre.float(), nan=0.5).to(pre.dtype)
+    xq = q.quantize_four_six(x.to(dev), rowwise=True, packed=True, decoded_amax=True)
+    wq = q.quantize_four_six(w.to(dev), rowwise=False, packed=True)
+    outs = []
+    for hand_over in (False, True):
+        sc = pkg.LinearBackwardScratch(tokens, in_dim, out_dim, dev)
+        if hand_over:
+            e, chunks = mlp.relu2_backward_amax(pre_clean.to(dev), d.to(dev), sc.e_h["chunk_amax"])
+        else:
+            e, chunks = mlp.relu2_backward(pre_clean.to(dev), d.to(dev)), 0
+        dx, dw, db = bwd.backward_ms_eden(e=e, weight=wq, input=xq, scratch=sc, sign_seed=SIGN, scale_seed=SCALE,
+                                          precomputed_e_amax_chunks=chunks)
+        outs.append((cpu(sc.e_h["global_scale"]), cpu(sc.e_h["bytes"]), cpu(sc.e_t_h["bytes"]),
+                     cpu(sc.e_t_h["scales_packed"]), cpu(dx), cpu(dw), cpu(db)))
+    for a, b in zip(*outs):
+        assert a.tobytes() == b.tobytes()
+    assert_no_timeouts(pkg)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_linear_backward_edge_values_whole_tiles(pkg, oracle, dev, dtype):
     """The whole-tile quantizers (two chunks per thread, integer scale rounding with its range
@@ -765,4 +814,28 @@ def test_projection_set_step_streams_and_graph(pkg, dev):
     graph.replay()
     for x, y in zip(second_a, buckets(b)):
         assert torch.equal(x, y)
+    assert_no_timeouts(pkg)
+
+
+def test_projection_set_reuses_packed_weights(pkg, dev):
+    """A micro-step that keeps the packed NVFP4 weights of the previous step (no optimizer update in
+    between) launches fewer kernels and yields the same gradients as one that re-quantizes them."""
+    from nanogpt_120a_b200.projection_set import ModelShape, ProjectionSet
+
+    shape = ModelShape("tiny-proj-set", 2, 128, 256, 512)
+    a = ProjectionSet(shape, 256, dev, seed=9)
+    b = ProjectionSet(shape, 256, dev, seed=9)
+    a.step(), b.step()
+    lib = pkg.library()
+    n0 = lib.nvfp4_launch_count()
+    a.step(weights_changed=True)
+    n1 = lib.nvfp4_launch_count()
+    b.step(weights_changed=False)
+    n2 = lib.nvfp4_launch_count()
+    torch.cuda.synchronize()
+    assert (n1 - n0) - (n2 - n1) >= len(a.all_linears())  # at least the four-six launch of every weight
+    for x, y in zip(a.buckets, b.buckets):
+        assert torch.equal(x, y)
+    for la, lb in zip(a.all_linears(), b.all_linears()):
+        assert torch.equal(la.wq.bytes, lb.wq.bytes) and torch.equal(la.wq.scales, lb.wq.scales)
     assert_no_timeouts(pkg)
