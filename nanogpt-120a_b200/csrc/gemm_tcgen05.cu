@@ -734,6 +734,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       // reference order: (weight * a_scale) * b_scale, then acc * scale
       const float scale = __fmul_rn(__fmul_rn(p.weight, ga), gb);
       const uint32_t taddr_row = tmem_base + acc * kBlockN + ((ew * 32u) << 16);
+      // The accumulator buffer goes back to the MMA warp as soon as this warp's last tcgen05.ld of the
+      // tile has landed in registers: scaling, staging and the stores of that last sub-tile then run
+      // beside the next tile's main loop.
+      auto release_accumulator = [&]() {
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * acc);
+      };
       if (p.tma_store) {
         // Sub-tiles of 128 rows x 128 bytes go through the group's shared-memory ring and leave
         // with TMA stores (TMA reduce-add for split-K partial sums); rows / columns outside the
@@ -749,6 +757,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           epilogue_barrier(eg);
         }
+        // a group whose first sub-tile already lies outside the matrix reads nothing
+        if (n_blk * kBlockN + eg * kSub >= p.n) release_accumulator();
 #pragma unroll 1
         for (int c = eg * kSub; c < kBlockN; c += 2 * kSub) {
           const uint32_t col0 = n_blk * kBlockN + c;
@@ -759,6 +769,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int h = 0; h < kSub / 32; ++h) tcgen05_ld_32x32b_x32(taddr_row + c + 32 * h, r[h]);
             tcgen05_wait_ld();
+            if (c + 2 * kSub >= kBlockN || col0 + 2 * kSub >= p.n) release_accumulator();  // the group's last sub-tile
             if (add_bias) {
               // acc * scale + bias in one rounding (the reference rounds the product first; the
               // difference is below the f32 ulp and far inside the GEMM tolerance)
@@ -813,6 +824,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t r[32];
         tcgen05_ld_32x32b_x32(taddr_row + c, r);
         tcgen05_wait_ld();
+        if (c + 64 >= kBlockN) release_accumulator();
         const uint32_t col0 = n_blk * kBlockN + c;
         if (row_ok && col0 < p.n) {
           const uint32_t valid = min(32u, p.n - col0);
@@ -852,9 +864,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
       }  // direct-store path
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * acc);
       if (++acc == C::kAccStages) {
         acc = 0;
         acc_phase ^= 1u;
