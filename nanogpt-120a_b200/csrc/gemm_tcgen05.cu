@@ -726,6 +726,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       decode(w, m_blk, n_blk, split);
       const float ga_row = ga_next;
       if (w + w_step < w_end) ga_next = row_scale(w + w_step);
+      // the tile's bias slice goes through shared memory once (every row then reads it broadcast); it is
+      // fetched before the wait for the accumulator so that its latency hides behind the main loop.  The
+      // group's last barrier of the previous tile comes after that tile's last read of the slice.
+      const bool add_bias = p.tma_store && p.epilogue != NVFP4_EPI_NONE && (p.k_splits == 1 || split == 0);
+      if (add_bias) {
+        for (uint32_t i = gtid; i < static_cast<uint32_t>(kBlockN); i += 128) {
+          const uint32_t col = n_blk * kBlockN + i;
+          const float bv = col < p.n ? __ldg(p.bias + col) : 0.0f;
+          asm volatile("st.shared.f32 [%0], %1;" ::"r"(my_bias + i * 4), "f"(bv) : "memory");
+        }
+        epilogue_barrier(eg);
+      }
       if (!mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, kStatusEpilogueTimeout)) break;
       tcgen05_fence_after();
       const uint32_t row = m_blk * kBlockM + gtid;
@@ -747,16 +759,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         // with TMA stores (TMA reduce-add for split-K partial sums); rows / columns outside the
         // matrix are clipped by the tensor map.
         constexpr int kSub = SubTile<OutT>::kCols;
-        const bool add_bias = p.epilogue != NVFP4_EPI_NONE && (p.k_splits == 1 || split == 0);
-        if (add_bias) {
-          // the tile's bias slice goes through shared memory once; every row then reads it broadcast
-          for (uint32_t i = gtid; i < static_cast<uint32_t>(kBlockN); i += 128) {
-            const uint32_t col = n_blk * kBlockN + i;
-            const float bv = col < p.n ? __ldg(p.bias + col) : 0.0f;
-            asm volatile("st.shared.f32 [%0], %1;" ::"r"(my_bias + i * 4), "f"(bv) : "memory");
-          }
-          epilogue_barrier(eg);
-        }
         // a group whose first sub-tile already lies outside the matrix reads nothing
         if (n_blk * kBlockN + eg * kSub >= p.n) release_accumulator();
 #pragma unroll 1
