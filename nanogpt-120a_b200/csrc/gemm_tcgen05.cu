@@ -8,9 +8,8 @@
 // kernel in which
 //   warp 0      streams A / B nibble tiles with TMA (128-byte swizzle) and the packed
 //               scale-factor tiles with bulk copies into a shared-memory ring,
-//   warp 1      copies scale factors shared -> tensor memory (tcgen05.cp) and issues
-//               tcgen05.mma.kind::mxf4nvf4.block_scale (128 x BLOCK_N x 64 per instruction),
-//               FP32 accumulators in tensor memory,
+//   warp 1      issues tcgen05.mma.kind::mxf4nvf4.block_scale (128 x BLOCK_N x 64 per
+//               instruction), FP32 accumulators in tensor memory,
 //   warp 2      owns the tensor-memory allocation,
 //   warps 4..7 and 12..15  two epilogue groups: drain accumulators (tcgen05.ld), apply global
 //               scales / bias / ReLU^2 / residual, cast and store; the groups take alternate
@@ -18,7 +17,9 @@
 //               its index modulo four, so warps w and w + 8 share a lane quadrant),
 //   warps 8..11 move the scale factors shared -> tensor memory (tcgen05.st).
 // Accumulators are double buffered when BLOCK_N = 128 so the epilogue of one tile overlaps
-// the main loop of the next.  Every mbarrier wait is bounded: on expiry the kernel records
+// the main loop of the next; the 256-column tile has one accumulator buffer, which every epilogue
+// warp hands back as soon as its last tcgen05.ld of the tile has landed in registers, so that
+// scaling, staging and storing of that last sub-tile overlap the next main loop.  Every mbarrier wait is bounded: on expiry the kernel records
 // a status word, drains, frees its tensor memory and returns.
 //
 // No thread-block clusters, no multicast: every load reads this GPU's own memory.
