@@ -164,7 +164,7 @@ def run_reference(args):
         "note": "CPU restatement of the reference's math (the reference ships no CPU path; its Rust/cuda-oxide "
                 "kernels cannot be built on this box)",
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # --------------------------------------------------------------------------------------------
@@ -435,12 +435,33 @@ def run_gpu(args):
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
+_RESULT_STREAM = None
+
+
+def _reserve_stdout() -> None:
+    """Keeps the process's original stdout for the one JSON line and points file descriptor 1 at stderr for
+    everything else: libraries that write to stdout on their own (NCCL prints its version banner there when
+    NCCL_DEBUG is set in the environment) would otherwise put text in front of the result."""
+    global _RESULT_STREAM
+    if _RESULT_STREAM is None:
+        sys.stdout.flush()
+        _RESULT_STREAM = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    out = _RESULT_STREAM if _RESULT_STREAM is not None else sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def main():
+    _reserve_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
