@@ -218,6 +218,27 @@ __device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t (
       : "r"(taddr)
       : "memory");
 }
+// Packed FP32 pairs for the epilogue arithmetic: one instruction per two accumulator columns, each lane
+// rounded exactly like the scalar operation.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void fma_f32x2(float& lo, float& hi, uint32_t a_lo, uint32_t a_hi, uint64_t b, uint64_t c) {
+  asm("{\n\t.reg .b64 a, d;\n\tmov.b64 a, {%2, %3};\n\tfma.rn.f32x2 d, a, %4, %5;\n\tmov.b64 {%0, %1}, d;\n\t}"
+      : "=f"(lo), "=f"(hi)
+      : "r"(a_lo), "r"(a_hi), "l"(b), "l"(c));
+}
+__device__ __forceinline__ void mul_f32x2(float& lo, float& hi, float a_lo, float a_hi, uint64_t b) {
+  asm("{\n\t.reg .b64 a, d;\n\tmov.b64 a, {%2, %3};\n\tmul.rn.f32x2 d, a, %4;\n\tmov.b64 {%0, %1}, d;\n\t}"
+      : "=f"(lo), "=f"(hi)
+      : "f"(a_lo), "f"(a_hi), "l"(b));
+}
+__device__ __forceinline__ void square_f32x2(float& lo, float& hi) {
+  asm("{\n\t.reg .b64 a;\n\tmov.b64 a, {%0, %1};\n\tmul.rn.f32x2 a, a, a;\n\tmov.b64 {%0, %1}, a;\n\t}"
+      : "+f"(lo), "+f"(hi));
+}
 __device__ __forceinline__ void tcgen05_st_x4(uint32_t taddr, const uint32_t* r) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
                "r"(r[2]), "r"(r[3])
@@ -721,6 +742,21 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t r = mb * kBlockM + gtid;
       return (p.mode == NVFP4_GS_ROWWISE_A && r < p.m) ? __ldg(p.a_global + r) : 0.0f;
     };
+    // The bias slice of a tile travels the same way: its values are fetched into registers one tile ahead
+    // and reach shared memory only when the column block changes (a banded schedule keeps a CTA on one
+    // column block for many tiles).
+    float bias_next[kBlockN / 128];
+    uint32_t staged_bias_blk = 0xffffffffu;
+    auto fetch_bias = [&](uint32_t w) {
+      uint32_t mb, nb, sp;
+      decode(w, mb, nb, sp);
+#pragma unroll
+      for (int j = 0; j < kBlockN / 128; ++j) {
+        const uint32_t col = nb * kBlockN + gtid + 128 * j;
+        bias_next[j] = (p.tma_store && p.epilogue != NVFP4_EPI_NONE && col < p.n) ? __ldg(p.bias + col) : 0.0f;
+      }
+    };
+    if (w_begin < w_end) fetch_bias(w_begin);
     float ga_next = w_begin < w_end ? row_scale(w_begin) : 0.0f;
     for (uint32_t w = w_begin; w < w_end; w += w_step) {
       uint32_t m_blk, n_blk, split;
@@ -731,14 +767,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       // fetched before the wait for the accumulator so that its latency hides behind the main loop.  The
       // group's last barrier of the previous tile comes after that tile's last read of the slice.
       const bool add_bias = p.tma_store && p.epilogue != NVFP4_EPI_NONE && (p.k_splits == 1 || split == 0);
-      if (add_bias) {
-        for (uint32_t i = gtid; i < static_cast<uint32_t>(kBlockN); i += 128) {
-          const uint32_t col = n_blk * kBlockN + i;
-          const float bv = col < p.n ? __ldg(p.bias + col) : 0.0f;
-          asm volatile("st.shared.f32 [%0], %1;" ::"r"(my_bias + i * 4), "f"(bv) : "memory");
-        }
+      if (add_bias && n_blk != staged_bias_blk) {  // uniform across the group
+#pragma unroll
+        for (int j = 0; j < kBlockN / 128; ++j)
+          asm volatile("st.shared.f32 [%0], %1;" ::"r"(my_bias + (gtid + 128 * j) * 4), "f"(bias_next[j]) : "memory");
         epilogue_barrier(eg);
+        staged_bias_blk = n_blk;
       }
+      if (w + w_step < w_end) fetch_bias(w + w_step);
       if (!mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, kStatusEpilogueTimeout)) break;
       tcgen05_fence_after();
       const uint32_t row = m_blk * kBlockM + gtid;
@@ -746,6 +782,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const float ga = p.mode == NVFP4_GS_ROWWISE_A ? ga_row : ga_scalar;
       // reference order: (weight * a_scale) * b_scale, then acc * scale
       const float scale = __fmul_rn(__fmul_rn(p.weight, ga), gb);
+      const uint64_t scale2 = pack_f32x2(scale, scale);
       const uint32_t taddr_row = tmem_base + acc * kBlockN + ((ew * 32u) << 16);
       // The accumulator buffer goes back to the MMA warp as soon as this warp's last tcgen05.ld of the
       // tile has landed in registers: scaling, staging and the stores of that last sub-tile then run
@@ -779,14 +816,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
               for (int i = 0; i < kSub; i += 4) {
                 const float4 b = *reinterpret_cast<const float4*>(my_bias_gen + c + i);
-                v[i] = __fmaf_rn(__uint_as_float(r[i / 32][i % 32]), scale, b.x);
-                v[i + 1] = __fmaf_rn(__uint_as_float(r[(i + 1) / 32][(i + 1) % 32]), scale, b.y);
-                v[i + 2] = __fmaf_rn(__uint_as_float(r[(i + 2) / 32][(i + 2) % 32]), scale, b.z);
-                v[i + 3] = __fmaf_rn(__uint_as_float(r[(i + 3) / 32][(i + 3) % 32]), scale, b.w);
+                fma_f32x2(v[i], v[i + 1], r[i / 32][i % 32], r[i / 32][i % 32 + 1], scale2, pack_f32x2(b.x, b.y));
+                fma_f32x2(v[i + 2], v[i + 3], r[i / 32][i % 32 + 2], r[i / 32][i % 32 + 3], scale2, pack_f32x2(b.z, b.w));
               }
             } else {
 #pragma unroll
-              for (int i = 0; i < kSub; ++i) v[i] = __fmul_rn(__uint_as_float(r[i / 32][i % 32]), scale);
+              for (int i = 0; i < kSub; i += 2)
+                mul_f32x2(v[i], v[i + 1], __uint_as_float(r[i / 32][i % 32]), __uint_as_float(r[i / 32][i % 32 + 1]),
+                          scale2);
             }
           }
           const int passes = (p.epilogue == NVFP4_EPI_RELU2 && p.aux) ? 2 : 1;
@@ -794,9 +831,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             const bool is_pre = passes == 2 && pass == 0;
             if (p.epilogue == NVFP4_EPI_RELU2 && !is_pre) {
 #pragma unroll
-              for (int i = 0; i < kSub; ++i) {
-                const float t = fmaxf(v[i], 0.0f);
-                v[i] = __fmul_rn(t, t);
+              for (int i = 0; i < kSub; i += 2) {
+                v[i] = fmaxf(v[i], 0.0f);
+                v[i + 1] = fmaxf(v[i + 1], 0.0f);
+                square_f32x2(v[i], v[i + 1]);
               }
             }
             const uint32_t buf = my_store + store_buf * kStoreStageBytes;
