@@ -241,6 +241,7 @@ def run_gpu(args):
     import __graft_entry__ as entry
 
     pkg = entry.load_package()
+    pkg.set_deterministic_reductions(bool(args.deterministic))
     from nanogpt_120a_b200.projection_set import SHAPES, ProjectionSet  # noqa: E402
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -416,6 +417,7 @@ def run_gpu(args):
                                    f"({tokens_rank} per GPU)",
                        "parallelism": f"token-sharded dp{world}, weights replicated, per-layer NCCL all-reduce of dW",
                        "l2": "inputs larger than L2 (>= 100 MB per activation tensor)",
+                       "deterministic_reductions": bool(args.deterministic),
                        "flop_per_step": flops_step_total},
             "pct_of_fp4_peak": 100.0 * value / (NOMINAL_FP4_DENSE_TFLOPS * world),
             "roofline": {"bound": "tensor", "kernel": "nvfp4_gemm_tcgen05_kernel", "achieved": achieved,
@@ -472,6 +474,9 @@ def main():
                     help="tokens per GPU (weak scaling) or in total (strong scaling)")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--deterministic", action="store_true",
+                    help="cap split-K at two splits (run-to-run identical dW); the default lets small dW GEMMs "
+                         "take as many splits as fill the SMs")
     ap.add_argument("--small-case", default=None, choices=["quantizers", "gemm"],
                     help="run a small single-GPU case of one kernel family (for profiler captures) and exit")
     args = ap.parse_args()

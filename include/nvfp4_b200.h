@@ -372,6 +372,15 @@ int nvfp4_gemm_tma_nvfp4_rowwise_a_scale_padded_output(
     uint32_t output_dim, uint32_t padded_output_dim, const float* a_global_scales,
     const float* b_global_scale);
 
+/* Run-to-run reproducibility of split-K GEMMs (no reference counterpart: the reference's GEMM never splits K).
+ * Long-K f32 GEMMs with few output tiles (dW = dY^T.X) split K over several CTAs whose partial tiles are summed
+ * with TMA reduce-add in arrival order: with two splits the sum is order-free, with more (small dW such as
+ * 768 x 768) the last bits can differ from run to run, always inside the GEMM tolerance.  on = 1 caps the split
+ * count at two (process-wide; those GEMMs then fill fewer SMs); the default 0 takes as many splits as fill the
+ * SMs.  Quantizer outputs, dbias and every unsplit GEMM are reproducible either way. */
+int nvfp4_set_deterministic_reductions(int on);
+int nvfp4_get_deterministic_reductions(void);
+
 /* Measurement aid (no reference counterpart; off by default).  Between begin and end every GEMM
  * launch of this process is bracketed by a CUDA event pair recorded on the launch stream (up to
  * max_records launches; the events are created by begin, once).  end waits for the recorded

@@ -132,6 +132,7 @@ _SIGNATURES = {
     "nvfp4_gemm_tma_nvfp4_device_scales_and_global_scale_buffers": [_P] * 6 + [_U] * 3 + [_P] * 2,
     "nvfp4_gemm_tma_nvfp4_rowwise_a_scale_and_global_scale_buffer": [_P] * 6 + [_U] * 3 + [_P] * 2,
     "nvfp4_gemm_tma_nvfp4_rowwise_a_scale_padded_output": [_P] * 6 + [_U] * 4 + [_P] * 2,
+    "nvfp4_set_deterministic_reductions": [c_int],
     "nvfp4_gemm_timing_begin": [_U],
     "nvfp4_gemm_timing_end": [POINTER(c_uint32), POINTER(ctypes.c_double), POINTER(ctypes.c_double),
                               POINTER(c_float), POINTER(ctypes.c_double), _U],
@@ -144,6 +145,7 @@ _SIGNATURES = {
 }
 _SPECIAL = {
     "nvfp4_abi_version": (c_int, []),
+    "nvfp4_get_deterministic_reductions": (c_int, []),
     "nvfp4_launch_count": (ctypes.c_uint64, []),
     "nvfp4_last_error": (c_char_p, []),
     "nvfp4_padded_k": (c_uint32, [_U]),
@@ -224,6 +226,16 @@ def tensor_amax_chunks(n: int) -> int:
 def launch_count() -> int:
     """Kernels launched by the library so far in this process."""
     return int(library().nvfp4_launch_count())
+
+
+def set_deterministic_reductions(on: bool) -> None:
+    """Caps split-K at two splits so that dW is bit-identical from run to run (small dW GEMMs then fill fewer
+    SMs).  Off by default: more than two partial tiles are summed by TMA reduce-add in arrival order."""
+    _call("nvfp4_set_deterministic_reductions", 1 if on else 0)
+
+
+def deterministic_reductions() -> bool:
+    return bool(library().nvfp4_get_deterministic_reductions())
 
 
 def gemm_timing_begin(max_records: int) -> None:

@@ -561,6 +561,11 @@ int nvfp4_gemm_tma_nvfp4_rowwise_a_scale_padded_output(
                     output_dim, output_dim, NVFP4_GS_ROWWISE_A, a_global_scales, b_global_scale);
 }
 
+int nvfp4_set_deterministic_reductions(int on) {
+  gemm_set_deterministic(on);
+  return 0;
+}
+int nvfp4_get_deterministic_reductions(void) { return gemm_get_deterministic(); }
 int nvfp4_gemm_timing_begin(uint32_t max_records) { return gemm_timing_begin(max_records); }
 int nvfp4_gemm_timing_end(uint32_t* count, double* total_ms, double* total_flops, float* per_launch_ms,
                           double* per_launch_flops, uint32_t capacity) {

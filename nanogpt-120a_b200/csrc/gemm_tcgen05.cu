@@ -27,6 +27,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -1053,6 +1054,13 @@ int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb,
 
 }  // namespace
 
+// Split-K sums its partial tiles with TMA reduce-add in arrival order: with two splits the sum is
+// order-free (0 + a + b), with more it can differ in the last bits from run to run.  The switch below
+// caps the split count at two for callers that need run-to-run identical dW.
+static std::atomic<int> g_deterministic_splits{0};
+void gemm_set_deterministic(int on) { g_deterministic_splits.store(on ? 1 : 0, std::memory_order_relaxed); }
+int gemm_get_deterministic() { return g_deterministic_splits.load(std::memory_order_relaxed); }
+
 int gemm_timing_begin(uint32_t max_records) {
   std::lock_guard<std::mutex> lock(g_timing.mu);
   while (g_timing.pool.size() < max_records) {
@@ -1163,6 +1171,7 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
     uint32_t splits = static_cast<uint32_t>(sms) / tiles;
     const uint32_t max_splits = p.num_k_tiles / 8;
     if (splits > max_splits) splits = max_splits;
+    if (splits > 2 && gemm_get_deterministic()) splits = 2;
     if (splits > 1) p.k_splits = splits;
   }
   p.k_tiles_per_split = (p.num_k_tiles + p.k_splits - 1) / p.k_splits;

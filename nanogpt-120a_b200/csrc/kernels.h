@@ -59,6 +59,9 @@ uint32_t relu2_backward_grid(uint64_t n);
 
 // gemm_tcgen05.cu ---------------------------------------------------------------------------
 int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a);
+// 1: split-K never uses more than two splits (run-to-run identical sums); 0 (default): as many as fill the SMs
+void gemm_set_deterministic(int on);
+int gemm_get_deterministic();
 int gemm_timing_begin(uint32_t max_records);
 int gemm_timing_end(uint32_t* count, double* total_ms, double* total_flops, float* per_launch_ms,
                     double* per_launch_flops, uint32_t capacity);

@@ -839,3 +839,29 @@ def test_projection_set_reuses_packed_weights(pkg, dev):
     for la, lb in zip(a.all_linears(), b.all_linears()):
         assert torch.equal(la.wq.bytes, lb.wq.bytes) and torch.equal(la.wq.scales, lb.wq.scales)
     assert_no_timeouts(pkg)
+
+
+def test_split_k_deterministic_switch(pkg, oracle, dev):
+    """Split-K dW GEMMs: with the switch on (at most two splits) repeated launches agree bit for bit; with it
+    off (as many splits as fill the SMs) they stay within the GEMM tolerance of the same result."""
+    gemm = pkg.Nvfp4GemmModule()
+    rng = np.random.default_rng(77)
+    m, n, k = 256, 256, 16384  # 2 x 1 wide tiles, 64 k-tiles: up to 8 splits
+    a, b = _rand_nvfp4(rng, m, k, True), _rand_nvfp4(rng, n, k, False)
+    A, B = _to_dev(pkg, dev, a, m, k, True), _to_dev(pkg, dev, b, n, k, False)
+    A.scales, B.scales = pkg.Sm120ScalePackModule().pack(A.scales, m, k), pkg.Sm120ScalePackModule().pack(B.scales, n, k)
+    A.packed = B.packed = True
+    assert not pkg.deterministic_reductions()
+    try:
+        pkg.set_deterministic_reductions(True)
+        assert pkg.deterministic_reductions()
+        first = cpu(gemm.gemm(A, B, out_dtype=torch.float32))
+        for _ in range(10):
+            assert cpu(gemm.gemm(A, B, out_dtype=torch.float32)).tobytes() == first.tobytes()
+    finally:
+        pkg.set_deterministic_reductions(False)
+    fast = cpu(gemm.gemm(A, B, out_dtype=torch.float32))
+    assert rel_fro(fast, first) <= 1e-6
+    want = oracle.gemm(a, b, m, k, n, 2)
+    assert rel_fro(first, want) <= GEMM_TOL and rel_fro(fast, want) <= GEMM_TOL
+    assert_no_timeouts(pkg)
