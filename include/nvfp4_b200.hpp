@@ -356,6 +356,10 @@ class LinearBackwardModule {
   }
 };
 
+// Caps split-K at two splits so that dW is bit-identical from run to run (process-wide; off by default).
+inline void set_deterministic_reductions(bool on) { nvfp4_set_deterministic_reductions(on ? 1 : 0); }
+inline bool deterministic_reductions() { return nvfp4_get_deterministic_reductions() != 0; }
+
 // Reads and clears the device status word written by kernels whose bounded waits gave up
 // (0 = none did).  Synchronises the stream.
 inline DriverError read_device_status(Stream s, uint32_t* status) {
