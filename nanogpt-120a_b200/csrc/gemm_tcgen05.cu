@@ -1158,7 +1158,7 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   const bool can_split = a.out_dtype == NVFP4_DTYPE_F32 &&
                          (a.epilogue == NVFP4_EPI_NONE || a.epilogue == NVFP4_EPI_BIAS) && p.num_k_tiles >= 16;
   const bool wide_shape = a.n % 256 == 0 || a.n > 1024;
-  const bool wide_long_k = wide_shape && p.num_k_tiles >= 8 && (tiles256 >= static_cast<uint32_t>(sms) || can_split);
+  const bool wide_long_k = wide_shape && p.num_k_tiles >= 4 && (tiles256 >= static_cast<uint32_t>(sms) || can_split);
   const bool wide_short_k = a.n % 256 == 0 && p.num_k_tiles <= 3 && tiles256 >= 4u * static_cast<uint32_t>(sms);
   const bool wide = wide_long_k || wide_short_k;
   const uint32_t block_n = wide ? 256 : 128;
