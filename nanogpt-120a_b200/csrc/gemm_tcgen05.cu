@@ -1168,11 +1168,21 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   // split-K for long GEMMs with few tiles (dW = dY^T.X): f32 output, linear epilogue only
   p.k_splits = 1;
   if (can_split && tiles * 2 <= static_cast<uint32_t>(sms)) {
-    uint32_t splits = static_cast<uint32_t>(sms) / tiles;
-    const uint32_t max_splits = p.num_k_tiles / 8;
-    if (splits > max_splits) splits = max_splits;
-    if (splits > 2 && gemm_get_deterministic()) splits = 2;
-    if (splits > 1) p.k_splits = splits;
+    // The split count that minimises waves x (main loop + accumulator drain) of one work item, in units of
+    // k-tiles (a drain costs about four k-tiles of main loop); ties go to fewer splits.
+    uint32_t max_splits = p.num_k_tiles / 8;
+    if (max_splits > 32) max_splits = 32;
+    if (max_splits > 2 && gemm_get_deterministic()) max_splits = 2;
+    uint32_t best = 1;
+    uint64_t best_cost = ~0ull;
+    for (uint32_t sp = 1; sp <= max_splits; ++sp) {
+      const uint32_t per = (p.num_k_tiles + sp - 1) / sp;
+      const uint32_t real = (p.num_k_tiles + per - 1) / per;
+      const uint64_t waves = (static_cast<uint64_t>(tiles) * real + sms - 1) / sms;
+      const uint64_t cost = waves * (per + 4);
+      if (cost < best_cost) best_cost = cost, best = sp;
+    }
+    if (best > 1) p.k_splits = best;
   }
   p.k_tiles_per_split = (p.num_k_tiles + p.k_splits - 1) / p.k_splits;
   p.k_splits = (p.num_k_tiles + p.k_tiles_per_split - 1) / p.k_tiles_per_split;
