@@ -63,7 +63,10 @@ extern "C" {
 /* Library / device ------------------------------------------------------------------------ */
 
 /* Version of this ABI (bumped on incompatible change).  2: nvfp4_linear_backward_args gained
- * x_decoded_amax, nvfp4_quantize_four_six_rowwise_fused gained out_decoded_amax. */
+ * x_decoded_amax, nvfp4_quantize_four_six_rowwise_fused gained out_decoded_amax.  3: nvfp4_gemm_args gained
+ * the NVFP4 bias and relu2_row_amax members, nvfp4_linear_backward_args gained side_stream / fork_event /
+ * join_event and total_token_count, nvfp4_ms_eden_args gained group_row_stride, element counts of the
+ * tensor-amax entries became 64-bit. */
 int nvfp4_abi_version(void);
 /* Number of kernels this library has launched in this process (host-side tally). */
 uint64_t nvfp4_launch_count(void);
@@ -83,7 +86,7 @@ uint32_t nvfp4_scale_padded_mn_extent(uint32_t mn_extent);
  * (mn_extent is padded to 128 internally). */
 size_t nvfp4_scale_packed_len(uint32_t mn_extent, uint32_t k_dim);
 /* utils/nvfp4/quant/mod.rs:36-39 -- number of 1024-value chunks of a tensor amax. */
-uint32_t nvfp4_tensor_amax_chunks(uint32_t element_count);
+uint32_t nvfp4_tensor_amax_chunks(uint64_t element_count);
 
 /* amax ------------------------------------------------------------------------------------ */
 
@@ -93,8 +96,8 @@ int nvfp4_row_amax_f32(void* stream, const float* x, float* out, uint32_t row_co
 int nvfp4_row_amax_bf16(void* stream, const void* x, float* out, uint32_t row_count, uint32_t row_len);
 /* utils/nvfp4/quant/amax.rs:19-23  Nvfp4QuantModule::tensor_amax_f32
  * chunk_amax[ceil(n/1024)] and out[1] are both written. */
-int nvfp4_tensor_amax_f32(void* stream, const float* x, float* chunk_amax, float* out, uint32_t element_count);
-int nvfp4_tensor_amax_bf16(void* stream, const void* x, float* chunk_amax, float* out, uint32_t element_count);
+int nvfp4_tensor_amax_f32(void* stream, const float* x, float* chunk_amax, float* out, uint64_t element_count);
+int nvfp4_tensor_amax_bf16(void* stream, const void* x, float* chunk_amax, float* out, uint64_t element_count);
 /* No counterpart in the reference.  Same out[0] as nvfp4_tensor_amax_f32, for callers that cannot
  * supply the chunk_amax scratch because they cannot allocate at the point of the call (device
  * handed to an arena sized earlier, a loop where an allocation would synchronise the device, a
@@ -149,6 +152,17 @@ int nvfp4_quantize_four_six(void* stream, const void* x, int dtype, const float*
 int nvfp4_quantize_four_six_rowwise_fused(void* stream, const void* x, int dtype, uint32_t rows, uint32_t cols,
                                           uint8_t* out_fp4, uint8_t* out_scales, int scale_layout,
                                           float* out_global_scale, float* out_row_amax, float* out_decoded_amax);
+
+/* The same quantizer applied to relu(pre)^2 computed on load (f32 arithmetic: max(pre, 0) then one multiply),
+ * for an MLP whose up projection stored only its pre-activation: the activation relu(pre)^2 is never written
+ * to memory (the reference writes both, gpt/projection_postop.rs:140-162, and hands the row amax of the
+ * activation to this quantizer, crates/gpt2-nvfp4/src/types/l3_mlp/forward.rs:60-76).  row_amax_in (f32[rows],
+ * optional): the row amax of relu(pre)^2 if the producer already has it (nvfp4_gemm_args.relu2_row_amax);
+ * NULL = computed here.  Same bytes as materialising relu(pre)^2 in f32 and quantizing that. */
+int nvfp4_quantize_relu2_four_six_rowwise(void* stream, const void* pre_activation, int dtype, uint32_t rows,
+                                          uint32_t cols, const float* row_amax_in, uint8_t* out_fp4,
+                                          uint8_t* out_scales, int scale_layout, float* out_global_scale,
+                                          float* out_row_amax, float* out_decoded_amax);
 
 /* gpt/mlp/launcher.rs:66-76  MlpModule::relu2_backward / relu2_backward_f16 (kernels gpt/mlp/kernels.rs:72-104):
  * d_pre = (d_out * 2) * max(pre, 0) between the two MLP linears of the backward pass. */
@@ -209,6 +223,9 @@ typedef struct nvfp4_ms_eden_args {
   uint32_t scale_seed;
   uint32_t col_offset;          /* added to the K index of the sign hash (token sharding)    */
   uint32_t group_offset;        /* added to the flat group id of the scale RNG (even)        */
+  uint32_t group_row_stride;    /* 16-groups per output row in the scale RNG's index space; 0 = dst_row_len / 16.
+                                   A token shard of a transposed operand passes the unsharded K / 16 here and
+                                   first_token / 16 as group_offset to draw the unsharded tensor's bits.    */
   uint8_t* out_fp4;
   uint8_t* out_scales;
   int scale_layout;             /* NVFP4_SCALES_*                                            */
@@ -347,12 +364,59 @@ typedef struct nvfp4_gemm_args {
   float weight_global_scale;    /* the reference passes 1.0                                   */
   int epilogue;                 /* NVFP4_EPI_*                                                */
   int out_dtype;                /* NVFP4_DTYPE_*                                              */
+  /* Optional members (zero the struct first).  An NVFP4-encoded bias [n], the form the reference's
+   * projections take it in (gpt/attention/qkv_projection/launcher.rs:8-25: bias.bytes, bias.scales,
+   * bias.global_scale), decoded in the epilogue as (e2m1 * e4m3) * global_scale; read when `bias` is NULL. */
+  const uint8_t* bias_nvfp4_bytes;   /* u8[n/2]                                               */
+  const uint8_t* bias_nvfp4_scales;  /* u8[n/16], logical layout                              */
+  const float* bias_nvfp4_global;    /* f32[1]                                                */
+  /* f32[m] or NULL: receives, per output row, max over the columns of relu(stored value)^2 -- the row amax
+   * of the activation a ReLU^2 MLP feeds to its down projection, handed to the next quantizer the way the
+   * reference's post-op hands it over (gpt/projection_postop.rs:140-162,
+   * crates/gpt2-nvfp4/src/types/l3_mlp/forward.rs:60-76).  Needs a 16-byte aligned output / row pitch. */
+  float* relu2_row_amax;
 } nvfp4_gemm_args;
 
 /* out[m][n] = epilogue( (sum_k A*sa * B*sb) * weight * ga * gb ), FP32 accumulation in tensor
  * memory by tcgen05.mma kind::mxf4nvf4.  Replaces pack + prepare_tma + gemm_tma + post-op
  * (utils/nvfp4_tma_matmul/launcher.rs:106-328, gpt/projection_postop.rs:50-162).           */
 int nvfp4_gemm(void* stream, const nvfp4_gemm_args* args /* host */);
+
+/* What nvfp4_gemm would choose for `args` on the current device, without launching (no reference
+ * counterpart: the reference has one tile shape, utils/nvfp4_tma_matmul/kernels.rs:1314).  Lets a caller
+ * or a test see which kernel instantiation and schedule a shape takes. */
+typedef struct nvfp4_gemm_plan {
+  uint32_t block_n;       /* tile width: 128, 192 or 256 output columns (tile height is 128 rows)         */
+  uint32_t acc_stages;    /* accumulator buffers in tensor memory: 2 (128, 192) or 1 (256)                 */
+  uint32_t k_splits;      /* > 1: K split over CTAs, partial tiles summed with TMA reduce-add              */
+  uint32_t b_resident;    /* 1: the B panel of a column block stays in shared memory (short K)             */
+  uint32_t resident_cpn;  /* resident mode: CTAs per column block of the banded schedule, 0 = contiguous   */
+  uint32_t stages;        /* depth of the shared-memory operand ring                                       */
+  uint32_t grid;          /* CTAs (persistent, at most one per SM)                                         */
+  uint32_t tma_store;     /* 1: epilogue stores through shared memory + TMA, 0: direct stores              */
+  uint32_t smem_bytes;    /* dynamic shared memory of the launch                                           */
+} nvfp4_gemm_plan;
+int nvfp4_gemm_plan_query(const nvfp4_gemm_args* args /* host */, nvfp4_gemm_plan* out /* host */);
+
+/* utils/nvfp4_tma_matmul/launcher.rs:39-166  Nvfp4GemmModule::prepare_tma_nvfp4_device_scales{,_into}.
+ * The reference encodes four tensor maps per GEMM on the host and copies them into caller-owned device
+ * memory (4 x 128 bytes, TmaNvfp4DeviceScaleDescriptors, tma.rs:8-13) before every launch.  Here tensor
+ * maps travel as kernel parameters and the scale planes need no map at all (a k-tile's scales are
+ * contiguous in the packed layout), so `descriptors` is accepted and left untouched.  The call validates
+ * the shapes like the reference (input_dim % 64, 16-byte aligned operands; 1 = invalid value) and encodes
+ * the two operand maps into the calling thread's tensor-map cache, where every later nvfp4_gemm* call on
+ * the same buffers finds them: persistent buffers are encoded once, not once per launch.  Optional --
+ * a GEMM call on buffers it has not seen encodes and caches the maps itself. */
+int nvfp4_prepare_tma_nvfp4_device_scales(void* stream, const uint8_t* input_bytes, const uint8_t* input_scale_data,
+                                          const uint8_t* weight_bytes, const uint8_t* weight_scale_data,
+                                          uint32_t token_count, uint32_t input_dim, uint32_t output_dim);
+int nvfp4_prepare_tma_nvfp4_device_scales_into(void* stream, const uint8_t* input_bytes,
+                                               const uint8_t* input_scale_data, const uint8_t* weight_bytes,
+                                               const uint8_t* weight_scale_data, uint32_t token_count,
+                                               uint32_t input_dim, uint32_t output_dim,
+                                               void* descriptors /* device, 4 x 128 bytes, may be NULL */);
+/* Tensor maps encoded (misses) and reused (hits) by the calling thread so far. */
+int nvfp4_tensor_map_cache_stats(uint64_t* hits, uint64_t* misses);
 
 /* utils/nvfp4_tma_matmul/launcher.rs:172-222  gemm_tma_nvfp4_device_scales_and_global_scale_buffers */
 int nvfp4_gemm_tma_nvfp4_device_scales_and_global_scale_buffers(
@@ -381,6 +445,21 @@ int nvfp4_gemm_tma_nvfp4_rowwise_a_scale_padded_output(
 int nvfp4_set_deterministic_reductions(int on);
 int nvfp4_get_deterministic_reductions(void);
 
+/* Measurement aid (no reference counterpart): forces the tile width of every following GEMM of this process
+ * (128, 192 or 256; 0 = automatic choice, the default; the environment variable NVFP4_GEMM_TILE sets the
+ * initial value). */
+int nvfp4_gemm_set_tile_override(int block_n);
+/* Limit of every bounded wait inside the GEMM kernel in nanoseconds (default 2 s; 0 restores it).  A wait
+ * that runs out sets a bit of the device status word (nvfp4_read_device_status: 1 producer, 2 MMA /
+ * scale-factor warps, 4 epilogue), all roles of that CTA leave their loops, tensor memory is freed and
+ * the kernel returns; the CTA's output tiles are then unspecified.  The reference's waits spin without a
+ * limit (utils/nvfp4_tma_matmul/kernels.rs:172-174). */
+int nvfp4_gemm_set_wait_timeout_ns(uint64_t ns);
+/* Test aid: bit 0 makes CTA 0 of every following GEMM skip the loads of its first k-tile, so that the
+ * waits on that stage run out (the safe way to exercise the time-out path: nothing faults, the kernel
+ * returns).  0 (default) = normal operation. */
+int nvfp4_gemm_set_debug_flags(uint32_t flags);
+
 /* Measurement aid (no reference counterpart; off by default).  Between begin and end every GEMM
  * launch of this process is bracketed by a CUDA event pair recorded on the launch stream (up to
  * max_records launches; the events are created by begin, once).  end waits for the recorded
@@ -389,6 +468,53 @@ int nvfp4_get_deterministic_reductions(void);
 int nvfp4_gemm_timing_begin(uint32_t max_records);
 int nvfp4_gemm_timing_end(uint32_t* count, double* total_ms, double* total_flops, float* per_launch_ms,
                           double* per_launch_flops, uint32_t capacity);
+
+/* forward projections with the reference's argument lists -------------------------------------- */
+
+/* One forward projection Y = X . W^T + b the way the reference's module methods take it: X a rowwise NVFP4
+ * activation, W an NVFP4 tensor-scale weight, b an NVFP4-encoded bias (bytes, logical scales, global_scale),
+ * dimensions as u32.  Scale bytes of X and W may be logical (the reference's tensor format; the matching
+ * *_scales_packed_scratch must then hold nvfp4_scale_packed_len(rows, input_dim) bytes and is filled by the
+ * call -- the scratch LmHeadTmaArgs carries, gpt/lm_head.rs:41-54) or already packed (what this library's
+ * quantizers write; no scratch).  One fused launch: global scales, bias, activation / residual and the cast
+ * all happen in the GEMM epilogue. */
+typedef struct nvfp4_projection_args {
+  const uint8_t* input_bytes;          /* X [token_count][input_dim] nibbles                       */
+  const uint8_t* input_scales;
+  int input_scale_layout;              /* NVFP4_SCALES_*                                           */
+  const float* input_global_scales;    /* f32[token_count]                                         */
+  const uint8_t* weight_bytes;         /* W [output_dim][input_dim] nibbles                        */
+  const uint8_t* weight_scales;
+  int weight_scale_layout;
+  const float* weight_global_scale;    /* f32[1]                                                   */
+  const uint8_t* bias_bytes;           /* NVFP4 bias [output_dim]; all three NULL = no bias        */
+  const uint8_t* bias_scales;
+  const float* bias_global_scale;
+  void* out;                           /* the method's output (see each entry), [token_count][output_dim] */
+  void* pre_activation;                /* up_relu2 only                                            */
+  int out_dtype;                       /* NVFP4_DTYPE_F32 (the reference's type) or NVFP4_DTYPE_BF16 */
+  float* relu2_row_amax;               /* up_relu2 only, optional f32[token_count]                 */
+  uint32_t token_count, input_dim, output_dim;
+  uint8_t* input_scales_packed_scratch;
+  uint8_t* weight_scales_packed_scratch;
+} nvfp4_projection_args;
+/* gpt/attention/qkv_projection/launcher.rs:8-25  AttentionModule::qkv_projection : out = X . W^T + b */
+int nvfp4_qkv_projection(void* stream, const nvfp4_projection_args* args /* host */);
+/* gpt/attention/qkv_projection/launcher.rs:27-42  AttentionModule::c_proj : out (the f32 residual stream, in
+ * place) = fma(1, X . W^T + b, out); output_dim = input_dim = embedding_dim */
+int nvfp4_c_proj(void* stream, const nvfp4_projection_args* args);
+/* gpt/mlp/launcher.rs:53-59  MlpModule::up_relu2 : pre_activation = X . W^T + b, out = max(pre, 0)^2.  `out`
+ * may be NULL: only the pre-activation is stored (see nvfp4_quantize_relu2_four_six_rowwise). */
+int nvfp4_mlp_up_relu2(void* stream, const nvfp4_projection_args* args);
+/* gpt/mlp/launcher.rs:60-66  MlpModule::down_residual : out (residual, f32, in place) += X . W^T + b */
+int nvfp4_mlp_down_residual(void* stream, const nvfp4_projection_args* args);
+/* gpt/lm_head.rs:65-87  LmHeadModule::logits : out = X . W^T (no bias; weight_global_scale as given) */
+int nvfp4_lm_head_logits(void* stream, const nvfp4_projection_args* args);
+/* gpt/lm_head.rs:89-125  LmHeadModule::logits_tma : the same product through the reference's pack +
+ * prepare_tma + TMA GEMM sequence; one launch here */
+int nvfp4_lm_head_logits_tma(void* stream, const nvfp4_projection_args* args);
+/* gpt/next_latent/launch_projection.rs:10-29  NextLatModule::projection : out = X . W^T + b */
+int nvfp4_nextlat_projection(void* stream, const nvfp4_projection_args* args);
 
 /* post-ops as separate passes (gpt/projection_postop.rs:50-162); bias is NVFP4 encoded ----- */
 int nvfp4_projection_bias_inplace(void* stream, float* raw, const uint8_t* bias_bytes,
@@ -452,12 +578,54 @@ typedef struct nvfp4_linear_backward_args {
   const float* e_global_scale_override; /* device f32[1] shared across shards, or NULL        */
   const float* x_decoded_amax;       /* device f32[1]: max |decoded X| (from the forward quantizer),
                                         or NULL = compute it here with a pass over X             */
+  /* Optional second stream (cudaStream_t) with two events (cudaEvent_t), all caller owned: the two NVFP4
+   * transposers (W^T, X^T) depend on nothing else in the call and are ALU bound, so they can run beside the
+   * bandwidth-bound dY amax pass.  The call forks onto side_stream after recording fork_event on `stream` and
+   * joins through join_event before the GEMMs, on every path including errors; NULL side_stream = everything
+   * in order on `stream`.  The library owns no stream, event or lock. */
+  void* side_stream;
+  void* fork_event;
+  void* join_event;
+  /* Token sharding: tokens of the unsharded batch (0 = token_count, i.e. not sharded).  With token_offset,
+   * e_global_scale_override and x_decoded_amax (both derived from the all-reduced amax) a shard then draws
+   * exactly the bits of the unsharded operands, so the shards' dW partial sums add up to the unsharded dW
+   * up to f32 summation order. */
+  uint32_t total_token_count;
 } nvfp4_linear_backward_args;
 
 /* gpt/linear_backward/ms_eden.rs:15-55  LinearBackwardModule::backward_ms_eden :
  * dbias, MS-EDEN quantization of dY (rows + transposed), W^T, X^T, then
  * dX = dY.W and dW = dY^T.X on the tcgen05 GEMM. */
 int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args* args /* host */);
+
+/* gpt/linear_backward/device_scale.rs:38-187  LinearBackwardModule::backward_device_scale_tma,
+ * backward_device_scale, backward_device_scale_cta and gpt/linear_backward.rs:40-67 backward: the two gradient
+ * GEMMs over operands that are already MS-EDEN quantized, dX[token][in] = e_h . weight_t_h^T and
+ * dW[out][in] = e_t_h . input_t_h^T (K = padded_k(output_dim) and padded_k(token_count)).  The reference's
+ * three variants differ only in which of its kernels runs (TMA, warp, CTA pair); all three names resolve to
+ * the one tcgen05 GEMM here.  Operand scale bytes may be logical (the reference's layout; scales_packed_scratch
+ * of that operand must then hold nvfp4_scale_packed_len(rows, k) bytes, the LinearBackwardTmaScratch of the
+ * reference) or already packed (scratch unused).  e_h / e_t_h carry per-row global scales, weight_t_h /
+ * input_t_h one scale (global_scale[0]). */
+typedef struct nvfp4_backward_operand {
+  const uint8_t* bytes;
+  const uint8_t* scales;
+  int scale_layout;                /* NVFP4_SCALES_*                                            */
+  const float* global_scales;      /* f32[rows] (e_h, e_t_h) or f32[1] (weight_t_h, input_t_h)  */
+  uint8_t* scales_packed_scratch;  /* used when scale_layout == NVFP4_SCALES_LOGICAL            */
+} nvfp4_backward_operand;
+typedef struct nvfp4_linear_backward_device_scale_args {
+  nvfp4_backward_operand e_h, weight_t_h, e_t_h, input_t_h;
+  void* dinput;                    /* [token][in]                                               */
+  int dinput_dtype;
+  void* dweight;                   /* [out][in]                                                 */
+  int dweight_dtype;
+  uint32_t token_count, input_dim, output_dim;
+} nvfp4_linear_backward_device_scale_args;
+int nvfp4_linear_backward_device_scale_tma(void* stream, const nvfp4_linear_backward_device_scale_args* args);
+int nvfp4_linear_backward_device_scale(void* stream, const nvfp4_linear_backward_device_scale_args* args);
+int nvfp4_linear_backward_device_scale_cta(void* stream, const nvfp4_linear_backward_device_scale_args* args);
+int nvfp4_linear_backward(void* stream, const nvfp4_linear_backward_device_scale_args* args);
 
 /* utils/nvfp4_tc_matmul/launcher.rs:23-87  Nvfp4TcMatmulModule::matmul_ms_eden : out[m][n] (f32) = a[m][k] . b_t[n][k]^T
  * with both operands MS-EDEN quantized (caller-given global scales, the second with scale_seed ^ 0x9e3779b9) and K

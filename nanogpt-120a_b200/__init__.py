@@ -48,7 +48,8 @@ class MsEdenArgs(Structure):
         ("cols", c_uint32),
         ("dst_row_len", c_uint32), ("global_scale", c_void_p), ("host_global_scale", c_float),
         ("host_global_scale_valid", c_int), ("scale_override", c_float), ("sign_seed", c_uint32),
-        ("scale_seed", c_uint32), ("col_offset", c_uint32), ("group_offset", c_uint32), ("out_fp4", c_void_p),
+        ("scale_seed", c_uint32), ("col_offset", c_uint32), ("group_offset", c_uint32), ("group_row_stride", c_uint32),
+        ("out_fp4", c_void_p),
         ("out_scales", c_void_p), ("scale_layout", c_int), ("out_global_scales", c_void_p),
         ("out_chunk_amax", c_void_p),
     ]
@@ -60,7 +61,38 @@ class GemmArgs(Structure):
         ("b_scales", c_void_p), ("b_global", c_void_p), ("out", c_void_p), ("aux", c_void_p), ("bias", c_void_p),
         ("m", c_uint32), ("n", c_uint32), ("k", c_uint32), ("ldo", c_uint32), ("global_scale_mode", c_int),
         ("weight_global_scale", c_float), ("epilogue", c_int), ("out_dtype", c_int),
+        ("bias_nvfp4_bytes", c_void_p), ("bias_nvfp4_scales", c_void_p), ("bias_nvfp4_global", c_void_p),
+        ("relu2_row_amax", c_void_p),
     ]
+
+
+class GemmPlan(Structure):
+    """nvfp4_gemm_plan: what the library chooses for one GEMM (tile width, schedule, launch shape)."""
+    _fields_ = [("block_n", c_uint32), ("acc_stages", c_uint32), ("k_splits", c_uint32), ("b_resident", c_uint32),
+                ("resident_cpn", c_uint32), ("stages", c_uint32), ("grid", c_uint32), ("tma_store", c_uint32),
+                ("smem_bytes", c_uint32)]
+
+
+class ProjectionArgs(Structure):
+    _fields_ = [
+        ("input_bytes", c_void_p), ("input_scales", c_void_p), ("input_scale_layout", c_int),
+        ("input_global_scales", c_void_p), ("weight_bytes", c_void_p), ("weight_scales", c_void_p),
+        ("weight_scale_layout", c_int), ("weight_global_scale", c_void_p), ("bias_bytes", c_void_p),
+        ("bias_scales", c_void_p), ("bias_global_scale", c_void_p), ("out", c_void_p), ("pre_activation", c_void_p),
+        ("out_dtype", c_int), ("relu2_row_amax", c_void_p), ("token_count", c_uint32), ("input_dim", c_uint32),
+        ("output_dim", c_uint32), ("input_scales_packed_scratch", c_void_p), ("weight_scales_packed_scratch", c_void_p),
+    ]
+
+
+class BackwardOperand(Structure):
+    _fields_ = [("bytes", c_void_p), ("scales", c_void_p), ("scale_layout", c_int), ("global_scales", c_void_p),
+                ("scales_packed_scratch", c_void_p)]
+
+
+class LinearBackwardDeviceScaleArgs(Structure):
+    _fields_ = [("e_h", BackwardOperand), ("weight_t_h", BackwardOperand), ("e_t_h", BackwardOperand),
+                ("input_t_h", BackwardOperand), ("dinput", c_void_p), ("dinput_dtype", c_int), ("dweight", c_void_p),
+                ("dweight_dtype", c_int), ("token_count", c_uint32), ("input_dim", c_uint32), ("output_dim", c_uint32)]
 
 
 class MsEdenOperand(Structure):
@@ -77,7 +109,8 @@ class LinearBackwardArgs(Structure):
         ("dinput_dtype", c_int), ("dweight", c_void_p), ("dweight_dtype", c_int), ("dbias", c_void_p), ("token_count", c_uint32),
         ("input_dim", c_uint32), ("output_dim", c_uint32), ("sign_seed", c_uint32), ("scale_seed", c_uint32),
         ("precomputed_e_amax_chunks", c_uint32), ("token_offset", c_uint32), ("e_global_scale_override", c_void_p),
-        ("x_decoded_amax", c_void_p),
+        ("x_decoded_amax", c_void_p), ("side_stream", c_void_p), ("fork_event", c_void_p), ("join_event", c_void_p),
+        ("total_token_count", c_uint32),
     ]
 
 
@@ -87,8 +120,8 @@ _SIGNATURES = {
     "nvfp4_read_device_status": [_P, POINTER(c_uint32)],
     "nvfp4_row_amax_f32": [_P, _P, _P, _U, _U],
     "nvfp4_row_amax_bf16": [_P, _P, _P, _U, _U],
-    "nvfp4_tensor_amax_f32": [_P, _P, _P, _P, _U],
-    "nvfp4_tensor_amax_bf16": [_P, _P, _P, _P, _U],
+    "nvfp4_tensor_amax_f32": [_P, _P, _P, _P, ctypes.c_uint64],
+    "nvfp4_tensor_amax_bf16": [_P, _P, _P, _P, ctypes.c_uint64],
     "nvfp4_tensor_amax_from_chunks_f32": [_P, _P, _P, _U],
     "nvfp4_tensor_amax_f32_static_scratch": [_P, _P, _P, ctypes.c_uint64],
     "nvfp4_fp32_to_nvfp4_four_six": [_P, _P, _P, _P, _P, _P, _U],
@@ -97,6 +130,7 @@ _SIGNATURES = {
     "nvfp4_fp32_transpose_to_nvfp4_four_six_padded": [_P, _P, _P, _P, _P, _P, _U, _U, _U, _U],
     "nvfp4_quantize_four_six": [_P, _P, c_int, _P, c_int, _U, _U, _P, _P, c_int, _P],
     "nvfp4_quantize_four_six_rowwise_fused": [_P, _P, c_int, _U, _U, _P, _P, c_int, _P, _P, _P],
+    "nvfp4_quantize_relu2_four_six_rowwise": [_P, _P, c_int, _U, _U, _P, _P, _P, c_int, _P, _P, _P],
     "nvfp4_tc_matmul_ms_eden": [_P, _P, _P, _P, POINTER(MsEdenOperand), _F, POINTER(MsEdenOperand), _F, _U, _U, _U, _U, _U],
     "nvfp4_relu2_backward": [_P, _P, _P, _P, _U],
     "nvfp4_relu2_backward_f16": [_P, _P, _P, _P, _U],
@@ -129,6 +163,24 @@ _SIGNATURES = {
     "nvfp4_transpose_pad_f32": [_P, _P, _P, _U, _U, _U, _U],
     "nvfp4_crop_f32": [_P, _P, _P, _U, _U, _U],
     "nvfp4_gemm": [_P, POINTER(GemmArgs)],
+    "nvfp4_gemm_plan_query": [POINTER(GemmArgs), POINTER(GemmPlan)],
+    "nvfp4_prepare_tma_nvfp4_device_scales": [_P, _P, _P, _P, _P, _U, _U, _U],
+    "nvfp4_prepare_tma_nvfp4_device_scales_into": [_P, _P, _P, _P, _P, _U, _U, _U, _P],
+    "nvfp4_tensor_map_cache_stats": [POINTER(ctypes.c_uint64), POINTER(ctypes.c_uint64)],
+    "nvfp4_gemm_set_tile_override": [c_int],
+    "nvfp4_gemm_set_wait_timeout_ns": [ctypes.c_uint64],
+    "nvfp4_gemm_set_debug_flags": [_U],
+    "nvfp4_qkv_projection": [_P, POINTER(ProjectionArgs)],
+    "nvfp4_c_proj": [_P, POINTER(ProjectionArgs)],
+    "nvfp4_mlp_up_relu2": [_P, POINTER(ProjectionArgs)],
+    "nvfp4_mlp_down_residual": [_P, POINTER(ProjectionArgs)],
+    "nvfp4_lm_head_logits": [_P, POINTER(ProjectionArgs)],
+    "nvfp4_lm_head_logits_tma": [_P, POINTER(ProjectionArgs)],
+    "nvfp4_nextlat_projection": [_P, POINTER(ProjectionArgs)],
+    "nvfp4_linear_backward_device_scale_tma": [_P, POINTER(LinearBackwardDeviceScaleArgs)],
+    "nvfp4_linear_backward_device_scale": [_P, POINTER(LinearBackwardDeviceScaleArgs)],
+    "nvfp4_linear_backward_device_scale_cta": [_P, POINTER(LinearBackwardDeviceScaleArgs)],
+    "nvfp4_linear_backward": [_P, POINTER(LinearBackwardDeviceScaleArgs)],
     "nvfp4_gemm_tma_nvfp4_device_scales_and_global_scale_buffers": [_P] * 6 + [_U] * 3 + [_P] * 2,
     "nvfp4_gemm_tma_nvfp4_rowwise_a_scale_and_global_scale_buffer": [_P] * 6 + [_U] * 3 + [_P] * 2,
     "nvfp4_gemm_tma_nvfp4_rowwise_a_scale_padded_output": [_P] * 6 + [_U] * 4 + [_P] * 2,
@@ -151,7 +203,7 @@ _SPECIAL = {
     "nvfp4_padded_k": (c_uint32, [_U]),
     "nvfp4_scale_padded_mn_extent": (c_uint32, [_U]),
     "nvfp4_scale_packed_len": (c_size_t, [_U, _U]),
-    "nvfp4_tensor_amax_chunks": (c_uint32, [_U]),
+    "nvfp4_tensor_amax_chunks": (c_uint32, [ctypes.c_uint64]),
     "nvfp4_relu2_backward_amax_chunks": (c_uint32, [ctypes.c_uint64]),
 }
 EXPORTED_SYMBOLS = sorted(list(_SIGNATURES) + list(_SPECIAL))
@@ -236,6 +288,28 @@ def set_deterministic_reductions(on: bool) -> None:
 
 def deterministic_reductions() -> bool:
     return bool(library().nvfp4_get_deterministic_reductions())
+
+
+def set_gemm_tile_override(block_n: int) -> None:
+    """Measurement aid: force the GEMM tile width (128, 192, 256) of every following launch; 0 = automatic."""
+    _call("nvfp4_gemm_set_tile_override", block_n)
+
+
+def set_gemm_wait_timeout_ns(ns: int) -> None:
+    """Limit of the GEMM kernel's bounded waits (default 2 s; 0 restores the default)."""
+    _call("nvfp4_gemm_set_wait_timeout_ns", ns)
+
+
+def set_gemm_debug_flags(flags: int) -> None:
+    """Test aid: bit 0 makes CTA 0 of every following GEMM skip the loads of its first k-tile."""
+    _call("nvfp4_gemm_set_debug_flags", flags)
+
+
+def tensor_map_cache_stats():
+    """(hits, misses) of the calling thread's tensor-map cache."""
+    h, m = ctypes.c_uint64(0), ctypes.c_uint64(0)
+    _call("nvfp4_tensor_map_cache_stats", ctypes.byref(h), ctypes.byref(m))
+    return int(h.value), int(m.value)
 
 
 def gemm_timing_begin(max_records: int) -> None:
@@ -396,11 +470,35 @@ class Nvfp4QuantModule:
               _ptr(out.global_scales))
         return out
 
+    def quantize_relu2_four_six_rowwise(self, pre_activation: torch.Tensor, row_amax: Optional[torch.Tensor] = None,
+                                        packed: bool = True, out: Optional[Nvfp4Tensor] = None,
+                                        decoded_amax: bool = False) -> Nvfp4Tensor:
+        """Rowwise four-six of relu(pre)^2 computed on load (the MLP activation is never stored).  `row_amax`:
+        the row amax of relu(pre)^2 when the producing GEMM already wrote it (`relu2_row_amax`)."""
+        _require_cuda()
+        rows, cols = pre_activation.shape
+        if out is None:
+            n = rows * cols
+            nsc = scale_packed_len(rows, cols) if packed else n // 16
+            out = Nvfp4Tensor(_empty_u8(n // 2, pre_activation.device), _empty_u8(nsc, pre_activation.device),
+                              torch.empty(rows, dtype=torch.float32, device=pre_activation.device), rows, cols,
+                              packed=packed, rowwise=True)
+        if decoded_amax and out.decoded_amax is None:
+            out.decoded_amax = torch.empty(1, dtype=torch.float32, device=pre_activation.device)
+        elif not decoded_amax:
+            out.decoded_amax = None
+        _call("nvfp4_quantize_relu2_four_six_rowwise", _stream(), _ptr(pre_activation), _dtype_code(pre_activation),
+              rows, cols, _ptr(row_amax), _ptr(out.bytes), _ptr(out.scales),
+              SCALES_PACKED if packed else SCALES_LOGICAL, _ptr(out.global_scales), c_void_p(None),
+              _ptr(out.decoded_amax))
+        return out
+
     # ---- MS-EDEN ------------------------------------------------------------------------
     def ms_eden_quantize(self, *, src_kind: int, x: Optional[torch.Tensor] = None, src: Optional[Nvfp4Tensor] = None,
                          rows: int, cols: int, dst_row_len: int, global_scale, sign_seed: int, scale_seed: int,
                          scale_override: float = QUARTET_MS_EDEN_SCALE_OVERRIDE, packed: bool = False,
-                         want_chunk_amax: bool = False, col_offset: int = 0, group_offset: int = 0) -> tuple:
+                         want_chunk_amax: bool = False, col_offset: int = 0, group_offset: int = 0,
+                         group_row_stride: int = 0) -> tuple:
         """Generic entry.  Returns (Nvfp4Tensor with per-row copies of the global scale, chunk_amax|None)."""
         _require_cuda()
         dev = x.device if x is not None else src.bytes.device
@@ -427,7 +525,7 @@ class Nvfp4QuantModule:
             a.host_global_scale_valid = 1
         a.scale_override = scale_override
         a.sign_seed, a.scale_seed = sign_seed & 0xFFFFFFFF, scale_seed & 0xFFFFFFFF
-        a.col_offset, a.group_offset = col_offset, group_offset
+        a.col_offset, a.group_offset, a.group_row_stride = col_offset, group_offset, group_row_stride
         a.out_fp4, a.out_scales = _ptr(out.bytes), _ptr(out.scales)
         a.scale_layout = SCALES_PACKED if packed else SCALES_LOGICAL
         a.out_global_scales = _ptr(out.global_scales)
@@ -542,6 +640,28 @@ class Nvfp4TcMatmulModule:
 class MlpModule:
     """gpt/mlp/launcher.rs:66-76: the element-wise step between the two MLP linears of the backward pass
     (the forward projections of that module are `projection_forward` with the ReLU^2 epilogue)."""
+
+    def up_relu2(self, input: Nvfp4Tensor, weight: Nvfp4Tensor, bias: Nvfp4Tensor, pre_activation=None, out=None,
+                 out_dtype: torch.dtype = torch.float32, store_activation: bool = True, relu2_row_amax=None):
+        """gpt/mlp/launcher.rs:53-59: pre = X . W^T + b, out = max(pre, 0)^2.  `store_activation=False` keeps only
+        the pre-activation (relu^2 is then applied on load by `quantize_relu2_four_six_rowwise`).  Returns
+        (pre_activation, out | None)."""
+        _require_cuda()
+        dev = input.bytes.device
+        if pre_activation is None:
+            pre_activation = torch.empty((input.rows, weight.rows), dtype=out_dtype, device=dev)
+        if store_activation and out is None:
+            out = torch.empty((input.rows, weight.rows), dtype=pre_activation.dtype, device=dev)
+        a, keep = _projection_args(input, weight, bias, out if store_activation else None, pre_activation, relu2_row_amax)
+        _call("nvfp4_mlp_up_relu2", _stream(), ctypes.byref(a))
+        return pre_activation, (out if store_activation else None)
+
+    def down_residual(self, input: Nvfp4Tensor, weight: Nvfp4Tensor, bias: Nvfp4Tensor, residual: torch.Tensor):
+        """gpt/mlp/launcher.rs:60-66: residual (f32, in place) += X . W^T + b."""
+        _require_cuda()
+        a, keep = _projection_args(input, weight, bias, residual)
+        _call("nvfp4_mlp_down_residual", _stream(), ctypes.byref(a))
+        return residual
 
     def relu2_backward(self, pre_activation: torch.Tensor, d_out: torch.Tensor,
                        d_pre_activation: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -677,33 +797,65 @@ class Nvfp4GemmModule:
     """utils/nvfp4_tma_matmul/launcher.rs:23-328.  The tensor maps the reference prepares in a
     separate call are encoded inside each launch and passed as kernel parameters."""
 
-    def gemm(self, a: Nvfp4Tensor, b: Nvfp4Tensor, *, mode: Optional[int] = None, bias: Optional[torch.Tensor] = None,
+    def _args(self, a: Nvfp4Tensor, b: Nvfp4Tensor, out, aux, bias, mode, epilogue, weight_global_scale, n, ldo,
+              relu2_row_amax):
+        g = GemmArgs()
+        # keep the (possibly temporary) packed planes referenced until the launch is enqueued
+        keep = (_packed_scales(a), _packed_scales(b))
+        g.a_bytes, g.a_scales, g.a_global = _ptr(a.bytes), _ptr(keep[0]), _ptr(a.global_scales)
+        g.b_bytes, g.b_scales, g.b_global = _ptr(b.bytes), _ptr(keep[1]), _ptr(b.global_scales)
+        g.out, g.aux = _ptr(out), _ptr(aux)
+        if isinstance(bias, Nvfp4Tensor):  # NVFP4-encoded bias, decoded in the epilogue
+            assert not bias.packed and not bias.rowwise, "an NVFP4 bias carries logical scales and one global scale"
+            g.bias_nvfp4_bytes, g.bias_nvfp4_scales = _ptr(bias.bytes), _ptr(bias.scales)
+            g.bias_nvfp4_global = _ptr(bias.global_scales)
+        else:
+            g.bias = _ptr(bias)
+        g.m, g.n, g.k, g.ldo = a.rows, n, a.cols, ldo
+        g.global_scale_mode = mode
+        g.weight_global_scale = weight_global_scale
+        g.epilogue = epilogue
+        g.out_dtype = _dtype_code(out)
+        g.relu2_row_amax = _ptr(relu2_row_amax)
+        return g, keep
+
+    def gemm(self, a: Nvfp4Tensor, b: Nvfp4Tensor, *, mode: Optional[int] = None, bias=None,
              epilogue: int = EPI_NONE, out_dtype: torch.dtype = torch.float32, out: Optional[torch.Tensor] = None,
              aux: Optional[torch.Tensor] = None, weight_global_scale: float = 1.0, n: Optional[int] = None,
-             ldo: Optional[int] = None) -> torch.Tensor:
-        """out[m][n] = epilogue((A . B^T) * weight * ga * gb); A [m][k], B [n][k] NVFP4."""
+             ldo: Optional[int] = None, relu2_row_amax: Optional[torch.Tensor] = None,
+             plan_only: bool = False):
+        """out[m][n] = epilogue((A . B^T) * weight * ga * gb); A [m][k], B [n][k] NVFP4.  `bias` is an f32
+        vector or an NVFP4-encoded `Nvfp4Tensor` [1, n]; `relu2_row_amax` (f32[m]) receives the row amax of
+        relu(stored value)^2; `plan_only` returns the `GemmPlan` the library would choose instead of launching."""
         _require_cuda()
         assert a.cols == b.cols, "A and B must share K"
-        m, k = a.rows, a.cols
+        m = a.rows
         n = b.rows if n is None else n
         ldo = n if ldo is None else ldo
         if mode is None:
             mode = GS_ROWWISE_A if a.rowwise else GS_TENSOR
         if out is None:
             out = torch.empty((m, ldo), dtype=out_dtype, device=a.bytes.device)
-        g = GemmArgs()
-        # keep the (possibly temporary) packed planes referenced until the launch is enqueued
-        a_packed, b_packed = _packed_scales(a), _packed_scales(b)
-        g.a_bytes, g.a_scales, g.a_global = _ptr(a.bytes), _ptr(a_packed), _ptr(a.global_scales)
-        g.b_bytes, g.b_scales, g.b_global = _ptr(b.bytes), _ptr(b_packed), _ptr(b.global_scales)
-        g.out, g.aux, g.bias = _ptr(out), _ptr(aux), _ptr(bias)
-        g.m, g.n, g.k, g.ldo = m, n, k, ldo
-        g.global_scale_mode = mode
-        g.weight_global_scale = weight_global_scale
-        g.epilogue = epilogue
-        g.out_dtype = _dtype_code(out)
+        g, keep = self._args(a, b, out, aux, bias, mode, epilogue, weight_global_scale, n, ldo, relu2_row_amax)
+        if plan_only:
+            plan = GemmPlan()
+            _call("nvfp4_gemm_plan_query", ctypes.byref(g), ctypes.byref(plan))
+            return plan
         _call("nvfp4_gemm", _stream(), ctypes.byref(g))
+        del keep
         return out
+
+    def plan(self, a: Nvfp4Tensor, b: Nvfp4Tensor, **kw) -> "GemmPlan":
+        """The tile width / schedule `gemm(a, b, **kw)` takes on this device (nothing is launched)."""
+        return self.gemm(a, b, plan_only=True, **kw)
+
+    def prepare_tma_nvfp4_device_scales(self, a: Nvfp4Tensor, b: Nvfp4Tensor) -> None:
+        """utils/nvfp4_tma_matmul/launcher.rs:39-166: validates the operands and encodes their tensor maps into
+        the calling thread's cache ahead of the launches that use them."""
+        _require_cuda()
+        assert a.packed and b.packed
+        _call("nvfp4_prepare_tma_nvfp4_device_scales", _stream(), _ptr(a.bytes), _ptr(a.scales), _ptr(b.bytes),
+              _ptr(b.scales), a.rows, a.cols, b.rows)
 
     def _named(self, name, a, b, extra_dims=()):
         _require_cuda()
@@ -723,6 +875,79 @@ class Nvfp4GemmModule:
 
     def gemm_tma_nvfp4_rowwise_a_scale_padded_output(self, a, b, output_dim):
         return self._named("nvfp4_gemm_tma_nvfp4_rowwise_a_scale_padded_output", a, b, extra_dims=(output_dim,))
+
+
+def _projection_args(input: Nvfp4Tensor, weight: Nvfp4Tensor, bias: Optional[Nvfp4Tensor], out, pre_activation=None,
+                     relu2_row_amax=None):
+    assert input.rowwise and not weight.rowwise and input.cols == weight.cols
+    a = ProjectionArgs()
+    dev = input.bytes.device
+    keep = []
+    a.input_bytes, a.input_scales, a.input_global_scales = _ptr(input.bytes), _ptr(input.scales), _ptr(input.global_scales)
+    a.input_scale_layout = SCALES_PACKED if input.packed else SCALES_LOGICAL
+    a.weight_bytes, a.weight_scales, a.weight_global_scale = _ptr(weight.bytes), _ptr(weight.scales), _ptr(weight.global_scales)
+    a.weight_scale_layout = SCALES_PACKED if weight.packed else SCALES_LOGICAL
+    if not input.packed:
+        keep.append(_empty_u8(scale_packed_len(input.rows, input.cols), dev))
+        a.input_scales_packed_scratch = _ptr(keep[-1])
+    if not weight.packed:
+        keep.append(_empty_u8(scale_packed_len(weight.rows, weight.cols), dev))
+        a.weight_scales_packed_scratch = _ptr(keep[-1])
+    if bias is not None:
+        assert not bias.packed and not bias.rowwise
+        a.bias_bytes, a.bias_scales, a.bias_global_scale = _ptr(bias.bytes), _ptr(bias.scales), _ptr(bias.global_scales)
+    ref = out if out is not None else pre_activation
+    a.out, a.pre_activation = _ptr(out), _ptr(pre_activation)
+    a.out_dtype = _dtype_code(ref)
+    a.relu2_row_amax = _ptr(relu2_row_amax)
+    a.token_count, a.input_dim, a.output_dim = input.rows, input.cols, weight.rows
+    return a, keep
+
+
+class AttentionModule:
+    """gpt/attention/qkv_projection/launcher.rs:8-42 (the two projections of the attention block)."""
+
+    def qkv_projection(self, input: Nvfp4Tensor, weight: Nvfp4Tensor, bias: Nvfp4Tensor, out=None,
+                       out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        _require_cuda()
+        out = torch.empty((input.rows, weight.rows), dtype=out_dtype, device=input.bytes.device) if out is None else out
+        a, keep = _projection_args(input, weight, bias, out)
+        _call("nvfp4_qkv_projection", _stream(), ctypes.byref(a))
+        return out
+
+    def c_proj(self, input: Nvfp4Tensor, weight: Nvfp4Tensor, bias: Nvfp4Tensor, residual: torch.Tensor) -> torch.Tensor:
+        """residual (f32, in place) = fma(1, X . W^T + b, residual)."""
+        _require_cuda()
+        a, keep = _projection_args(input, weight, bias, residual)
+        _call("nvfp4_c_proj", _stream(), ctypes.byref(a))
+        return residual
+
+
+class LmHeadModule:
+    """gpt/lm_head.rs:65-125."""
+
+    def logits(self, input: Nvfp4Tensor, weight: Nvfp4Tensor, logits=None, out_dtype: torch.dtype = torch.float32,
+               tma: bool = False) -> torch.Tensor:
+        _require_cuda()
+        logits = torch.empty((input.rows, weight.rows), dtype=out_dtype, device=input.bytes.device) if logits is None else logits
+        a, keep = _projection_args(input, weight, None, logits)
+        _call("nvfp4_lm_head_logits_tma" if tma else "nvfp4_lm_head_logits", _stream(), ctypes.byref(a))
+        return logits
+
+    def logits_tma(self, input, weight, logits=None, out_dtype: torch.dtype = torch.float32):
+        return self.logits(input, weight, logits, out_dtype, tma=True)
+
+
+class NextLatModule:
+    """gpt/next_latent/launch_projection.rs:10-29."""
+
+    def projection(self, input: Nvfp4Tensor, weight: Nvfp4Tensor, bias: Nvfp4Tensor, out=None,
+                   out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        _require_cuda()
+        out = torch.empty((input.rows, weight.rows), dtype=out_dtype, device=input.bytes.device) if out is None else out
+        a, keep = _projection_args(input, weight, bias, out)
+        _call("nvfp4_nextlat_projection", _stream(), ctypes.byref(a))
+        return out
 
 
 class ProjectionPostOpModule:
@@ -783,8 +1008,43 @@ class LinearBackwardScratch:
         return Nvfp4Tensor(op["bytes"], op["scales_packed"], op["global_scales"], rows, k, packed=True, rowwise=True)
 
 
+class SideStream:
+    """A caller-owned second stream with its fork / join events for `LinearBackwardModule.backward_ms_eden`
+    (the library owns no stream: the transposers of a backward call run on this one beside the dY amax pass)."""
+
+    def __init__(self, device):
+        with torch.cuda.device(device):
+            self.stream = torch.cuda.Stream(device=device)
+            self.fork, self.join = torch.cuda.Event(), torch.cuda.Event()
+            # torch creates the underlying cudaEvent_t lazily: one record materialises it
+            self.fork.record(self.stream)
+            self.join.record(self.stream)
+
+    def handles(self):
+        return (c_void_p(self.stream.cuda_stream), c_void_p(self.fork.cuda_event), c_void_p(self.join.cuda_event))
+
+
 class LinearBackwardModule:
     """gpt/linear_backward.rs:31-67, gpt/linear_backward/ms_eden.rs:15-55."""
+
+    def backward_device_scale(self, scratch: "LinearBackwardScratch", dinput: torch.Tensor, dweight: torch.Tensor,
+                              variant: str = "tma") -> None:
+        """gpt/linear_backward/device_scale.rs:38-187 / linear_backward.rs:40-67: the two gradient GEMMs over
+        operands already quantized into `scratch` (variant: tma | plain | cta | backward)."""
+        _require_cuda()
+        t, i, o = scratch.dims
+        a = LinearBackwardDeviceScaleArgs()
+        for name, scalar in (("e_h", False), ("weight_t_h", True), ("e_t_h", False), ("input_t_h", True)):
+            op = getattr(scratch, name)
+            setattr(a, name, BackwardOperand(_ptr(op["bytes"]), _ptr(op["scales_packed"]), SCALES_PACKED,
+                                             _ptr(op["global_scale"] if scalar else op["global_scales"]),
+                                             c_void_p(None)))
+        a.dinput, a.dinput_dtype = _ptr(dinput), _dtype_code(dinput)
+        a.dweight, a.dweight_dtype = _ptr(dweight), _dtype_code(dweight)
+        a.token_count, a.input_dim, a.output_dim = t, i, o
+        name = {"tma": "nvfp4_linear_backward_device_scale_tma", "plain": "nvfp4_linear_backward_device_scale",
+                "cta": "nvfp4_linear_backward_device_scale_cta", "backward": "nvfp4_linear_backward"}[variant]
+        _call(name, _stream(), ctypes.byref(a))
 
     def linear_bias_grad(self, e: torch.Tensor, dbias: Optional[torch.Tensor] = None) -> torch.Tensor:
         _require_cuda()
@@ -798,7 +1058,8 @@ class LinearBackwardModule:
                          scratch: LinearBackwardScratch, sign_seed: int, scale_seed: int, want_dbias: bool = True,
                          grad_dtype: torch.dtype = torch.float32, dinput=None, dweight=None, dbias=None,
                          token_offset: int = 0, e_global_scale: Optional[torch.Tensor] = None,
-                         precomputed_e_amax_chunks: int = 0):
+                         precomputed_e_amax_chunks: int = 0, side: Optional["SideStream"] = None,
+                         total_token_count: int = 0, x_decoded_amax: Optional[torch.Tensor] = None):
         """dbias, dX = dY.W, dW = dY^T.X with MS-EDEN quantized operands.  `weight` is the NVFP4
         tensor-scale W[out][in], `input` the rowwise NVFP4 X[tokens][in] saved by the forward."""
         _require_cuda()
@@ -827,7 +1088,10 @@ class LinearBackwardModule:
         a.precomputed_e_amax_chunks = precomputed_e_amax_chunks
         a.token_offset = token_offset
         a.e_global_scale_override = _ptr(e_global_scale)
-        a.x_decoded_amax = _ptr(input.decoded_amax)
+        a.x_decoded_amax = _ptr(x_decoded_amax if x_decoded_amax is not None else input.decoded_amax)
+        a.total_token_count = total_token_count
+        if side is not None:
+            a.side_stream, a.fork_event, a.join_event = side.handles()
         _call("nvfp4_linear_backward_ms_eden", _stream(), ctypes.byref(a))
         return dinput, dweight, (dbias if want_dbias else None)
 

@@ -4,7 +4,6 @@
 #include <atomic>
 #include <cstdio>
 #include <cstring>
-#include <mutex>
 
 #include "kernels.h"
 
@@ -27,33 +26,6 @@ static int invalid(const char* msg) {
 
 static inline cudaStream_t S(void* stream) { return static_cast<cudaStream_t>(stream); }
 
-// A second stream per device for the one place where two independent kernel chains of a call use
-// different resources (the backward's NVFP4 transposers are ALU bound, its dY amax pass is HBM
-// bound).  Created on first use, never destroyed; fork / join are event waits, so it also works
-// while the caller's stream is being captured into a graph.
-struct SideStream {
-  cudaStream_t stream = nullptr;
-  cudaEvent_t fork = nullptr, join = nullptr;
-};
-static std::mutex g_side_mutex;
-static SideStream g_side[64];
-
-static SideStream* side_stream() {
-  int device = -1;
-  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
-  std::lock_guard<std::mutex> lock(g_side_mutex);
-  SideStream& ss = g_side[device];
-  if (!ss.stream) {
-    if (cudaStreamCreateWithFlags(&ss.stream, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaEventCreateWithFlags(&ss.fork, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&ss.join, cudaEventDisableTiming) != cudaSuccess) {
-      ss = SideStream();
-      return nullptr;
-    }
-  }
-  return &ss;
-}
-
 static inline uint32_t padded_k(uint32_t k) { return (k + 63u) / 64u * 64u; }
 static inline uint32_t chunks1024(uint64_t n) { return static_cast<uint32_t>((n + 1023) / 1024); }
 static const float kQuartetSO = (17.0f / 16.0f) * 0.93f;  // utils/quartet.rs:1
@@ -64,7 +36,7 @@ using namespace nvfp4;
 
 extern "C" {
 
-int nvfp4_abi_version(void) { return 2; }
+int nvfp4_abi_version(void) { return 3; }
 uint64_t nvfp4_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 const char* nvfp4_last_error(void) { return g_last_error; }
 
@@ -82,7 +54,7 @@ uint32_t nvfp4_scale_padded_mn_extent(uint32_t mn) { return (mn + 127u) / 128u *
 size_t nvfp4_scale_packed_len(uint32_t mn, uint32_t k) {
   return static_cast<size_t>((mn + 127u) / 128u) * (k / 64u) * 512u;
 }
-uint32_t nvfp4_tensor_amax_chunks(uint32_t n) { return chunks1024(n); }
+uint32_t nvfp4_tensor_amax_chunks(uint64_t n) { return chunks1024(n); }
 
 // ---- amax -------------------------------------------------------------------------------
 int nvfp4_row_amax_f32(void* stream, const float* x, float* out, uint32_t rows, uint32_t row_len) {
@@ -91,10 +63,10 @@ int nvfp4_row_amax_f32(void* stream, const float* x, float* out, uint32_t rows, 
 int nvfp4_row_amax_bf16(void* stream, const void* x, float* out, uint32_t rows, uint32_t row_len) {
   return launch_row_amax(S(stream), x, NVFP4_DTYPE_BF16, out, rows, row_len);
 }
-int nvfp4_tensor_amax_f32(void* stream, const float* x, float* chunk_amax, float* out, uint32_t n) {
+int nvfp4_tensor_amax_f32(void* stream, const float* x, float* chunk_amax, float* out, uint64_t n) {
   return launch_tensor_amax(S(stream), x, NVFP4_DTYPE_F32, chunk_amax, out, n);
 }
-int nvfp4_tensor_amax_bf16(void* stream, const void* x, float* chunk_amax, float* out, uint32_t n) {
+int nvfp4_tensor_amax_bf16(void* stream, const void* x, float* chunk_amax, float* out, uint64_t n) {
   return launch_tensor_amax(S(stream), x, NVFP4_DTYPE_BF16, chunk_amax, out, n);
 }
 int nvfp4_tensor_amax_from_chunks_f32(void* stream, const float* chunk_amax, float* out, uint32_t chunk_count) {
@@ -104,6 +76,7 @@ int nvfp4_tensor_amax_from_chunks_f32(void* stream, const float* chunk_amax, flo
 // ---- four-six ---------------------------------------------------------------------------
 int nvfp4_fp32_to_nvfp4_four_six(void* stream, const float* x, const float* amax, uint8_t* out_fp4,
                                  uint8_t* out_scales, float* out_gs, uint32_t group_count) {
+  if (group_count > 0x0fffffffu) return invalid("fp32_to_nvfp4_four_six: more than 2^32 - 16 elements in one call");
   return launch_four_six(S(stream), x, NVFP4_DTYPE_F32, amax, 0, 1, group_count * 16u, out_fp4, out_scales, 0, out_gs);
 }
 int nvfp4_fp32_to_nvfp4_four_six_rowwise(void* stream, const float* x, const float* amax, uint8_t* out_fp4,
@@ -160,6 +133,33 @@ int nvfp4_quantize_four_six_rowwise_fused(void* stream, const void* x, int dtype
   if (rc || !out_decoded_amax) return rc;
   return launch_nvfp4_amax(S(stream), out_fp4, out_scales, out_global_scale, rows, cols, 1, packed, nullptr,
                            out_decoded_amax);
+}
+
+int nvfp4_quantize_relu2_four_six_rowwise(void* stream, const void* pre_activation, int dtype, uint32_t rows,
+                                          uint32_t cols, const float* row_amax_in, uint8_t* out_fp4,
+                                          uint8_t* out_scales, int scale_layout, float* out_global_scale,
+                                          float* out_row_amax, float* out_decoded_amax) {
+  if (cols % 16 != 0) return invalid("quantize_relu2_four_six_rowwise: cols must be a multiple of 16");
+  if (scale_layout == NVFP4_SCALES_PACKED && cols % 64 != 0)
+    return invalid("quantize_relu2_four_six_rowwise: the packed scale layout needs cols % 64 == 0");
+  if (dtype != NVFP4_DTYPE_F32 && dtype != NVFP4_DTYPE_BF16) return invalid("quantize_relu2_four_six_rowwise: dtype");
+  if (reinterpret_cast<uintptr_t>(pre_activation) & 15u)
+    return invalid("quantize_relu2_four_six_rowwise: input must be 16-byte aligned");
+  const int packed = scale_layout == NVFP4_SCALES_PACKED;
+  if (row_amax_in) {
+    // the producer (the GEMM epilogue) already has the row amax of relu(pre)^2: one flat pass, no reduction
+    if (out_row_amax && out_row_amax != row_amax_in) {
+      const cudaError_t e = cudaMemcpyAsync(out_row_amax, row_amax_in, static_cast<size_t>(rows) * sizeof(float),
+                                            cudaMemcpyDeviceToDevice, S(stream));
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    return launch_four_six(S(stream), pre_activation, dtype, row_amax_in, 1, rows, cols, out_fp4, out_scales, packed,
+                           out_global_scale, 1, out_decoded_amax);
+  }
+  int rc = launch_four_six_rowwise_fused(S(stream), pre_activation, dtype, rows, cols, out_fp4, out_scales, packed,
+                                         out_global_scale, out_row_amax, out_decoded_amax, 1);
+  if (rc != -1) return rc;
+  return invalid("quantize_relu2_four_six_rowwise: rows longer than 4096 need row_amax_in");
 }
 
 // ---- ReLU^2 backward -------------------------------------------------------------------------
@@ -398,7 +398,7 @@ static int nvfp4_source_transpose(void* stream, int kind, const uint8_t* in_byte
                                   uint32_t dst_row_len, uint32_t sign_seed, uint32_t scale_seed, bool chunk_amax_out,
                                   int scale_layout, uint32_t col_offset, uint32_t group_offset,
                                   int src_scale_layout = NVFP4_SCALES_LOGICAL,
-                                  const float* precomputed_amax = nullptr) {
+                                  const float* precomputed_amax = nullptr, uint32_t group_row_stride = 0) {
   const uint64_t n = static_cast<uint64_t>(source_rows) * source_cols;
   if (source_cols % 16 != 0) return invalid("nvfp4 transpose: source_cols must be a multiple of 16");
   if (src_scale_layout == NVFP4_SCALES_PACKED && source_cols % 64 != 0)
@@ -431,6 +431,7 @@ static int nvfp4_source_transpose(void* stream, int kind, const uint8_t* in_byte
   a.scale_seed = scale_seed;
   a.col_offset = col_offset;
   a.group_offset = group_offset;
+  a.group_row_stride = group_row_stride;
   a.out_fp4 = out_fp4;
   a.out_scales = out_scales;
   a.scale_layout = scale_layout;
@@ -514,6 +515,142 @@ int nvfp4_gemm(void* stream, const nvfp4_gemm_args* args) {
   if (!args) return invalid("nvfp4_gemm: null args");
   return launch_gemm(S(stream), *args);
 }
+
+int nvfp4_gemm_plan_query(const nvfp4_gemm_args* args, nvfp4_gemm_plan* out) {
+  if (!args || !out) return invalid("nvfp4_gemm_plan_query: null pointer");
+  return gemm_plan_query(*args, out);
+}
+int nvfp4_prepare_tma_nvfp4_device_scales_into(void* stream, const uint8_t* input_bytes,
+                                               const uint8_t* input_scale_data, const uint8_t* weight_bytes,
+                                               const uint8_t* weight_scale_data, uint32_t token_count,
+                                               uint32_t input_dim, uint32_t output_dim, void* descriptors) {
+  (void)stream;
+  (void)descriptors;  // tensor maps travel as kernel parameters; the device copies of the reference are not needed
+  if (!input_bytes || !weight_bytes || !input_scale_data || !weight_scale_data)
+    return invalid("prepare_tma_nvfp4_device_scales: null operand");
+  if ((reinterpret_cast<uintptr_t>(input_bytes) | reinterpret_cast<uintptr_t>(weight_bytes) |
+       reinterpret_cast<uintptr_t>(input_scale_data) | reinterpret_cast<uintptr_t>(weight_scale_data)) & 15u)
+    return invalid("prepare_tma_nvfp4_device_scales: operand and scale pointers must be 16-byte aligned");
+  if (token_count == 0 || output_dim == 0) return 0;
+  return gemm_prepare_operand_maps(input_bytes, weight_bytes, token_count, input_dim, output_dim);
+}
+int nvfp4_prepare_tma_nvfp4_device_scales(void* stream, const uint8_t* input_bytes, const uint8_t* input_scale_data,
+                                          const uint8_t* weight_bytes, const uint8_t* weight_scale_data,
+                                          uint32_t token_count, uint32_t input_dim, uint32_t output_dim) {
+  return nvfp4_prepare_tma_nvfp4_device_scales_into(stream, input_bytes, input_scale_data, weight_bytes,
+                                                    weight_scale_data, token_count, input_dim, output_dim, nullptr);
+}
+int nvfp4_tensor_map_cache_stats(uint64_t* hits, uint64_t* misses) {
+  gemm_map_cache_stats(hits, misses);
+  return 0;
+}
+int nvfp4_gemm_set_tile_override(int block_n) {
+  if (block_n != 0 && block_n != 128 && block_n != 192 && block_n != 256)
+    return invalid("gemm_set_tile_override: 0, 128, 192 or 256");
+  gemm_set_tile_override(block_n);
+  return 0;
+}
+int nvfp4_gemm_set_wait_timeout_ns(uint64_t ns) {
+  gemm_set_wait_timeout_ns(ns);
+  return 0;
+}
+int nvfp4_gemm_set_debug_flags(uint32_t flags) {
+  gemm_set_debug_flags(flags);
+  return 0;
+}
+
+// ---- forward projections (reference argument lists) ------------------------------------------
+// Packed scale plane of an operand: the caller's plane if it is packed already, else packed into the scratch.
+static int packed_plane(void* stream, const uint8_t* scales, int layout, uint8_t* scratch, uint32_t rows, uint32_t k,
+                        const uint8_t** out, const char* who) {
+  if (layout == NVFP4_SCALES_PACKED) {
+    *out = scales;
+    return 0;
+  }
+  if (layout != NVFP4_SCALES_LOGICAL) return invalid("unknown scale layout");
+  if (!scratch) {
+    set_last_error(who);
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  *out = scratch;
+  return launch_scale_pack(S(stream), scales, scratch, rows, k);
+}
+
+enum ProjectionKind { kProjPlain, kProjResidual, kProjRelu2, kProjLogits };
+
+static int projection(void* stream, const nvfp4_projection_args* a, ProjectionKind kind) {
+  if (!a) return invalid("projection: null args");
+  if (a->token_count == 0 || a->output_dim == 0) return 0;
+  if (a->input_dim == 0 || a->input_dim % 64 != 0) return invalid("projection: input_dim must be a non-zero multiple of 64");
+  if (!a->input_bytes || !a->input_scales || !a->input_global_scales || !a->weight_bytes || !a->weight_scales ||
+      !a->weight_global_scale)
+    return invalid("projection: null operand");
+  const bool has_bias = a->bias_bytes && a->bias_scales && a->bias_global_scale;
+  if (kind != kProjLogits && !has_bias) return invalid("projection: this method takes an NVFP4 bias");
+  if (kind == kProjResidual && a->out_dtype != NVFP4_DTYPE_F32) return invalid("projection: the residual stream is f32");
+  if (kind == kProjRelu2 ? (!a->pre_activation && !a->out) : !a->out) return invalid("projection: null output");
+  const uint8_t *xs = nullptr, *ws = nullptr;
+  int rc = packed_plane(stream, a->input_scales, a->input_scale_layout, a->input_scales_packed_scratch, a->token_count,
+                        a->input_dim, &xs, "projection: logical input scales need input_scales_packed_scratch");
+  if (rc) return rc;
+  rc = packed_plane(stream, a->weight_scales, a->weight_scale_layout, a->weight_scales_packed_scratch, a->output_dim,
+                    a->input_dim, &ws, "projection: logical weight scales need weight_scales_packed_scratch");
+  if (rc) return rc;
+  nvfp4_gemm_args g;
+  std::memset(&g, 0, sizeof(g));
+  g.a_bytes = a->input_bytes;
+  g.a_scales = xs;
+  g.a_global = a->input_global_scales;
+  g.b_bytes = a->weight_bytes;
+  g.b_scales = ws;
+  g.b_global = a->weight_global_scale;
+  g.m = a->token_count;
+  g.n = a->output_dim;
+  g.k = a->input_dim;
+  g.ldo = a->output_dim;
+  g.global_scale_mode = NVFP4_GS_ROWWISE_A;
+  g.weight_global_scale = 1.0f;
+  g.out_dtype = a->out_dtype;
+  g.out = a->out;
+  if (has_bias) {
+    g.bias_nvfp4_bytes = a->bias_bytes;
+    g.bias_nvfp4_scales = a->bias_scales;
+    g.bias_nvfp4_global = a->bias_global_scale;
+  }
+  switch (kind) {
+    case kProjPlain:
+      g.epilogue = NVFP4_EPI_BIAS;
+      break;
+    case kProjResidual:
+      g.epilogue = NVFP4_EPI_RESIDUAL;
+      break;
+    case kProjLogits:
+      g.epilogue = has_bias ? NVFP4_EPI_BIAS : NVFP4_EPI_NONE;
+      break;
+    case kProjRelu2:
+      if (a->out) {
+        g.epilogue = NVFP4_EPI_RELU2;
+        g.aux = a->pre_activation;
+      } else {  // only the pre-activation is kept: a plain biased projection into it
+        g.epilogue = NVFP4_EPI_BIAS;
+        g.out = a->pre_activation;
+      }
+      g.relu2_row_amax = a->relu2_row_amax;
+      break;
+  }
+  return launch_gemm(S(stream), g);
+}
+
+int nvfp4_qkv_projection(void* stream, const nvfp4_projection_args* a) { return projection(stream, a, kProjPlain); }
+int nvfp4_c_proj(void* stream, const nvfp4_projection_args* a) {
+  if (a && a->input_dim != a->output_dim) return invalid("c_proj: output_dim must equal input_dim (embedding_dim)");
+  return projection(stream, a, kProjResidual);
+}
+int nvfp4_mlp_up_relu2(void* stream, const nvfp4_projection_args* a) { return projection(stream, a, kProjRelu2); }
+int nvfp4_mlp_down_residual(void* stream, const nvfp4_projection_args* a) { return projection(stream, a, kProjResidual); }
+int nvfp4_lm_head_logits(void* stream, const nvfp4_projection_args* a) { return projection(stream, a, kProjLogits); }
+int nvfp4_lm_head_logits_tma(void* stream, const nvfp4_projection_args* a) { return projection(stream, a, kProjLogits); }
+int nvfp4_nextlat_projection(void* stream, const nvfp4_projection_args* a) { return projection(stream, a, kProjPlain); }
 
 static int gemm_plain(void* stream, const uint8_t* a_bytes, const uint8_t* a_scales, const uint8_t* b_bytes,
                       const uint8_t* b_scales, float* out, uint32_t m, uint32_t k, uint32_t n, uint32_t ldo, int mode,
@@ -641,32 +778,99 @@ int nvfp4_tc_matmul_ms_eden(void* stream, const float* a, const float* b_t, floa
   return nvfp4_gemm(stream, &g);
 }
 
-int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args* a) {
-  if (!a) return invalid("linear_backward: null args");
+// The gradient GEMMs over quantized operands: dX = e_h . weight_t_h^T, dW = e_t_h . input_t_h^T.
+static int backward_gemms(cudaStream_t s, const uint8_t* eh_b, const uint8_t* eh_s, const float* eh_g,
+                          const uint8_t* wt_b, const uint8_t* wt_s, const float* wt_g, const uint8_t* et_b,
+                          const uint8_t* et_s, const float* et_g, const uint8_t* xt_b, const uint8_t* xt_s,
+                          const float* xt_g, void* dinput, int dinput_dtype, void* dweight, int dweight_dtype,
+                          uint32_t T, uint32_t I, uint32_t O) {
+  const uint32_t ok = padded_k(O), tk = padded_k(T);
+  nvfp4_gemm_args g;
+  std::memset(&g, 0, sizeof(g));
+  g.global_scale_mode = NVFP4_GS_ROWWISE_A;
+  g.weight_global_scale = 1.0f;
+  g.epilogue = NVFP4_EPI_NONE;
+  g.out_dtype = dinput_dtype;
+  g.a_bytes = eh_b;
+  g.a_scales = eh_s;
+  g.a_global = eh_g;
+  g.b_bytes = wt_b;
+  g.b_scales = wt_s;
+  g.b_global = wt_g;
+  g.out = dinput;
+  g.m = T;
+  g.n = I;
+  g.k = ok;
+  g.ldo = I;
+  int rc = launch_gemm(s, g);
+  if (rc) return rc;
+  g.a_bytes = et_b;
+  g.a_scales = et_s;
+  g.a_global = et_g;
+  g.b_bytes = xt_b;
+  g.b_scales = xt_s;
+  g.b_global = xt_g;
+  g.out = dweight;
+  g.out_dtype = dweight_dtype;
+  g.m = O;
+  g.n = I;
+  g.k = tk;
+  return launch_gemm(s, g);
+}
+
+static int backward_device_scale(void* stream, const nvfp4_linear_backward_device_scale_args* a) {
+  if (!a) return invalid("backward_device_scale: null args");
   const uint32_t T = a->token_count, I = a->input_dim, O = a->output_dim;
-  if (I % 16 != 0) return invalid("linear_backward: input_dim must be a multiple of 16");
+  if (T == 0 || I == 0 || O == 0) return 0;
+  if (!a->dinput || !a->dweight) return invalid("backward_device_scale: null gradient buffer");
+  const uint32_t ok = padded_k(O), tk = padded_k(T);
+  const nvfp4_backward_operand* ops[4] = {&a->e_h, &a->weight_t_h, &a->e_t_h, &a->input_t_h};
+  const uint32_t rows[4] = {T, I, O, I}, ks[4] = {ok, ok, tk, tk};
+  const uint8_t* planes[4];
+  for (int i = 0; i < 4; ++i) {
+    if (!ops[i]->bytes || !ops[i]->scales || !ops[i]->global_scales) return invalid("backward_device_scale: null operand");
+    const int rc = packed_plane(stream, ops[i]->scales, ops[i]->scale_layout, ops[i]->scales_packed_scratch, rows[i],
+                                ks[i], &planes[i], "backward_device_scale: logical scales need scales_packed_scratch");
+    if (rc) return rc;
+  }
+  return backward_gemms(S(stream), a->e_h.bytes, planes[0], a->e_h.global_scales, a->weight_t_h.bytes, planes[1],
+                        a->weight_t_h.global_scales, a->e_t_h.bytes, planes[2], a->e_t_h.global_scales,
+                        a->input_t_h.bytes, planes[3], a->input_t_h.global_scales, a->dinput, a->dinput_dtype,
+                        a->dweight, a->dweight_dtype, T, I, O);
+}
+int nvfp4_linear_backward_device_scale_tma(void* stream, const nvfp4_linear_backward_device_scale_args* a) {
+  return backward_device_scale(stream, a);
+}
+int nvfp4_linear_backward_device_scale(void* stream, const nvfp4_linear_backward_device_scale_args* a) {
+  return backward_device_scale(stream, a);
+}
+int nvfp4_linear_backward_device_scale_cta(void* stream, const nvfp4_linear_backward_device_scale_args* a) {
+  return backward_device_scale(stream, a);
+}
+int nvfp4_linear_backward(void* stream, const nvfp4_linear_backward_device_scale_args* a) {
+  return backward_device_scale(stream, a);
+}
+
+// Everything of nvfp4_linear_backward_ms_eden that runs between the fork onto the caller's side stream and the
+// join; `ts` is the stream the two transposers go to (the side stream, or the main one when there is none).
+static int backward_ms_eden_quantize(void* stream, void* ts, const nvfp4_linear_backward_args* a) {
+  const uint32_t T = a->token_count, I = a->input_dim, O = a->output_dim;
   const uint32_t ok = padded_k(O), tk = padded_k(T);
   cudaStream_t s = S(stream);
+  // Scale-RNG index space of the transposed operands (K = tokens): a shard addresses the groups of the
+  // unsharded operand, row * (K_total / 16) + first_token / 16 + local group.
+  const uint32_t total_tk = a->total_token_count ? padded_k(a->total_token_count) : tk;
+  const uint32_t t_stride = total_tk / 16u, t_offset = a->total_token_count ? a->token_offset / 16u : 0u;
   int rc;
 
-  // 3. W^T and 4. X^T from their NVFP4 forms (quantize/transpose.rs:14-93).  Enqueued first and on
-  //    the side stream: they depend on nothing computed below, are ALU bound, and so run beside the
-  //    HBM-bound dY amax pass of step 2.  Without a side stream they simply run first on `s`.
-  SideStream* side = side_stream();
-  // the fork / join events are per device: keep concurrent host threads from interleaving their use
-  static std::mutex enqueue_mutex;
-  std::unique_lock<std::mutex> enqueue_lock(enqueue_mutex, std::defer_lock);
-  if (side) enqueue_lock.lock();
-  if (side) {
-    if (cudaEventRecord(side->fork, s) != cudaSuccess || cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess)
-      side = nullptr;
-  }
-  void* ts = side ? static_cast<void*>(side->stream) : stream;
+  // 3. W^T and 4. X^T from their NVFP4 forms (quantize/transpose.rs:14-93).  Enqueued first: they depend on
+  //    nothing computed below and are ALU bound, so on a side stream they run beside the HBM-bound dY amax
+  //    pass of step 2.
   rc = nvfp4_source_transpose(ts, NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED, a->x_bytes, a->x_scales, a->x_globals,
                               a->input_t_h.bytes, a->input_t_h.scales_packed, a->input_t_h.global_scales,
                               a->input_t_h.chunk_amax, a->input_t_h.global_scale, T, I, tk, a->sign_seed,
-                              a->scale_seed ^ 0xc2b2ae35u, false, NVFP4_SCALES_PACKED, a->token_offset, 0, a->x_scale_layout,
-                              a->x_decoded_amax);
+                              a->scale_seed ^ 0xc2b2ae35u, false, NVFP4_SCALES_PACKED, a->token_offset, t_offset,
+                              a->x_scale_layout, a->x_decoded_amax, t_stride);
   if (rc) return rc;
   rc = nvfp4_source_transpose(ts, NVFP4_SRC_NVFP4_TRANSPOSED, a->w_bytes, a->w_scales, a->w_global,
                               a->weight_t_h.bytes, a->weight_t_h.scales_packed, a->weight_t_h.global_scales,
@@ -713,7 +917,8 @@ int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args
   qt.dst_row_len = tk;
   qt.scale_seed = a->scale_seed ^ 0x85ebca6bu;  // gpt/linear_backward/ms_eden/quantize/pair.rs:36
   qt.col_offset = a->token_offset;
-  qt.group_offset = 0;
+  qt.group_offset = t_offset;
+  qt.group_row_stride = t_stride;
   qt.out_fp4 = a->e_t_h.bytes;
   qt.out_scales = a->e_t_h.scales_packed;
   qt.out_global_scales = a->e_t_h.global_scales;
@@ -742,49 +947,56 @@ int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args
   // one pass over dY for both orientations (+ column sums)
   rc = ms_eden_pair(stream, q, qt, partials, amax_in, amax_in ? a->e_h.global_scale : nullptr);
   if (rc) return rc;
-  if (fuse_dbias) {
-    rc = launch_col_sum_reduce(s, partials, a->dbias, ms_eden_pair_row_tiles(T), O);
-    if (rc) return rc;
-  }
+  if (fuse_dbias) rc = launch_col_sum_reduce(s, partials, a->dbias, ms_eden_pair_row_tiles(T), O);
+  return rc;
+}
 
-  // join: the GEMMs need W^T and X^T
-  if (side) {
-    if (cudaEventRecord(side->join, side->stream) != cudaSuccess || cudaStreamWaitEvent(s, side->join, 0) != cudaSuccess)
-      return invalid("linear_backward: could not join the side stream");
+int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args* a) {
+  if (!a) return invalid("linear_backward: null args");
+  const uint32_t T = a->token_count, I = a->input_dim, O = a->output_dim;
+  if (I % 16 != 0) return invalid("linear_backward: input_dim must be a multiple of 16");
+  if (!a->e || !a->w_bytes || !a->w_scales || !a->w_global || !a->x_bytes || !a->x_scales || !a->x_globals ||
+      !a->dinput || !a->dweight)
+    return invalid("linear_backward: null tensor pointer");
+  const nvfp4_ms_eden_operand* ops[4] = {&a->e_h, &a->e_t_h, &a->weight_t_h, &a->input_t_h};
+  for (const nvfp4_ms_eden_operand* op : ops)
+    if (!op->bytes || !op->scales_packed || !op->global_scales || !op->global_scale || !op->chunk_amax)
+      return invalid("linear_backward: null scratch pointer");
+  if ((a->e_dtype != NVFP4_DTYPE_F32 && a->e_dtype != NVFP4_DTYPE_BF16) ||
+      (a->dinput_dtype != NVFP4_DTYPE_F32 && a->dinput_dtype != NVFP4_DTYPE_BF16) ||
+      (a->dweight_dtype != NVFP4_DTYPE_F32 && a->dweight_dtype != NVFP4_DTYPE_BF16))
+    return invalid("linear_backward: unknown dtype code");
+  if (a->total_token_count && (a->token_offset % 128 != 0 || a->token_offset + T > a->total_token_count))
+    return invalid("linear_backward: a token shard starts on a multiple of 128 and ends inside the batch");
+  if (a->side_stream && (!a->fork_event || !a->join_event))
+    return invalid("linear_backward: side_stream needs fork_event and join_event");
+  cudaStream_t s = S(stream);
+
+  // fork: every failure above happens before it, and every path below goes through the join
+  void* ts = stream;
+  bool forked = false;
+  if (a->side_stream) {
+    cudaError_t e = cudaEventRecord(static_cast<cudaEvent_t>(a->fork_event), s);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(S(a->side_stream), static_cast<cudaEvent_t>(a->fork_event), 0);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    ts = a->side_stream;
+    forked = true;
   }
+  int rc = backward_ms_eden_quantize(stream, ts, a);
+  if (forked) {
+    // join: the GEMMs need W^T and X^T; on an error path this leaves neither stream (nor a capture in
+    // progress) dangling
+    cudaError_t e = cudaEventRecord(static_cast<cudaEvent_t>(a->join_event), S(a->side_stream));
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(s, static_cast<cudaEvent_t>(a->join_event), 0);
+    if (rc == 0 && e != cudaSuccess) rc = static_cast<int>(e);
+  }
+  if (rc) return rc;
 
   // 5. dX = dY . W   (contraction over output features) and dW = dY^T . X (over tokens)
-  nvfp4_gemm_args g;
-  std::memset(&g, 0, sizeof(g));
-  g.global_scale_mode = NVFP4_GS_ROWWISE_A;
-  g.weight_global_scale = 1.0f;
-  g.epilogue = NVFP4_EPI_NONE;
-  g.out_dtype = a->dinput_dtype;
-  g.a_bytes = a->e_h.bytes;
-  g.a_scales = a->e_h.scales_packed;
-  g.a_global = a->e_h.global_scales;
-  g.b_bytes = a->weight_t_h.bytes;
-  g.b_scales = a->weight_t_h.scales_packed;
-  g.b_global = a->weight_t_h.global_scale;
-  g.out = a->dinput;
-  g.m = T;
-  g.n = I;
-  g.k = ok;
-  g.ldo = I;
-  rc = launch_gemm(s, g);
-  if (rc) return rc;
-  g.a_bytes = a->e_t_h.bytes;
-  g.a_scales = a->e_t_h.scales_packed;
-  g.a_global = a->e_t_h.global_scales;
-  g.b_bytes = a->input_t_h.bytes;
-  g.b_scales = a->input_t_h.scales_packed;
-  g.b_global = a->input_t_h.global_scale;
-  g.out = a->dweight;
-  g.out_dtype = a->dweight_dtype;
-  g.m = O;
-  g.n = I;
-  g.k = tk;
-  return launch_gemm(s, g);
+  return backward_gemms(s, a->e_h.bytes, a->e_h.scales_packed, a->e_h.global_scales, a->weight_t_h.bytes,
+                        a->weight_t_h.scales_packed, a->weight_t_h.global_scale, a->e_t_h.bytes, a->e_t_h.scales_packed,
+                        a->e_t_h.global_scales, a->input_t_h.bytes, a->input_t_h.scales_packed,
+                        a->input_t_h.global_scale, a->dinput, a->dinput_dtype, a->dweight, a->dweight_dtype, T, I, O);
 }
 
 }  // extern "C"

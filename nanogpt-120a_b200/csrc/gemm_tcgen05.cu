@@ -16,11 +16,12 @@
 //               128-byte column sub-tiles of a tile (a warp reaches the tensor-memory lanes of
 //               its index modulo four, so warps w and w + 8 share a lane quadrant),
 //   warps 8..11 move the scale factors shared -> tensor memory (tcgen05.st).
-// Accumulators are double buffered when BLOCK_N = 128 so the epilogue of one tile overlaps
-// the main loop of the next; the 256-column tile has one accumulator buffer, which every epilogue
-// warp hands back as soon as its last tcgen05.ld of the tile has landed in registers, so that
-// scaling, staging and storing of that last sub-tile overlap the next main loop.  Every mbarrier wait is bounded: on expiry the kernel records
-// a status word, drains, frees its tensor memory and returns.
+// Three tile widths.  BLOCK_N = 128 and 192 double buffer the accumulator (2 x 192 accumulator
+// columns + 3 x 40 scale-factor columns fill the 512 columns of tensor memory), so the epilogue of
+// one tile overlaps the main loop of the next; the 256-column tile has one accumulator buffer,
+// which every epilogue warp hands back as soon as its last tcgen05.ld of the tile has landed in
+// registers.  Every mbarrier wait is bounded: on expiry the kernel records a status word, drains,
+// frees its tensor memory and returns.
 //
 // No thread-block clusters, no multicast: every load reads this GPU's own memory.
 #include <cuda.h>
@@ -28,7 +29,10 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
+#include <unordered_map>
 #include <vector>
 
 #include "kernels.h"
@@ -50,34 +54,36 @@ constexpr int kTmemCols = 512;
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 227 * 1024;
 constexpr int kThreads = 512;
-constexpr uint64_t kWaitTimeoutNs = 2000000000ull;  // 2 s
+constexpr uint64_t kDefaultWaitTimeoutNs = 2000000000ull;  // 2 s
 
 constexpr uint32_t kStatusProducerTimeout = 1u, kStatusMmaTimeout = 2u, kStatusEpilogueTimeout = 4u;
 
 template <int kBlockN>
 struct Cfg {
-  static constexpr int kNBlocks128 = kBlockN / 128;
+  // 128-row scale-factor blocks of B a tile can touch: a 192-column tile starts either on a block
+  // boundary or in the middle of a block, and spans two blocks either way
+  static constexpr int kSfBlocks = (kBlockN + 127) / 128;
   static constexpr int kBStageBytes = kBlockN * kBlockKBytes;
-  static constexpr int kSfbStageBytes = kNBlocks128 * kKAtomsPerStage * kSfTileBytes;
-  static constexpr int kAccStages = kBlockN == 128 ? 2 : 1;
-  // Scale factors live in a 4-deep ring of column sets behind the accumulators (one set per
-  // k-tile), so the copies for the next k-tile never overwrite columns an MMA in flight reads.
+  static constexpr int kSfbStageBytes = kSfBlocks * kKAtomsPerStage * kSfTileBytes;
+  static constexpr int kAccStages = kBlockN == 256 ? 1 : 2;
+  // Scale factors live in a ring of column sets behind the accumulators (one set per k-tile), so
+  // the copies for the next k-tile never overwrite columns an MMA in flight reads.
   static constexpr int kSfbColsPerAtom = kBlockN / 32;
   static constexpr int kSfSetCols = 4 * kKAtomsPerStage + kSfbColsPerAtom * kKAtomsPerStage;
-  static constexpr int kSfSets = 4;
-  static constexpr int kTmemSfa = 256;                       // A scale factors of set 0
-  static constexpr int kTmemSfb = 256 + 4 * kKAtomsPerStage;  // B scale factors of set 0
+  static constexpr int kSfSets = kBlockN == 192 ? 3 : 4;
+  static constexpr int kTmemSfa = kAccStages * kBlockN;            // A scale factors of set 0
+  static constexpr int kTmemSfb = kTmemSfa + 4 * kKAtomsPerStage;  // B scale factors of set 0
   static constexpr int kStreamStageBytes = kAStageBytes + kBStageBytes + kSfaStageBytes + kSfbStageBytes;
   static constexpr int kResidentStageBytes = kAStageBytes + kSfaStageBytes;
   static constexpr int kPanelSlotBytes = kBStageBytes + kSfbStageBytes;
   // epilogue staging ring: deep for the narrow tile (short-K GEMMs are epilogue bound), shallow for
-  // the wide one (long-K GEMMs need the shared memory for pipeline stages)
+  // the wide ones (long-K GEMMs need the shared memory for pipeline stages)
   static constexpr int kStoreBufs = kBlockN == 128 ? 4 : 2;
+  static constexpr int kBiasSlots = (kBlockN + 127) / 128;  // bias values a thread of an epilogue group fetches
   static constexpr int kFixedBytes =
       1024 /*alignment slack*/ + kStoreBufs * kStoreStageBytes + 512 /*barriers*/ +
-      2 * kBlockN * 4 /*bias of the tile, one copy per epilogue group*/;
-  static_assert(256 + kSfSets * kSfSetCols <= kTmemCols, "tensor memory overflow");
-  static_assert(kAccStages * kBlockN <= 256, "accumulators overlap the scale-factor columns");
+      2 * kBiasSlots * 128 * 4 /*bias of the tile, one copy per epilogue group*/;
+  static_assert(kTmemSfa + kSfSets * kSfSetCols <= kTmemCols, "tensor memory overflow");
 };
 
 struct GemmParams {
@@ -86,6 +92,11 @@ struct GemmParams {
   const float* a_global;
   const float* b_global;
   const float* bias;
+  // NVFP4-encoded bias [n] (bytes, logical scale bytes, f32[1] global scale): used when bias == nullptr
+  const uint8_t* bias_bytes;
+  const uint8_t* bias_scales;
+  const float* bias_global;
+  float* row_amax;  // optional f32[m]: max over the row of relu(stored value)^2 (red.max, zeroed by the launcher)
   void* out;
   void* aux;
   uint32_t m, n, k, ldo;
@@ -96,6 +107,8 @@ struct GemmParams {
   uint32_t resident_cpn;  // resident mode: CTAs per column block (0 = contiguous tile ranges instead)
   int mode, epilogue, vec_store, tma_store;
   float weight;
+  uint64_t wait_timeout_ns;  // limit of every mbarrier wait
+  uint32_t debug_flags;      // bit 0: CTA 0 never loads its first k-tile (exercises the bounded waits)
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -131,7 +144,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Bounded wait.  Returns false when the CTA is aborting (this waiter timed out, or another
 // role already did); the caller then leaves its loop and goes to the common teardown.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t status_bit) {
+                                          uint32_t status_bit, uint64_t timeout_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t polls = 0;
@@ -139,7 +152,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 255u) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitTimeoutNs) {
+      if (global_timer_ns() - t0 > timeout_ns) {
         *abort_flag = 1;
         atomicOr(&g_device_status, status_bit);
         return false;
@@ -182,6 +195,22 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 // one named barrier per epilogue warp group (ids 1 and 2), 128 threads each
 __device__ __forceinline__ void epilogue_barrier(uint32_t group) {
   asm volatile("bar.sync %0, 128;" ::"r"(group + 1u) : "memory");
+}
+
+// Named barrier of one epilogue group that also ANDs a predicate over its 128 threads: the decision to
+// go on with a tile or to leave for the teardown is then the same in every thread of the group, so no
+// thread can be left alone in a later bar.sync.
+__device__ __forceinline__ bool epilogue_all(uint32_t group, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %2, 0;\n\t"
+      "bar.red.and.pred q, %1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"(group + 1u), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return r != 0;
 }
 
 __device__ __forceinline__ bool elect_one() {
@@ -245,6 +274,14 @@ __device__ __forceinline__ void tcgen05_st_x4(uint32_t taddr, const uint32_t* r)
                "r"(r[2]), "r"(r[3])
                : "memory");
 }
+__device__ __forceinline__ void tcgen05_st_x2(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(taddr), "r"(r[0]), "r"(r[1]) : "memory");
+}
+__device__ __forceinline__ void tcgen05_st_x8(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
 __device__ __forceinline__ void tcgen05_st_x16(uint32_t taddr, const uint32_t* r) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -272,6 +309,21 @@ template <int kBlockN>
 __device__ __forceinline__ constexpr uint32_t make_idesc() {
   return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kBlockN >> 3) << 17) | (0u << 23) |
          (static_cast<uint32_t>(kBlockM >> 4) << 24);
+}
+
+// Bias of one output column: an f32 vector, or an NVFP4-encoded one decoded as the reference's post-op
+// kernels decode it, (e2m1 * e4m3) * global_scale (utils/nvfp4/tensor.rs:48-57, gpt/projection_postop.rs:97-115).
+__device__ __forceinline__ float bias_value(const GemmParams& p, uint32_t col) {
+  if (p.bias) return __ldg(p.bias + col);
+  const uint32_t byte = __ldg(p.bias_bytes + (col >> 1));
+  const uint32_t nib = (col & 1u) ? (byte >> 4) : (byte & 0xfu);
+  uint32_t h2;
+  asm("{ .reg .b8 t; cvt.u8.u32 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(h2) : "r"(nib));
+  const float q = __low2float(*reinterpret_cast<__half2*>(&h2));
+  uint32_t s2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(s2) : "h"(static_cast<uint16_t>(__ldg(p.bias_scales + (col >> 4)))));
+  const float sc = __low2float(*reinterpret_cast<__half2*>(&s2));
+  return __fmul_rn(__fmul_rn(q, sc), __ldg(p.bias_global));
 }
 
 // ---- epilogue stores ------------------------------------------------------------------------
@@ -386,7 +438,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t smem_bar = smem_store + C::kStoreBufs * kStoreStageBytes;
   // barrier block: full[8], empty[8], tmem_full[2], tmem_empty[2], b_full, b_empty, sf_full[4], sf_empty[4],
   // tmem base, abort flag
-  const uint32_t smem_bias = smem_bar + 512;  // kBlockN floats
+  const uint32_t smem_bias = smem_bar + 512;  // C::kBiasSlots * 128 floats per epilogue group
   const uint32_t bar_full = smem_bar;
   const uint32_t bar_empty = bar_full + 8 * kMaxStages;
   const uint32_t bar_tmem_full = bar_empty + 8 * kMaxStages;
@@ -395,8 +447,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t bar_b_empty = bar_b_full + 8;
   const uint32_t bar_sf_full = bar_b_empty + 8;
   const uint32_t bar_sf_empty = bar_sf_full + 8 * C::kSfSets;
+  const uint32_t bar_mma_drain = bar_sf_empty + 8 * C::kSfSets;  // abort path only: issued MMAs have retired
   uint32_t* tmem_base_ptr =
-      reinterpret_cast<uint32_t*>(smem_gen + (smem_bar - smem_base) + 8 * (2 * kMaxStages + 6 + 2 * C::kSfSets));
+      reinterpret_cast<uint32_t*>(smem_gen + (smem_bar - smem_base) + 8 * (2 * kMaxStages + 7 + 2 * C::kSfSets));
   volatile uint32_t* abort_flag = tmem_base_ptr + 1;
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -422,6 +475,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     mbar_init(bar_b_full, 1);
     mbar_init(bar_b_empty, 1);
+    mbar_init(bar_mma_drain, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -486,11 +540,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         decode(w, m_blk, n_blk, split);
         const uint32_t kt_begin = split * p.k_tiles_per_split;
         const uint32_t kt_end = min(p.num_k_tiles, kt_begin + p.k_tiles_per_split);
-        const uint32_t first_blk128 = n_blk * C::kNBlocks128;
-        const uint32_t blks128 = min(static_cast<uint32_t>(C::kNBlocks128), p.sfb_blocks128 - first_blk128);
+        const uint32_t first_blk128 = n_blk * kBlockN / 128u;
+        const uint32_t blks128 = min(static_cast<uint32_t>(C::kSfBlocks), p.sfb_blocks128 - first_blk128);
         if (p.b_resident && n_blk != prev_n) {
           // new column block: wait until the MMAs of the previous run have retired, then load the panel
-          if (runs > 0 && !mbar_wait(bar_b_empty, (runs - 1) & 1u, abort_flag, kStatusProducerTimeout)) {
+          if (runs > 0 && !mbar_wait(bar_b_empty, (runs - 1) & 1u, abort_flag, kStatusProducerTimeout, p.wait_timeout_ns)) {
             ok = false;
             break;
           }
@@ -509,13 +563,22 @@ __global__ void __launch_bounds__(kThreads, 1)
           ++runs;
         }
         for (uint32_t kt = kt_begin; kt < kt_end; ++kt) {
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusProducerTimeout)) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusProducerTimeout, p.wait_timeout_ns)) {
             ok = false;
             break;
           }
           const uint32_t atoms = min(static_cast<uint32_t>(kKAtomsPerStage), p.k_atoms - kt * kKAtomsPerStage);
           const uint32_t sf_bytes = atoms * kSfTileBytes;
           const uint32_t full = bar_full + 8 * stage;
+          if ((p.debug_flags & 1u) && blockIdx.x == 0 && issued == 0) {
+            // test hook: this stage is never armed nor loaded, so its consumers' waits run out
+            ++issued;
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            continue;
+          }
           if (p.b_resident) {
             mbar_expect_tx(full, kAStageBytes + sf_bytes);
           } else {
@@ -565,23 +628,24 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t kt_begin = split * p.k_tiles_per_split;
         const uint32_t kt_end = min(p.num_k_tiles, kt_begin + p.k_tiles_per_split);
         if (p.b_resident && n_blk != prev_n) {
-          if (!__all_sync(0xffffffffu, mbar_wait(bar_b_full, runs & 1u, abort_flag, kStatusMmaTimeout))) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_b_full, runs & 1u, abort_flag, kStatusMmaTimeout, p.wait_timeout_ns))) {
             ok = false;
             break;
           }
           prev_n = n_blk;
           ++runs;
         }
-        if (!__all_sync(0xffffffffu, mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kStatusMmaTimeout))) {
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kStatusMmaTimeout, p.wait_timeout_ns))) {
           ok = false;
           break;
         }
         tcgen05_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * kBlockN;
         for (uint32_t kt = kt_begin; kt < kt_end; ++kt) {
-          // operands landed in shared memory, and the scale-factor warps filled column set `sf_set`
-          bool ready = mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout);
-          ready = ready && mbar_wait(bar_sf_full + 8 * sf_set, sf_phase, abort_flag, kStatusMmaTimeout);
+          // The scale-factor warps arrive on `sf_full` only after they have seen the stage's `full` barrier
+          // complete (operands and scale tiles share it), so this one wait covers both: operands in
+          // shared memory and column set `sf_set` filled.
+          const bool ready = mbar_wait(bar_sf_full + 8 * sf_set, sf_phase, abort_flag, kStatusMmaTimeout, p.wait_timeout_ns);
           if (!__all_sync(0xffffffffu, ready)) {
             ok = false;
             break;
@@ -634,6 +698,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           acc_phase ^= 1u;
         }
       }
+      if (!ok) {
+        // aborting: give the MMAs already issued a bounded chance to retire before tensor memory is freed
+        if (elect_one()) tcgen05_commit(bar_mma_drain);
+        __syncwarp();
+        for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(bar_mma_drain, 0); ++spin) {
+        }
+      }
     }
   } else if (warp >= 8 && warp < 12) {
     // ===================== scale-factor warps =====================
@@ -651,13 +722,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t kt_begin = split * p.k_tiles_per_split;
       const uint32_t kt_end = min(p.num_k_tiles, kt_begin + p.k_tiles_per_split);
       if (p.b_resident && n_blk != prev_n) {
-        if (!mbar_wait(bar_b_full, runs & 1u, abort_flag, kStatusMmaTimeout)) break;
+        if (!mbar_wait(bar_b_full, runs & 1u, abort_flag, kStatusMmaTimeout, p.wait_timeout_ns)) break;
         prev_n = n_blk;
         ++runs;
       }
       for (uint32_t kt = kt_begin; kt < kt_end; ++kt) {
-        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout) ||
-            !mbar_wait(bar_sf_empty + 8 * sf_set, sf_phase ^ 1u, abort_flag, kStatusMmaTimeout)) {
+        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout, p.wait_timeout_ns) ||
+            !mbar_wait(bar_sf_empty + 8 * sf_set, sf_phase ^ 1u, abort_flag, kStatusMmaTimeout, p.wait_timeout_ns)) {
           ok = false;
           break;
         }
@@ -670,7 +741,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t tsfb = tmem_base + C::kTmemSfb + sf_set * C::kSfSetCols + ((quad * 32u) << 16);
         // all shared-memory reads first (independent, pipelined), then the tensor-memory stores
         uint32_t ra[kKAtomsPerStage][4];
-        uint32_t rb[kKAtomsPerStage][C::kNBlocks128][4];
+        uint32_t rb[kKAtomsPerStage][C::kSfBlocks * 4];
 #pragma unroll
         for (uint32_t kb = 0; kb < kKAtomsPerStage; ++kb) {
           if (kb < atoms) {
@@ -678,28 +749,48 @@ __global__ void __launch_bounds__(kThreads, 1)
                          : "=r"(ra[kb][0]), "=r"(ra[kb][1]), "=r"(ra[kb][2]), "=r"(ra[kb][3])
                          : "r"(sfa_s + kb * kSfTileBytes));
 #pragma unroll
-            for (int i = 0; i < C::kNBlocks128; ++i)
+            for (int i = 0; i < C::kSfBlocks; ++i)
               asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(rb[kb][i][0]), "=r"(rb[kb][i][1]), "=r"(rb[kb][i][2]), "=r"(rb[kb][i][3])
+                           : "=r"(rb[kb][4 * i]), "=r"(rb[kb][4 * i + 1]), "=r"(rb[kb][4 * i + 2]), "=r"(rb[kb][4 * i + 3])
                            : "r"(sfb_s + i * kSfaStageBytes + kb * kSfTileBytes));
           }
         }
-        if (atoms == kKAtomsPerStage) {
+        if constexpr (kBlockN == 192) {
+          // Six scale words (192 rows of B) per k-atom out of the eight loaded: words 0..5 when the tile
+          // starts on a 128-row block boundary (even column block), words 2..7 when it starts in the
+          // middle of the first block (odd column block).
+          const bool odd = (n_blk & 1u) != 0;
+          uint32_t sel[kKAtomsPerStage][6];
+#pragma unroll
+          for (uint32_t kb = 0; kb < kKAtomsPerStage; ++kb)
+#pragma unroll
+            for (int j = 0; j < 6; ++j) sel[kb][j] = odd ? rb[kb][j + 2] : rb[kb][j];
+          if (atoms == kKAtomsPerStage) {
+            tcgen05_st_x16(tsfa, &ra[0][0]);
+            tcgen05_st_x16(tsfb, &sel[0][0]);
+            tcgen05_st_x8(tsfb + 16, &sel[0][0] + 16);
+          } else {
+#pragma unroll
+            for (uint32_t kb = 0; kb < kKAtomsPerStage; ++kb) {
+              if (kb < atoms) {
+                tcgen05_st_x4(tsfa + kb * 4, ra[kb]);
+                tcgen05_st_x4(tsfb + kb * 6, sel[kb]);
+                tcgen05_st_x2(tsfb + kb * 6 + 4, sel[kb] + 4);
+              }
+            }
+          }
+        } else if (atoms == kKAtomsPerStage) {
           // one 16-column store for the A scales, one 16- or 32-column store for the B scales
           tcgen05_st_x16(tsfa, &ra[0][0]);
-          if (C::kNBlocks128 == 1) {
-            tcgen05_st_x16(tsfb, &rb[0][0][0]);
-          } else {
-            tcgen05_st_x16(tsfb, &rb[0][0][0]);
-            tcgen05_st_x16(tsfb + 16, &rb[2][0][0]);
-          }
+          tcgen05_st_x16(tsfb, &rb[0][0]);
+          if constexpr (C::kSfBlocks == 2) tcgen05_st_x16(tsfb + 16, &rb[2][0]);
         } else {
 #pragma unroll
           for (uint32_t kb = 0; kb < kKAtomsPerStage; ++kb) {
             if (kb < atoms) {
               tcgen05_st_x4(tsfa + kb * 4, ra[kb]);
 #pragma unroll
-              for (int i = 0; i < C::kNBlocks128; ++i) tcgen05_st_x4(tsfb + kb * C::kSfbColsPerAtom + i * 4, rb[kb][i]);
+              for (int i = 0; i < C::kSfBlocks; ++i) tcgen05_st_x4(tsfb + kb * C::kSfbColsPerAtom + i * 4, &rb[kb][4 * i]);
             }
           }
         }
@@ -729,8 +820,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     constexpr uint32_t kRing = C::kStoreBufs / 2;  // staging buffers per group
     OutT* out = static_cast<OutT*>(p.out);
     OutT* aux = static_cast<OutT*>(p.aux);
-    uint32_t acc = 0, acc_phase = 0, store_buf = 0;
-    const uint32_t my_bias = smem_bias + eg * kBlockN * 4;
+    uint32_t acc = 0, acc_phase = 0, store_buf = 0, tile_iter = 0;
+    const uint32_t my_bias = smem_bias + eg * C::kBiasSlots * 128 * 4;
     const float* my_bias_gen = reinterpret_cast<const float*>(smem_gen + (my_bias - smem_base));
     const uint32_t my_store = smem_store + eg * kRing * kStoreStageBytes;
     const float gb = p.mode == NVFP4_GS_NONE ? 1.0f : __ldg(p.b_global);
@@ -746,20 +837,23 @@ __global__ void __launch_bounds__(kThreads, 1)
     // The bias slice of a tile travels the same way: its values are fetched into registers one tile ahead
     // and reach shared memory only when the column block changes (a banded schedule keeps a CTA on one
     // column block for many tiles).
-    float bias_next[kBlockN / 128];
+    float bias_next[C::kBiasSlots];
     uint32_t staged_bias_blk = 0xffffffffu;
     auto fetch_bias = [&](uint32_t w) {
       uint32_t mb, nb, sp;
       decode(w, mb, nb, sp);
 #pragma unroll
-      for (int j = 0; j < kBlockN / 128; ++j) {
-        const uint32_t col = nb * kBlockN + gtid + 128 * j;
-        bias_next[j] = (p.tma_store && p.epilogue != NVFP4_EPI_NONE && col < p.n) ? __ldg(p.bias + col) : 0.0f;
+      for (int j = 0; j < C::kBiasSlots; ++j) {
+        const uint32_t in_tile = gtid + 128 * j;
+        const uint32_t col = nb * kBlockN + in_tile;
+        bias_next[j] = (p.tma_store && p.epilogue != NVFP4_EPI_NONE && in_tile < static_cast<uint32_t>(kBlockN) && col < p.n)
+                           ? bias_value(p, col)
+                           : 0.0f;
       }
     };
     if (w_begin < w_end) fetch_bias(w_begin);
     float ga_next = w_begin < w_end ? row_scale(w_begin) : 0.0f;
-    for (uint32_t w = w_begin; w < w_end; w += w_step) {
+    for (uint32_t w = w_begin; w < w_end; w += w_step, ++tile_iter) {
       uint32_t m_blk, n_blk, split;
       decode(w, m_blk, n_blk, split);
       const float ga_row = ga_next;
@@ -770,13 +864,17 @@ __global__ void __launch_bounds__(kThreads, 1)
       const bool add_bias = p.tma_store && p.epilogue != NVFP4_EPI_NONE && (p.k_splits == 1 || split == 0);
       if (add_bias && n_blk != staged_bias_blk) {  // uniform across the group
 #pragma unroll
-        for (int j = 0; j < kBlockN / 128; ++j)
+        for (int j = 0; j < C::kBiasSlots; ++j)
           asm volatile("st.shared.f32 [%0], %1;" ::"r"(my_bias + (gtid + 128 * j) * 4), "f"(bias_next[j]) : "memory");
         epilogue_barrier(eg);
         staged_bias_blk = n_blk;
       }
       if (w + w_step < w_end) fetch_bias(w + w_step);
-      if (!mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, kStatusEpilogueTimeout)) break;
+      // go on only if every thread of the group saw the accumulator arrive (no thread may be left in a
+      // later barrier of the group when another one gives up)
+      if (!epilogue_all(eg, mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, kStatusEpilogueTimeout,
+                                      p.wait_timeout_ns)))
+        break;
       tcgen05_fence_after();
       const uint32_t row = m_blk * kBlockM + gtid;
       const bool row_ok = row < p.m;
@@ -796,12 +894,17 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (p.tma_store) {
         // Sub-tiles of 128 rows x 128 bytes go through the group's shared-memory ring and leave
         // with TMA stores (TMA reduce-add for split-K partial sums); rows / columns outside the
-        // matrix are clipped by the tensor map.
+        // matrix are clipped by the tensor map.  The groups take alternate sub-tiles; with an odd
+        // number of sub-tiles per tile (192 bf16 columns = 3) the group that takes two alternates
+        // from tile to tile, which the double-buffered accumulator evens out.
         constexpr int kSub = SubTile<OutT>::kCols;
+        constexpr int kNumSub = kBlockN / kSub;
+        const int first_sub = static_cast<int>((kNumSub & 1) ? (eg ^ (tile_iter & 1u)) : eg);
         // a group whose first sub-tile already lies outside the matrix reads nothing
-        if (n_blk * kBlockN + eg * kSub >= p.n) release_accumulator();
+        if (n_blk * kBlockN + first_sub * kSub >= p.n) release_accumulator();
+        float row_max = -INFINITY;  // largest value this thread stores for its row in this tile
 #pragma unroll 1
-        for (int c = eg * kSub; c < kBlockN; c += 2 * kSub) {
+        for (int c = first_sub * kSub; c < kBlockN; c += 2 * kSub) {
           const uint32_t col0 = n_blk * kBlockN + c;
           if (col0 >= p.n) break;  // uniform across the group
           float v[kSub];
@@ -826,6 +929,13 @@ __global__ void __launch_bounds__(kThreads, 1)
                 mul_f32x2(v[i], v[i + 1], __uint_as_float(r[i / 32][i % 32]), __uint_as_float(r[i / 32][i % 32 + 1]),
                           scale2);
             }
+          }
+          if (p.row_amax) {
+            // columns past n hold zero-filled operands (acc = 0): only real columns count
+            const uint32_t valid = min(static_cast<uint32_t>(kSub), p.n - col0);
+#pragma unroll
+            for (int i = 0; i < kSub; ++i)
+              if (static_cast<uint32_t>(i) < valid) row_max = fmaxf(row_max, v[i]);
           }
           const int passes = (p.epilogue == NVFP4_EPI_RELU2 && p.aux) ? 2 : 1;
           for (int pass = 0; pass < passes; ++pass) {
@@ -860,6 +970,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             store_buf = (store_buf + 1) % kRing;
           }
         }
+        if (p.row_amax && row_ok && row_max > 0.0f) {
+          // max over the row of relu(stored value)^2: rounding to the stored type and relu^2 are both
+          // monotonic, so they apply to the maximum instead of to every element
+          const float stored = sizeof(OutT) == 2 ? __bfloat162float(__float2bfloat16_rn(row_max)) : row_max;
+          atomicMax(reinterpret_cast<unsigned int*>(p.row_amax) + row, __float_as_uint(__fmul_rn(stored, stored)));
+        }
       } else {
 #pragma unroll 1
       for (int c = eg * 32; c < kBlockN; c += 64) {
@@ -880,14 +996,14 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int i = 0; i < 32; ++i)
               if (static_cast<uint32_t>(i) < valid) {
                 float t = v[i];
-                if (p.epilogue == NVFP4_EPI_BIAS && split == 0) t = __fadd_rn(t, __ldg(p.bias + col0 + i));
+                if (p.epilogue == NVFP4_EPI_BIAS && split == 0) t = __fadd_rn(t, bias_value(p, col0 + i));
                 atomicAdd(reinterpret_cast<float*>(p.out) + off + i, t);
               }
           } else {
             if (p.epilogue != NVFP4_EPI_NONE) {
 #pragma unroll
               for (int i = 0; i < 32; ++i)
-                if (static_cast<uint32_t>(i) < valid) v[i] = __fadd_rn(v[i], __ldg(p.bias + col0 + i));
+                if (static_cast<uint32_t>(i) < valid) v[i] = __fadd_rn(v[i], bias_value(p, col0 + i));
             }
             if (p.epilogue == NVFP4_EPI_RELU2) {
               if (aux) store_row32<OutT>(aux + off, v, valid, p.vec_store != 0);
@@ -944,8 +1060,46 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// Tensor maps are pure functions of (address, extents, pitch, box): they say nothing about the bytes in
+// memory.  Buffers of a training step never move, so every host thread keeps the maps it has encoded
+// (the reference encodes four maps and copies them to the device before every GEMM,
+// utils/nvfp4_tma_matmul/launcher.rs:106-166).
+struct MapKey {
+  uint64_t base;
+  uint32_t kind, rows, cols, ld_or_box;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && kind == o.kind && rows == o.rows && cols == o.cols && ld_or_box == o.ld_or_box;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = k.base * 0x9E3779B97F4A7C15ull;
+    h ^= (static_cast<uint64_t>(k.kind) << 56) ^ (static_cast<uint64_t>(k.rows) << 24) ^ k.cols;
+    h = (h ^ (h >> 29)) * 0xBF58476D1CE4E5B9ull;
+    h ^= k.ld_or_box;
+    return static_cast<size_t>(h ^ (h >> 32));
+  }
+};
+struct MapCache {
+  std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
+  uint64_t hits = 0, misses = 0;
+};
+MapCache& map_cache() {
+  static thread_local MapCache cache;
+  return cache;
+}
+constexpr size_t kMapCacheLimit = 8192;  // entries per host thread; the cache starts over when it is full
+
 // Nibble matrix [rows][k] seen as bytes [rows][k/2]; box = 128 bytes x box_rows, 128-byte swizzle.
 int encode_operand_map(CUtensorMap* map, const uint8_t* base, uint32_t rows, uint32_t k, uint32_t box_rows) {
+  MapCache& cache = map_cache();
+  const MapKey key{reinterpret_cast<uint64_t>(base), 0u, rows, k, box_rows};
+  auto it = cache.maps.find(key);
+  if (it != cache.maps.end()) {
+    ++cache.hits;
+    *map = it->second;
+    return 0;
+  }
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) {
     set_last_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
@@ -962,11 +1116,22 @@ int encode_operand_map(CUtensorMap* map, const uint8_t* base, uint32_t rows, uin
     set_last_error("cuTensorMapEncodeTiled rejected the operand (base must be 16-byte aligned, k % 32 == 0)");
     return static_cast<int>(cudaErrorInvalidValue);
   }
+  ++cache.misses;
+  if (cache.maps.size() >= kMapCacheLimit) cache.maps.clear();
+  cache.maps.emplace(key, *map);
   return 0;
 }
 
 // Output matrix [rows][ld] of f32 / bf16; box = 128 bytes x 128 rows, 128-byte swizzle.
 int encode_output_map(CUtensorMap* map, void* base, int dtype, uint32_t rows, uint32_t cols, uint32_t ld) {
+  MapCache& cache = map_cache();
+  const MapKey key{reinterpret_cast<uint64_t>(base), dtype == NVFP4_DTYPE_F32 ? 1u : 2u, rows, cols, ld};
+  auto it = cache.maps.find(key);
+  if (it != cache.maps.end()) {
+    ++cache.hits;
+    *map = it->second;
+    return 0;
+  }
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return static_cast<int>(cudaErrorNotSupported);
   const size_t esz = dtype == NVFP4_DTYPE_F32 ? 4 : 2;
@@ -977,18 +1142,32 @@ int encode_output_map(CUtensorMap* map, void* base, int dtype, uint32_t rows, ui
   CUresult r = fn(map, dtype == NVFP4_DTYPE_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                   base, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : static_cast<int>(cudaErrorInvalidValue);
+  if (r != CUDA_SUCCESS) return static_cast<int>(cudaErrorInvalidValue);
+  ++cache.misses;
+  if (cache.maps.size() >= kMapCacheLimit) cache.maps.clear();
+  cache.maps.emplace(key, *map);
+  return 0;
 }
 
+constexpr int kMaxDevices = 64;
+
+int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+
+// SM count of the current device (cached per device ordinal).
 int sm_count() {
-  static int count = 0;
-  if (count == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
-    if (count <= 0) count = 148;
+  static std::atomic<int> counts[kMaxDevices];
+  const int dev = current_device();
+  if (dev < 0) return 148;
+  int c = counts[dev].load(std::memory_order_relaxed);
+  if (c == 0) {
+    if (cudaDeviceGetAttribute(&c, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || c <= 0) c = 148;
+    counts[dev].store(c, std::memory_order_relaxed);
   }
-  return count;
+  return c;
 }
 
 // Optional event timing of GEMM launches (off by default; a measurement aid for benchmarks).
@@ -1003,39 +1182,40 @@ struct GemmTiming {
   size_t used = 0;
 } g_timing;
 
+// Everything the host decides about one launch.
+struct GemmPlan {
+  uint32_t block_n = 128, num_n_blocks = 0, k_splits = 1, k_tiles_per_split = 0;
+  uint32_t stages = 0, grid = 0, b_resident = 0, resident_cpn = 0, tma_store = 0, vec_store = 0;
+  size_t smem_bytes = 0;
+};
+
+struct TileBytes {
+  int fixed, stream_stage, resident_stage, panel_slot;
+};
+template <int kBlockN>
+constexpr TileBytes tile_bytes_of() {
+  return {Cfg<kBlockN>::kFixedBytes, Cfg<kBlockN>::kStreamStageBytes, Cfg<kBlockN>::kResidentStageBytes,
+          Cfg<kBlockN>::kPanelSlotBytes};
+}
+TileBytes tile_bytes(uint32_t block_n) {
+  return block_n == 256 ? tile_bytes_of<256>() : block_n == 192 ? tile_bytes_of<192>() : tile_bytes_of<128>();
+}
+
 template <int kBlockN, typename OutT>
 int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
-                   const CUtensorMap& mx, GemmParams p, uint32_t grid, bool want_resident) {
-  using C = Cfg<kBlockN>;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(nvfp4_gemm_tcgen05_kernel<kBlockN, OutT>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-  });
-  if (attr_err != cudaSuccess) return static_cast<int>(attr_err);
-  // shared-memory plan
-  const int budget = kSmemBudget - C::kFixedBytes;
-  p.b_resident = 0;
-  p.resident_cpn = 0;
-  if (want_resident) {
-    const int left = budget - static_cast<int>(p.num_k_tiles) * C::kPanelSlotBytes;
-    const int st = left / C::kResidentStageBytes;
-    if (st >= 4) {
-      p.b_resident = 1;
-      p.stages = static_cast<uint32_t>(st > kMaxStages ? kMaxStages : st);
-      // banded schedule when the column blocks divide the grid almost evenly
-      const uint32_t cpn = grid / p.num_n_blocks;
-      if (cpn >= 1 && cpn * p.num_n_blocks * 20 >= grid * 19 && p.num_m_blocks >= 4 * cpn) p.resident_cpn = cpn;
-    }
+                   const CUtensorMap& mx, const GemmParams& p, const GemmPlan& pl) {
+  // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel
+  static std::atomic<int> attr_state[kMaxDevices];  // 0 = not set, 1 = set, -(error) = failed
+  const int dev = current_device();
+  if (dev < 0) return static_cast<int>(cudaErrorInvalidDevice);
+  int st = attr_state[dev].load(std::memory_order_acquire);
+  if (st == 0) {
+    const cudaError_t e = cudaFuncSetAttribute(nvfp4_gemm_tcgen05_kernel<kBlockN, OutT>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    st = e == cudaSuccess ? 1 : -static_cast<int>(e);
+    attr_state[dev].store(st, std::memory_order_release);
   }
-  if (!p.b_resident) {
-    const int st = budget / C::kStreamStageBytes;
-    p.stages = static_cast<uint32_t>(st > kMaxStages ? kMaxStages : st);
-  }
-  const uint32_t b_slots = p.b_resident ? p.num_k_tiles : p.stages;
-  const size_t smem_bytes = C::kFixedBytes + static_cast<size_t>(p.stages) * (kAStageBytes + kSfaStageBytes) +
-                            static_cast<size_t>(b_slots) * C::kPanelSlotBytes;
+  if (st < 0) return -st;
   GemmTimingRecord* rec = nullptr;
   if (g_timing.enabled) {
     std::lock_guard<std::mutex> lock(g_timing.mu);
@@ -1045,11 +1225,149 @@ int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb,
     rec->flops = 2.0 * p.m * p.n * p.k;
     cudaEventRecord(rec->start, s);
   }
-  nvfp4_gemm_tcgen05_kernel<kBlockN, OutT><<<grid, kThreads, smem_bytes, s>>>(ma, mb, mo, mx, p);
+  nvfp4_gemm_tcgen05_kernel<kBlockN, OutT><<<pl.grid, kThreads, pl.smem_bytes, s>>>(ma, mb, mo, mx, p);
   count_launch();
   const int rc = static_cast<int>(cudaGetLastError());
   if (rec) cudaEventRecord(rec->stop, s);
   return rc;
+}
+
+std::atomic<int> g_tile_override{-1};       // -1 = read NVFP4_GEMM_TILE once, 0 = automatic, else forced width
+std::atomic<uint64_t> g_wait_timeout_ns{kDefaultWaitTimeoutNs};
+std::atomic<uint32_t> g_debug_flags{0};
+
+int tile_override() {
+  int v = g_tile_override.load(std::memory_order_relaxed);
+  if (v < 0) {
+    const char* env = std::getenv("NVFP4_GEMM_TILE");
+    v = env ? std::atoi(env) : 0;
+    if (v != 128 && v != 192 && v != 256) v = 0;
+    g_tile_override.store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
+int validate_gemm(const nvfp4_gemm_args& a) {
+  if (a.k == 0 || a.k % 64 != 0 || a.ldo < a.n) {
+    set_last_error("nvfp4_gemm: k must be a non-zero multiple of 64 and ldo >= n");
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if ((reinterpret_cast<uintptr_t>(a.a_bytes) | reinterpret_cast<uintptr_t>(a.b_bytes) |
+       reinterpret_cast<uintptr_t>(a.a_scales) | reinterpret_cast<uintptr_t>(a.b_scales)) & 15u) {
+    set_last_error("nvfp4_gemm: operand and scale pointers must be 16-byte aligned");
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  const bool has_bias = a.bias || (a.bias_nvfp4_bytes && a.bias_nvfp4_scales && a.bias_nvfp4_global);
+  if (a.epilogue < NVFP4_EPI_NONE || a.epilogue > NVFP4_EPI_RESIDUAL || (a.epilogue != NVFP4_EPI_NONE && !has_bias) ||
+      a.global_scale_mode < NVFP4_GS_NONE || a.global_scale_mode > NVFP4_GS_ROWWISE_A ||
+      (a.global_scale_mode != NVFP4_GS_NONE && (!a.a_global || !a.b_global)) ||
+      (a.out_dtype != NVFP4_DTYPE_F32 && a.out_dtype != NVFP4_DTYPE_BF16) || !a.out) {
+    set_last_error("nvfp4_gemm: inconsistent epilogue / scale mode / dtype arguments");
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  return 0;
+}
+
+// Tile width, split-K count, shared-memory plan and grid of one GEMM on `sms` SMs.
+void plan_gemm(const nvfp4_gemm_args& a, int sms, GemmPlan& pl) {
+  const uint32_t k_atoms = a.k / 64;
+  const uint32_t num_k_tiles = (k_atoms + kKAtomsPerStage - 1) / kKAtomsPerStage;
+  const uint32_t num_m_blocks = (a.m + kBlockM - 1) / kBlockM;
+  const uint32_t usms = static_cast<uint32_t>(sms);
+  // Tile width.  A block-scaled FP4 tcgen05.mma occupies the tensor pipe for about as long at N = 128 as
+  // at N = 256 (the 128-column form is bound by shared-memory operand reads), so wide tiles do more work
+  // per instruction and are preferred whenever the shape can still fill the SMs:
+  //  * long K: enough wide tiles, or (f32 output, linear epilogue) enough tiles x K splits;
+  //  * short K with many row blocks: wide tile with its whole B panel resident in shared memory.
+  // 192 columns keep a double-buffered accumulator (the drain of one tile hides behind the next main
+  // loop); 256 columns have one buffer; 128 columns remain for everything else.
+  const bool can_split = a.out_dtype == NVFP4_DTYPE_F32 &&
+                         (a.epilogue == NVFP4_EPI_NONE || a.epilogue == NVFP4_EPI_BIAS) && num_k_tiles >= 16;
+  uint32_t block_n = 128;
+  const int forced = tile_override();
+  if (forced) {
+    block_n = static_cast<uint32_t>(forced);
+  } else {
+    const uint32_t tiles192 = num_m_blocks * ((a.n + 191) / 192);
+    const uint32_t tiles256 = num_m_blocks * ((a.n + 255) / 256);
+    // columns of the last 192-wide block that lie outside the matrix, as a share of all columns computed
+    const uint32_t cols192 = (a.n + 191) / 192 * 192;
+    const bool fits192 = (cols192 - a.n) * 16u <= cols192;  // at most 1/16 wasted
+    const bool wide192 = fits192 && a.n >= 192 && (tiles192 >= usms || can_split);
+    const bool wide_shape = a.n % 256 == 0 || a.n > 1024;
+    const bool wide_long_k = wide_shape && num_k_tiles >= 4 && (tiles256 >= usms || can_split);
+    const bool wide_short_k = a.n % 256 == 0 && num_k_tiles <= 3 && tiles256 >= 4u * usms;
+    if (wide192)
+      block_n = 192;
+    else if (wide_long_k || wide_short_k)
+      block_n = 256;
+  }
+  pl.block_n = block_n;
+  pl.num_n_blocks = (a.n + block_n - 1) / block_n;
+  const uint32_t tiles = num_m_blocks * pl.num_n_blocks;
+
+  // split-K for long GEMMs with few tiles (dW = dY^T.X): f32 output, linear epilogue only
+  pl.k_splits = 1;
+  if (can_split && tiles < 2 * usms) {
+    // The split count that minimises waves x (main loop + accumulator drain) of one work item, in units of
+    // k-tiles (a drain that is not hidden behind the next main loop costs about four k-tiles); ties go to
+    // fewer splits.
+    const uint32_t drain = block_n == 256 ? 4u : 1u;
+    uint32_t max_splits = num_k_tiles / 8;
+    if (max_splits > 32) max_splits = 32;
+    if (max_splits > 2 && gemm_get_deterministic()) max_splits = 2;
+    uint32_t best = 1;
+    uint64_t best_cost = ~0ull;
+    for (uint32_t sp = 1; sp <= max_splits; ++sp) {
+      const uint32_t per = (num_k_tiles + sp - 1) / sp;
+      const uint32_t real = (num_k_tiles + per - 1) / per;
+      const uint64_t waves = (static_cast<uint64_t>(tiles) * real + usms - 1) / usms;
+      const uint64_t cost = waves * (per + drain);
+      if (cost < best_cost) best_cost = cost, best = sp;
+    }
+    if (best > 1) pl.k_splits = best;
+  }
+  pl.k_tiles_per_split = (num_k_tiles + pl.k_splits - 1) / pl.k_splits;
+  pl.k_splits = (num_k_tiles + pl.k_tiles_per_split - 1) / pl.k_tiles_per_split;
+
+  const size_t esz = a.out_dtype == NVFP4_DTYPE_F32 ? 4 : 2;
+  const uint32_t vec_elems = 16 / static_cast<uint32_t>(esz);
+  pl.vec_store = ((reinterpret_cast<uintptr_t>(a.out) & 15u) == 0 && a.ldo % vec_elems == 0 &&
+                  (!a.aux || (reinterpret_cast<uintptr_t>(a.aux) & 15u) == 0))
+                     ? 1
+                     : 0;
+  // TMA-store epilogue whenever the output satisfies the tensor-map rules (16-byte aligned base
+  // and row pitch); the in-place residual epilogue and odd layouts use direct stores.
+  pl.tma_store = (pl.vec_store && a.epilogue != NVFP4_EPI_RESIDUAL) ? 1 : 0;
+
+  const uint32_t work = tiles * pl.k_splits;
+  pl.grid = work < usms ? work : usms;
+  // Short K and many row blocks: keep the B panel resident and stream only A (halves the
+  // operand traffic per tile; these shapes are otherwise bound by L2 -> SM bandwidth).
+  const bool want_resident =
+      pl.k_splits == 1 && num_k_tiles <= (block_n == 256 ? 3u : 4u) && tiles >= 4 * pl.grid;
+  const TileBytes tb = tile_bytes(block_n);
+  const int budget = kSmemBudget - tb.fixed;
+  pl.b_resident = 0;
+  pl.resident_cpn = 0;
+  if (want_resident) {
+    const int left = budget - static_cast<int>(num_k_tiles) * tb.panel_slot;
+    const int st = left / tb.resident_stage;
+    if (st >= 4) {
+      pl.b_resident = 1;
+      pl.stages = static_cast<uint32_t>(st > kMaxStages ? kMaxStages : st);
+      // banded schedule when the column blocks divide the grid almost evenly
+      const uint32_t cpn = pl.grid / pl.num_n_blocks;
+      if (cpn >= 1 && cpn * pl.num_n_blocks * 20 >= pl.grid * 19 && num_m_blocks >= 4 * cpn) pl.resident_cpn = cpn;
+    }
+  }
+  if (!pl.b_resident) {
+    const int st = budget / tb.stream_stage;
+    pl.stages = static_cast<uint32_t>(st > kMaxStages ? kMaxStages : st);
+  }
+  const uint32_t b_slots = pl.b_resident ? num_k_tiles : pl.stages;
+  pl.smem_bytes = tb.fixed + static_cast<size_t>(pl.stages) * (kAStageBytes + kSfaStageBytes) +
+                  static_cast<size_t>(b_slots) * tb.panel_slot;
 }
 
 }  // namespace
@@ -1104,22 +1422,59 @@ uint32_t* device_status_word() {
   return ptr;
 }
 
+int gemm_plan_query(const nvfp4_gemm_args& a, nvfp4_gemm_plan* out) {
+  if (!out) return static_cast<int>(cudaErrorInvalidValue);
+  std::memset(out, 0, sizeof(*out));
+  if (a.m == 0 || a.n == 0) return 0;
+  const int rc = validate_gemm(a);
+  if (rc) return rc;
+  GemmPlan pl;
+  plan_gemm(a, sm_count(), pl);
+  // the kernel falls back to direct stores when the output map cannot be encoded; that cannot happen for
+  // outputs that pass the alignment test above, so the plan reports the test's verdict
+  out->block_n = pl.block_n;
+  out->acc_stages = pl.block_n == 256 ? 1 : 2;
+  out->k_splits = pl.k_splits;
+  out->b_resident = pl.b_resident;
+  out->resident_cpn = pl.resident_cpn;
+  out->stages = pl.stages;
+  out->grid = pl.grid;
+  out->tma_store = pl.tma_store;
+  out->smem_bytes = static_cast<uint32_t>(pl.smem_bytes);
+  return 0;
+}
+
+void gemm_set_tile_override(int block_n) {
+  g_tile_override.store((block_n == 128 || block_n == 192 || block_n == 256) ? block_n : 0, std::memory_order_relaxed);
+}
+void gemm_set_wait_timeout_ns(uint64_t ns) { g_wait_timeout_ns.store(ns ? ns : kDefaultWaitTimeoutNs, std::memory_order_relaxed); }
+void gemm_set_debug_flags(uint32_t flags) { g_debug_flags.store(flags, std::memory_order_relaxed); }
+void gemm_map_cache_stats(uint64_t* hits, uint64_t* misses) {
+  if (hits) *hits = map_cache().hits;
+  if (misses) *misses = map_cache().misses;
+}
+
+int gemm_prepare_operand_maps(const uint8_t* a_bytes, const uint8_t* b_bytes, uint32_t m, uint32_t k, uint32_t n) {
+  if (k == 0 || k % 64 != 0) {
+    set_last_error("prepare_tma: input_dim must be a non-zero multiple of 64");
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  CUtensorMap tmp;
+  int rc = encode_operand_map(&tmp, a_bytes, m, k, kBlockM);
+  // B is read with a box as tall as the tile the launch will choose: encode all three
+  for (uint32_t box : {128u, 192u, 256u})
+    if (!rc) rc = encode_operand_map(&tmp, b_bytes, n, k, box);
+  return rc;
+}
+
 int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   if (a.m == 0 || a.n == 0) return 0;
-  if (a.k == 0 || a.k % 64 != 0 || a.ldo < a.n) {
-    set_last_error("nvfp4_gemm: k must be a non-zero multiple of 64 and ldo >= n");
-    return static_cast<int>(cudaErrorInvalidValue);
-  }
-  if ((reinterpret_cast<uintptr_t>(a.a_bytes) | reinterpret_cast<uintptr_t>(a.b_bytes) |
-       reinterpret_cast<uintptr_t>(a.a_scales) | reinterpret_cast<uintptr_t>(a.b_scales)) & 15u) {
-    set_last_error("nvfp4_gemm: operand and scale pointers must be 16-byte aligned");
-    return static_cast<int>(cudaErrorInvalidValue);
-  }
-  if (a.epilogue < NVFP4_EPI_NONE || a.epilogue > NVFP4_EPI_RESIDUAL || (a.epilogue != NVFP4_EPI_NONE && !a.bias) ||
-      a.global_scale_mode < NVFP4_GS_NONE || a.global_scale_mode > NVFP4_GS_ROWWISE_A ||
-      (a.global_scale_mode != NVFP4_GS_NONE && (!a.a_global || !a.b_global)) ||
-      (a.out_dtype != NVFP4_DTYPE_F32 && a.out_dtype != NVFP4_DTYPE_BF16) || !a.out) {
-    set_last_error("nvfp4_gemm: inconsistent epilogue / scale mode / dtype arguments");
+  int rc = validate_gemm(a);
+  if (rc) return rc;
+  GemmPlan pl;
+  plan_gemm(a, sm_count(), pl);
+  if (a.relu2_row_amax && !pl.tma_store) {
+    set_last_error("nvfp4_gemm: relu2_row_amax needs a 16-byte aligned output and row pitch and no residual epilogue");
     return static_cast<int>(cudaErrorInvalidValue);
   }
 
@@ -1129,6 +1484,10 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   p.a_global = a.a_global;
   p.b_global = a.b_global;
   p.bias = a.bias;
+  p.bias_bytes = a.bias_nvfp4_bytes;
+  p.bias_scales = a.bias_nvfp4_scales;
+  p.bias_global = a.bias_nvfp4_global;
+  p.row_amax = a.relu2_row_amax;
   p.out = a.out;
   p.aux = a.aux;
   p.m = a.m;
@@ -1141,91 +1500,56 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   p.k_atoms = a.k / 64;
   p.num_k_tiles = (p.k_atoms + kKAtomsPerStage - 1) / kKAtomsPerStage;
   p.num_m_blocks = (a.m + kBlockM - 1) / kBlockM;
+  p.num_n_blocks = pl.num_n_blocks;
   p.sfb_blocks128 = (a.n + 127) / 128;
-
-  const int sms = sm_count();
-  // Tile width: 256 columns halves the shared-memory traffic per flop; 128 columns double
-  // buffers the accumulator so the (output-bound) epilogue hides behind the next main loop.
-  // Short-K GEMMs are epilogue bound, long-K GEMMs are main-loop bound.
-  // Tile width.  A block-scaled FP4 tcgen05.mma occupies the tensor pipe for about as long at
-  // N = 128 as at N = 256 (measured ~140 cycles per instruction either way), so the wide tile does
-  // twice the work per instruction and is preferred whenever the shape can still fill the SMs:
-  //  * long K: enough wide tiles, or (f32 output, linear epilogue) enough tiles x K splits;
-  //  * short K with many row blocks: wide tile with its whole B panel resident -- the next tile's
-  //    A stages fill while the single-buffered accumulator drains.
-  // The narrow tile double buffers its accumulator and remains for everything else.
-  const uint32_t tiles256 = p.num_m_blocks * ((a.n + 255) / 256);
-  const bool can_split = a.out_dtype == NVFP4_DTYPE_F32 &&
-                         (a.epilogue == NVFP4_EPI_NONE || a.epilogue == NVFP4_EPI_BIAS) && p.num_k_tiles >= 16;
-  const bool wide_shape = a.n % 256 == 0 || a.n > 1024;
-  const bool wide_long_k = wide_shape && p.num_k_tiles >= 4 && (tiles256 >= static_cast<uint32_t>(sms) || can_split);
-  const bool wide_short_k = a.n % 256 == 0 && p.num_k_tiles <= 3 && tiles256 >= 4u * static_cast<uint32_t>(sms);
-  const bool wide = wide_long_k || wide_short_k;
-  const uint32_t block_n = wide ? 256 : 128;
-  p.num_n_blocks = (a.n + block_n - 1) / block_n;
-  const uint32_t tiles = p.num_m_blocks * p.num_n_blocks;
-
-  // split-K for long GEMMs with few tiles (dW = dY^T.X): f32 output, linear epilogue only
-  p.k_splits = 1;
-  if (can_split && tiles * 2 <= static_cast<uint32_t>(sms)) {
-    // The split count that minimises waves x (main loop + accumulator drain) of one work item, in units of
-    // k-tiles (a drain costs about four k-tiles of main loop); ties go to fewer splits.
-    uint32_t max_splits = p.num_k_tiles / 8;
-    if (max_splits > 32) max_splits = 32;
-    if (max_splits > 2 && gemm_get_deterministic()) max_splits = 2;
-    uint32_t best = 1;
-    uint64_t best_cost = ~0ull;
-    for (uint32_t sp = 1; sp <= max_splits; ++sp) {
-      const uint32_t per = (p.num_k_tiles + sp - 1) / sp;
-      const uint32_t real = (p.num_k_tiles + per - 1) / per;
-      const uint64_t waves = (static_cast<uint64_t>(tiles) * real + sms - 1) / sms;
-      const uint64_t cost = waves * (per + 4);
-      if (cost < best_cost) best_cost = cost, best = sp;
-    }
-    if (best > 1) p.k_splits = best;
-  }
-  p.k_tiles_per_split = (p.num_k_tiles + p.k_splits - 1) / p.k_splits;
-  p.k_splits = (p.num_k_tiles + p.k_tiles_per_split - 1) / p.k_tiles_per_split;
-
-  const size_t esz = a.out_dtype == NVFP4_DTYPE_F32 ? 4 : 2;
-  const uint32_t vec_elems = 16 / static_cast<uint32_t>(esz);
-  p.vec_store = ((reinterpret_cast<uintptr_t>(a.out) & 15u) == 0 && a.ldo % vec_elems == 0 &&
-                 (!a.aux || (reinterpret_cast<uintptr_t>(a.aux) & 15u) == 0))
-                    ? 1
-                    : 0;
+  p.k_splits = pl.k_splits;
+  p.k_tiles_per_split = pl.k_tiles_per_split;
+  p.stages = pl.stages;
+  p.b_resident = static_cast<int>(pl.b_resident);
+  p.resident_cpn = pl.resident_cpn;
+  p.vec_store = static_cast<int>(pl.vec_store);
+  p.tma_store = static_cast<int>(pl.tma_store);
+  p.wait_timeout_ns = g_wait_timeout_ns.load(std::memory_order_relaxed);
+  p.debug_flags = g_debug_flags.load(std::memory_order_relaxed);
 
   CUtensorMap ma, mb, mo, mx;
-  int rc = encode_operand_map(&ma, a.a_bytes, a.m, a.k, kBlockM);
+  rc = encode_operand_map(&ma, a.a_bytes, a.m, a.k, kBlockM);
   if (rc) return rc;
-  rc = encode_operand_map(&mb, a.b_bytes, a.n, a.k, block_n);
+  rc = encode_operand_map(&mb, a.b_bytes, a.n, a.k, pl.block_n);
   if (rc) return rc;
-  // TMA-store epilogue whenever the output satisfies the tensor-map rules (16-byte aligned base
-  // and row pitch); the in-place residual epilogue and odd layouts use direct stores.
-  p.tma_store = (p.vec_store && a.epilogue != NVFP4_EPI_RESIDUAL) ? 1 : 0;
   mo = ma;
   mx = ma;
   if (p.tma_store) {
     if (encode_output_map(&mo, a.out, a.out_dtype, a.m, a.n, a.ldo) != 0) p.tma_store = 0;
     if (p.tma_store && a.aux && encode_output_map(&mx, a.aux, a.out_dtype, a.m, a.n, a.ldo) != 0) p.tma_store = 0;
+    if (!p.tma_store && a.relu2_row_amax) {
+      set_last_error("nvfp4_gemm: relu2_row_amax needs an output the TMA store path accepts");
+      return static_cast<int>(cudaErrorInvalidValue);
+    }
   }
 
+  const size_t esz = a.out_dtype == NVFP4_DTYPE_F32 ? 4 : 2;
   if (p.k_splits > 1) {
     cudaError_t e = cudaMemset2DAsync(a.out, static_cast<size_t>(a.ldo) * esz, 0, static_cast<size_t>(a.n) * esz, a.m, s);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-
-  const uint32_t work = tiles * p.k_splits;
-  const uint32_t grid = work < static_cast<uint32_t>(sms) ? work : static_cast<uint32_t>(sms);
-  // Short K and many row blocks: keep the B panel resident and stream only A (halves the
-  // operand traffic per tile; these shapes are otherwise bound by L2 -> SM bandwidth).
-  const bool want_resident =
-      p.k_splits == 1 && p.num_k_tiles <= (block_n == 128 ? 4u : 3u) && tiles >= 4 * grid;
-  if (block_n == 256) {
-    return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<256, float>(s, ma, mb, mo, mx, p, grid, want_resident)
-                                          : launch_variant<256, __nv_bfloat16>(s, ma, mb, mo, mx, p, grid, want_resident);
+  if (a.relu2_row_amax) {
+    cudaError_t e = cudaMemsetAsync(a.relu2_row_amax, 0, static_cast<size_t>(a.m) * sizeof(float), s);
+    if (e != cudaSuccess) return static_cast<int>(e);
   }
-  return a.out_dtype == NVFP4_DTYPE_F32 ? launch_variant<128, float>(s, ma, mb, mo, mx, p, grid, want_resident)
-                                        : launch_variant<128, __nv_bfloat16>(s, ma, mb, mo, mx, p, grid, want_resident);
+
+  const bool f32 = a.out_dtype == NVFP4_DTYPE_F32;
+  switch (pl.block_n) {
+    case 256:
+      return f32 ? launch_variant<256, float>(s, ma, mb, mo, mx, p, pl)
+                 : launch_variant<256, __nv_bfloat16>(s, ma, mb, mo, mx, p, pl);
+    case 192:
+      return f32 ? launch_variant<192, float>(s, ma, mb, mo, mx, p, pl)
+                 : launch_variant<192, __nv_bfloat16>(s, ma, mb, mo, mx, p, pl);
+    default:
+      return f32 ? launch_variant<128, float>(s, ma, mb, mo, mx, p, pl)
+                 : launch_variant<128, __nv_bfloat16>(s, ma, mb, mo, mx, p, pl);
+  }
 }
 
 }  // namespace nvfp4

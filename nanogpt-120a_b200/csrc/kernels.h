@@ -16,11 +16,13 @@ int launch_nvfp4_amax(cudaStream_t s, const uint8_t* bytes, const uint8_t* scale
 // transform 0: out[0] = max(chunks); 1: out[0] = MS-EDEN global scale of that max
 int launch_amax_from_chunks(cudaStream_t s, const float* chunk_amax, float* out, uint32_t chunk_count, int transform);
 int launch_ms_eden_scale_from_amax(cudaStream_t s, const float* amax, float* out);
+// relu2: quantize relu(x)^2 computed on load; decoded_amax (optional f32[1]): max |decoded value| of the result
 int launch_four_six(cudaStream_t s, const void* x, int dtype, const float* amax, int rowwise, uint32_t rows,
-                    uint32_t cols, uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs);
+                    uint32_t cols, uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs, int relu2 = 0,
+                    float* decoded_amax = nullptr);
 int launch_four_six_rowwise_fused(cudaStream_t s, const void* x, int dtype, uint32_t rows, uint32_t cols,
                                   uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs, float* out_amax,
-                                  float* decoded_amax);
+                                  float* decoded_amax, int relu2 = 0);
 int launch_four_six_padded(cudaStream_t s, const float* x, const float* amax, uint8_t* out_fp4, uint8_t* out_scales,
                            float* out_gs, uint32_t rows, uint32_t cols, uint32_t padded_rows, uint32_t padded_cols,
                            int transposed);
@@ -59,6 +61,16 @@ uint32_t relu2_backward_grid(uint64_t n);
 
 // gemm_tcgen05.cu ---------------------------------------------------------------------------
 int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a);
+// What launch_gemm would choose for these arguments on the current device (no launch).
+int gemm_plan_query(const nvfp4_gemm_args& a, nvfp4_gemm_plan* out);
+// Encodes (and keeps in the calling thread's cache) the operand tensor maps of a GEMM ahead of its launch.
+int gemm_prepare_operand_maps(const uint8_t* a_bytes, const uint8_t* b_bytes, uint32_t m, uint32_t k, uint32_t n);
+// Measurement / test aids: forced tile width (0 = automatic), limit of the kernel's bounded waits,
+// debug flags (bit 0: CTA 0 of every GEMM never loads its first k-tile), tensor-map cache counters.
+void gemm_set_tile_override(int block_n);
+void gemm_set_wait_timeout_ns(uint64_t ns);
+void gemm_set_debug_flags(uint32_t flags);
+void gemm_map_cache_stats(uint64_t* hits, uint64_t* misses);
 // 1: split-K never uses more than two splits (run-to-run identical sums); 0 (default): as many as fill the SMs
 void gemm_set_deterministic(int on);
 int gemm_get_deterministic();

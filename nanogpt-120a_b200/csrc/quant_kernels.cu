@@ -290,27 +290,42 @@ __device__ __forceinline__ uint32_t four_six_group(const float (&v)[16], float g
   return six ? b6 : b4;
 }
 
-// One thread per 16-group of a [rows][cols] tensor.
-template <typename T, bool kRowwise, bool kPacked>
+// relu(x)^2 of the values a quantizer has just loaded (the MLP activation computed on load from the stored
+// pre-activation): max(x, 0) drops NaN like the reference's max_f32, the square is one rounded multiply.
+__device__ __forceinline__ void relu2_inplace16(float (&v)[16]) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float r = max_f32(v[i], 0.0f);
+    v[i] = r * r;
+  }
+}
+
+// One thread per 16-group of a [rows][cols] tensor.  kRelu2: the tensor quantized is relu(x)^2.
+// decoded_amax (optional, zeroed by the launcher): max |decoded value| of the quantized tensor.
+template <typename T, bool kRowwise, bool kPacked, bool kRelu2>
 __global__ void __launch_bounds__(256) four_six_kernel(const T* __restrict__ x, const float* __restrict__ amax,
                                                         uint8_t* __restrict__ out_fp4, uint8_t* __restrict__ out_scales,
-                                                        float* __restrict__ out_gs, uint64_t group_count,
-                                                        uint32_t groups_per_row) {
+                                                        float* __restrict__ out_gs, float* __restrict__ decoded_amax,
+                                                        uint64_t group_count, uint32_t groups_per_row) {
   const uint64_t g = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
-  if (g >= group_count) return;
-  const uint32_t row = static_cast<uint32_t>(g / groups_per_row);
-  const uint32_t kg = static_cast<uint32_t>(g - static_cast<uint64_t>(row) * groups_per_row);
-  const float gs = four_six_global_scale(amax[kRowwise ? row : 0]);
-  float v[16];
-  Load16<T>::run(x + g * 16, v);
-  uint2 packed;
-  const uint32_t b = four_six_group(v, gs, packed);
-  *reinterpret_cast<uint2*>(out_fp4 + g * 8) = packed;
-  if (kPacked)
-    out_scales[packed_scale_offset(row, kg, groups_per_row >> 2)] = static_cast<uint8_t>(b);
-  else
-    out_scales[g] = static_cast<uint8_t>(b);
-  if (kRowwise ? (kg == 0) : (g == 0)) out_gs[kRowwise ? row : 0] = gs;
+  float dec = 0.0f;
+  if (g < group_count) {
+    const uint32_t row = static_cast<uint32_t>(g / groups_per_row);
+    const uint32_t kg = static_cast<uint32_t>(g - static_cast<uint64_t>(row) * groups_per_row);
+    const float gs = four_six_global_scale(amax[kRowwise ? row : 0]);
+    float v[16];
+    Load16<T>::run(x + g * 16, v);
+    if (kRelu2) relu2_inplace16(v);
+    uint2 packed;
+    const uint32_t b = four_six_group(v, gs, packed, decoded_amax ? &dec : nullptr);
+    *reinterpret_cast<uint2*>(out_fp4 + g * 8) = packed;
+    if (kPacked)
+      out_scales[packed_scale_offset(row, kg, groups_per_row >> 2)] = static_cast<uint8_t>(b);
+    else
+      out_scales[g] = static_cast<uint8_t>(b);
+    if (kRowwise ? (kg == 0) : (g == 0)) out_gs[kRowwise ? row : 0] = gs;
+  }
+  if (decoded_amax) cta_atomic_max(warp_max(dec), decoded_amax);  // uniform across the CTA
 }
 
 // Row amax and rowwise four-six in ONE pass over the input: a CTA owns whole rows (one thread
@@ -320,7 +335,7 @@ __global__ void __launch_bounds__(256) four_six_kernel(const T* __restrict__ x, 
 // decoded_amax (optional, zeroed by the launcher): max |decoded value| of the whole quantized
 // tensor, i.e. what utils/nvfp4/quant/kernels/ms_eden/amax.rs:23-64 computes from the stored
 // tensor before the backward transposer -- handed over so that pass can be skipped.
-template <typename T, bool kPacked>
+template <typename T, bool kPacked, bool kRelu2>
 __global__ void __launch_bounds__(256) four_six_rowwise_fused_kernel(const T* __restrict__ x,
                                                                       uint8_t* __restrict__ out_fp4,
                                                                       uint8_t* __restrict__ out_scales,
@@ -340,6 +355,7 @@ __global__ void __launch_bounds__(256) four_six_rowwise_fused_kernel(const T* __
   float ga = 0.0f;
   if (active) {
     Load16<T>::run(x + (static_cast<size_t>(row) * groups_per_row + kg) * 16, v);
+    if (kRelu2) relu2_inplace16(v);
 #pragma unroll
     for (int i = 0; i < 16; i += 2) ga = max3_abs(ga, v[i], v[i + 1]);
   }
@@ -652,6 +668,7 @@ struct MsEdenOut {
   uint32_t dst_row_len;   // output K (multiple of 32)
   uint32_t scale_seed;
   uint32_t group_offset;  // added to the flat group id of the scale RNG
+  uint32_t group_row_stride;  // 16-groups per row in the scale RNG's index space (dst_row_len / 16 unless sharded)
   uint32_t sign_offset;   // added to the K index of the sign hash
   int packed;             // scale bytes in the packed tile layout
 };
@@ -690,7 +707,7 @@ __device__ __forceinline__ void ms_eden_emit_chunk(f32x2_t (&P)[16], const MsEde
   }
   const float safe_gs = nz(gs);
   const float inv6 = inv_scale(6.0f, safe_gs);
-  const uint32_t group0 = static_cast<uint32_t>(chunk) * 2u + o.group_offset;
+  const uint32_t group0 = row * o.group_row_stride + chunk_in_row * 2u + o.group_offset;
   uint4 nibbles;
   const uint32_t sb = ms_eden_groups_x2(P, safe_gs, so, inv6, o.scale_seed, group0, nibbles);
   *reinterpret_cast<uint4*>(o.fp4 + chunk * 16) = nibbles;
@@ -737,8 +754,8 @@ __device__ __forceinline__ void ms_eden_emit_chunk_lanes(f32x2_t (&P)[32], const
   }
   const float safe_gs = nz(gs);
   const float inv6 = inv_scale(6.0f, safe_gs);
-  const uint32_t g_lo = static_cast<uint32_t>(chunk_lo) * 2u + o.group_offset;
-  const uint32_t g_hi = static_cast<uint32_t>(chunk_hi) * 2u + o.group_offset;
+  const uint32_t g_lo = row_lo * o.group_row_stride + chunk_in_row * 2u + o.group_offset;
+  const uint32_t g_hi = row_hi * o.group_row_stride + chunk_in_row * 2u + o.group_offset;
   uint2 lo0, hi0, lo1, hi1;
   const uint32_t sb0 = ms_eden_group_lanes(&P[0], safe_gs, so, inv6, o.scale_seed, g_lo, g_hi, lo0, hi0);
   const uint32_t sb1 = ms_eden_group_lanes(&P[16], safe_gs, so, inv6, o.scale_seed, g_lo + 1, g_hi + 1, lo1, hi1);
@@ -1549,34 +1566,44 @@ int launch_ms_eden_scale_from_amax(cudaStream_t s, const float* amax, float* out
   NVFP4_RETURN_LAST();
 }
 
-template <typename T>
+template <typename T, bool kRelu2>
 static int launch_four_six_t(cudaStream_t s, const T* x, const float* amax, int rowwise, uint32_t rows, uint32_t cols,
-                             uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs) {
+                             uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs, float* decoded_amax) {
   const uint32_t gpr = cols / 16;
   const uint64_t groups = static_cast<uint64_t>(rows) * gpr;
   const uint32_t grid = blocks_for(groups, 256);
+#define NVFP4_LAUNCH_FS(R, P) \
+  four_six_kernel<T, R, P, kRelu2><<<grid, 256, 0, s>>>(x, amax, out_fp4, out_scales, out_gs, decoded_amax, groups, gpr)
   if (rowwise) {
-    if (packed)
-      four_six_kernel<T, true, true><<<grid, 256, 0, s>>>(x, amax, out_fp4, out_scales, out_gs, groups, gpr);
-    else
-      four_six_kernel<T, true, false><<<grid, 256, 0, s>>>(x, amax, out_fp4, out_scales, out_gs, groups, gpr);
+    if (packed) NVFP4_LAUNCH_FS(true, true);
+    else NVFP4_LAUNCH_FS(true, false);
   } else {
-    if (packed)
-      four_six_kernel<T, false, true><<<grid, 256, 0, s>>>(x, amax, out_fp4, out_scales, out_gs, groups, gpr);
-    else
-      four_six_kernel<T, false, false><<<grid, 256, 0, s>>>(x, amax, out_fp4, out_scales, out_gs, groups, gpr);
+    if (packed) NVFP4_LAUNCH_FS(false, true);
+    else NVFP4_LAUNCH_FS(false, false);
   }
+#undef NVFP4_LAUNCH_FS
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 
 int launch_four_six(cudaStream_t s, const void* x, int dtype, const float* amax, int rowwise, uint32_t rows,
-                    uint32_t cols, uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs) {
+                    uint32_t cols, uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs, int relu2,
+                    float* decoded_amax) {
+  if (decoded_amax) {
+    const cudaError_t err = cudaMemsetAsync(decoded_amax, 0, sizeof(float), s);
+    if (err != cudaSuccess) return static_cast<int>(err);
+  }
   if (rows == 0 || cols == 0) return 0;
-  int rc = dtype == 0 ? launch_four_six_t(s, static_cast<const float*>(x), amax, rowwise, rows, cols, out_fp4,
-                                          out_scales, packed, out_gs)
-                      : launch_four_six_t(s, static_cast<const __nv_bfloat16*>(x), amax, rowwise, rows, cols, out_fp4,
-                                          out_scales, packed, out_gs);
+  int rc;
+  if (dtype == 0) {
+    const float* xf = static_cast<const float*>(x);
+    rc = relu2 ? launch_four_six_t<float, true>(s, xf, amax, rowwise, rows, cols, out_fp4, out_scales, packed, out_gs, decoded_amax)
+               : launch_four_six_t<float, false>(s, xf, amax, rowwise, rows, cols, out_fp4, out_scales, packed, out_gs, decoded_amax);
+  } else {
+    const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+    rc = relu2 ? launch_four_six_t<__nv_bfloat16, true>(s, xb, amax, rowwise, rows, cols, out_fp4, out_scales, packed, out_gs, decoded_amax)
+               : launch_four_six_t<__nv_bfloat16, false>(s, xb, amax, rowwise, rows, cols, out_fp4, out_scales, packed, out_gs, decoded_amax);
+  }
   if (rc) return rc;
   if (packed) return launch_packed_scale_pad(s, out_scales, rows, cols);
   return 0;
@@ -1586,7 +1613,7 @@ int launch_four_six(cudaStream_t s, const void* x, int dtype, const float* amax,
 // caller then runs the two-kernel path).
 int launch_four_six_rowwise_fused(cudaStream_t s, const void* x, int dtype, uint32_t rows, uint32_t cols,
                                   uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs, float* out_amax,
-                                  float* decoded_amax) {
+                                  float* decoded_amax, int relu2) {
   const uint32_t gpr = cols / 16;
   if (gpr == 0 || gpr > 256) return -1;
   if (decoded_amax) {
@@ -1598,16 +1625,22 @@ int launch_four_six_rowwise_fused(cudaStream_t s, const void* x, int dtype, uint
   const uint32_t threads = (rpc * gpr + 31) / 32 * 32;
   const uint32_t grid = (rows + rpc - 1) / rpc;
   const size_t smem = (rpc + 1) * sizeof(unsigned int);
-#define NVFP4_LAUNCH_FUSED(T, P) \
-  four_six_rowwise_fused_kernel<T, P><<<grid, threads, smem, s>>>(static_cast<const T*>(x), out_fp4, out_scales, \
-                                                                  out_gs, out_amax, decoded_amax, rows, gpr, rpc)
+#define NVFP4_LAUNCH_FUSED(T, P, R) \
+  four_six_rowwise_fused_kernel<T, P, R><<<grid, threads, smem, s>>>(static_cast<const T*>(x), out_fp4, out_scales, \
+                                                                     out_gs, out_amax, decoded_amax, rows, gpr, rpc)
+#define NVFP4_LAUNCH_FUSED_R(T, P)       \
+  do {                                   \
+    if (relu2) NVFP4_LAUNCH_FUSED(T, P, true); \
+    else NVFP4_LAUNCH_FUSED(T, P, false);      \
+  } while (0)
   if (dtype == NVFP4_DTYPE_F32) {
-    if (packed) NVFP4_LAUNCH_FUSED(float, true);
-    else NVFP4_LAUNCH_FUSED(float, false);
+    if (packed) NVFP4_LAUNCH_FUSED_R(float, true);
+    else NVFP4_LAUNCH_FUSED_R(float, false);
   } else {
-    if (packed) NVFP4_LAUNCH_FUSED(__nv_bfloat16, true);
-    else NVFP4_LAUNCH_FUSED(__nv_bfloat16, false);
+    if (packed) NVFP4_LAUNCH_FUSED_R(__nv_bfloat16, true);
+    else NVFP4_LAUNCH_FUSED_R(__nv_bfloat16, false);
   }
+#undef NVFP4_LAUNCH_FUSED_R
 #undef NVFP4_LAUNCH_FUSED
   count_launch();
   int rc = static_cast<int>(cudaGetLastError());
@@ -1673,6 +1706,7 @@ static MsEdenOut make_out(const nvfp4_ms_eden_args& a, uint32_t out_rows) {
   o.dst_row_len = a.dst_row_len;
   o.scale_seed = a.scale_seed;
   o.group_offset = a.group_offset;
+  o.group_row_stride = a.group_row_stride ? a.group_row_stride : a.dst_row_len / 16u;
   o.sign_offset = a.col_offset;
   o.packed = a.scale_layout == NVFP4_SCALES_PACKED;
   return o;

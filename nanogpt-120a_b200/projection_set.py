@@ -21,9 +21,9 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from .sharding import GradBuckets
+from .sharding import GradBuckets, sync_amax
 from . import (EPI_BIAS, EPI_NONE, EPI_RELU2, LinearBackwardModule, LinearBackwardScratch, Nvfp4GemmModule,
-               Nvfp4QuantModule, Nvfp4Tensor, padded_k, scale_packed_len)
+               Nvfp4QuantModule, Nvfp4Tensor, SideStream, padded_k, scale_packed_len)
 
 MASK64 = (1 << 64) - 1
 
@@ -105,10 +105,23 @@ class _Linear:
 
 class ProjectionSet:
     def __init__(self, shape: ModelShape, tokens: int, device, seed: int = 1234, token_offset: int = 0,
-                 process_group=None, grad_dtype: torch.dtype = torch.bfloat16, overlap_weight_quantization: bool = True):
+                 process_group=None, grad_dtype: torch.dtype = torch.bfloat16, overlap_weight_quantization: bool = True,
+                 fused_mlp: bool = True, total_tokens: int = 0, reproducible_sharding: bool = False,
+                 input_seed_offset: Optional[int] = None):
+        """fused_mlp: the fc projection stores only its pre-activation (plus the row amax of relu(pre)^2 from the
+        GEMM epilogue) and the down projection's input quantizer applies relu^2 on load, so the MLP activation is
+        never written; False = the fc GEMM writes both tensors and the down projection reads a separate input.
+        total_tokens / reproducible_sharding: this rank holds tokens [token_offset, token_offset + tokens) of a
+        batch of total_tokens; with reproducible_sharding every amax that feeds a per-tensor scale is
+        all-reduced (max) over the ranks in one collective per step and the scale-RNG index spaces are those
+        of the unsharded batch, so quantized operands are bit-identical to a single-GPU run."""
         assert tokens % 128 == 0, "token shards are multiples of 128 rows (scale tiles stay intact)"
         self.shape, self.tokens, self.device = shape, tokens, device
         self.token_offset = token_offset
+        self.total_tokens = total_tokens
+        self.reproducible = reproducible_sharding
+        assert not reproducible_sharding or total_tokens >= token_offset + tokens
+        self.fused_mlp = fused_mlp
         self.pg = process_group
         self.grad_dtype = grad_dtype
         self.quant, self.gemm, self.bwd = Nvfp4QuantModule(), Nvfp4GemmModule(), LinearBackwardModule()
@@ -131,13 +144,20 @@ class ProjectionSet:
         # per input width, one upstream gradient per output width (larger than L2 at bench sizes).
         widths_in = sorted({i for _, i, _, _ in shape.linears()} | {d})
         widths_out = sorted({o for _, _, o, _ in shape.linears()} | {v})
-        self.x: Dict[int, torch.Tensor] = {w: _randn_bf16((tokens, w), 1.0, seed + 7 * w + token_offset, device)
+        in_seed = token_offset if input_seed_offset is None else input_seed_offset
+        self.x: Dict[int, torch.Tensor] = {w: _randn_bf16((tokens, w), 1.0, seed + 7 * w + in_seed, device)
                                            for w in widths_in}
-        self.dy: Dict[int, torch.Tensor] = {w: _randn_bf16((tokens, w), 1e-3, seed + 11 * w + token_offset, device)
+        self.dy: Dict[int, torch.Tensor] = {w: _randn_bf16((tokens, w), 1e-3, seed + 11 * w + in_seed, device)
                                             for w in widths_out}
         self.y: Dict[int, torch.Tensor] = {w: torch.empty((tokens, w), dtype=torch.bfloat16, device=device)
                                            for w in widths_out}
         self.pre: Dict[int, torch.Tensor] = {h: torch.empty((tokens, h), dtype=torch.bfloat16, device=device)}
+        self.pre_row_amax = torch.empty(tokens, dtype=torch.float32, device=device)
+        # caller-owned second stream of the linear backward (its two transposers run beside the dY amax pass)
+        self.side = SideStream(device)
+        n_lin = 4 * shape.n_layer + 1
+        self.amax_vec = torch.zeros(2 * n_lin, dtype=torch.float32, device=device)  # [dY amax | decoded X amax]
+        self.e_scales = torch.empty(n_lin, dtype=torch.float32, device=device)
         self.dx: Dict[int, torch.Tensor] = {w: torch.empty((tokens, w), dtype=grad_dtype, device=device)
                                             for w in widths_in}
         # backward scratch is shared by all linears of the same (in, out) shape
@@ -178,23 +198,57 @@ class ProjectionSet:
                 lin.wq_ready.record(self._weight_stream)
 
     def _forward_linear(self, lin: _Linear) -> None:
-        x = self.x[lin.in_dim]
-        # row amax fused; the decoded amax rides along so that backward need not re-read X for it
-        self.quant.quantize_four_six(x, rowwise=True, packed=True, out=lin.xq, decoded_amax=True)
+        if self.fused_mlp and lin.name == "mlp_proj":
+            # the MLP activation relu(pre)^2 is computed on load from the fc projection's pre-activation;
+            # its row amax came out of that GEMM's epilogue
+            self.quant.quantize_relu2_four_six_rowwise(self.pre[lin.in_dim], row_amax=self.pre_row_amax, packed=True,
+                                                       out=lin.xq, decoded_amax=True)
+        else:
+            # row amax fused; the decoded amax rides along so that backward need not re-read X for it
+            self.quant.quantize_four_six(self.x[lin.in_dim], rowwise=True, packed=True, out=lin.xq, decoded_amax=True)
         if lin.wq_ready is not None:
             torch.cuda.current_stream().wait_event(lin.wq_ready)
+        flops = 2 * self.tokens * lin.in_dim * lin.out_dim
+        if self.fused_mlp and lin.epilogue == EPI_RELU2:
+            self._timed_gemm(lambda: self.gemm.gemm(lin.xq, lin.wq, bias=lin.bias, epilogue=EPI_BIAS,
+                                                    out=self.pre[lin.out_dim], relu2_row_amax=self.pre_row_amax), flops)
+            return
         aux = self.pre[lin.out_dim] if lin.epilogue == EPI_RELU2 else None
         self._timed_gemm(lambda: self.gemm.gemm(lin.xq, lin.wq, bias=lin.bias, epilogue=lin.epilogue,
-                                                out=self.y[lin.out_dim], aux=aux),
-                         2 * self.tokens * lin.in_dim * lin.out_dim)
+                                                out=self.y[lin.out_dim], aux=aux), flops)
 
-    def _backward_linear(self, lin: _Linear) -> None:
+    def _backward_order(self) -> List[_Linear]:
+        order = [self.lm_head]
+        for l in range(self.shape.n_layer - 1, -1, -1):
+            order += list(reversed(self.layers[l]))
+        return order
+
+    def _sync_scales(self) -> None:
+        """Reproducible sharding: the amax of every dY and of every decoded X of this step as ONE f32 vector,
+        all-reduced (max) over the ranks; the dY scales are derived from the reduced values."""
+        order = self._backward_order()
+        n = len(order)
+        for i, lin in enumerate(order):
+            self.quant.tensor_amax(self.dy[lin.out_dim], out=self.amax_vec[i:i + 1],
+                                   chunk_amax=self.scratch[(lin.in_dim, lin.out_dim)].e_h["chunk_amax"])
+            self.amax_vec[n + i:n + i + 1].copy_(lin.xq.decoded_amax)
+        sync_amax(self.amax_vec, self.pg)
+        for i in range(n):
+            self.quant.quartet_backward_ms_eden_global_scale_from_chunks(self.amax_vec[i:i + 1], 1,
+                                                                         out=self.e_scales[i:i + 1])
+
+    def _backward_linear(self, lin: _Linear, index: int = 0) -> None:
         sign_seed, scale_seed = self.rng.next_u32(), self.rng.next_u32()
+        extra = {}
+        if self.reproducible:
+            n = 4 * self.shape.n_layer + 1
+            extra = dict(total_token_count=self.total_tokens, e_global_scale=self.e_scales[index:index + 1],
+                         x_decoded_amax=self.amax_vec[n + index:n + index + 1])
         self.bwd.backward_ms_eden(e=self.dy[lin.out_dim], weight=lin.wq, input=lin.xq,
                                   scratch=self.scratch[(lin.in_dim, lin.out_dim)], sign_seed=sign_seed,
                                   scale_seed=scale_seed, want_dbias=lin.dbias is not None,
                                   dinput=self.dx[lin.in_dim], dweight=lin.dweight, dbias=lin.dbias,
-                                  token_offset=self.token_offset)
+                                  token_offset=self.token_offset, side=self.side, **extra)
 
     def _timed_gemm(self, fn, flops: int) -> None:
         if self.record_gemm_events:
@@ -218,11 +272,15 @@ class ProjectionSet:
         self._forward_linear(self.lm_head)
 
     def backward(self) -> None:
-        self._backward_linear(self.lm_head)
+        if self.reproducible:
+            self._sync_scales()
+        self._backward_linear(self.lm_head, 0)
         self._reduce(self.shape.n_layer)
+        index = 1
         for l in range(self.shape.n_layer - 1, -1, -1):
             for x in reversed(self.layers[l]):
-                self._backward_linear(x)
+                self._backward_linear(x, index)
+                index += 1
             self._reduce(l)
         self.grads.wait()
 

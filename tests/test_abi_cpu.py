@@ -28,7 +28,7 @@ def test_library_exports_every_declared_symbol(pkg):
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert sorted(pkg.EXPORTED_SYMBOLS) == declared, "python binding and header disagree"
-    assert lib.nvfp4_abi_version() == 2
+    assert lib.nvfp4_abi_version() == 3
 
 
 def test_size_helpers(pkg):
