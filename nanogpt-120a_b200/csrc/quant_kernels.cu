@@ -12,6 +12,7 @@
 // in the same order as the reference's xor butterflies, so the bytes are identical.
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -404,6 +405,150 @@ __global__ void __launch_bounds__(256) four_six_rowwise_fused_kernel(const T* __
   }
 }
 
+// Raw 16-element group as loaded (two or four 128-bit words) and its widening to f32: kept apart so that
+// the next group's words can be in flight while the current one is quantized.
+template <typename T>
+struct RawGroup;
+template <>
+struct RawGroup<float> {
+  uint4 w[4];
+  __device__ __forceinline__ void load(const float* p) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = __ldg(reinterpret_cast<const uint4*>(p) + i);
+  }
+  __device__ __forceinline__ void widen(float (&v)[16]) const {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[4 * i] = __uint_as_float(w[i].x);
+      v[4 * i + 1] = __uint_as_float(w[i].y);
+      v[4 * i + 2] = __uint_as_float(w[i].z);
+      v[4 * i + 3] = __uint_as_float(w[i].w);
+    }
+  }
+};
+template <>
+struct RawGroup<__nv_bfloat16> {
+  uint4 w[2];
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) w[i] = __ldg(reinterpret_cast<const uint4*>(p) + i);
+  }
+  __device__ __forceinline__ void widen(float (&v)[16]) const {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint32_t t[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[8 * i + 2 * j] = __uint_as_float(t[j] << 16);
+        v[8 * i + 2 * j + 1] = __uint_as_float(t[j] & 0xffff0000u);
+      }
+    }
+  }
+};
+
+// The same outputs as four_six_rowwise_fused_kernel from persistent CTAs: a CTA walks row blocks
+// blockIdx.x, blockIdx.x + gridDim.x, ... and every thread has the raw words of its next group in flight
+// while it quantizes the current one, so global-load latency no longer sits in front of the row-amax
+// barrier (one CTA-wide barrier per row block; the per-row maxima rotate through three shared-memory
+// buffers so that clearing a buffer is always separated from its next use by a barrier).
+constexpr int kStreamMaxRowsPerCta = 256;
+template <typename T, bool kPacked, bool kRelu2>
+__global__ void __launch_bounds__(256) four_six_rowwise_stream_kernel(const T* __restrict__ x,
+                                                                       uint8_t* __restrict__ out_fp4,
+                                                                       uint8_t* __restrict__ out_scales,
+                                                                       float* __restrict__ out_gs,
+                                                                       float* __restrict__ out_amax,
+                                                                       float* __restrict__ decoded_amax, uint32_t rows,
+                                                                       uint32_t groups_per_row, uint32_t rows_per_cta,
+                                                                       uint32_t row_blocks) {
+  __shared__ unsigned int row_amax_bits[3][kStreamMaxRowsPerCta];
+  const uint32_t t = threadIdx.x, lane_id = t & 31u;
+  for (uint32_t i = t; i < 3 * kStreamMaxRowsPerCta; i += blockDim.x) (&row_amax_bits[0][0])[i] = 0u;
+  __syncthreads();
+  const uint32_t local_row = t / groups_per_row;
+  const uint32_t kg = t - local_row * groups_per_row;
+  const bool in_use = local_row < rows_per_cta;
+  const bool quads = (groups_per_row & 3u) == 0;  // four neighbouring lanes hold four neighbouring scale bytes
+  RawGroup<T> raw;
+  uint32_t blk = blockIdx.x;
+  {
+    const uint32_t row = blk * rows_per_cta + local_row;
+    if (blk < row_blocks && in_use && row < rows) raw.load(x + (static_cast<size_t>(row) * groups_per_row + kg) * 16);
+  }
+  float dec_running = 0.0f;
+  uint32_t buf = 0;
+  for (; blk < row_blocks; blk += gridDim.x) {
+    const uint32_t row = blk * rows_per_cta + local_row;
+    const bool active = in_use && row < rows;
+    float v[16];
+    float ga = 0.0f;
+    if (active) {
+      raw.widen(v);
+      if (kRelu2) relu2_inplace16(v);
+#pragma unroll
+      for (int i = 0; i < 16; i += 2) ga = max3_abs(ga, v[i], v[i + 1]);
+    }
+    {
+      // the next row block's words: in flight across the barrier and the whole quantization below
+      const uint32_t nblk = blk + gridDim.x;
+      const uint32_t nrow = nblk * rows_per_cta + local_row;
+      if (nblk < row_blocks && in_use && nrow < rows) raw.load(x + (static_cast<size_t>(nrow) * groups_per_row + kg) * 16);
+    }
+    // Row max: non-negative floats order like their bit patterns.  With at least 32 groups per row a warp
+    // touches at most two rows: two warp-wide integer maxima and two shared-memory atomics.
+    const uint32_t ga_bits = active ? __float_as_uint(ga) : 0u;
+    if (groups_per_row >= 32) {
+      const uint32_t first_row = __shfl_sync(0xffffffffu, local_row, 0);
+      const bool in_first = local_row == first_row;
+      const uint32_t m_first = __reduce_max_sync(0xffffffffu, in_first ? ga_bits : 0u);
+      const uint32_t m_other = __reduce_max_sync(0xffffffffu, in_first ? 0u : ga_bits);
+      const uint32_t other_lanes = __ballot_sync(0xffffffffu, !in_first && active);
+      if (lane_id == 0 && active) atomicMax(&row_amax_bits[buf][local_row], m_first);
+      if (other_lanes != 0u && lane_id == static_cast<uint32_t>(__ffs(other_lanes) - 1))
+        atomicMax(&row_amax_bits[buf][local_row], m_other);
+    } else if (active) {
+      atomicMax(&row_amax_bits[buf][local_row], ga_bits);
+    }
+    __syncthreads();
+    // every thread is past its reads of the buffer of the previous row block: clear it for the block after next
+    const uint32_t stale = buf == 0 ? 2u : buf - 1u;
+    if (t < rows_per_cta) row_amax_bits[stale][t] = 0u;
+    uint32_t b = 0;
+    if (active) {
+      const float amax = __uint_as_float(row_amax_bits[buf][local_row]);
+      const float gs = four_six_global_scale(amax);
+      uint2 packed;
+      float dec = 0.0f;
+      b = four_six_group(v, gs, packed, decoded_amax ? &dec : nullptr);
+      const size_t g = static_cast<size_t>(row) * groups_per_row + kg;
+      *reinterpret_cast<uint2*>(out_fp4 + g * 8) = packed;
+      if (!quads) {
+        if (kPacked)
+          out_scales[packed_scale_offset(row, kg, groups_per_row >> 2)] = static_cast<uint8_t>(b);
+        else
+          out_scales[g] = static_cast<uint8_t>(b);
+      }
+      if (kg == 0) {
+        out_gs[row] = gs;
+        if (out_amax) out_amax[row] = amax;
+      }
+      dec_running = max_f32(dec_running, dec);
+    }
+    if (quads) {
+      // lanes 4j .. 4j+3 hold k-groups 4i .. 4i+3 of one row (one k-atom): one 32-bit store instead of four bytes
+      uint32_t word = b | (__shfl_down_sync(0xffffffffu, b, 1) << 8);
+      word |= __shfl_down_sync(0xffffffffu, word, 2) << 16;
+      if (active && (kg & 3u) == 0) {
+        const size_t off = kPacked ? packed_scale_offset(row, kg, groups_per_row >> 2)
+                                   : static_cast<size_t>(row) * groups_per_row + kg;
+        *reinterpret_cast<uint32_t*>(out_scales + off) = word;
+      }
+    }
+    buf = buf == 2 ? 0u : buf + 1u;
+  }
+  if (decoded_amax) cta_atomic_max(warp_max(dec_running), decoded_amax);  // uniform across the CTA
+}
+
 // Schedule-free weight materialisation (gpt/optimizer/schedule_free/{value,amax,four_six}.rs):
 // the weight quantized every step is y = z + beta * (x - z) of the two f32 masters; it is never
 // written out in f32.  Kernel 1: tensor amax of y (1024-value chunks per warp, chunk amax kept for
@@ -720,6 +865,10 @@ __device__ __forceinline__ void ms_eden_emit_chunk(f32x2_t (&P)[16], const MsEde
 // Two chunks at once, one per packed lane (low lane = chunk of row_lo, high lane = chunk of
 // row_hi, both at chunk_in_row): P[k] holds the signed inputs of K position k of both, so all
 // five butterfly strides act between registers.
+// kRolled: the two 16-groups of the chunks go through ONE copy of the group code (a two-trip loop that moves
+// the second half of P down in between) instead of two inlined copies: a third less code for the
+// instruction cache at the price of 32 register moves.
+template <bool kRolled = false>
 __device__ __forceinline__ void ms_eden_emit_chunk_lanes(f32x2_t (&P)[32], const MsEdenOut& o, float gs, float so,
                                                          uint32_t row_lo, uint32_t row_hi, uint32_t chunk_in_row) {
   const uint32_t chunks_per_row = o.dst_row_len >> 5;
@@ -757,8 +906,26 @@ __device__ __forceinline__ void ms_eden_emit_chunk_lanes(f32x2_t (&P)[32], const
   const uint32_t g_lo = row_lo * o.group_row_stride + chunk_in_row * 2u + o.group_offset;
   const uint32_t g_hi = row_hi * o.group_row_stride + chunk_in_row * 2u + o.group_offset;
   uint2 lo0, hi0, lo1, hi1;
-  const uint32_t sb0 = ms_eden_group_lanes(&P[0], safe_gs, so, inv6, o.scale_seed, g_lo, g_hi, lo0, hi0);
-  const uint32_t sb1 = ms_eden_group_lanes(&P[16], safe_gs, so, inv6, o.scale_seed, g_lo + 1, g_hi + 1, lo1, hi1);
+  uint32_t sb0, sb1;
+  if (kRolled) {
+    lo0 = hi0 = lo1 = hi1 = make_uint2(0u, 0u);
+    sb0 = sb1 = 0u;
+#pragma unroll 1
+    for (uint32_t g = 0; g < 2; ++g) {
+      uint2 l, h;
+      const uint32_t sb = ms_eden_group_lanes(&P[0], safe_gs, so, inv6, o.scale_seed, g_lo + g, g_hi + g, l, h);
+      if (g == 0) {
+        lo0 = l, hi0 = h, sb0 = sb;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) P[i] = P[16 + i];
+      } else {
+        lo1 = l, hi1 = h, sb1 = sb;
+      }
+    }
+  } else {
+    sb0 = ms_eden_group_lanes(&P[0], safe_gs, so, inv6, o.scale_seed, g_lo, g_hi, lo0, hi0);
+    sb1 = ms_eden_group_lanes(&P[16], safe_gs, so, inv6, o.scale_seed, g_lo + 1, g_hi + 1, lo1, hi1);
+  }
   *reinterpret_cast<uint4*>(o.fp4 + chunk_lo * 16) = make_uint4(lo0.x, lo0.y, lo1.x, lo1.y);
   *reinterpret_cast<uint4*>(o.fp4 + chunk_hi * 16) = make_uint4(hi0.x, hi0.y, hi1.x, hi1.y);
   const uint32_t k_atoms = o.dst_row_len >> 6;
@@ -1027,7 +1194,7 @@ struct PairTile {
   static constexpr int kPiecesPerThread = kTileRows * kPiecesPerRow / 256;
 };
 
-template <typename T>
+template <typename T, bool kRolled = false>
 __global__ void __launch_bounds__(256, 2) ms_eden_pair_kernel(const MsEdenTileParams p, uint32_t tiles_x,
                                                                uint32_t tile_count) {
   using PT = PairTile<T>;
@@ -1152,7 +1319,7 @@ __global__ void __launch_bounds__(256, 2) ms_eden_pair_kernel(const MsEdenTilePa
       chunk_in_row = (c0 >> 5) + chunk;
     }
     // one copy of the quantizer body for both roles (the role is warp-uniform)
-    ms_eden_emit_chunk_lanes(P, warp < 4 ? p.t : p.r, gs, p.scale_override, row_lo, row_hi, chunk_in_row);
+    ms_eden_emit_chunk_lanes<kRolled>(P, warp < 4 ? p.t : p.r, gs, p.scale_override, row_lo, row_hi, chunk_in_row);
     __syncthreads();
     if (p.col_sum_partials && tid < kTileCols)
       p.col_sum_partials[static_cast<size_t>(ty) * p.src_cols + c0 + tid] =
@@ -1174,7 +1341,7 @@ constexpr int kNvStageBytes = kTileRows * kNvBytePitch;   // 10240
 // Register budget of three CTAs per SM (80 registers, a few spilled words, same speed as the
 // unconstrained 113), launched two per SM: the free third of the register file lets the
 // bandwidth-bound dY amax kernel of the same backward call run beside it on another stream.
-template <bool kRowwise>
+template <bool kRowwise, bool kRolled = false>
 __global__ void __launch_bounds__(256, 3) ms_eden_nvfp4_transpose_kernel(const MsEdenTileParams p, uint32_t tiles_x,
                                                                           uint32_t tile_count) {
   __shared__ __align__(16) uint8_t stage[2][kNvStageBytes];
@@ -1247,7 +1414,7 @@ __global__ void __launch_bounds__(256, 3) ms_eden_nvfp4_transpose_kernel(const M
       P[i] = mul2_rounded(mul2(pack2(qv.x, qv.y), pack2(sc.x, sc.y)), pack2(sg.x, sg.y));
     }
     const uint32_t out_row = c0 + 2 * cp;
-    ms_eden_emit_chunk_lanes(P, p.t, gs, p.scale_override, out_row, out_row + 1, (r0 >> 5) + q);
+    ms_eden_emit_chunk_lanes<kRolled>(P, p.t, gs, p.scale_override, out_row, out_row + 1, (r0 >> 5) + q);
     __syncthreads();
     sw = sw_next;
   }
@@ -1623,11 +1790,30 @@ int launch_four_six_rowwise_fused(cudaStream_t s, const void* x, int dtype, uint
   if (rows == 0) return 0;
   const uint32_t rpc = 256 / gpr;
   const uint32_t threads = (rpc * gpr + 31) / 32 * 32;
-  const uint32_t grid = (rows + rpc - 1) / rpc;
+  const uint32_t row_blocks = (rows + rpc - 1) / rpc;
   const size_t smem = (rpc + 1) * sizeof(unsigned int);
-#define NVFP4_LAUNCH_FUSED(T, P, R) \
-  four_six_rowwise_fused_kernel<T, P, R><<<grid, threads, smem, s>>>(static_cast<const T*>(x), out_fp4, out_scales, \
-                                                                     out_gs, out_amax, decoded_amax, rows, gpr, rpc)
+  // Persistent CTAs (three fit an SM) once there are more row blocks than resident CTAs; the grid
+  // is sized so that every CTA walks the same number of row blocks.
+  static const int variant = [] {
+    const char* e = std::getenv("NVFP4_FOUR_SIX_VARIANT");
+    return e ? std::atoi(e) : 1;
+  }();
+  const uint32_t resident = 148u * 3u;  // 80 registers x 256 threads: three CTAs per SM
+  const bool stream = variant != 0 && row_blocks > resident &&
+                      ((reinterpret_cast<uintptr_t>(out_scales) & 3u) == 0);
+  const uint32_t per_cta = (row_blocks + resident - 1) / resident;
+  const uint32_t grid = stream ? (row_blocks + per_cta - 1) / per_cta : row_blocks;
+#define NVFP4_LAUNCH_FUSED(T, P, R)                                                                                   \
+  do {                                                                                                                \
+    if (stream)                                                                                                       \
+      four_six_rowwise_stream_kernel<T, P, R><<<grid, threads, 0, s>>>(static_cast<const T*>(x), out_fp4, out_scales, \
+                                                                       out_gs, out_amax, decoded_amax, rows, gpr, rpc, \
+                                                                       row_blocks);                                   \
+    else                                                                                                              \
+      four_six_rowwise_fused_kernel<T, P, R><<<grid, threads, smem, s>>>(static_cast<const T*>(x), out_fp4,           \
+                                                                         out_scales, out_gs, out_amax, decoded_amax,  \
+                                                                         rows, gpr, rpc);                             \
+  } while (0)
 #define NVFP4_LAUNCH_FUSED_R(T, P)       \
   do {                                   \
     if (relu2) NVFP4_LAUNCH_FUSED(T, P, true); \
@@ -1696,6 +1882,16 @@ int launch_four_six_padded(cudaStream_t s, const float* x, const float* amax, ui
   NVFP4_RETURN_LAST();
 }
 
+// Measurement switch (environment variable NVFP4_MS_EDEN_VARIANT, read once): bit 0 = rolled group loop in
+// the whole-tile kernels.
+static int ms_eden_variant() {
+  static const int v = [] {
+    const char* e = std::getenv("NVFP4_MS_EDEN_VARIANT");
+    return e ? std::atoi(e) : 0;
+  }();
+  return v;
+}
+
 static MsEdenOut make_out(const nvfp4_ms_eden_args& a, uint32_t out_rows) {
   MsEdenOut o;
   o.fp4 = a.out_fp4;
@@ -1752,19 +1948,24 @@ int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a) {
                                 a.dst_row_len == a.rows && (reinterpret_cast<uintptr_t>(a.src_bytes) & 15u) == 0 &&
                                 (reinterpret_cast<uintptr_t>(a.src_scales) & 3u) == 0;
     const uint32_t nv_tiles_x = a.cols / kNvTileCols, nv_tiles = nv_tiles_x * (a.rows / kTileRows);
+    const bool rolled = ms_eden_variant() & 1;
     switch (a.src_kind) {
       case NVFP4_SRC_F32_TRANSPOSED:
         if (bf16) launch_tile<0, __nv_bfloat16, false>(s, p);
         else launch_tile<0, float, false>(s, p);
         break;
       case NVFP4_SRC_NVFP4_TRANSPOSED:
-        if (nv_whole_tiles)
+        if (nv_whole_tiles && rolled)
+          ms_eden_nvfp4_transpose_kernel<false, true><<<min(nv_tiles, 148u * 2u), 256, 0, s>>>(p, nv_tiles_x, nv_tiles);
+        else if (nv_whole_tiles)
           ms_eden_nvfp4_transpose_kernel<false><<<min(nv_tiles, 148u * 2u), 256, 0, s>>>(p, nv_tiles_x, nv_tiles);
         else
           launch_tile<2, float, false>(s, p);
         break;
       case NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED:
-        if (nv_whole_tiles)
+        if (nv_whole_tiles && rolled)
+          ms_eden_nvfp4_transpose_kernel<true, true><<<min(nv_tiles, 148u * 2u), 256, 0, s>>>(p, nv_tiles_x, nv_tiles);
+        else if (nv_whole_tiles)
           ms_eden_nvfp4_transpose_kernel<true><<<min(nv_tiles, 148u * 2u), 256, 0, s>>>(p, nv_tiles_x, nv_tiles);
         else
           launch_tile<3, float, false>(s, p);
@@ -1869,7 +2070,10 @@ int launch_ms_eden_pair(cudaStream_t s, const nvfp4_ms_eden_args& r, const nvfp4
   if (whole_tiles) {
     const uint32_t tiles_x = cols / kTileCols, tile_count = tiles_x * (rows / kTileRows);
     const uint32_t grid = min(tile_count, 148u * 2u);
-    if (r.src_dtype == NVFP4_DTYPE_BF16) {
+    if (r.src_dtype == NVFP4_DTYPE_BF16 && (ms_eden_variant() & 1)) {
+      ms_eden_pair_kernel<__nv_bfloat16, true>
+          <<<grid, 256, 2 * PairTile<__nv_bfloat16>::kStageBytes, s>>>(p, tiles_x, tile_count);
+    } else if (r.src_dtype == NVFP4_DTYPE_BF16) {
       ms_eden_pair_kernel<__nv_bfloat16>
           <<<grid, 256, 2 * PairTile<__nv_bfloat16>::kStageBytes, s>>>(p, tiles_x, tile_count);
     } else {

@@ -118,6 +118,30 @@ def test_four_six_rowwise_long_rows(pkg, oracle, dev):
         _check_four_six(pkg, oracle, dev, x, rowwise=True, packed=False)
 
 
+@pytest.mark.parametrize("shape,packed,dtype", [((3001, 768), True, torch.bfloat16), ((4099, 192), True, torch.float32),
+                                                ((23011, 80), False, torch.bfloat16), ((1300, 3072), True, torch.bfloat16)])
+def test_four_six_rowwise_persistent_kernel(pkg, oracle, dev, shape, packed, dtype):
+    """More row blocks than resident CTAs: the fused rowwise quantizer runs persistent CTAs that prefetch
+    their next row block.  Ragged row counts, a group count that is not a multiple of four (byte stores
+    instead of gathered words), decoded amax, and relu^2 on load."""
+    q = pkg.Nvfp4QuantModule()
+    x = with_outliers(bf16_normal(29, shape), seed=4, every=211).to(dtype)
+    xf = x.float().numpy()
+    t = q.quantize_four_six(x.to(dev), rowwise=True, packed=packed, decoded_amax=True)
+    ob, os_, og = oracle.four_six(xf, oracle.row_amax(xf), True)
+    assert np.array_equal(cpu(t.bytes), ob)
+    assert np.array_equal(cpu(t.scales), oracle.scale_pack(os_, *shape) if packed else os_)
+    assert np.array_equal(cpu(t.global_scales), og)
+    assert cpu(t.decoded_amax).tobytes() == np.asarray(oracle.nvfp4_amax(ob, os_, og, *shape, True)[1], np.float32).tobytes()
+    relu = np.maximum(xf, np.float32(0))
+    act = relu * relu
+    t = q.quantize_relu2_four_six_rowwise(x.to(dev), packed=packed)
+    ob, os_, og = oracle.four_six(act, oracle.row_amax(act), True)
+    assert np.array_equal(cpu(t.bytes), ob)
+    assert np.array_equal(cpu(t.scales), oracle.scale_pack(os_, *shape) if packed else os_)
+    assert np.array_equal(cpu(t.global_scales), og)
+
+
 def test_four_six_edge_values(pkg, oracle, dev):
     """Zero rows, ties on the E2M1 grid, huge and tiny magnitudes, negative zero."""
     x = torch.zeros(8, 64)
@@ -132,9 +156,9 @@ def test_four_six_edge_values(pkg, oracle, dev):
         _check_four_six(pkg, oracle, dev, x, rowwise, packed=False)
 
 
-def test_config1_quantize_full_size(pkg, oracle, dev):
-    """BASELINE config 1: [8192 x 768] bf16 ~N(0,1), 0.1% outliers x50, per-tensor and rowwise scale,
-    then the dequantize round trip."""
+def test_quantize_round_trip_8192x768(pkg, oracle, dev):
+    """The round-trip case of the specification: [8192 x 768] bf16 ~N(0,1) with 0.1 % of the elements scaled
+    by 50, per-tensor and rowwise scale, then the dequantize round trip."""
     x = with_outliers(bf16_normal(1, (8192, 768)), seed=2, every=1000, factor=50.0)
     _check_four_six(pkg, oracle, dev, x, rowwise=False, packed=True)
     _check_four_six(pkg, oracle, dev, x, rowwise=True, packed=False)
@@ -522,8 +546,9 @@ def test_gemm_rejects_bad_shapes(pkg, dev):
     assert err.value.code == 1  # CUDA_ERROR_INVALID_VALUE, like utils/nvfp4_tma_matmul/launcher.rs:183-190
 
 
-def test_config2_c_attn_forward(pkg, oracle, dev):
-    """BASELINE config 2: X [8192 x 768] ~N(0,1), W [2304 x 768] ~N(0,0.02), b ~N(0,0.02), bf16 out."""
+def test_c_attn_forward_8192_tokens(pkg, oracle, dev):
+    """One forward projection of the c_attn shape: X [8192 x 768] ~N(0,1), W [2304 x 768] ~N(0,0.02),
+    b ~N(0,0.02), per-tensor scales, bf16 out."""
     q, gemm = pkg.Nvfp4QuantModule(), pkg.Nvfp4GemmModule()
     m, k, n = 8192, 768, 2304
     x, w = bf16_normal(101, (m, k)), bf16_normal(102, (n, k), 0.02)
