@@ -4,16 +4,17 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload: the full 12-layer GPT-2-small training-step projection set (48 block linears + the
-tied LM head with a 32000-entry vocabulary), forward and backward, 65536 tokens per GPU, on
-seeded synthetic bf16 tensors (activations ~N(0,1), weights ~N(0,0.02), upstream gradients
-~N(0,1e-3)).  One step = weight quantization + forward + backward of every projection, plus
-(N > 1) one NCCL all-reduce per layer of dW/dbias.  The metric is useful TFLOP/s:
-6 * tokens * sum(N*K) per step, padding never counted.
+Workload: the full 12-layer GPT-2-small training-step projection set (48 block linears + the tied LM head
+with a 32000-entry vocabulary), forward and backward, 65536 tokens per step IN TOTAL, token-sharded over the
+N GPUs (strong scaling), on seeded synthetic bf16 tensors (activations ~N(0,1), weights ~N(0,0.02), upstream
+gradients ~N(0,1e-3)).  One step = weight quantization + forward + backward of every projection, plus (N > 1)
+one NCCL all-reduce per layer of dW / dbias.  The step is enqueued by the C++ step driver (one host call per
+step; NCCL issued from C++).  The metric is useful TFLOP/s: 6 * tokens * sum(N*K) per step, padding never
+counted.
 
-Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the
-reference's math (the reference has no CPU implementation of its own and its kernels do not
-build here) on a bounded sample of the same workload.
+Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the reference's math (the
+reference has no CPU implementation of its own and its kernels do not build here) on a bounded sample of the
+same workload.
 """
 from __future__ import annotations
 
@@ -33,7 +34,11 @@ if ROOT not in sys.path:
 NOMINAL_FP4_DENSE_TFLOPS = 9000.0  # B200 dense FP4 (vendor figure; no FP4 peak is measured on this pool)
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "NVFP4 proj fwd+bwd TFLOP/s"
-TOKENS_PER_GPU = 65536
+TOTAL_TOKENS = 65536
+# DRAM bytes moved per algorithmic byte by the GEMM kernel (operands read once + output written once), from a
+# profiler capture of a small case of the same kernel (three GEMMs of the c_attn shape at 32768 tokens);
+# traffic of a full launch = this ratio x the launch's algorithmic bytes (both grow with the token count).
+GEMM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.08
 
 
 def measured_peaks():
@@ -47,13 +52,6 @@ def measured_peaks():
 # --------------------------------------------------------------------------------------------
 # clocks
 # --------------------------------------------------------------------------------------------
-
-# dram__bytes_read.sum + dram__bytes_write.sum over the 147 GEMM launches of one step of the default
-# workload (GPT-2-small projection set, 65536 tokens, 1 GPU): 17.15 GB read + 23.36 GB written.
-GEMM_DRAM_BYTES_PER_STEP_65536 = 17.154715e9 + 23.360743e9
-GEMM_TRAFFIC_SOURCE = ("ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum over one step's 147 GEMM launches "
-                       "(profiles/gemm_tcgen05_ncu.md); algorithmic bytes of the same launches: 37.5 GB")
-
 
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
@@ -155,7 +153,7 @@ def run_reference(args):
     sample = f"one GPT-2-small layer (c_attn, c_proj, fc, proj) fwd+bwd at {tokens} tokens per step"
     line = {
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate)", "data": "synthetic",
         "config": {"workload": "gpt2-small training-step projection set, fwd+bwd (CPU: bounded sample)",
                    "sample": sample},
@@ -168,34 +166,190 @@ def run_reference(args):
 
 
 # --------------------------------------------------------------------------------------------
-# GPU arm
+# GPU arm: helpers
 # --------------------------------------------------------------------------------------------
 
-def quantize_bandwidth(pkg, torch, dev, peak_gbs):
-    """Config-1 quantizer: [8192 x 768] bf16 -> NVFP4, rotating over 16 buffers (201 MB > L2)."""
-    q = pkg.Nvfp4QuantModule()
+def cuda_time_us(torch, fn, iters, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / iters
+
+
+def quantize_records(pkg, torch, dev, peak_gbs):
+    """The quantizer on [8192 x 768] bf16 (201 MB over 16 rotating buffers, larger than L2): rowwise scale
+    with the row amax fused (what the projections call), per-tensor scale (an amax pass, then the quantizer),
+    and the dequantize round trip.  GB/s on the algorithmic 2.5625 B/element."""
+    q, d = pkg.Nvfp4QuantModule(), pkg.Nvfp4DecodeModule()
     rows, cols, nbuf = 8192, 768, 16
     xs = [torch.randn(rows, cols, device=dev).to(torch.bfloat16) for _ in range(nbuf)]
+    algo = rows * cols * 2.5625
+    i = [0]
+
+    def rot():
+        i[0] += 1
+        return i[0] % nbuf
+
+    row_out = [q.quantize_four_six(x, rowwise=True, packed=True) for x in xs]
+
+    def rowwise():
+        k = rot()
+        q.quantize_four_six(xs[k], rowwise=True, packed=True, out=row_out[k])
+
     amax = [q.row_amax(x) for x in xs]
-    outs = [q.quantize_four_six(x, amax=a, rowwise=True, packed=True) for x, a in zip(xs, amax)]
-    for _ in range(3):
-        for x, a, o in zip(xs, amax, outs):
-            q.quantize_four_six(x, amax=a, rowwise=True, packed=True, out=o)
-    torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 5
-    start.record()
-    for _ in range(reps):
-        for x, a, o in zip(xs, amax, outs):
-            q.quantize_four_six(x, amax=a, rowwise=True, packed=True, out=o)
-    stop.record()
-    torch.cuda.synchronize()
-    us = start.elapsed_time(stop) * 1e3 / (reps * nbuf)
-    algo_bytes = rows * cols * 2.5625
-    gbs = algo_bytes / (us * 1e-6) / 1e9
-    return {"workload": "four-six quantize [8192x768] bf16 -> NVFP4, rowwise scale, packed scale layout "
-                        "(amax precomputed), 16 rotating buffers", "us": us, "achieved_gbs": gbs,
-            "algorithmic_bytes": algo_bytes, "frac_of_hbm_peak": gbs / peak_gbs}
+
+    def rowwise_given_amax():
+        k = rot()
+        q.quantize_four_six(xs[k], amax=amax[k], rowwise=True, packed=True, out=row_out[k])
+
+    ten_out = [q.quantize_four_six(x, rowwise=False, packed=False) for x in xs]
+    ten_amax = torch.empty(1, device=dev)
+    chunks = torch.empty(rows * cols // 1024, device=dev)
+
+    def per_tensor():
+        k = rot()
+        q.tensor_amax(xs[k], chunks, ten_amax)
+        q.quantize_four_six(xs[k], amax=ten_amax, rowwise=False, packed=False, out=ten_out[k])
+
+    def round_trip():
+        k = rot()
+        q.tensor_amax(xs[k], chunks, ten_amax)
+        q.quantize_four_six(xs[k], amax=ten_amax, rowwise=False, packed=False, out=ten_out[k])
+        d.decode(ten_out[k])
+
+    out = {"workload": "four-six quantize [8192x768] bf16 -> NVFP4, 16 rotating buffers (201 MB > L2)",
+           "algorithmic_bytes": algo}
+    for name, fn in (("rowwise_fused_amax", rowwise), ("rowwise_amax_given", rowwise_given_amax),
+                     ("per_tensor_amax_plus_quantize", per_tensor), ("per_tensor_round_trip_with_dequantize", round_trip)):
+        us = cuda_time_us(torch, fn, 80)
+        gbs = algo / (us * 1e-6) / 1e9
+        out[name] = {"us": us, "achieved_gbs": gbs, "frac_of_hbm_peak": gbs / peak_gbs}
+    out["us"] = out["rowwise_fused_amax"]["us"]
+    out["achieved_gbs"] = out["rowwise_fused_amax"]["achieved_gbs"]
+    out["frac_of_hbm_peak"] = out["rowwise_fused_amax"]["frac_of_hbm_peak"]
+    return out
+
+
+def write_roofline(torch, dev):
+    """Write-only HBM bandwidth: a plain device fill of 1 GiB (what bounds the short-K forward GEMMs)."""
+    buf = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+    us = cuda_time_us(torch, lambda: buf.zero_(), 10)
+    del buf
+    return (1 << 30) / (us * 1e-6) / 1e9
+
+
+def gemm_self_check(pkg, torch, dev, tokens, shape):
+    """Before anything is timed: the four GEMM kinds of the step (forward with bias, dX, dW, LM head) at this
+    run's own sizes, on random NVFP4 operands, sampled 128-row blocks of the output against the CPU oracle's
+    FP32-dequantized product.  Returns the largest relative Frobenius error and what was checked."""
+    import numpy as np
+
+    from oracle import oracle
+
+    oracle.set_threads(os.cpu_count() or 1)
+    gemm, pack = pkg.Nvfp4GemmModule(), pkg.Sm120ScalePackModule()
+    d, v = shape.d_model, shape.vocab
+    rng = np.random.default_rng(7)
+    cases = [("forward c_attn", tokens, 3 * d, d, torch.bfloat16, 1), ("dX c_attn", tokens, d, 3 * d, torch.bfloat16, 0),
+             ("dW c_attn", 3 * d, d, tokens, torch.float32, 0), ("lm_head logits", tokens, v, d, torch.bfloat16, 0)]
+    worst, report = 0.0, []
+    for name, m, n, k, dt, epi in cases:
+        def rand(rows, rowwise):
+            b = rng.integers(0, 256, size=rows * k // 2, dtype=np.uint8)
+            s = rng.integers(0x28, 0x48, size=rows * k // 16, dtype=np.uint8)
+            g = (0.5 + rng.random(rows if rowwise else 1)).astype(np.float32)
+            t = pkg.Nvfp4Tensor(torch.from_numpy(b).to(dev), pack.pack(torch.from_numpy(s).to(dev), rows, k),
+                                torch.from_numpy(g).to(dev), rows, k, packed=True, rowwise=rowwise)
+            return (b, s, g), t
+
+        (ab, as_, ag), A = rand(m, True)
+        bh, B = rand(n, False)
+        bias = rng.normal(0, 40.0, n).astype(np.float32) if epi else None
+        out = gemm.gemm(A, B, bias=None if bias is None else torch.from_numpy(bias).to(dev), epilogue=epi, out_dtype=dt)
+        plan = gemm.plan(A, B, bias=None if bias is None else torch.from_numpy(bias).to(dev), epilogue=epi, out=out)
+        nb = (m + 127) // 128
+        blocks = sorted({0, nb // 2, nb - 1})
+        for blk in blocks:
+            r0, r1 = blk * 128, min(m, blk * 128 + 128)
+            a_s = (ab[r0 * k // 2:r1 * k // 2], as_[r0 * k // 16:r1 * k // 16], ag[r0:r1])
+            want = oracle.gemm(a_s, bh, r1 - r0, k, n, 2, bias=bias, epi=epi)
+            if dt == torch.bfloat16:
+                want = torch.from_numpy(want).to(torch.bfloat16).float().numpy()
+            got = out[r0:r1].float().cpu().numpy().astype(np.float64)
+            err = float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
+            worst = max(worst, err)
+        report.append({"gemm": name, "m": m, "n": n, "k": k, "tile": plan.block_n, "k_splits": plan.k_splits,
+                       "resident": plan.b_resident, "row_blocks": len(blocks)})
+        del A, B, out
+    torch.cuda.empty_cache()
+    return {"max_rel_fro": worst, "tolerance": 1e-3, "row_blocks": 3, "checked": report,
+            "device_status": pkg.read_device_status()}
+
+
+def small_configs(pkg, torch, dev, peaks, write_gbs):
+    """The two single-GPU configurations below the full step: one c_attn forward projection at 8192 tokens
+    (per-tensor scales, bf16 out) and one GPT-2-small layer forward + backward at 8192 tokens."""
+    from nanogpt_120a_b200.host_step import HostStep
+    from nanogpt_120a_b200.projection_set import ModelShape, ProjectionSet
+
+    q, gemm = pkg.Nvfp4QuantModule(), pkg.Nvfp4GemmModule()
+    m, k, n = 8192, 768, 2304
+    # rotate over enough operand sets that nothing is served from L2 (each set: 12.6 + 3.5 + 37.7 MB)
+    sets = []
+    for i in range(6):
+        x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        w = (torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16)
+        sets.append((x, w, q.quantize_four_six(x, rowwise=False, packed=True), q.quantize_four_six(w, rowwise=False, packed=True),
+                     torch.empty(m, n, dtype=torch.bfloat16, device=dev)))
+    bias = torch.randn(n, device=dev) * 0.02
+    i = [0]
+
+    def gemm_only():
+        i[0] += 1
+        x, w, xq, wq, y = sets[i[0] % len(sets)]
+        gemm.gemm(xq, wq, bias=bias, epilogue=pkg.EPI_BIAS, out=y)
+
+    amax, chunks = torch.empty(1, device=dev), torch.empty(m * k // 1024, device=dev)
+
+    def quantize_and_gemm():
+        i[0] += 1
+        x, w, xq, wq, y = sets[i[0] % len(sets)]
+        q.tensor_amax(x, chunks, amax)
+        q.quantize_four_six(x, amax=amax, rowwise=False, packed=True, out=xq)
+        gemm.gemm(xq, wq, bias=bias, epilogue=pkg.EPI_BIAS, out=y)
+
+    flops = 2.0 * m * n * k
+    us_g = cuda_time_us(torch, gemm_only, 60)
+    us_qg = cuda_time_us(torch, quantize_and_gemm, 60)
+    t_compute = flops / (NOMINAL_FP4_DENSE_TFLOPS * 1e12) * 1e6
+    t_write = m * n * 2 / (write_gbs * 1e9) * 1e6
+    c2 = {"workload": "c_attn forward projection, X [8192x768] W [2304x768], NVFP4 x NVFP4, bias, bf16 out",
+          "gemm_us": us_g, "gemm_tflops": flops / (us_g * 1e-6) / 1e12,
+          "quantize_x_plus_gemm_us": us_qg,
+          "roofline_us": {"tensor": t_compute, "output_write": t_write, "bound": "output_write" if t_write > t_compute else "tensor"},
+          "frac_of_min_roofline": max(t_compute, t_write) / us_g}
+    del sets
+    torch.cuda.empty_cache()
+    # one layer through the step driver: a one-layer set whose head is 128 columns wide (1.4 % of the FLOPs)
+    layer_shape = ModelShape("gpt2-small-one-layer", 1, 768, 3072, 128)
+    ps = ProjectionSet(layer_shape, 8192, dev, seed=4321, inputs_only=True)
+    host = HostStep(ps)
+    us_layer = cuda_time_us(torch, lambda: host.step(), 20)
+    flops_layer = 6.0 * 8192 * (768 * 2304 + 768 * 768 + 2 * 768 * 3072)
+    head_flops = 6.0 * 8192 * 768 * 128
+    c3 = {"workload": "one GPT-2-small layer (c_attn, c_proj, fc, proj) fwd+bwd at 8192 tokens, weight quantization "
+                      "included (plus a 128-column head, 1.4 % of the FLOPs, that the step driver always carries)",
+          "ms": us_layer / 1e3, "tflops": (flops_layer + head_flops) / (us_layer * 1e-6) / 1e12}
+    host.close()
+    del host, ps
+    torch.cuda.empty_cache()
+    return c2, c3
 
 
 def run_small_case(args):
@@ -234,6 +388,10 @@ def run_small_case(args):
         raise SystemExit(1)
 
 
+# --------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -242,6 +400,7 @@ def run_gpu(args):
 
     pkg = entry.load_package()
     pkg.set_deterministic_reductions(bool(args.deterministic))
+    from nanogpt_120a_b200.host_step import HostStep  # noqa: E402
     from nanogpt_120a_b200.projection_set import SHAPES, ProjectionSet  # noqa: E402
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -257,16 +416,6 @@ def run_gpu(args):
         pg = dist.group.WORLD
     if args.gpus != world and rank == 0:
         print(f"[bench] --gpus {args.gpus} but WORLD_SIZE={world}; using {world}", file=sys.stderr)
-
-    shape = SHAPES[args.model]
-    if args.scaling == "weak":
-        tokens_rank = args.tokens
-        total_tokens = args.tokens * world
-    else:
-        tokens_rank = args.tokens // world
-        total_tokens = tokens_rank * world
-    ps = ProjectionSet(shape, tokens_rank, dev, seed=1234, token_offset=rank * tokens_rank, process_group=pg)
-    flops_step_total = shape.flops_per_token() * total_tokens
     peaks, peak_kind = measured_peaks()
 
     def barrier():
@@ -281,54 +430,98 @@ def run_gpu(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- device-resident timing -----------------------------------------------------------
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def time_steps(step, steps, warmup):
+        """(ms per step on the device, max over ranks; host milliseconds spent enqueueing one step)."""
+        for _ in range(warmup):
+            step()
+        barrier()
+        start.record()
+        h0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        host_ms = (time.perf_counter() - h0) * 1e3 / steps
+        stop.record()
+        barrier()
+        return max_over_ranks(start.elapsed_time(stop)) / steps, host_ms
+
+    def make(shape, tokens_rank, total, with_comm=True, seed=1234):
+        ps = ProjectionSet(shape, tokens_rank, dev, seed=seed, token_offset=rank * tokens_rank, total_tokens=total,
+                           inputs_only=True)
+        return ps, HostStep(ps, process_group=pg if with_comm else None)
+
+    # ---- correctness of the kernel instantiations this run uses, before anything is timed -------------
+    shape = SHAPES[args.model]
+    if args.scaling == "strong":
+        tokens_rank = args.tokens // world // 128 * 128
+    else:
+        tokens_rank = args.tokens
+    total_tokens = tokens_rank * world
+    parity = None
+    if rank == 0 and not args.no_parity_check:
+        parity = gemm_self_check(pkg, torch, dev, tokens_rank, shape)
+        if not parity["max_rel_fro"] <= parity["tolerance"] or parity["device_status"] != 0:
+            emit({"metric": METRIC, "error": "GEMM self-check failed", "parity_check": parity})
+            raise SystemExit(2)
+    barrier()
+
+    # ---- the headline workload, device-resident -----------------------------------------------------------
+    ps, host = make(shape, tokens_rank, total_tokens)
+    flops_step_total = shape.flops_per_token() * total_tokens
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()  # nvidia-smi needs a moment to come up: started ahead of the warm-up steps
-    for _ in range(max(args.warmup, 3)):
-        ps.step()
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        host.step()
     barrier()
     launches_before = pkg.launch_count()
-    gemm_per_step = 3 * (4 * shape.n_layer + 1)
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
     t_begin = time.time()
-    start.record()
-    for _ in range(args.steps):
-        ps.step()
-    stop.record()
-    barrier()
+    ms_step, host_ms = time_steps(host.step, args.steps, 0)
     t_end = time.time()
-    ms_total = max_over_ranks(start.elapsed_time(stop))
     launches = pkg.launch_count() - launches_before
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
 
-    # ---- the dominant kernel: a second pass of K steps with every GEMM launch bracketed by a CUDA
-    # event pair on its stream (the brackets cost a little, so they stay out of the region above)
+    # ---- the dominant kernel: a second pass of K steps with every GEMM launch bracketed by a CUDA event pair on
+    # its stream (the brackets cost a little, so they stay out of the region above)
+    gemm_per_step = 3 * (4 * shape.n_layer + 1)
     pkg.gemm_timing_begin(gemm_per_step * args.steps)
     barrier()
     start.record()
     for _ in range(args.steps):
-        ps.step()
+        host.step()
     stop.record()
     barrier()
     ms_total_bracketed = start.elapsed_time(stop)
     n_gemm, gemm_ms, gemm_flops, _, _ = pkg.gemm_timing_end(0)
-    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     status = pkg.read_device_status()
-    ms_step = ms_total / args.steps
     value = flops_step_total / (ms_step * 1e-3) / 1e12
 
-    # ---- end to end: host buffers, H2D + step + D2H every step ------------------------------
-    # Every step's activations and output gradients start in pinned host memory.  They are copied
-    # into one of two device input sets on a copy stream while the previous step computes on the
-    # other set (what a prefetching loader does); each step ends with a device -> host read of the
-    # gradient digest.  All copies of all timed steps lie inside the timed region.
+    # ---- where the step time goes at N > 1: the same shard without the collective -------------------------------
+    timeline = None
+    if world > 1:
+        ps_nc, host_nc = make(shape, tokens_rank, total_tokens, with_comm=False)
+        ms_nc, _ = time_steps(host_nc.step, min(args.steps, 10), 3)
+        host_nc.close()
+        del ps_nc, host_nc
+        timeline = {"step_ms": ms_step, "compute_only_ms": ms_nc, "exposed_allreduce_ms": max(0.0, ms_step - ms_nc),
+                    "host_enqueue_ms_per_step": host_ms,
+                    "allreduce_bytes_per_step": 4 * sum(b.numel() for b in host.buckets),
+                    "note": "compute_only = the same shard stepped without a communicator; the difference is the part "
+                            "of the all-reduces (and their SM use) that backward does not hide"}
+
+    # ---- end to end: host buffers, H2D + step + D2H every step -------------------------------------------------
+    # Every step's activations and output gradients start in pinned host memory.  They are copied into one of two
+    # device input sets on a copy stream while the previous step computes on the other set (what a prefetching
+    # loader does); each step ends with a device -> host read of the gradient digest.  All copies of all timed
+    # steps lie inside the timed region.
     host_in = {}
     for name, group in (("x", ps.x), ("dy", ps.dy)):
         for w, t in group.items():
             host_in[(name, w)] = torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
     h2d_bytes = sum(h.numel() * h.element_size() for h in host_in.values())
-    digest_host = torch.empty(len(ps.buckets), dtype=torch.float32, pin_memory=True)
+    digest_host = torch.empty(len(host.buckets), dtype=torch.float32, pin_memory=True)
     d2h_bytes = digest_host.numel() * 4
     input_sets = [(ps.x, ps.dy),
                   ({w: torch.empty_like(t) for w, t in ps.x.items()}, {w: torch.empty_like(t) for w, t in ps.dy.items()})]
@@ -355,11 +548,11 @@ def run_gpu(args):
                 stage(i + 1)
             which = i % 2
             main_stream.wait_event(ready[which])
-            ps.x, ps.dy = input_sets[which]
-            ps.step()
-            digest_host.copy_(ps.result_digest(), non_blocking=True)
+            host.set_inputs(*input_sets[which])
+            host.step()
+            digest_host.copy_(host.result_digest(), non_blocking=True)
             done[which].record(main_stream)
-        ps.x, ps.dy = input_sets[0]
+        host.set_inputs(*input_sets[0])
 
     e2e_run(2)
     barrier()
@@ -370,14 +563,15 @@ def run_gpu(args):
     barrier()
     e2e_ms = max_over_ranks(start.elapsed_time(stop)) / e2e_steps
     e2e_value = flops_step_total / (e2e_ms * 1e-3) / 1e12
-
-    quant = quantize_bandwidth(pkg, torch, dev, peaks["hbm_gbs"]) if rank == 0 else None
+    del input_sets, host_in
 
     # ---- the same step replayed from a CUDA graph (launch-overhead-free figure, single rank) ------
     graph_info = None
     if world == 1:
         try:
-            graph = ps.capture_step()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                host.step()
             for _ in range(2):
                 graph.replay()
             torch.cuda.synchronize()
@@ -388,9 +582,47 @@ def run_gpu(args):
             torch.cuda.synchronize()
             g_ms = start.elapsed_time(stop) / args.steps
             graph_info = {"ms_per_step": g_ms, "value": flops_step_total / (g_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                          "device_status": pkg.read_device_status()}
+                          "device_status": pkg.read_device_status(),
+                          "note": "the seeds drawn during capture are baked into the graph; the headline is the eager step"}
+            del graph
         except Exception as exc:  # the eager figures above stand on their own
             graph_info = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+    buckets_bytes = 4 * sum(b.numel() for b in host.buckets)
+    host.close()
+    del host, ps
+    torch.cuda.empty_cache()
+
+    # ---- sub-records: the other configurations the specification names --------------------------------------------------
+    extra_steps = max(2, min(args.steps, 5))
+    weak = None
+    if world > 1 and not args.skip_extra and args.scaling == "strong":
+        psw, hw = make(shape, TOTAL_TOKENS, TOTAL_TOKENS * world)
+        ms_w, _ = time_steps(hw.step, extra_steps, 3)
+        weak = {"scaling": "weak", "tokens_per_gpu": TOTAL_TOKENS, "ms_per_step": ms_w,
+                "value": shape.flops_per_token() * TOTAL_TOKENS * world / (ms_w * 1e-3) / 1e12, "unit": "TFLOP/s"}
+        hw.close()
+        del psw, hw
+        torch.cuda.empty_cache()
+    medium = None
+    if not args.skip_extra and args.model == "gpt2-small":
+        med = SHAPES["gpt2-medium"]
+        tok = 32768
+        psm, hm = make(med, tok, tok * world, seed=99)
+        ms_m, _ = time_steps(hm.step, extra_steps, 3)
+        medium = {"workload": f"{med.name}: 24 layers, d_model 1024, MLP 4096, vocab 32000, fwd+bwd, {tok} tokens per GPU "
+                              f"({tok * world} per step)", "scaling": "weak (32768 tokens per GPU at every N; 262144 at N = 8)",
+                  "ms_per_step": ms_m, "value": med.flops_per_token() * tok * world / (ms_m * 1e-3) / 1e12,
+                  "unit": "TFLOP/s", "flop_per_step": med.flops_per_token() * tok * world}
+        hm.close()
+        del psm, hm
+        torch.cuda.empty_cache()
+
+    quant = write_gbs = c2 = c3 = None
+    if rank == 0:
+        write_gbs = write_roofline(torch, dev)
+        quant = quantize_records(pkg, torch, dev, peaks["hbm_gbs"])
+        if world == 1 and not args.skip_extra:
+            c2, c3 = small_configs(pkg, torch, dev, peaks, write_gbs)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -402,23 +634,29 @@ def run_gpu(args):
 
     if rank == 0:
         achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
-        # DRAM bytes per GEMM launch (average over the launches of a step): profiler capture of one full
-        # step of this workload at 65536 tokens per GPU; operand and output bytes grow with the tokens
-        gemm_traffic = None
-        if args.model == "gpt2-small" and n_gemm > 0:
-            gemm_traffic = GEMM_DRAM_BYTES_PER_STEP_65536 * (tokens_rank / 65536.0) / gemm_per_step
+        # algorithmic bytes of the step's GEMM launches on this rank: NVFP4 operands (0.5625 B/element) read once,
+        # output written once
+        d, h, v, T = shape.d_model, shape.d_mlp, shape.vocab, tokens_rank
+        lin = [(i, o) for _, i, o, _ in shape.linears()] * shape.n_layer + [(d, v)]
+        algo = 0.0
+        for i, o in lin:
+            algo += (T * i + o * i) * 0.5625 + T * o * 2      # forward, bf16 out
+            algo += (T * o + i * o) * 0.5625 + T * i * 2      # dX, bf16 out
+            algo += (o * T + i * T) * 0.5625 + o * i * 4      # dW, f32 out
+        n_launch = max(n_gemm // max(args.steps, 1), 1)
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
+            "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate, bf16 in/out)",
             "data": "synthetic",
             "config": {"workload": f"{shape.name}: {shape.n_layer} layers x (c_attn, c_proj, fc, proj) + LM head "
                                    f"(vocab {shape.vocab}), fwd+bwd, {total_tokens} tokens/step "
                                    f"({tokens_rank} per GPU)",
-                       "parallelism": f"token-sharded dp{world}, weights replicated, per-layer NCCL all-reduce of dW",
-                       "l2": "inputs larger than L2 (>= 100 MB per activation tensor)",
+                       "parallelism": f"token-sharded dp{world}, weights replicated, per-layer NCCL all-reduce of dW "
+                                      f"issued from the C++ step driver",
+                       "l2": "inputs larger than L2 (every activation / gradient tensor of the step; 126 MB L2)",
                        "deterministic_reductions": bool(args.deterministic),
-                       "flop_per_step": flops_step_total},
+                       "flop_per_step": flops_step_total, "host": "C++ step driver, one host call per step"},
             "pct_of_fp4_peak": 100.0 * value / (NOMINAL_FP4_DENSE_TFLOPS * world),
             "roofline": {"bound": "tensor", "kernel": "nvfp4_gemm_tcgen05_kernel", "achieved": achieved,
                          "peak": NOMINAL_FP4_DENSE_TFLOPS, "unit": "TFLOP/s", "frac": achieved / NOMINAL_FP4_DENSE_TFLOPS,
@@ -428,17 +666,33 @@ def run_gpu(args):
                          "launches": n_gemm, "avg_launch_ms": gemm_ms / max(n_gemm, 1),
                          "gemm_share_of_step": gemm_ms / ms_total_bracketed if ms_total_bracketed > 0 else None,
                          "bracketed_ms_per_step": ms_total_bracketed / args.steps,
-                         "traffic": gemm_traffic, "traffic_source": GEMM_TRAFFIC_SOURCE if gemm_traffic else None,
-                         "peaks_file": peak_kind},
+                         "algorithmic_bytes_per_launch": algo / n_launch,
+                         "traffic": GEMM_TRAFFIC_PER_ALGORITHMIC_BYTE * algo / n_launch,
+                         "traffic_source": "DRAM read + write bytes of a small-case profiler capture of this kernel, "
+                                           "as a ratio to its algorithmic bytes, times this run's algorithmic bytes",
+                         "write_roofline_gbs": write_gbs, "peaks_file": peak_kind},
             "quantize": quant, "cuda_graph_replay": graph_info,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d_bytes,
-                    "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
-            "gpu_launches": launches, "clocks": clocks, "device_status": status,
+                    "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps,
+                    "d2h": "digest only: one f32 per gradient bucket; the gradients themselves stay on the device "
+                           f"({buckets_bytes} bytes per step), as they do in a training step",
+                    "note": "bound by the host's PCIe links (shared by the ranks of a node)"},
+            "gpu_launches": launches, "host_enqueue_ms_per_step": host_ms, "clocks": clocks, "device_status": status,
+            "parity_check": parity,
         }
+        if timeline:
+            line["timeline"] = timeline
+        if weak:
+            line["weak"] = weak
+        if medium:
+            line["gpt2_medium"] = medium
+        if c2:
+            line["configs"] = {"c_attn_forward_8192": c2, "one_layer_8192": c3}
         if cpu is not None:
             line["cpu_baseline"] = cpu
         emit(line)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -470,10 +724,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="gpt2-small", choices=["gpt2-small", "gpt2-medium"])
-    ap.add_argument("--tokens", type=int, default=TOKENS_PER_GPU,
-                    help="tokens per GPU (weak scaling) or in total (strong scaling)")
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--tokens", type=int, default=TOTAL_TOKENS,
+                    help="tokens per step in total (strong scaling, the default) or per GPU (weak scaling)")
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity-check", action="store_true", help="skip the GEMM self-check that precedes the timing")
+    ap.add_argument("--skip-extra", action="store_true",
+                    help="skip the sub-records (weak scaling, GPT-2-medium, the 8192-token configurations)")
     ap.add_argument("--deterministic", action="store_true",
                     help="cap split-K at two splits (run-to-run identical dW); the default lets small dW GEMMs "
                          "take as many splits as fill the SMs")

@@ -154,6 +154,37 @@ class Nvfp4QuantModule {
                                                                  out.global_scales.ptr, row_amax.ptr,
                                                                  out.decoded_amax.ptr));
   }
+  // The same quantizer applied to relu(pre)^2 computed on load: the MLP activation is never stored
+  // (`RowwiseNvfp4Scratch::quantize_precomputed_amax` fed by the ReLU^2 post-op's row amax in the reference,
+  // crates/gpt2-nvfp4/src/types/l3_mlp/forward.rs:60-76).  `row_amax_in` may be empty.
+  template <typename T>
+  DriverError quantize_relu2(Stream s, DeviceBuffer<const T> pre_activation, DeviceBuffer<const float> row_amax_in,
+                             const Nvfp4TensorView& out) const {
+    if (auto e = out.check()) return e;
+    if (!out.rowwise) return detail::invalid("quantize_relu2: output must be rowwise");
+    if (pre_activation.len < static_cast<size_t>(out.rows) * out.cols) return detail::invalid("quantize_relu2: input too short");
+    if (row_amax_in.ptr && row_amax_in.len < out.rows) return detail::invalid("quantize_relu2: row_amax_in too short");
+    return detail::from_rc(nvfp4_quantize_relu2_four_six_rowwise(s, pre_activation.ptr, dtype_of<T>::value, out.rows,
+                                                                 out.cols, row_amax_in.ptr, out.bytes.ptr, out.scales.ptr,
+                                                                 out.scale_layout, out.global_scales.ptr, nullptr,
+                                                                 out.decoded_amax.ptr));
+  }
+  // Tensor amax of an f32 / bf16 tensor (quant/amax.rs:19-23)
+  template <typename T>
+  DriverError tensor_amax(Stream s, DeviceBuffer<const T> x, DeviceBuffer<float> chunk_amax, DeviceBuffer<float> out) const {
+    if (chunk_amax.len < (x.len + 1023) / 1024 || out.len < 1) return detail::invalid("tensor_amax: buffer too short");
+    if (dtype_of<T>::value == NVFP4_DTYPE_F32)
+      return detail::from_rc(nvfp4_tensor_amax_f32(s, reinterpret_cast<const float*>(x.ptr), chunk_amax.ptr, out.ptr, x.len));
+    return detail::from_rc(nvfp4_tensor_amax_bf16(s, x.ptr, chunk_amax.ptr, out.ptr, x.len));
+  }
+};
+
+// An NVFP4-encoded bias [n]: bytes n/2, logical scale bytes n/16, one global scale
+// (the `bias: Nvfp4DeviceTensor` of the reference's projection args, gpt/mlp/args.rs:6-27).
+struct Nvfp4BiasView {
+  DeviceBuffer<const uint8_t> bytes, scales;
+  DeviceBuffer<const float> global_scale;
+  bool present() const { return bytes.ptr && scales.ptr && global_scale.ptr; }
 };
 
 // Fused epilogue of a projection (gpt/projection_postop.rs:97-162 as separate passes in the reference).
@@ -175,7 +206,7 @@ class Nvfp4GemmModule {
   template <typename T>
   DriverError gemm(Stream s, const Nvfp4TensorView& a, const Nvfp4TensorView& b, DeviceBuffer<T> out,
                    Epilogue epilogue = Epilogue::None, DeviceBuffer<const float> bias = {},
-                   DeviceBuffer<T> aux = {}) const {
+                   DeviceBuffer<T> aux = {}, DeviceBuffer<float> relu2_row_amax = {}) const {
     if (auto e = a.check()) return e;
     if (auto e = b.check()) return e;
     if (a.cols != b.cols) return detail::invalid("gemm: A and B must share K");
@@ -194,7 +225,17 @@ class Nvfp4GemmModule {
     g.weight_global_scale = 1.0f;
     g.epilogue = static_cast<int>(epilogue);
     g.out_dtype = dtype_of<T>::value;
+    if (relu2_row_amax.ptr && relu2_row_amax.len < a.rows) return detail::invalid("gemm: relu2_row_amax too short");
+    g.relu2_row_amax = relu2_row_amax.ptr;
     return detail::from_rc(nvfp4_gemm(s, &g));
+  }
+  // launcher.rs:39-166: validates the operands and puts their tensor maps into the calling thread's cache
+  DriverError prepare_tma_nvfp4_device_scales(Stream s, const Nvfp4TensorView& a, const Nvfp4TensorView& b) const {
+    if (auto e = a.check()) return e;
+    if (auto e = b.check()) return e;
+    if (a.cols != b.cols) return detail::invalid("prepare_tma: A and B must share K");
+    return detail::from_rc(nvfp4_prepare_tma_nvfp4_device_scales(s, a.bytes.ptr, a.scales.ptr, b.bytes.ptr, b.scales.ptr,
+                                                                 a.rows, a.cols, b.rows));
   }
   // launcher.rs:224-274, the reference's own entry (f32 output, no epilogue)
   DriverError gemm_tma_nvfp4_rowwise_a_scale_and_global_scale_buffer(Stream s, const Nvfp4TensorView& a,
@@ -207,6 +248,98 @@ class Nvfp4GemmModule {
     return detail::from_rc(nvfp4_gemm_tma_nvfp4_rowwise_a_scale_and_global_scale_buffer(
         s, a.bytes.ptr, a.scales.ptr, b.bytes.ptr, b.scales.ptr, out.ptr, a.rows, a.cols, b.rows, a.global_scales.ptr,
         b.global_scales.ptr));
+  }
+};
+
+namespace detail {
+// One forward projection with the reference's argument list; scale planes in the logical layout need the
+// packed scratch of the same operand (`LmHeadTmaArgs`, gpt/lm_head.rs:41-54).
+struct ProjectionScratch {
+  DeviceBuffer<uint8_t> input_scales_packed, weight_scales_packed;
+};
+inline DriverError fill_projection(nvfp4_projection_args& c, const Nvfp4TensorView& input, const Nvfp4TensorView& weight,
+                                   const Nvfp4BiasView& bias, const ProjectionScratch& scratch) {
+  if (auto e = input.check()) return e;
+  if (auto e = weight.check()) return e;
+  if (!input.rowwise || weight.rowwise || input.cols != weight.cols)
+    return invalid("projection: rowwise input, tensor-scale weight, common input_dim");
+  if (input.scale_layout == NVFP4_SCALES_LOGICAL &&
+      scratch.input_scales_packed.len < scale_packed_len(input.rows, input.cols))
+    return invalid("projection: input_scales_packed scratch too short");
+  if (weight.scale_layout == NVFP4_SCALES_LOGICAL &&
+      scratch.weight_scales_packed.len < scale_packed_len(weight.rows, weight.cols))
+    return invalid("projection: weight_scales_packed scratch too short");
+  if (bias.present() && (bias.bytes.len < weight.rows / 2 || bias.scales.len < weight.rows / 16))
+    return invalid("projection: bias too short");
+  c.input_bytes = input.bytes.ptr, c.input_scales = input.scales.ptr, c.input_scale_layout = input.scale_layout;
+  c.input_global_scales = input.global_scales.ptr;
+  c.weight_bytes = weight.bytes.ptr, c.weight_scales = weight.scales.ptr, c.weight_scale_layout = weight.scale_layout;
+  c.weight_global_scale = weight.global_scales.ptr;
+  c.bias_bytes = bias.bytes.ptr, c.bias_scales = bias.scales.ptr, c.bias_global_scale = bias.global_scale.ptr;
+  c.token_count = input.rows, c.input_dim = input.cols, c.output_dim = weight.rows;
+  c.input_scales_packed_scratch = scratch.input_scales_packed.ptr;
+  c.weight_scales_packed_scratch = scratch.weight_scales_packed.ptr;
+  return {};
+}
+}  // namespace detail
+using ProjectionScratch = detail::ProjectionScratch;
+
+// gpt/attention/qkv_projection/launcher.rs:8-42 `AttentionModule` (its two projections).
+class AttentionModule {
+ public:
+  static AttentionModule from_module() { return {}; }
+  template <typename T>
+  DriverError qkv_projection(Stream s, const Nvfp4TensorView& input, const Nvfp4TensorView& weight,
+                             const Nvfp4BiasView& bias, DeviceBuffer<T> out, const ProjectionScratch& scratch = {}) const {
+    nvfp4_projection_args c{};
+    if (auto e = detail::fill_projection(c, input, weight, bias, scratch)) return e;
+    if (out.len < static_cast<size_t>(input.rows) * weight.rows) return detail::invalid("qkv_projection: out too short");
+    c.out = out.ptr, c.out_dtype = dtype_of<T>::value;
+    return detail::from_rc(nvfp4_qkv_projection(s, &c));
+  }
+  // residual (f32, in place) = fma(1, X . W^T + b, residual)
+  DriverError c_proj(Stream s, const Nvfp4TensorView& input, const Nvfp4TensorView& weight, const Nvfp4BiasView& bias,
+                     DeviceBuffer<float> residual, const ProjectionScratch& scratch = {}) const {
+    nvfp4_projection_args c{};
+    if (auto e = detail::fill_projection(c, input, weight, bias, scratch)) return e;
+    if (residual.len < static_cast<size_t>(input.rows) * weight.rows) return detail::invalid("c_proj: residual too short");
+    c.out = residual.ptr, c.out_dtype = NVFP4_DTYPE_F32;
+    return detail::from_rc(nvfp4_c_proj(s, &c));
+  }
+};
+
+// gpt/lm_head.rs:65-125 `LmHeadModule`.
+class LmHeadModule {
+ public:
+  static LmHeadModule from_module() { return {}; }
+  template <typename T>
+  DriverError logits(Stream s, const Nvfp4TensorView& input, const Nvfp4TensorView& weight, DeviceBuffer<T> logits_out,
+                     const ProjectionScratch& scratch = {}, bool tma = false) const {
+    nvfp4_projection_args c{};
+    if (auto e = detail::fill_projection(c, input, weight, Nvfp4BiasView{}, scratch)) return e;
+    if (logits_out.len < static_cast<size_t>(input.rows) * weight.rows) return detail::invalid("logits: output too short");
+    c.out = logits_out.ptr, c.out_dtype = dtype_of<T>::value;
+    return detail::from_rc(tma ? nvfp4_lm_head_logits_tma(s, &c) : nvfp4_lm_head_logits(s, &c));
+  }
+  template <typename T>
+  DriverError logits_tma(Stream s, const Nvfp4TensorView& input, const Nvfp4TensorView& weight, DeviceBuffer<T> logits_out,
+                         const ProjectionScratch& scratch = {}) const {
+    return logits<T>(s, input, weight, logits_out, scratch, true);
+  }
+};
+
+// gpt/next_latent/launch_projection.rs:10-29 `NextLatModule::projection`.
+class NextLatModule {
+ public:
+  static NextLatModule from_module() { return {}; }
+  template <typename T>
+  DriverError projection(Stream s, const Nvfp4TensorView& input, const Nvfp4TensorView& weight, const Nvfp4BiasView& bias,
+                         DeviceBuffer<T> out, const ProjectionScratch& scratch = {}) const {
+    nvfp4_projection_args c{};
+    if (auto e = detail::fill_projection(c, input, weight, bias, scratch)) return e;
+    if (out.len < static_cast<size_t>(input.rows) * weight.rows) return detail::invalid("projection: out too short");
+    c.out = out.ptr, c.out_dtype = dtype_of<T>::value;
+    return detail::from_rc(nvfp4_nextlat_projection(s, &c));
   }
 };
 
@@ -227,6 +360,31 @@ class MlpModule {
   DriverError down(Stream s, const Nvfp4TensorView& hidden, const Nvfp4TensorView& w_proj, DeviceBuffer<const float> bias,
                    DeviceBuffer<T> out) const {
     return Nvfp4GemmModule{}.gemm<T>(s, hidden, w_proj, out, Epilogue::Bias, bias);
+  }
+  // launcher.rs:53-59 with the reference's argument list (NVFP4 bias): pre = X . W^T + b, hidden = relu(pre)^2;
+  // an empty `hidden` keeps only the pre-activation, `relu2_row_amax` (optional) receives the row amax of relu(pre)^2
+  template <typename T>
+  DriverError up_relu2(Stream s, const Nvfp4TensorView& input, const Nvfp4TensorView& weight, const Nvfp4BiasView& bias,
+                       DeviceBuffer<T> pre_activation, DeviceBuffer<T> hidden, DeviceBuffer<float> relu2_row_amax = {},
+                       const ProjectionScratch& scratch = {}) const {
+    nvfp4_projection_args c{};
+    if (auto e = detail::fill_projection(c, input, weight, bias, scratch)) return e;
+    const size_t mn = static_cast<size_t>(input.rows) * weight.rows;
+    if (pre_activation.len < mn || (hidden.ptr && hidden.len < mn)) return detail::invalid("up_relu2: output too short");
+    if (relu2_row_amax.ptr && relu2_row_amax.len < input.rows) return detail::invalid("up_relu2: relu2_row_amax too short");
+    c.out = hidden.ptr, c.pre_activation = pre_activation.ptr, c.out_dtype = dtype_of<T>::value;
+    c.relu2_row_amax = relu2_row_amax.ptr;
+    return detail::from_rc(nvfp4_mlp_up_relu2(s, &c));
+  }
+  // launcher.rs:60-66: residual (f32, in place) += X . W^T + b
+  DriverError down_residual(Stream s, const Nvfp4TensorView& input, const Nvfp4TensorView& weight,
+                            const Nvfp4BiasView& bias, DeviceBuffer<float> residual,
+                            const ProjectionScratch& scratch = {}) const {
+    nvfp4_projection_args c{};
+    if (auto e = detail::fill_projection(c, input, weight, bias, scratch)) return e;
+    if (residual.len < static_cast<size_t>(input.rows) * weight.rows) return detail::invalid("down_residual: residual too short");
+    c.out = residual.ptr, c.out_dtype = NVFP4_DTYPE_F32;
+    return detail::from_rc(nvfp4_mlp_down_residual(s, &c));
   }
   // launcher.rs:66-76: d_pre = (d_out * 2) * max(pre, 0)
   DriverError relu2_backward(Stream s, DeviceBuffer<const float> pre_activation, DeviceBuffer<const float> d_out,
@@ -303,6 +461,12 @@ struct LinearBackwardMsEdenArgs {
   uint32_t precomputed_e_amax_chunks = 0;
   uint32_t token_offset = 0;
   DeviceBuffer<const float> e_global_scale_override;  // empty = derive from dY here
+  DeviceBuffer<const float> x_decoded_amax;           // empty = input.decoded_amax, or a pass over X
+  uint32_t total_token_count = 0;                     // tokens of the unsharded batch (0 = not sharded)
+  // caller-owned second stream with its fork / join events (cudaStream_t, cudaEvent_t); null = serial
+  Stream side_stream = nullptr;
+  void* fork_event = nullptr;
+  void* join_event = nullptr;
 };
 
 // gpt/linear_backward.rs:31-67, gpt/linear_backward/ms_eden.rs:15-55 `LinearBackwardModule`.
@@ -351,7 +515,9 @@ class LinearBackwardModule {
     c.precomputed_e_amax_chunks = a.precomputed_e_amax_chunks;
     c.token_offset = a.token_offset;
     c.e_global_scale_override = a.e_global_scale_override.ptr;
-    c.x_decoded_amax = a.input.decoded_amax.ptr;
+    c.x_decoded_amax = a.x_decoded_amax.ptr ? a.x_decoded_amax.ptr : a.input.decoded_amax.ptr;
+    c.total_token_count = a.total_token_count;
+    c.side_stream = a.side_stream, c.fork_event = a.fork_event, c.join_event = a.join_event;
     return detail::from_rc(nvfp4_linear_backward_ms_eden(s, &c));
   }
 };

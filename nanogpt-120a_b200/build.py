@@ -67,6 +67,23 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+STEP_LIB = os.path.join(HERE, "libnvfp4_b200_step.so")
+
+
+def build_step_library(force: bool = False) -> str:
+    """Compiles the C++ training-step driver (include/nvfp4_b200_step.hpp behind the C ABI of
+    include/nvfp4_b200_step.h) into libnvfp4_b200_step.so next to the kernel library."""
+    root = os.path.abspath(os.path.join(HERE, ".."))
+    include = os.path.join(root, "include")
+    src = os.path.join(HERE, "host", "step_capi.cpp")
+    deps = [src, build()] + [os.path.join(include, f) for f in ("nvfp4_b200.h", "nvfp4_b200.hpp", "nvfp4_b200_step.h",
+                                                                "nvfp4_b200_step.hpp")]
+    if force or _stale(STEP_LIB, deps):
+        subprocess.check_call([_nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-I", include, src, "-o",
+                               STEP_LIB, "-L", HERE, "-lnvfp4_b200", "-ldl", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"])
+    return STEP_LIB
+
+
 def build_cpp_driver(force: bool = False) -> str:
     """Compiles tests/cpp/mlp_layer_driver.cpp (a C++ caller of include/nvfp4_b200.hpp that walks one MLP
     block forward and backward) against the in-tree library; returns the binary's path."""
@@ -85,4 +102,5 @@ def build_cpp_driver(force: bool = False) -> str:
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_step_library(force="--force" in sys.argv))
     print(build_cpp_driver(force="--force" in sys.argv))

@@ -1283,6 +1283,35 @@ void plan_gemm(const nvfp4_gemm_args& a, int sms, GemmPlan& pl) {
   // loop); 256 columns have one buffer; 128 columns remain for everything else.
   const bool can_split = a.out_dtype == NVFP4_DTYPE_F32 &&
                          (a.epilogue == NVFP4_EPI_NONE || a.epilogue == NVFP4_EPI_BIAS) && num_k_tiles >= 16;
+  // Work items, waves and an estimated duration (SM cycles) of a candidate width.  The constants are fits
+  // to B200 measurements of the training step's shapes: a streamed k-tile costs what its operand bytes take
+  // through the SM's L2 port (128: 700, 192: 980, 256: 1150 cycles), a tile adds the part of its epilogue
+  // that the next main loop does not hide (one accumulator buffer: all of the drain).
+  struct Candidate {
+    uint32_t splits;
+    uint64_t cost;
+  };
+  auto evaluate = [&](uint32_t bn) {
+    const uint32_t tiles = num_m_blocks * ((a.n + bn - 1) / bn);
+    const uint64_t ck = bn == 256 ? 1150 : bn == 192 ? 980 : 700;
+    const uint64_t ce = bn == 256 ? 3500 : bn == 192 ? 2000 : 1500;
+    Candidate best{1, ~0ull};
+    uint32_t max_splits = 1;
+    if (can_split && tiles < 2 * usms) {
+      max_splits = num_k_tiles / 8;
+      if (max_splits > 32) max_splits = 32;
+      if (max_splits > 2 && gemm_get_deterministic()) max_splits = 2;
+      if (max_splits < 1) max_splits = 1;
+    }
+    for (uint32_t sp = 1; sp <= max_splits; ++sp) {
+      const uint32_t per = (num_k_tiles + sp - 1) / sp;
+      const uint32_t real = (num_k_tiles + per - 1) / per;
+      const uint64_t waves = (static_cast<uint64_t>(tiles) * real + usms - 1) / usms;
+      const uint64_t cost = waves * (per * ck + ce);
+      if (cost < best.cost) best = Candidate{real, cost};  // ties go to fewer splits
+    }
+    return best;
+  };
   uint32_t block_n = 128;
   const int forced = tile_override();
   if (forced) {
@@ -1293,40 +1322,29 @@ void plan_gemm(const nvfp4_gemm_args& a, int sms, GemmPlan& pl) {
     // columns of the last 192-wide block that lie outside the matrix, as a share of all columns computed
     const uint32_t cols192 = (a.n + 191) / 192 * 192;
     const bool fits192 = (cols192 - a.n) * 16u <= cols192;  // at most 1/16 wasted
-    const bool wide192 = fits192 && a.n >= 192 && (tiles192 >= usms || can_split);
+    const bool ok192 = fits192 && a.n >= 192 && (tiles192 >= usms || can_split);
     const bool wide_shape = a.n % 256 == 0 || a.n > 1024;
-    const bool wide_long_k = wide_shape && num_k_tiles >= 4 && (tiles256 >= usms || can_split);
-    const bool wide_short_k = a.n % 256 == 0 && num_k_tiles <= 3 && tiles256 >= 4u * usms;
-    if (wide192)
-      block_n = 192;
-    else if (wide_long_k || wide_short_k)
+    const bool ok256 = wide_shape && ((num_k_tiles >= 4 && (tiles256 >= usms || can_split)) ||
+                                      (a.n % 256 == 0 && num_k_tiles <= 3 && tiles256 >= 4u * usms));
+    if (ok192 && ok256) {
+      // short K (resident B panel, bound by writing the output): the wider tile; otherwise the cheaper estimate
+      if (num_k_tiles <= 3)
+        block_n = a.n % 256 == 0 ? 256 : 192;
+      else
+        block_n = evaluate(192).cost < evaluate(256).cost ? 192 : 256;
+    } else if (ok256) {
       block_n = 256;
+    } else if (ok192) {
+      block_n = 192;
+    }
   }
   pl.block_n = block_n;
   pl.num_n_blocks = (a.n + block_n - 1) / block_n;
   const uint32_t tiles = num_m_blocks * pl.num_n_blocks;
 
-  // split-K for long GEMMs with few tiles (dW = dY^T.X): f32 output, linear epilogue only
-  pl.k_splits = 1;
-  if (can_split && tiles < 2 * usms) {
-    // The split count that minimises waves x (main loop + accumulator drain) of one work item, in units of
-    // k-tiles (a drain that is not hidden behind the next main loop costs about four k-tiles); ties go to
-    // fewer splits.
-    const uint32_t drain = block_n == 256 ? 4u : 1u;
-    uint32_t max_splits = num_k_tiles / 8;
-    if (max_splits > 32) max_splits = 32;
-    if (max_splits > 2 && gemm_get_deterministic()) max_splits = 2;
-    uint32_t best = 1;
-    uint64_t best_cost = ~0ull;
-    for (uint32_t sp = 1; sp <= max_splits; ++sp) {
-      const uint32_t per = (num_k_tiles + sp - 1) / sp;
-      const uint32_t real = (num_k_tiles + per - 1) / per;
-      const uint64_t waves = (static_cast<uint64_t>(tiles) * real + usms - 1) / usms;
-      const uint64_t cost = waves * (per + drain);
-      if (cost < best_cost) best_cost = cost, best = sp;
-    }
-    if (best > 1) pl.k_splits = best;
-  }
+  // split-K for long GEMMs with few tiles (dW = dY^T.X): f32 output, linear epilogue only; the split count is
+  // the one that minimises waves x (main loop + exposed epilogue) of one work item
+  pl.k_splits = evaluate(block_n).splits;
   pl.k_tiles_per_split = (num_k_tiles + pl.k_splits - 1) / pl.k_splits;
   pl.k_splits = (num_k_tiles + pl.k_tiles_per_split - 1) / pl.k_tiles_per_split;
 

@@ -546,7 +546,15 @@ __global__ void __launch_bounds__(256) four_six_rowwise_stream_kernel(const T* _
     }
     buf = buf == 2 ? 0u : buf + 1u;
   }
-  if (decoded_amax) cta_atomic_max(warp_max(dec_running), decoded_amax);  // uniform across the CTA
+  if (decoded_amax) {  // uniform across the CTA; the CTA may have fewer than eight warps
+    __shared__ unsigned int dec_bits;
+    if (t == 0) dec_bits = 0u;
+    __syncthreads();
+    const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(dec_running));
+    if (lane_id == 0) atomicMax(&dec_bits, m);
+    __syncthreads();
+    if (t == 0) atomicMax(reinterpret_cast<unsigned int*>(decoded_amax), dec_bits);
+  }
 }
 
 // Schedule-free weight materialisation (gpt/optimizer/schedule_free/{value,amax,four_six}.rs):
@@ -865,10 +873,6 @@ __device__ __forceinline__ void ms_eden_emit_chunk(f32x2_t (&P)[16], const MsEde
 // Two chunks at once, one per packed lane (low lane = chunk of row_lo, high lane = chunk of
 // row_hi, both at chunk_in_row): P[k] holds the signed inputs of K position k of both, so all
 // five butterfly strides act between registers.
-// kRolled: the two 16-groups of the chunks go through ONE copy of the group code (a two-trip loop that moves
-// the second half of P down in between) instead of two inlined copies: a third less code for the
-// instruction cache at the price of 32 register moves.
-template <bool kRolled = false>
 __device__ __forceinline__ void ms_eden_emit_chunk_lanes(f32x2_t (&P)[32], const MsEdenOut& o, float gs, float so,
                                                          uint32_t row_lo, uint32_t row_hi, uint32_t chunk_in_row) {
   const uint32_t chunks_per_row = o.dst_row_len >> 5;
@@ -906,26 +910,8 @@ __device__ __forceinline__ void ms_eden_emit_chunk_lanes(f32x2_t (&P)[32], const
   const uint32_t g_lo = row_lo * o.group_row_stride + chunk_in_row * 2u + o.group_offset;
   const uint32_t g_hi = row_hi * o.group_row_stride + chunk_in_row * 2u + o.group_offset;
   uint2 lo0, hi0, lo1, hi1;
-  uint32_t sb0, sb1;
-  if (kRolled) {
-    lo0 = hi0 = lo1 = hi1 = make_uint2(0u, 0u);
-    sb0 = sb1 = 0u;
-#pragma unroll 1
-    for (uint32_t g = 0; g < 2; ++g) {
-      uint2 l, h;
-      const uint32_t sb = ms_eden_group_lanes(&P[0], safe_gs, so, inv6, o.scale_seed, g_lo + g, g_hi + g, l, h);
-      if (g == 0) {
-        lo0 = l, hi0 = h, sb0 = sb;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) P[i] = P[16 + i];
-      } else {
-        lo1 = l, hi1 = h, sb1 = sb;
-      }
-    }
-  } else {
-    sb0 = ms_eden_group_lanes(&P[0], safe_gs, so, inv6, o.scale_seed, g_lo, g_hi, lo0, hi0);
-    sb1 = ms_eden_group_lanes(&P[16], safe_gs, so, inv6, o.scale_seed, g_lo + 1, g_hi + 1, lo1, hi1);
-  }
+  const uint32_t sb0 = ms_eden_group_lanes(&P[0], safe_gs, so, inv6, o.scale_seed, g_lo, g_hi, lo0, hi0);
+  const uint32_t sb1 = ms_eden_group_lanes(&P[16], safe_gs, so, inv6, o.scale_seed, g_lo + 1, g_hi + 1, lo1, hi1);
   *reinterpret_cast<uint4*>(o.fp4 + chunk_lo * 16) = make_uint4(lo0.x, lo0.y, lo1.x, lo1.y);
   *reinterpret_cast<uint4*>(o.fp4 + chunk_hi * 16) = make_uint4(hi0.x, hi0.y, hi1.x, hi1.y);
   const uint32_t k_atoms = o.dst_row_len >> 6;
@@ -1194,7 +1180,7 @@ struct PairTile {
   static constexpr int kPiecesPerThread = kTileRows * kPiecesPerRow / 256;
 };
 
-template <typename T, bool kRolled = false>
+template <typename T>
 __global__ void __launch_bounds__(256, 2) ms_eden_pair_kernel(const MsEdenTileParams p, uint32_t tiles_x,
                                                                uint32_t tile_count) {
   using PT = PairTile<T>;
@@ -1319,7 +1305,7 @@ __global__ void __launch_bounds__(256, 2) ms_eden_pair_kernel(const MsEdenTilePa
       chunk_in_row = (c0 >> 5) + chunk;
     }
     // one copy of the quantizer body for both roles (the role is warp-uniform)
-    ms_eden_emit_chunk_lanes<kRolled>(P, warp < 4 ? p.t : p.r, gs, p.scale_override, row_lo, row_hi, chunk_in_row);
+    ms_eden_emit_chunk_lanes(P, warp < 4 ? p.t : p.r, gs, p.scale_override, row_lo, row_hi, chunk_in_row);
     __syncthreads();
     if (p.col_sum_partials && tid < kTileCols)
       p.col_sum_partials[static_cast<size_t>(ty) * p.src_cols + c0 + tid] =
@@ -1341,7 +1327,7 @@ constexpr int kNvStageBytes = kTileRows * kNvBytePitch;   // 10240
 // Register budget of three CTAs per SM (80 registers, a few spilled words, same speed as the
 // unconstrained 113), launched two per SM: the free third of the register file lets the
 // bandwidth-bound dY amax kernel of the same backward call run beside it on another stream.
-template <bool kRowwise, bool kRolled = false>
+template <bool kRowwise>
 __global__ void __launch_bounds__(256, 3) ms_eden_nvfp4_transpose_kernel(const MsEdenTileParams p, uint32_t tiles_x,
                                                                           uint32_t tile_count) {
   __shared__ __align__(16) uint8_t stage[2][kNvStageBytes];
@@ -1414,7 +1400,7 @@ __global__ void __launch_bounds__(256, 3) ms_eden_nvfp4_transpose_kernel(const M
       P[i] = mul2_rounded(mul2(pack2(qv.x, qv.y), pack2(sc.x, sc.y)), pack2(sg.x, sg.y));
     }
     const uint32_t out_row = c0 + 2 * cp;
-    ms_eden_emit_chunk_lanes<kRolled>(P, p.t, gs, p.scale_override, out_row, out_row + 1, (r0 >> 5) + q);
+    ms_eden_emit_chunk_lanes(P, p.t, gs, p.scale_override, out_row, out_row + 1, (r0 >> 5) + q);
     __syncthreads();
     sw = sw_next;
   }
@@ -1792,15 +1778,12 @@ int launch_four_six_rowwise_fused(cudaStream_t s, const void* x, int dtype, uint
   const uint32_t threads = (rpc * gpr + 31) / 32 * 32;
   const uint32_t row_blocks = (rows + rpc - 1) / rpc;
   const size_t smem = (rpc + 1) * sizeof(unsigned int);
-  // Persistent CTAs (three fit an SM) once there are more row blocks than resident CTAs; the grid
-  // is sized so that every CTA walks the same number of row blocks.
-  static const int variant = [] {
-    const char* e = std::getenv("NVFP4_FOUR_SIX_VARIANT");
-    return e ? std::atoi(e) : 1;
-  }();
+  // Persistent CTAs (three fit an SM) once there are more row blocks than resident CTAs and a CTA holds several
+  // rows (measured on B200 at 65536 rows: 768 columns 62 against 67 us; rows of 3072 columns, one per CTA,
+  // are faster with one CTA per row: 207 against 228 us); the grid is sized so that every CTA walks the same
+  // number of row blocks.
   const uint32_t resident = 148u * 3u;  // 80 registers x 256 threads: three CTAs per SM
-  const bool stream = variant != 0 && row_blocks > resident &&
-                      ((reinterpret_cast<uintptr_t>(out_scales) & 3u) == 0);
+  const bool stream = row_blocks > resident && gpr <= 64 && ((reinterpret_cast<uintptr_t>(out_scales) & 3u) == 0);
   const uint32_t per_cta = (row_blocks + resident - 1) / resident;
   const uint32_t grid = stream ? (row_blocks + per_cta - 1) / per_cta : row_blocks;
 #define NVFP4_LAUNCH_FUSED(T, P, R)                                                                                   \
@@ -1882,16 +1865,6 @@ int launch_four_six_padded(cudaStream_t s, const float* x, const float* amax, ui
   NVFP4_RETURN_LAST();
 }
 
-// Measurement switch (environment variable NVFP4_MS_EDEN_VARIANT, read once): bit 0 = rolled group loop in
-// the whole-tile kernels.
-static int ms_eden_variant() {
-  static const int v = [] {
-    const char* e = std::getenv("NVFP4_MS_EDEN_VARIANT");
-    return e ? std::atoi(e) : 0;
-  }();
-  return v;
-}
-
 static MsEdenOut make_out(const nvfp4_ms_eden_args& a, uint32_t out_rows) {
   MsEdenOut o;
   o.fp4 = a.out_fp4;
@@ -1948,24 +1921,19 @@ int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a) {
                                 a.dst_row_len == a.rows && (reinterpret_cast<uintptr_t>(a.src_bytes) & 15u) == 0 &&
                                 (reinterpret_cast<uintptr_t>(a.src_scales) & 3u) == 0;
     const uint32_t nv_tiles_x = a.cols / kNvTileCols, nv_tiles = nv_tiles_x * (a.rows / kTileRows);
-    const bool rolled = ms_eden_variant() & 1;
     switch (a.src_kind) {
       case NVFP4_SRC_F32_TRANSPOSED:
         if (bf16) launch_tile<0, __nv_bfloat16, false>(s, p);
         else launch_tile<0, float, false>(s, p);
         break;
       case NVFP4_SRC_NVFP4_TRANSPOSED:
-        if (nv_whole_tiles && rolled)
-          ms_eden_nvfp4_transpose_kernel<false, true><<<min(nv_tiles, 148u * 2u), 256, 0, s>>>(p, nv_tiles_x, nv_tiles);
-        else if (nv_whole_tiles)
+        if (nv_whole_tiles)
           ms_eden_nvfp4_transpose_kernel<false><<<min(nv_tiles, 148u * 2u), 256, 0, s>>>(p, nv_tiles_x, nv_tiles);
         else
           launch_tile<2, float, false>(s, p);
         break;
       case NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED:
-        if (nv_whole_tiles && rolled)
-          ms_eden_nvfp4_transpose_kernel<true, true><<<min(nv_tiles, 148u * 2u), 256, 0, s>>>(p, nv_tiles_x, nv_tiles);
-        else if (nv_whole_tiles)
+        if (nv_whole_tiles)
           ms_eden_nvfp4_transpose_kernel<true><<<min(nv_tiles, 148u * 2u), 256, 0, s>>>(p, nv_tiles_x, nv_tiles);
         else
           launch_tile<3, float, false>(s, p);
@@ -2070,10 +2038,7 @@ int launch_ms_eden_pair(cudaStream_t s, const nvfp4_ms_eden_args& r, const nvfp4
   if (whole_tiles) {
     const uint32_t tiles_x = cols / kTileCols, tile_count = tiles_x * (rows / kTileRows);
     const uint32_t grid = min(tile_count, 148u * 2u);
-    if (r.src_dtype == NVFP4_DTYPE_BF16 && (ms_eden_variant() & 1)) {
-      ms_eden_pair_kernel<__nv_bfloat16, true>
-          <<<grid, 256, 2 * PairTile<__nv_bfloat16>::kStageBytes, s>>>(p, tiles_x, tile_count);
-    } else if (r.src_dtype == NVFP4_DTYPE_BF16) {
+    if (r.src_dtype == NVFP4_DTYPE_BF16) {
       ms_eden_pair_kernel<__nv_bfloat16>
           <<<grid, 256, 2 * PairTile<__nv_bfloat16>::kStageBytes, s>>>(p, tiles_x, tile_count);
     } else {

@@ -83,10 +83,15 @@ class _Linear:
     """One projection: master weight, its per-step NVFP4 form, the saved quantized input,
     caller-owned backward scratch and gradient views."""
 
-    def __init__(self, name, in_dim, out_dim, epilogue, tokens, device, seed, has_bias=True):
+    def __init__(self, name, in_dim, out_dim, epilogue, tokens, device, seed, has_bias=True, inputs_only=False):
         self.name, self.in_dim, self.out_dim, self.epilogue = name, in_dim, out_dim, epilogue
         self.weight = _randn_bf16((out_dim, in_dim), 0.02, seed, device)
         self.bias = _randn_bf16((out_dim,), 0.02, seed + 1, device).float() if has_bias else None
+        self.wq_ready: Optional[torch.cuda.Event] = None
+        self.dweight: Optional[torch.Tensor] = None
+        self.dbias: Optional[torch.Tensor] = None
+        if inputs_only:
+            return
         n = out_dim * in_dim
         u8 = dict(dtype=torch.uint8, device=device)
         f32 = dict(dtype=torch.float32, device=device)
@@ -98,25 +103,26 @@ class _Linear:
         self.xq = Nvfp4Tensor(torch.empty(nx // 2, **u8), torch.empty(scale_packed_len(tokens, in_dim), **u8),
                               torch.empty(tokens, **f32), tokens, in_dim, packed=True, rowwise=True)
         self.x_amax = torch.empty(tokens, **f32)
-        self.wq_ready: Optional[torch.cuda.Event] = None  # set when this step's NVFP4 weight is ready
-        self.dweight: Optional[torch.Tensor] = None  # views into the layer's gradient bucket
-        self.dbias: Optional[torch.Tensor] = None
 
 
 class ProjectionSet:
     def __init__(self, shape: ModelShape, tokens: int, device, seed: int = 1234, token_offset: int = 0,
                  process_group=None, grad_dtype: torch.dtype = torch.bfloat16, overlap_weight_quantization: bool = True,
                  fused_mlp: bool = True, total_tokens: int = 0, reproducible_sharding: bool = False,
-                 input_seed_offset: Optional[int] = None):
+                 input_seed_offset: Optional[int] = None, inputs_only: bool = False):
         """fused_mlp: the fc projection stores only its pre-activation (plus the row amax of relu(pre)^2 from the
         GEMM epilogue) and the down projection's input quantizer applies relu^2 on load, so the MLP activation is
         never written; False = the fc GEMM writes both tensors and the down projection reads a separate input.
         total_tokens / reproducible_sharding: this rank holds tokens [token_offset, token_offset + tokens) of a
         batch of total_tokens; with reproducible_sharding every amax that feeds a per-tensor scale is
         all-reduced (max) over the ranks in one collective per step and the scale-RNG index spaces are those
-        of the unsharded batch, so quantized operands are bit-identical to a single-GPU run."""
+        of the unsharded batch, so quantized operands are bit-identical to a single-GPU run.
+        inputs_only: allocate only what a step READS (master weights, biases, activations, upstream gradients):
+        for callers that hand those tensors to the C++ step driver (`host_step.HostStep`), which owns everything a
+        step writes."""
         assert tokens % 128 == 0, "token shards are multiples of 128 rows (scale tiles stay intact)"
         self.shape, self.tokens, self.device = shape, tokens, device
+        self.inputs_only = inputs_only
         self.token_offset = token_offset
         self.total_tokens = total_tokens
         self.reproducible = reproducible_sharding
@@ -125,13 +131,26 @@ class ProjectionSet:
         self.pg = process_group
         self.grad_dtype = grad_dtype
         self.quant, self.gemm, self.bwd = Nvfp4QuantModule(), Nvfp4GemmModule(), LinearBackwardModule()
+        self.seed = seed
         self.rng = Gpt2Rng(seed)
         d, h, v = shape.d_model, shape.d_mlp, shape.vocab
         self.layers: List[List[_Linear]] = []
         for l in range(shape.n_layer):
-            self.layers.append([_Linear(n, i, o, e, tokens, device, seed * 1000 + l * 10 + j)
+            self.layers.append([_Linear(n, i, o, e, tokens, device, seed * 1000 + l * 10 + j, inputs_only=inputs_only)
                                 for j, (n, i, o, e) in enumerate(shape.linears())])
-        self.lm_head = _Linear("lm_head", d, v, EPI_NONE, tokens, device, seed * 1000 + 999, has_bias=False)
+        self.lm_head = _Linear("lm_head", d, v, EPI_NONE, tokens, device, seed * 1000 + 999, has_bias=False,
+                               inputs_only=inputs_only)
+        widths_in = sorted({i for _, i, _, _ in shape.linears()} | {d})
+        widths_out = sorted({o for _, _, o, _ in shape.linears()} | {v})
+        in_seed = token_offset if input_seed_offset is None else input_seed_offset
+        # Synthetic stand-ins for the tensors the rest of the model would produce: one activation
+        # per input width, one upstream gradient per output width (larger than L2 at bench sizes).
+        self.x: Dict[int, torch.Tensor] = {w: _randn_bf16((tokens, w), 1.0, seed + 7 * w + in_seed, device)
+                                           for w in widths_in}
+        self.dy: Dict[int, torch.Tensor] = {w: _randn_bf16((tokens, w), 1e-3, seed + 11 * w + in_seed, device)
+                                            for w in widths_out}
+        if inputs_only:
+            return
         # one gradient bucket per layer (dW + dbias of its four linears) and one for the LM head
         self.grads = GradBuckets([[(x.out_dim, x.in_dim, True) for x in lin] for lin in self.layers] +
                                  [[(v, d, False)]], device)
@@ -140,15 +159,6 @@ class ProjectionSet:
                 x.dweight, x.dbias = dw, db
         self.buckets = self.grads.buffers
 
-        # Synthetic stand-ins for the tensors the rest of the model would produce: one activation
-        # per input width, one upstream gradient per output width (larger than L2 at bench sizes).
-        widths_in = sorted({i for _, i, _, _ in shape.linears()} | {d})
-        widths_out = sorted({o for _, _, o, _ in shape.linears()} | {v})
-        in_seed = token_offset if input_seed_offset is None else input_seed_offset
-        self.x: Dict[int, torch.Tensor] = {w: _randn_bf16((tokens, w), 1.0, seed + 7 * w + in_seed, device)
-                                           for w in widths_in}
-        self.dy: Dict[int, torch.Tensor] = {w: _randn_bf16((tokens, w), 1e-3, seed + 11 * w + in_seed, device)
-                                            for w in widths_out}
         self.y: Dict[int, torch.Tensor] = {w: torch.empty((tokens, w), dtype=torch.bfloat16, device=device)
                                            for w in widths_out}
         self.pre: Dict[int, torch.Tensor] = {h: torch.empty((tokens, h), dtype=torch.bfloat16, device=device)}

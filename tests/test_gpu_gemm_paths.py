@@ -119,34 +119,65 @@ def run_case(pkg, oracle, dev, m, n, k, *, out_dtype, epi=0, want_plan=None, see
 
 # ------------------------------------------------------------------------------------------ wide tiles, forward
 
+@pytest.mark.parametrize("width", [192, 256])
 @pytest.mark.parametrize("epi", [1, 2])
-def test_resident_banded_192_bf16(pkg, oracle, dev, epi):
-    """The forward GEMMs of the training step (K = 768, bf16 out, bias / ReLU^2 + pre-activation): 192-column
-    tile, B panel resident in shared memory, banded schedule, double-buffered accumulator."""
+def test_resident_banded_bf16(pkg, oracle, dev, tile, width, epi):
+    """The forward GEMMs of the training step (K = 768, bf16 out, bias / ReLU^2 + pre-activation) with both wide
+    tiles: B panel resident in shared memory, banded schedule; 192 columns with a double-buffered accumulator,
+    256 columns with one buffer handed back early."""
+    tile(width)
     run_case(pkg, oracle, dev, 19072, 2304, 768, out_dtype=torch.bfloat16, epi=epi,
-             want_plan=dict(block_n=192, acc_stages=2, b_resident=1, resident_cpn=lambda c: c >= 1, k_splits=1,
-                            tma_store=1))
+             want_plan=dict(block_n=width, acc_stages=1 if width == 256 else 2, b_resident=1,
+                            resident_cpn=lambda c: c >= 1, k_splits=1, tma_store=1))
 
 
 @pytest.mark.parametrize("epi", [1, 2])
-def test_resident_banded_256_bf16(pkg, oracle, dev, epi):
-    """N = 1024 does not divide into 192-column blocks: 256-column tile (one accumulator buffer, handed back
-    early), resident B panel, banded schedule, bias staged through shared memory."""
+def test_resident_banded_256_auto(pkg, oracle, dev, epi):
+    """N = 1024 does not divide into 192-column blocks: the automatic choice is the 256-column tile, resident B
+    panel, banded schedule, bias staged through shared memory."""
     run_case(pkg, oracle, dev, 19072, 1024, 768, out_dtype=torch.bfloat16, epi=epi,
              want_plan=dict(block_n=256, acc_stages=1, b_resident=1, resident_cpn=lambda c: c >= 1, tma_store=1))
 
 
-def test_resident_contiguous_vocab(pkg, oracle, dev):
-    """LM-head shape: 32000 columns = 166 full 192-column blocks and one of 128; more column blocks than CTAs,
-    so the resident schedule walks contiguous tile ranges (panel reloaded when the column block changes)."""
-    run_case(pkg, oracle, dev, 640, 32000, 768, out_dtype=torch.bfloat16, epi=0,
-             want_plan=dict(block_n=192, b_resident=1, resident_cpn=0))
+@pytest.mark.parametrize("width,epi", [(192, 0), (256, 1)])
+def test_resident_contiguous_vocab(pkg, oracle, dev, tile, width, epi):
+    """LM-head shape: 32000 columns (166 full 192-column blocks and one of 128, or 125 blocks of 256): more
+    column blocks than CTAs, so the resident schedule walks contiguous tile ranges and reloads the panel when
+    the column block changes."""
+    tile(width)
+    run_case(pkg, oracle, dev, 640, 32000, 768, out_dtype=torch.bfloat16, epi=epi,
+             want_plan=dict(block_n=width, b_resident=1, resident_cpn=0))
 
 
-def test_resident_256_forced_ragged_vocab(pkg, oracle, dev, tile):
-    tile(256)
-    run_case(pkg, oracle, dev, 640, 32000, 768, out_dtype=torch.bfloat16, epi=1,
-             want_plan=dict(block_n=256, b_resident=1, resident_cpn=0))
+def test_training_step_shapes_take_tested_paths(pkg, dev):
+    """What the automatic choice picks for every GEMM of the GPT-2-small training step at 65536 tokens on a
+    148-SM part: (tile width, K splits > 1, resident).  Each combination is covered by a parity test of this
+    file with the same width, output type and schedule; a change of the heuristics shows up here first."""
+    if torch.cuda.get_device_properties(dev).multi_processor_count != 148:
+        pytest.skip("the expectations are for a 148-SM part")
+    gemm = pkg.Nvfp4GemmModule()
+    T, d, h, v = 65536, 768, 3072, 32000
+    bf, f32 = torch.bfloat16, torch.float32
+    want = {  # name: (m, n, k, out dtype, epilogue) -> (block_n, split, resident)
+        "fwd c_attn": ((T, 3 * d, d, bf, 1), (256, False, 1)), "fwd c_proj": ((T, d, d, bf, 1), (256, False, 1)),
+        "fwd fc": ((T, h, d, bf, 1), (256, False, 1)), "fwd proj": ((T, d, h, bf, 1), (256, False, 0)),
+        "fwd lm_head": ((T, v, d, bf, 0), (256, False, 1)), "dX c_attn": ((T, d, 3 * d, bf, 0), (192, False, 0)),
+        "dX c_proj": ((T, d, d, bf, 0), (256, False, 1)), "dX fc": ((T, d, h, bf, 0), (256, False, 0)),
+        "dX proj": ((T, h, d, bf, 0), (256, False, 1)), "dX lm_head": ((T, d, v, bf, 0), (256, False, 0)),
+        "dW c_attn": ((3 * d, d, T, f32, 0), (256, True, 0)), "dW c_proj": ((d, d, T, f32, 0), (256, True, 0)),
+        "dW fc": ((h, d, T, f32, 0), (256, True, 0)), "dW proj": ((d, h, T, f32, 0), (256, True, 0)),
+        "dW lm_head": ((v, d, T, f32, 0), (192, False, 0)),
+    }
+    one = torch.ones(1, device=dev)
+    for name, ((m, n, k, dt, epi), (block_n, split, resident)) in want.items():
+        # the plan depends on shapes, types and alignment only: tiny placeholder buffers stand in for the operands
+        stub = torch.zeros(16, dtype=torch.uint8, device=dev)
+        A = pkg.Nvfp4Tensor(stub, stub, one, m, k, packed=True, rowwise=True)
+        B = pkg.Nvfp4Tensor(stub, stub, one, n, k, packed=True, rowwise=False)
+        out = torch.empty(16, dtype=dt, device=dev)
+        plan = gemm.plan(A, B, out=out, epilogue=epi, bias=one if epi else None)
+        got = (plan.block_n, plan.k_splits > 1, plan.b_resident)
+        assert got == (block_n, split, resident), (name, got)
 
 
 # ------------------------------------------------------------------------------------------ streaming (long K)
@@ -204,8 +235,7 @@ def test_lm_head_dw_unsplit_wide_f32(pkg, oracle, dev, tile, width):
 def test_output_larger_than_4gb(pkg, oracle, dev):
     """Logits of the full step: 65536 x 32000 bf16 = 4.19 GB in one launch (byte offsets beyond 2^32); first,
     middle and last row block checked."""
-    run_case(pkg, oracle, dev, 65536, 32000, 768, out_dtype=torch.bfloat16, epi=0,
-             want_plan=dict(block_n=192, b_resident=1))
+    run_case(pkg, oracle, dev, 65536, 32000, 768, out_dtype=torch.bfloat16, epi=0, want_plan=dict(b_resident=1))
 
 
 # ------------------------------------------------------------------------------------------ NVFP4 bias, row amax
