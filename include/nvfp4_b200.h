@@ -65,7 +65,7 @@ extern "C" {
 /* Version of this ABI (bumped on incompatible change).  2: nvfp4_linear_backward_args gained
  * x_decoded_amax, nvfp4_quantize_four_six_rowwise_fused gained out_decoded_amax.  3: nvfp4_gemm_args gained
  * the NVFP4 bias and relu2_row_amax members, nvfp4_linear_backward_args gained side_stream / fork_event /
- * join_event and total_token_count, nvfp4_ms_eden_args gained group_row_stride, element counts of the
+ * join_event, total_token_count and weight_t_prepared, nvfp4_ms_eden_args gained group_row_stride, element counts of the
  * tensor-amax entries became 64-bit. */
 int nvfp4_abi_version(void);
 /* Number of kernels this library has launched in this process (host-side tally). */
@@ -591,12 +591,21 @@ typedef struct nvfp4_linear_backward_args {
    * exactly the bits of the unsharded operands, so the shards' dW partial sums add up to the unsharded dW
    * up to f32 summation order. */
   uint32_t total_token_count;
+  /* 1: weight_t_h already holds W^T quantized for this call's seeds by nvfp4_linear_backward_prepare_weight_t
+   * (that step depends on the weight and the seeds only); the call then skips it. */
+  int weight_t_prepared;
 } nvfp4_linear_backward_args;
 
 /* gpt/linear_backward/ms_eden.rs:15-55  LinearBackwardModule::backward_ms_eden :
  * dbias, MS-EDEN quantization of dY (rows + transposed), W^T, X^T, then
  * dX = dY.W and dW = dY^T.X on the tcgen05 GEMM. */
 int nvfp4_linear_backward_ms_eden(void* stream, const nvfp4_linear_backward_args* args /* host */);
+/* The W^T step of backward_ms_eden alone (gpt/linear_backward/ms_eden/quantize/transpose.rs:14-93, weight half):
+ * amax of the decoded weight -> global scale -> MS-EDEN of W^T into args->weight_t_h, with the seeds of `args`.
+ * It reads only the weight, so a caller may enqueue it early and on another stream (beside the forward pass,
+ * right after the weight was quantized) and pass weight_t_prepared = 1 to the backward call: the replicated
+ * weight-side work of a token-sharded step then leaves the critical path. */
+int nvfp4_linear_backward_prepare_weight_t(void* stream, const nvfp4_linear_backward_args* args /* host */);
 
 /* gpt/linear_backward/device_scale.rs:38-187  LinearBackwardModule::backward_device_scale_tma,
  * backward_device_scale, backward_device_scale_cta and gpt/linear_backward.rs:40-67 backward: the two gradient

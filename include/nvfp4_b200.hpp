@@ -467,6 +467,7 @@ struct LinearBackwardMsEdenArgs {
   Stream side_stream = nullptr;
   void* fork_event = nullptr;
   void* join_event = nullptr;
+  bool weight_t_prepared = false;  // scratch.weight_t_h was filled by prepare_weight_t with these seeds
 };
 
 // gpt/linear_backward.rs:31-67, gpt/linear_backward/ms_eden.rs:15-55 `LinearBackwardModule`.
@@ -482,8 +483,19 @@ class LinearBackwardModule {
     return detail::from_rc(nvfp4_linear_bias_grad(s, e.ptr, dbias.ptr, token_count, output_dim));
   }
 
+  // The W^T step alone, for callers that run it early (it reads only the weight and the seeds).
+  template <typename T>
+  DriverError prepare_weight_t(Stream s, const LinearBackwardMsEdenArgs<T>& a) const {
+    return run(s, a, true);
+  }
   template <typename T>
   DriverError backward_ms_eden(Stream s, const LinearBackwardMsEdenArgs<T>& a) const {
+    return run(s, a, false);
+  }
+
+ private:
+  template <typename T>
+  DriverError run(Stream s, const LinearBackwardMsEdenArgs<T>& a, bool weight_t_only) const {
     if (auto e = a.weight.check()) return e;
     if (auto e = a.input.check()) return e;
     if (a.weight.rows != a.output_dim || a.weight.cols != a.input_dim || a.weight.rowwise)
@@ -518,6 +530,8 @@ class LinearBackwardModule {
     c.x_decoded_amax = a.x_decoded_amax.ptr ? a.x_decoded_amax.ptr : a.input.decoded_amax.ptr;
     c.total_token_count = a.total_token_count;
     c.side_stream = a.side_stream, c.fork_event = a.fork_event, c.join_event = a.join_event;
+    c.weight_t_prepared = a.weight_t_prepared ? 1 : 0;
+    if (weight_t_only) return detail::from_rc(nvfp4_linear_backward_prepare_weight_t(s, &c));
     return detail::from_rc(nvfp4_linear_backward_ms_eden(s, &c));
   }
 };

@@ -164,7 +164,9 @@ class ProjectionStep {
     const float* bias = nullptr;
     Nvfp4TensorView wq, xq;
     DeviceBuffer<float> w_amax, w_chunk, dweight, dbias;
-    cudaEvent_t wq_ready = nullptr;
+    MsEdenOperandBuffers weight_t_h;      // W^T of this step, quantized early on the weight stream
+    cudaEvent_t wq_ready = nullptr, wt_ready = nullptr;
+    uint32_t sign_seed = 0, scale_seed = 0;  // this step's MS-EDEN seeds
     uint32_t bucket = 0;
   };
 
@@ -173,8 +175,10 @@ class ProjectionStep {
   }
   ~ProjectionStep() {
     if (comm_ && nccl_) nccl_->comm_destroy(comm_);
-    for (auto& l : linears_)
+    for (auto& l : linears_) {
       if (l.wq_ready) cudaEventDestroy(l.wq_ready);
+      if (l.wt_ready) cudaEventDestroy(l.wt_ready);
+    }
     for (cudaEvent_t e : {fork_, join_, weights_free_, layer_done_, comm_done_})
       if (e) cudaEventDestroy(e);
     for (cudaStream_t s : {weight_stream_, side_stream_, comm_stream_})
@@ -222,10 +226,13 @@ class ProjectionStep {
   // One forward + backward pass over this rank's tokens, enqueued on `s`; returns without synchronising.
   DriverError step(cudaStream_t s, bool weights_changed = true) {
     if (!ok()) return DriverError{static_cast<int>(cudaErrorInvalidValue), error_};
-    if (weights_changed || !weights_quantized_) {
-      if (auto e = quantize_weights(s)) return e;
-      weights_quantized_ = true;
+    // this step's seeds, in the order the backward pass uses them (the forward pass draws none)
+    for (size_t i : backward_order()) {
+      linears_[i].sign_seed = rng_.next_u32();
+      linears_[i].scale_seed = rng_.next_u32();
     }
+    if (auto e = weight_side(s, weights_changed || !weights_quantized_)) return e;
+    weights_quantized_ = true;
     for (auto& l : linears_)
       if (auto e = forward(s, l)) return e;
     return backward(s);
@@ -291,7 +298,10 @@ class ProjectionStep {
       l.xq = alloc_tensor(T, l.in, true, true);
       l.w_amax = alloc(sizeof(float)).as<float>();
       l.w_chunk = alloc(sizeof(float) * ((static_cast<size_t>(l.out) * l.in + 1023) / 1024)).as<float>();
-      if (cudaEventCreateWithFlags(&l.wq_ready, cudaEventDisableTiming) != cudaSuccess) error_ = "cudaEventCreate failed";
+      l.weight_t_h = alloc_operand(LinearBackwardMsEdenScratchSizes(T, l.in, l.out).weight_t_h);
+      if (cudaEventCreateWithFlags(&l.wq_ready, cudaEventDisableTiming) != cudaSuccess ||
+          cudaEventCreateWithFlags(&l.wt_ready, cudaEventDisableTiming) != cudaSuccess)
+        error_ = "cudaEventCreate failed";
       if (!x_.count(l.in) || !dy_.count(l.out)) error_ = "StepInputs: an activation / gradient width is missing";
     }
     // gradient buckets: dW (+ dbias) of a layer's four linears in one flat f32 buffer, the LM head in its own
@@ -338,18 +348,50 @@ class ProjectionStep {
     if (!pre_.ok() || !pre_row_amax_.ok() || !amax_vec_.ok() || !e_scales_.ok()) error_ = "cudaMalloc failed";
   }
 
-  // Weights are re-quantized from their masters every step (four-six, tensor scale) on their own stream, in the
-  // order the forward pass needs them; each forward GEMM waits for its own weight's event.
-  DriverError quantize_weights(cudaStream_t s) {
-    if (auto e = cuda(cudaEventRecord(weights_free_, s), "event record")) return e;  // the previous step is done with the old NVFP4 weights
+  // The weight side of a step, on its own stream beside the forward pass: (when the masters changed) four-six of
+  // every weight in the order the forward pass needs them -- each forward GEMM waits for its own weight's event
+  // -- and then, always, the MS-EDEN form of every W^T with this step's seeds in the order the backward pass
+  // needs them.  This work is replicated on every rank of a token-sharded step; here it is off the critical path.
+  DriverError weight_side(cudaStream_t s, bool requantize) {
+    if (auto e = cuda(cudaEventRecord(weights_free_, s), "event record")) return e;  // the previous step is done with the old operands
     if (auto e = cuda(cudaStreamWaitEvent(weight_stream_, weights_free_, 0), "stream wait")) return e;
-    for (auto& l : linears_) {
-      const DeviceBuffer<const uint16_t> w{l.weight, static_cast<size_t>(l.out) * l.in};
-      if (auto e = quant_.tensor_amax<uint16_t>(weight_stream_, w, l.w_chunk, l.w_amax)) return e;
-      if (auto e = quant_.quantize_four_six<uint16_t>(weight_stream_, w, l.w_amax, l.wq)) return e;
-      if (auto e = cuda(cudaEventRecord(l.wq_ready, weight_stream_), "event record")) return e;
+    if (requantize) {
+      for (auto& l : linears_) {
+        const DeviceBuffer<const uint16_t> w{l.weight, static_cast<size_t>(l.out) * l.in};
+        if (auto e = quant_.tensor_amax<uint16_t>(weight_stream_, w, l.w_chunk, l.w_amax)) return e;
+        if (auto e = quant_.quantize_four_six<uint16_t>(weight_stream_, w, l.w_amax, l.wq)) return e;
+        if (auto e = cuda(cudaEventRecord(l.wq_ready, weight_stream_), "event record")) return e;
+      }
+    }
+    for (size_t i : backward_order()) {
+      Linear& l = linears_[i];
+      if (auto e = backward_.prepare_weight_t<uint16_t>(weight_stream_, backward_args(l, 0))) return e;
+      if (auto e = cuda(cudaEventRecord(l.wt_ready, weight_stream_), "event record")) return e;
     }
     return {};
+  }
+
+  // The arguments of one linear's backward call (`index` = its position in the backward order).
+  LinearBackwardMsEdenArgs<uint16_t> backward_args(Linear& l, size_t index) {
+    LinearBackwardMsEdenArgs<uint16_t> a;
+    a.e = {dy_.at(l.out), static_cast<size_t>(opt_.tokens) * l.out};
+    a.weight = l.wq, a.input = l.xq;
+    a.scratch = scratch_.at({l.in, l.out});
+    a.scratch.weight_t_h = l.weight_t_h;
+    a.weight_t_prepared = true;
+    a.dinput = dx_.at(l.in).as<uint16_t>();
+    a.dweight = l.dweight, a.dbias = l.dbias;
+    a.token_count = opt_.tokens, a.input_dim = l.in, a.output_dim = l.out;
+    a.sign_seed = l.sign_seed, a.scale_seed = l.scale_seed;
+    a.token_offset = opt_.token_offset;
+    a.side_stream = side_stream_, a.fork_event = fork_, a.join_event = join_;
+    if (opt_.reproducible_sharding) {
+      const size_t n = linears_.size();
+      a.total_token_count = opt_.total_tokens ? opt_.total_tokens : opt_.tokens;
+      a.e_global_scale_override = {e_scales_.as<float>().ptr + index, 1};
+      a.x_decoded_amax = {amax_vec_.as<float>().ptr + n + index, 1};
+    }
+    return a;
   }
 
   DriverError forward(cudaStream_t s, Linear& l) {
@@ -408,22 +450,8 @@ class ProjectionStep {
     bool reduced_any = false;
     for (size_t i = 0; i < n; ++i) {
       Linear& l = linears_[order[i]];
-      LinearBackwardMsEdenArgs<uint16_t> a;
-      a.e = {dy_.at(l.out), static_cast<size_t>(opt_.tokens) * l.out};
-      a.weight = l.wq, a.input = l.xq;
-      a.scratch = scratch_.at({l.in, l.out});
-      a.dinput = dx_.at(l.in).as<uint16_t>();
-      a.dweight = l.dweight, a.dbias = l.dbias;
-      a.token_count = opt_.tokens, a.input_dim = l.in, a.output_dim = l.out;
-      a.sign_seed = rng_.next_u32(), a.scale_seed = rng_.next_u32();
-      a.token_offset = opt_.token_offset;
-      a.side_stream = side_stream_, a.fork_event = fork_, a.join_event = join_;
-      if (opt_.reproducible_sharding) {
-        a.total_token_count = opt_.total_tokens ? opt_.total_tokens : opt_.tokens;
-        a.e_global_scale_override = {e_scales_.as<float>().ptr + i, 1};
-        a.x_decoded_amax = {amax_vec_.as<float>().ptr + n + i, 1};
-      }
-      if (auto e = backward_.backward_ms_eden<uint16_t>(s, a)) return e;
+      if (auto e = cuda(cudaStreamWaitEvent(s, l.wt_ready, 0), "stream wait")) return e;
+      if (auto e = backward_.backward_ms_eden<uint16_t>(s, backward_args(l, i))) return e;
       // last linear of its bucket: the bucket is complete, its all-reduce goes to the communication stream
       const bool bucket_done = i + 1 == n || linears_[order[i + 1]].bucket != l.bucket;
       if (bucket_done && comm_) {

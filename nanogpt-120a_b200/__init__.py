@@ -110,7 +110,7 @@ class LinearBackwardArgs(Structure):
         ("input_dim", c_uint32), ("output_dim", c_uint32), ("sign_seed", c_uint32), ("scale_seed", c_uint32),
         ("precomputed_e_amax_chunks", c_uint32), ("token_offset", c_uint32), ("e_global_scale_override", c_void_p),
         ("x_decoded_amax", c_void_p), ("side_stream", c_void_p), ("fork_event", c_void_p), ("join_event", c_void_p),
-        ("total_token_count", c_uint32),
+        ("total_token_count", c_uint32), ("weight_t_prepared", c_int),
     ]
 
 
@@ -194,6 +194,7 @@ _SIGNATURES = {
     "nvfp4_linear_bias_grad": [_P, _P, _P, _U, _U],
     "nvfp4_linear_bias_grad_bf16": [_P, _P, _P, _U, _U],
     "nvfp4_linear_backward_ms_eden": [_P, POINTER(LinearBackwardArgs)],
+    "nvfp4_linear_backward_prepare_weight_t": [_P, POINTER(LinearBackwardArgs)],
 }
 _SPECIAL = {
     "nvfp4_abi_version": (c_int, []),
@@ -1059,7 +1060,8 @@ class LinearBackwardModule:
                          grad_dtype: torch.dtype = torch.float32, dinput=None, dweight=None, dbias=None,
                          token_offset: int = 0, e_global_scale: Optional[torch.Tensor] = None,
                          precomputed_e_amax_chunks: int = 0, side: Optional["SideStream"] = None,
-                         total_token_count: int = 0, x_decoded_amax: Optional[torch.Tensor] = None):
+                         total_token_count: int = 0, x_decoded_amax: Optional[torch.Tensor] = None,
+                         weight_t_prepared: bool = False, prepare_weight_t_only: bool = False):
         """dbias, dX = dY.W, dW = dY^T.X with MS-EDEN quantized operands.  `weight` is the NVFP4
         tensor-scale W[out][in], `input` the rowwise NVFP4 X[tokens][in] saved by the forward."""
         _require_cuda()
@@ -1090,6 +1092,10 @@ class LinearBackwardModule:
         a.e_global_scale_override = _ptr(e_global_scale)
         a.x_decoded_amax = _ptr(x_decoded_amax if x_decoded_amax is not None else input.decoded_amax)
         a.total_token_count = total_token_count
+        a.weight_t_prepared = 1 if weight_t_prepared else 0
+        if prepare_weight_t_only:  # the W^T step alone (it reads only the weight and the seeds)
+            _call("nvfp4_linear_backward_prepare_weight_t", _stream(), ctypes.byref(a))
+            return None
         if side is not None:
             a.side_stream, a.fork_event, a.join_event = side.handles()
         _call("nvfp4_linear_backward_ms_eden", _stream(), ctypes.byref(a))

@@ -403,16 +403,15 @@ static int nvfp4_source_transpose(void* stream, int kind, const uint8_t* in_byte
   if (source_cols % 16 != 0) return invalid("nvfp4 transpose: source_cols must be a multiple of 16");
   if (src_scale_layout == NVFP4_SCALES_PACKED && source_cols % 64 != 0)
     return invalid("nvfp4 transpose: a packed source scale layout needs source_cols % 64 == 0");
-  // the amax kernel leaves max(chunk amax) in out_gs; turn it into the MS-EDEN global scale in place.
-  // A caller that already holds the decoded amax of the source (the forward quantizer can emit it)
-  // skips the pass over the source.
+  // The amax of the decoded source, unless the caller already holds it (the forward quantizer can emit it).
+  // When the chunk scratch is free (no chunk amax asked for) the amax accumulates in its word 0, away from
+  // out_gs, so that the transposer can derive the scale from it by itself.
   int rc = 0;
+  const bool amax_in_scratch = !precomputed_amax && !chunk_amax_out && out_chunk_amax != nullptr;
   if (!precomputed_amax)
     rc = launch_nvfp4_amax(S(stream), in_bytes, in_scales, in_global, source_rows, source_cols,
                            kind == NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED, src_scale_layout == NVFP4_SCALES_PACKED,
-                           out_chunk_amax, out_gs);
-  if (rc) return rc;
-  rc = launch_ms_eden_scale_from_amax(S(stream), precomputed_amax ? precomputed_amax : out_gs, out_gs);
+                           amax_in_scratch ? nullptr : out_chunk_amax, amax_in_scratch ? out_chunk_amax : out_gs);
   if (rc) return rc;
   (void)n;
   nvfp4_ms_eden_args a;
@@ -437,7 +436,17 @@ static int nvfp4_source_transpose(void* stream, int kind, const uint8_t* in_byte
   a.scale_layout = scale_layout;
   a.out_global_scales = out_gss;
   a.out_chunk_amax = chunk_amax_out ? out_chunk_amax : nullptr;
-  return nvfp4_ms_eden_quantize(stream, &a);
+  rc = validate_ms_eden(&a);
+  if (rc) return rc;
+  // amax -> global scale inside the transposer where it can (whole tiles), by a one-thread kernel otherwise;
+  // out_gs receives the scale either way
+  const float* amax_ptr = precomputed_amax ? precomputed_amax : (amax_in_scratch ? out_chunk_amax : out_gs);
+  if (amax_ptr == out_gs) {
+    // the amax sits where the scale will go: deriving it inside the kernel would race across CTAs
+    rc = launch_ms_eden_scale_from_amax(S(stream), out_gs, out_gs);
+    return rc ? rc : launch_ms_eden(S(stream), a);
+  }
+  return launch_ms_eden(S(stream), a, amax_ptr, out_gs);
 }
 
 int nvfp4_nvfp4_transpose_to_quartet_backward_ms_eden_derived_device_scale(
@@ -851,6 +860,24 @@ int nvfp4_linear_backward(void* stream, const nvfp4_linear_backward_device_scale
   return backward_device_scale(stream, a);
 }
 
+static int backward_weight_t(void* stream, const nvfp4_linear_backward_args* a) {
+  const uint32_t I = a->input_dim, O = a->output_dim;
+  return nvfp4_source_transpose(stream, NVFP4_SRC_NVFP4_TRANSPOSED, a->w_bytes, a->w_scales, a->w_global,
+                                a->weight_t_h.bytes, a->weight_t_h.scales_packed, a->weight_t_h.global_scales,
+                                a->weight_t_h.chunk_amax, a->weight_t_h.global_scale, O, I, padded_k(O), a->sign_seed,
+                                a->scale_seed ^ 0x9e3779b9u, false, NVFP4_SCALES_PACKED, 0, 0, a->w_scale_layout);
+}
+
+int nvfp4_linear_backward_prepare_weight_t(void* stream, const nvfp4_linear_backward_args* a) {
+  if (!a) return invalid("linear_backward_prepare_weight_t: null args");
+  if (a->input_dim % 16 != 0) return invalid("linear_backward_prepare_weight_t: input_dim must be a multiple of 16");
+  const nvfp4_ms_eden_operand& op = a->weight_t_h;
+  if (!a->w_bytes || !a->w_scales || !a->w_global || !op.bytes || !op.scales_packed || !op.global_scales ||
+      !op.global_scale || !op.chunk_amax)
+    return invalid("linear_backward_prepare_weight_t: null pointer");
+  return backward_weight_t(stream, a);
+}
+
 // Everything of nvfp4_linear_backward_ms_eden that runs between the fork onto the caller's side stream and the
 // join; `ts` is the stream the two transposers go to (the side stream, or the main one when there is none).
 static int backward_ms_eden_quantize(void* stream, void* ts, const nvfp4_linear_backward_args* a) {
@@ -872,11 +899,10 @@ static int backward_ms_eden_quantize(void* stream, void* ts, const nvfp4_linear_
                               a->scale_seed ^ 0xc2b2ae35u, false, NVFP4_SCALES_PACKED, a->token_offset, t_offset,
                               a->x_scale_layout, a->x_decoded_amax, t_stride);
   if (rc) return rc;
-  rc = nvfp4_source_transpose(ts, NVFP4_SRC_NVFP4_TRANSPOSED, a->w_bytes, a->w_scales, a->w_global,
-                              a->weight_t_h.bytes, a->weight_t_h.scales_packed, a->weight_t_h.global_scales,
-                              a->weight_t_h.chunk_amax, a->weight_t_h.global_scale, O, I, ok, a->sign_seed,
-                              a->scale_seed ^ 0x9e3779b9u, false, NVFP4_SCALES_PACKED, 0, 0, a->w_scale_layout);
-  if (rc) return rc;
+  if (!a->weight_t_prepared) {
+    rc = backward_weight_t(ts, a);
+    if (rc) return rc;
+  }
 
   // 1. dbias.  When the dY quantization below runs tiled, the column sums ride along with it:
   //    each row tile leaves its partial sums in the (not yet written) dinput buffer and a small

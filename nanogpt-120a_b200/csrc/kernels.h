@@ -31,7 +31,10 @@ int launch_packed_scale_pad(cudaStream_t s, uint8_t* packed, uint32_t rows, uint
 int launch_schedule_free_materialize(cudaStream_t s, const float* z, const float* x, float beta, float* chunk_amax,
                                      float* amax, uint8_t* out_fp4, uint8_t* out_scales, int packed, float* out_gs,
                                      uint32_t rows, uint32_t cols);
-int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a);
+// amax_in / gs_out (optional): the global scale is the MS-EDEN scale of amax_in[0] (derived inside the kernel
+// where the kernel supports it, by a one-thread kernel otherwise) and is written to gs_out[0]; a.global_scale
+// and a.host_global_scale are then not read.
+int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a, const float* amax_in = nullptr, float* gs_out = nullptr);
 // Pair quantization; when col_sum_partials != nullptr (and ms_eden_pair_is_tiled) it also writes the
 // per-row-tile column sums [ms_eden_pair_row_tiles(rows)][cols] for launch_col_sum_reduce.
 // amax_in / gs_out (only when ms_eden_pair_takes_amax): the kernel derives the global scale from amax_in[0]

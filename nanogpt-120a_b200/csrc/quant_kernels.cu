@@ -1334,7 +1334,15 @@ __global__ void __launch_bounds__(256, 3) ms_eden_nvfp4_transpose_kernel(const M
   __shared__ __align__(16) float2 scale2[kTileRows][kNvTileCols / 16];  // block scale of (row, group), duplicated
   __shared__ __align__(16) float2 sgs2[kTileRows];                      // signed global scale of the row, duplicated
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const float gs = p.use_host_scale ? p.global_scale_host : p.global_scale_dev[0];
+  float gs;
+  if (p.amax_in) {
+    // the global scale from the amax of the decoded source (every thread evaluates the same two operations),
+    // published for the GEMM that follows: no one-thread kernel in between
+    gs = ms_eden_scale_of_amax(p.amax_in[0]);
+    if (blockIdx.x == 0 && tid == 0) p.gs_out[0] = gs;
+  } else {
+    gs = p.use_host_scale ? p.global_scale_host : p.global_scale_dev[0];
+  }
   const uint32_t stage_base = static_cast<uint32_t>(__cvta_generic_to_shared(&stage[0][0]));
   const uint32_t k_atoms = p.src_cols >> 6;
 
@@ -1893,7 +1901,24 @@ static bool tile_covers(uint32_t src_rows, uint32_t dst_row_len) {
   return dst_row_len <= (src_rows + kTileRows - 1) / kTileRows * kTileRows;
 }
 
-int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a) {
+int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a_in, const float* amax_in, float* gs_out) {
+  nvfp4_ms_eden_args a = a_in;
+  if (amax_in) {
+    // the whole-tile NVFP4 transposers derive the scale from the amax themselves; every other kernel gets it
+    // from a one-thread kernel first
+    const bool nv_kind = a.src_kind == NVFP4_SRC_NVFP4_TRANSPOSED || a.src_kind == NVFP4_SRC_ROWWISE_NVFP4_TRANSPOSED;
+    const bool whole = nv_kind && a.src_scale_layout == NVFP4_SCALES_PACKED && a.rows % kTileRows == 0 &&
+                       a.cols % kNvTileCols == 0 && a.dst_row_len == a.rows &&
+                       (reinterpret_cast<uintptr_t>(a.src_bytes) & 15u) == 0 &&
+                       (reinterpret_cast<uintptr_t>(a.src_scales) & 3u) == 0 && a.rows != 0 && a.cols != 0;
+    if (!whole) {
+      const int rc = launch_ms_eden_scale_from_amax(s, amax_in, gs_out);
+      if (rc) return rc;
+      amax_in = nullptr;
+    }
+    a.global_scale = gs_out;
+    a.host_global_scale_valid = 0;
+  }
   const bool rows_kind = a.src_kind == NVFP4_SRC_F32_ROWS;
   const uint32_t out_rows = rows_kind ? a.rows : a.cols;
   const uint64_t chunks = static_cast<uint64_t>(out_rows) * (a.dst_row_len / 32);
@@ -1917,6 +1942,8 @@ int launch_ms_eden(cudaStream_t s, const nvfp4_ms_eden_args& a) {
     p.t = make_out(a, out_rows);
     p.r = p.t;
     p.col_sum_partials = nullptr;
+    p.amax_in = amax_in;
+    p.gs_out = gs_out;
     const bool nv_whole_tiles = p.src_packed && a.rows % kTileRows == 0 && a.cols % kNvTileCols == 0 &&
                                 a.dst_row_len == a.rows && (reinterpret_cast<uintptr_t>(a.src_bytes) & 15u) == 0 &&
                                 (reinterpret_cast<uintptr_t>(a.src_scales) & 3u) == 0;
