@@ -107,7 +107,6 @@ struct GemmParams {
   uint32_t resident_cpn;  // resident mode: CTAs per column block (0 = contiguous tile ranges instead)
   int mode, epilogue, vec_store, tma_store;
   float weight;
-  uint32_t prefetch_distance;  // k-tiles the producer's L2 prefetches run ahead of its loads (0 = none)
   uint64_t wait_timeout_ns;  // limit of every mbarrier wait
   uint32_t debug_flags;      // bit 0: CTA 0 never loads its first k-tile (exercises the bounded waits)
 };
@@ -172,18 +171,6 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
                : "memory");
-}
-
-// L2 prefetches of operand tiles that a later k-tile will load: the shared-memory ring holds only a few
-// stages, so the bytes it keeps in flight are bounded; fetching ahead into L2 turns the ring's loads into L2
-// hits, whose shorter latency the same ring covers at a higher rate.
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int32_t x, int32_t y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)),
-               "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_prefetch(const void* src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(src)), "r"(bytes) : "memory");
 }
 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int32_t x, int32_t y) {
@@ -548,41 +535,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       uint32_t stage = 0, phase = 0, issued = 0, runs = 0, prev_n = 0xffffffffu;
       bool ok = true;
-      // L2 prefetch cursor: walks the same (work item, k-tile) sequence as the loads, prefetch_distance steps ahead
-      uint32_t pf_w = w_begin, pf_kt = 0, pf_end = 0, pf_m = 0, pf_n = 0;
-      bool pf_valid = false;
-      auto pf_open = [&]() {
-        pf_valid = pf_w < w_end;
-        if (pf_valid) {
-          uint32_t sp;
-          decode(pf_w, pf_m, pf_n, sp);
-          pf_kt = sp * p.k_tiles_per_split;
-          pf_end = min(p.num_k_tiles, pf_kt + p.k_tiles_per_split);
-        }
-      };
-      auto pf_step = [&]() {
-        if (!pf_valid) return;
-        const uint32_t atoms = min(static_cast<uint32_t>(kKAtomsPerStage), p.k_atoms - pf_kt * kKAtomsPerStage);
-        tma_prefetch_2d(&tmap_a, static_cast<int32_t>(pf_kt * kBlockKBytes), static_cast<int32_t>(pf_m * kBlockM));
-        bulk_prefetch(p.sfa + (static_cast<size_t>(pf_m) * p.k_atoms + pf_kt * kKAtomsPerStage) * kSfTileBytes,
-                      atoms * kSfTileBytes);
-        if (!p.b_resident) {
-          tma_prefetch_2d(&tmap_b, static_cast<int32_t>(pf_kt * kBlockKBytes), static_cast<int32_t>(pf_n * kBlockN));
-          const uint32_t fb = pf_n * kBlockN / 128u;
-          const uint32_t nb = min(static_cast<uint32_t>(C::kSfBlocks), p.sfb_blocks128 - fb);
-          for (uint32_t i = 0; i < nb; ++i)
-            bulk_prefetch(p.sfb + (static_cast<size_t>(fb + i) * p.k_atoms + pf_kt * kKAtomsPerStage) * kSfTileBytes,
-                          atoms * kSfTileBytes);
-        }
-        if (++pf_kt == pf_end) {
-          pf_w += w_step;
-          pf_open();
-        }
-      };
-      if (p.prefetch_distance) {
-        pf_open();
-        for (uint32_t i = 0; i < p.prefetch_distance; ++i) pf_step();
-      }
       for (uint32_t w = w_begin; w < w_end && ok; w += w_step) {
         uint32_t m_blk, n_blk, split;
         decode(w, m_blk, n_blk, split);
@@ -643,7 +595,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           bulk_load(smem_sfa + stage * kSfaStageBytes,
                     p.sfa + (static_cast<size_t>(m_blk) * p.k_atoms + kt * kKAtomsPerStage) * kSfTileBytes, sf_bytes,
                     full);
-          if (p.prefetch_distance) pf_step();
           ++issued;
           if (++stage == stages) {
             stage = 0;
@@ -1284,19 +1235,6 @@ int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb,
 std::atomic<int> g_tile_override{-1};       // -1 = read NVFP4_GEMM_TILE once, 0 = automatic, else forced width
 std::atomic<uint64_t> g_wait_timeout_ns{kDefaultWaitTimeoutNs};
 std::atomic<uint32_t> g_debug_flags{0};
-std::atomic<int> g_prefetch_distance{-1};  // -1 = read NVFP4_GEMM_PREFETCH once
-
-uint32_t prefetch_distance() {
-  int v = g_prefetch_distance.load(std::memory_order_relaxed);
-  if (v < 0) {
-    const char* env = std::getenv("NVFP4_GEMM_PREFETCH");
-    v = env ? std::atoi(env) : 0;
-    if (v < 0 || v > 64) v = 0;
-    g_prefetch_distance.store(v, std::memory_order_relaxed);
-  }
-  return static_cast<uint32_t>(v);
-}
-
 int tile_override() {
   int v = g_tile_override.load(std::memory_order_relaxed);
   if (v < 0) {
@@ -1588,7 +1526,6 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   p.resident_cpn = pl.resident_cpn;
   p.vec_store = static_cast<int>(pl.vec_store);
   p.tma_store = static_cast<int>(pl.tma_store);
-  p.prefetch_distance = prefetch_distance();
   p.wait_timeout_ns = g_wait_timeout_ns.load(std::memory_order_relaxed);
   p.debug_flags = g_debug_flags.load(std::memory_order_relaxed);
 
