@@ -386,8 +386,9 @@ int nvfp4_gemm(void* stream, const nvfp4_gemm_args* args /* host */);
  * counterpart: the reference has one tile shape, utils/nvfp4_tma_matmul/kernels.rs:1314).  Lets a caller
  * or a test see which kernel instantiation and schedule a shape takes. */
 typedef struct nvfp4_gemm_plan {
-  uint32_t block_n;       /* tile width: 128, 192 or 256 output columns (tile height is 128 rows)         */
-  uint32_t acc_stages;    /* accumulator buffers in tensor memory: 2 (128, 192) or 1 (256)                 */
+  uint32_t block_m;       /* tile height: 128 rows, or 256 (two MMAs per k-atom sharing the B stage)       */
+  uint32_t block_n;       /* tile width: 128, 192 or 256 output columns (256 x 192 is the only tall shape) */
+  uint32_t acc_stages;    /* accumulator buffers in tensor memory: 2 (128 x 128, 128 x 192) or 1           */
   uint32_t k_splits;      /* > 1: K split over CTAs, partial tiles summed with TMA reduce-add              */
   uint32_t b_resident;    /* 1: the B panel of a column block stays in shared memory (short K)             */
   uint32_t resident_cpn;  /* resident mode: CTAs per column block of the banded schedule, 0 = contiguous   */
@@ -445,10 +446,10 @@ int nvfp4_gemm_tma_nvfp4_rowwise_a_scale_padded_output(
 int nvfp4_set_deterministic_reductions(int on);
 int nvfp4_get_deterministic_reductions(void);
 
-/* Measurement aid (no reference counterpart): forces the tile width of every following GEMM of this process
- * (128, 192 or 256; 0 = automatic choice, the default; the environment variable NVFP4_GEMM_TILE sets the
- * initial value). */
-int nvfp4_gemm_set_tile_override(int block_n);
+/* Measurement aid (no reference counterpart): forces the tile shape of every following GEMM of this process
+ * (128 x 128, 128 x 192, 128 x 256 or 256 x 192; block_n = 0 = automatic choice, the default; the environment
+ * variable NVFP4_GEMM_TILE = "<width>" or "<height>x<width>" sets the initial value). */
+int nvfp4_gemm_set_tile_override(int block_m, int block_n);
 /* Limit of every bounded wait inside the GEMM kernel in nanoseconds (default 2 s; 0 restores it).  A wait
  * that runs out sets a bit of the device status word (nvfp4_read_device_status: 1 producer, 2 MMA /
  * scale-factor warps, 4 epilogue), all roles of that CTA leave their loops, tensor memory is freed and

@@ -68,7 +68,7 @@ class GemmArgs(Structure):
 
 class GemmPlan(Structure):
     """nvfp4_gemm_plan: what the library chooses for one GEMM (tile width, schedule, launch shape)."""
-    _fields_ = [("block_n", c_uint32), ("acc_stages", c_uint32), ("k_splits", c_uint32), ("b_resident", c_uint32),
+    _fields_ = [("block_m", c_uint32), ("block_n", c_uint32), ("acc_stages", c_uint32), ("k_splits", c_uint32), ("b_resident", c_uint32),
                 ("resident_cpn", c_uint32), ("stages", c_uint32), ("grid", c_uint32), ("tma_store", c_uint32),
                 ("smem_bytes", c_uint32)]
 
@@ -167,7 +167,7 @@ _SIGNATURES = {
     "nvfp4_prepare_tma_nvfp4_device_scales": [_P, _P, _P, _P, _P, _U, _U, _U],
     "nvfp4_prepare_tma_nvfp4_device_scales_into": [_P, _P, _P, _P, _P, _U, _U, _U, _P],
     "nvfp4_tensor_map_cache_stats": [POINTER(ctypes.c_uint64), POINTER(ctypes.c_uint64)],
-    "nvfp4_gemm_set_tile_override": [c_int],
+    "nvfp4_gemm_set_tile_override": [c_int, c_int],
     "nvfp4_gemm_set_wait_timeout_ns": [ctypes.c_uint64],
     "nvfp4_gemm_set_debug_flags": [_U],
     "nvfp4_qkv_projection": [_P, POINTER(ProjectionArgs)],
@@ -291,9 +291,10 @@ def deterministic_reductions() -> bool:
     return bool(library().nvfp4_get_deterministic_reductions())
 
 
-def set_gemm_tile_override(block_n: int) -> None:
-    """Measurement aid: force the GEMM tile width (128, 192, 256) of every following launch; 0 = automatic."""
-    _call("nvfp4_gemm_set_tile_override", block_n)
+def set_gemm_tile_override(block_n: int, block_m: int = 128) -> None:
+    """Measurement aid: force the GEMM tile shape of every following launch (128 x {128, 192, 256} or
+    256 x 192); block_n = 0 = automatic."""
+    _call("nvfp4_gemm_set_tile_override", block_m, block_n)
 
 
 def set_gemm_wait_timeout_ns(ns: int) -> None:

@@ -553,10 +553,11 @@ int nvfp4_tensor_map_cache_stats(uint64_t* hits, uint64_t* misses) {
   gemm_map_cache_stats(hits, misses);
   return 0;
 }
-int nvfp4_gemm_set_tile_override(int block_n) {
-  if (block_n != 0 && block_n != 128 && block_n != 192 && block_n != 256)
-    return invalid("gemm_set_tile_override: 0, 128, 192 or 256");
-  gemm_set_tile_override(block_n);
+int nvfp4_gemm_set_tile_override(int block_m, int block_n) {
+  const bool ok = block_n == 0 || (block_m == 128 && (block_n == 128 || block_n == 192 || block_n == 256)) ||
+                  (block_m == 256 && block_n == 192);
+  if (!ok) return invalid("gemm_set_tile_override: 128 x {128, 192, 256}, 256 x 192, or block_n = 0 for automatic");
+  gemm_set_tile_override(block_m, block_n);
   return 0;
 }
 int nvfp4_gemm_set_wait_timeout_ns(uint64_t ns) {

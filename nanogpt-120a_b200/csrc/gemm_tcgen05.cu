@@ -43,13 +43,13 @@ __device__ uint32_t g_device_status = 0;
 
 namespace {
 
-constexpr int kBlockM = 128;
+constexpr int kRowBlock = 128;                    // rows of one MMA, one scale-factor block, one epilogue sub-tile
 constexpr int kBlockKBytes = 128;                 // 256 nibbles = one 128-byte swizzle row
-constexpr int kKAtomsPerStage = 4;                // 64-element k-atoms (one MMA each) per stage
-constexpr int kAStageBytes = kBlockM * kBlockKBytes;
+constexpr int kKAtomsPerStage = 4;                // 64-element k-atoms (one MMA each per row block) per stage
+constexpr int kAHalfBytes = kRowBlock * kBlockKBytes;  // A rows of one MMA in a stage
 constexpr int kSfTileBytes = 512;                 // 128 rows x 4 scale bytes
-constexpr int kSfaStageBytes = kKAtomsPerStage * kSfTileBytes;
-constexpr int kStoreStageBytes = kBlockM * 128;   // one epilogue sub-tile: 128 rows x 128 bytes
+constexpr int kSfBlockStageBytes = kKAtomsPerStage * kSfTileBytes;  // one 128-row scale block of a stage
+constexpr int kStoreStageBytes = kRowBlock * 128;  // one epilogue sub-tile: 128 rows x 128 bytes
 constexpr int kTmemCols = 512;
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 227 * 1024;
@@ -58,21 +58,32 @@ constexpr uint64_t kDefaultWaitTimeoutNs = 2000000000ull;  // 2 s
 
 constexpr uint32_t kStatusProducerTimeout = 1u, kStatusMmaTimeout = 2u, kStatusEpilogueTimeout = 4u;
 
-template <int kBlockN>
+// Tile shapes: 128 x {128, 192, 256} and the tall 256 x 192.  The tall tile issues two MMAs per k-atom (rows
+// 0..127 and 128..255 of the A stage against the same B stage), so a stage's B bytes feed twice the flops:
+// streaming GEMMs are bound by the operand bytes an SM can pull from L2, and the tall tile moves 21 % fewer of
+// them per flop than 128 x 256.  Its two 192-column accumulators and two scale-factor column sets fill tensor
+// memory (2 x 192 + 2 x 56 = 496 of 512 columns), so the accumulator is single buffered.
+template <int kBlockM, int kBlockN>
 struct Cfg {
+  static constexpr int kMHalves = kBlockM / kRowBlock;
+  static_assert(kBlockM == 128 || (kBlockM == 256 && kBlockN == 192), "unsupported tile shape");
+  static constexpr int kAStageBytes = kMHalves * kAHalfBytes;
+  static constexpr int kSfaStageBytes = kMHalves * kSfBlockStageBytes;
   // 128-row scale-factor blocks of B a tile can touch: a 192-column tile starts either on a block
   // boundary or in the middle of a block, and spans two blocks either way
   static constexpr int kSfBlocks = (kBlockN + 127) / 128;
   static constexpr int kBStageBytes = kBlockN * kBlockKBytes;
-  static constexpr int kSfbStageBytes = kSfBlocks * kKAtomsPerStage * kSfTileBytes;
-  static constexpr int kAccStages = kBlockN == 256 ? 1 : 2;
+  static constexpr int kSfbStageBytes = kSfBlocks * kSfBlockStageBytes;
+  static constexpr int kAccStages = (kBlockN == 256 || kMHalves == 2) ? 1 : 2;
+  static constexpr int kAccCols = kMHalves * kBlockN;  // columns of one accumulator buffer (row halves side by side)
   // Scale factors live in a ring of column sets behind the accumulators (one set per k-tile), so
   // the copies for the next k-tile never overwrite columns an MMA in flight reads.
+  static constexpr int kSfaSetCols = kMHalves * 4 * kKAtomsPerStage;
   static constexpr int kSfbColsPerAtom = kBlockN / 32;
-  static constexpr int kSfSetCols = 4 * kKAtomsPerStage + kSfbColsPerAtom * kKAtomsPerStage;
-  static constexpr int kSfSets = kBlockN == 192 ? 3 : 4;
-  static constexpr int kTmemSfa = kAccStages * kBlockN;            // A scale factors of set 0
-  static constexpr int kTmemSfb = kTmemSfa + 4 * kKAtomsPerStage;  // B scale factors of set 0
+  static constexpr int kSfSetCols = kSfaSetCols + kSfbColsPerAtom * kKAtomsPerStage;
+  static constexpr int kSfSets = kMHalves == 2 ? 2 : (kBlockN == 192 ? 3 : 4);
+  static constexpr int kTmemSfa = kAccStages * kAccCols;   // A scale factors of set 0
+  static constexpr int kTmemSfb = kTmemSfa + kSfaSetCols;  // B scale factors of set 0
   static constexpr int kStreamStageBytes = kAStageBytes + kBStageBytes + kSfaStageBytes + kSfbStageBytes;
   static constexpr int kResidentStageBytes = kAStageBytes + kSfaStageBytes;
   static constexpr int kPanelSlotBytes = kBStageBytes + kSfbStageBytes;
@@ -82,7 +93,7 @@ struct Cfg {
   static constexpr int kBiasSlots = (kBlockN + 127) / 128;  // bias values a thread of an epilogue group fetches
   static constexpr int kFixedBytes =
       1024 /*alignment slack*/ + kStoreBufs * kStoreStageBytes + 512 /*barriers*/ +
-      2 * kBiasSlots * 128 * 4 /*bias of the tile, one copy per epilogue group*/;
+      2 * kBlockN * 4 /*bias of the tile, one copy per epilogue group*/;
   static_assert(kTmemSfa + kSfSets * kSfSetCols <= kTmemCols, "tensor memory overflow");
 };
 
@@ -100,7 +111,7 @@ struct GemmParams {
   void* out;
   void* aux;
   uint32_t m, n, k, ldo;
-  uint32_t num_m_blocks, num_n_blocks, k_atoms, sfb_blocks128;
+  uint32_t num_m_blocks, num_n_blocks, k_atoms, sfa_blocks128, sfb_blocks128;
   uint32_t k_splits, k_tiles_per_split, num_k_tiles;
   uint32_t stages;  // depth of the A (and, when streaming, B) ring
   int b_resident;   // the B panel of a column block stays in shared memory (short K)
@@ -308,7 +319,7 @@ __device__ __forceinline__ uint64_t make_ab_desc(uint32_t smem_addr) {
 template <int kBlockN>
 __device__ __forceinline__ constexpr uint32_t make_idesc() {
   return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kBlockN >> 3) << 17) | (0u << 23) |
-         (static_cast<uint32_t>(kBlockM >> 4) << 24);
+         (static_cast<uint32_t>(kRowBlock >> 4) << 24);
 }
 
 // Bias of one output column: an f32 vector, or an NVFP4-encoded one decoded as the reference's post-op
@@ -418,12 +429,15 @@ struct SubTile<__nv_bfloat16> {
 // Streaming mode: one B slot per pipeline stage.  Resident mode (short K): the whole
 // [kBlockN x K] B panel of the current column block stays in shared memory -- one slot per
 // k-tile -- while a CTA walks down the row blocks, so only A tiles stream through the ring.
-template <int kBlockN, typename OutT>
+template <int kBlockM, int kBlockN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
     nvfp4_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                               const __grid_constant__ CUtensorMap tmap_out,
                               const __grid_constant__ CUtensorMap tmap_aux, const GemmParams p) {
-  using C = Cfg<kBlockN>;
+  using C = Cfg<kBlockM, kBlockN>;
+  constexpr int kMHalves = C::kMHalves;
+  constexpr int kAStageBytes = C::kAStageBytes;
+  constexpr int kSfaStageBytes = C::kSfaStageBytes;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -438,7 +452,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t smem_bar = smem_store + C::kStoreBufs * kStoreStageBytes;
   // barrier block: full[8], empty[8], tmem_full[2], tmem_empty[2], b_full, b_empty, sf_full[4], sf_empty[4],
   // tmem base, abort flag
-  const uint32_t smem_bias = smem_bar + 512;  // C::kBiasSlots * 128 floats per epilogue group
+  const uint32_t smem_bias = smem_bar + 512;  // kBlockN floats per epilogue group
   const uint32_t bar_full = smem_bar;
   const uint32_t bar_empty = bar_full + 8 * kMaxStages;
   const uint32_t bar_tmem_full = bar_empty + 8 * kMaxStages;
@@ -555,7 +569,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             tma_load_2d(smem_b + kt * C::kBStageBytes, &tmap_b, bar_b_full, static_cast<int32_t>(kt * kBlockKBytes),
                         static_cast<int32_t>(n_blk * kBlockN));
             for (uint32_t i = 0; i < blks128; ++i)
-              bulk_load(smem_sfb + kt * C::kSfbStageBytes + i * kSfaStageBytes,
+              bulk_load(smem_sfb + kt * C::kSfbStageBytes + i * kSfBlockStageBytes,
                         p.sfb + (static_cast<size_t>(first_blk128 + i) * p.k_atoms + kt * kKAtomsPerStage) * kSfTileBytes,
                         atoms * kSfTileBytes, bar_b_full);
           }
@@ -579,22 +593,25 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             continue;
           }
+          // scale blocks of A inside the matrix (the second row half of a tall tile may lie below it)
+          const uint32_t a_blks = min(static_cast<uint32_t>(kMHalves), p.sfa_blocks128 - m_blk * kMHalves);
           if (p.b_resident) {
-            mbar_expect_tx(full, kAStageBytes + sf_bytes);
+            mbar_expect_tx(full, kAStageBytes + sf_bytes * a_blks);
           } else {
-            mbar_expect_tx(full, kAStageBytes + C::kBStageBytes + sf_bytes * (1u + blks128));
+            mbar_expect_tx(full, kAStageBytes + C::kBStageBytes + sf_bytes * (a_blks + blks128));
             tma_load_2d(smem_b + stage * C::kBStageBytes, &tmap_b, full, static_cast<int32_t>(kt * kBlockKBytes),
                         static_cast<int32_t>(n_blk * kBlockN));
             for (uint32_t i = 0; i < blks128; ++i)
-              bulk_load(smem_sfb + stage * C::kSfbStageBytes + i * kSfaStageBytes,
+              bulk_load(smem_sfb + stage * C::kSfbStageBytes + i * kSfBlockStageBytes,
                         p.sfb + (static_cast<size_t>(first_blk128 + i) * p.k_atoms + kt * kKAtomsPerStage) * kSfTileBytes,
                         sf_bytes, full);
           }
           tma_load_2d(smem_a + stage * kAStageBytes, &tmap_a, full, static_cast<int32_t>(kt * kBlockKBytes),
                       static_cast<int32_t>(m_blk * kBlockM));
-          bulk_load(smem_sfa + stage * kSfaStageBytes,
-                    p.sfa + (static_cast<size_t>(m_blk) * p.k_atoms + kt * kKAtomsPerStage) * kSfTileBytes, sf_bytes,
-                    full);
+          for (uint32_t h = 0; h < a_blks; ++h)
+            bulk_load(smem_sfa + stage * kSfaStageBytes + h * kSfBlockStageBytes,
+                      p.sfa + (static_cast<size_t>(m_blk * kMHalves + h) * p.k_atoms + kt * kKAtomsPerStage) * kSfTileBytes,
+                      sf_bytes, full);
           ++issued;
           if (++stage == stages) {
             stage = 0;
@@ -640,7 +657,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           break;
         }
         tcgen05_fence_after();
-        const uint32_t tmem_acc = tmem_base + acc * kBlockN;
+        const uint32_t tmem_acc = tmem_base + acc * C::kAccCols;
         for (uint32_t kt = kt_begin; kt < kt_end; ++kt) {
           // The scale-factor warps arrive on `sf_full` only after they have seen the stage's `full` barrier
           // complete (operands and scale tiles share it), so this one wait covers both: operands in
@@ -660,10 +677,16 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (elect_one()) {
 #pragma unroll
             for (uint32_t kb = 0; kb < kKAtomsPerStage; ++kb) {
-              // 64 nibbles = 32 bytes further along the swizzled row: +2 in the 16-byte start field
-              if (kb < atoms)
-                tcgen05_mma_nvf4(tmem_acc, desc_a + kb * 2, desc_b + kb * 2, idesc, (kt > kt_begin || kb > 0) ? 1u : 0u,
-                                 tsfa + kb * 4, tsfb + kb * C::kSfbColsPerAtom);
+              // 64 nibbles = 32 bytes further along the swizzled row: +2 in the 16-byte start field; the
+              // second row half of a tall tile sits 16 KB further in the A stage and has its own accumulator
+              // and A scale columns
+              if (kb < atoms) {
+#pragma unroll
+                for (uint32_t h = 0; h < static_cast<uint32_t>(kMHalves); ++h)
+                  tcgen05_mma_nvf4(tmem_acc + h * kBlockN, desc_a + h * (kAHalfBytes >> 4) + kb * 2, desc_b + kb * 2, idesc,
+                                   (kt > kt_begin || kb > 0) ? 1u : 0u, tsfa + h * 4 * kKAtomsPerStage + kb * 4,
+                                   tsfb + kb * C::kSfbColsPerAtom);
+              }
             }
             tcgen05_commit(bar_empty + 8 * stage);       // frees the smem stage once these MMAs retire
             tcgen05_commit(bar_sf_empty + 8 * sf_set);   // ... and the scale-factor column set
@@ -740,19 +763,21 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t tsfa = tmem_base + C::kTmemSfa + sf_set * C::kSfSetCols + ((quad * 32u) << 16);
         const uint32_t tsfb = tmem_base + C::kTmemSfb + sf_set * C::kSfSetCols + ((quad * 32u) << 16);
         // all shared-memory reads first (independent, pipelined), then the tensor-memory stores
-        uint32_t ra[kKAtomsPerStage][4];
+        uint32_t ra[kMHalves][kKAtomsPerStage][4];
         uint32_t rb[kKAtomsPerStage][C::kSfBlocks * 4];
 #pragma unroll
         for (uint32_t kb = 0; kb < kKAtomsPerStage; ++kb) {
           if (kb < atoms) {
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(ra[kb][0]), "=r"(ra[kb][1]), "=r"(ra[kb][2]), "=r"(ra[kb][3])
-                         : "r"(sfa_s + kb * kSfTileBytes));
+#pragma unroll
+            for (int h = 0; h < kMHalves; ++h)
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(ra[h][kb][0]), "=r"(ra[h][kb][1]), "=r"(ra[h][kb][2]), "=r"(ra[h][kb][3])
+                           : "r"(sfa_s + h * kSfBlockStageBytes + kb * kSfTileBytes));
 #pragma unroll
             for (int i = 0; i < C::kSfBlocks; ++i)
               asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                            : "=r"(rb[kb][4 * i]), "=r"(rb[kb][4 * i + 1]), "=r"(rb[kb][4 * i + 2]), "=r"(rb[kb][4 * i + 3])
-                           : "r"(sfb_s + i * kSfaStageBytes + kb * kSfTileBytes));
+                           : "r"(sfb_s + i * kSfBlockStageBytes + kb * kSfTileBytes));
           }
         }
         if constexpr (kBlockN == 192) {
@@ -766,14 +791,16 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int j = 0; j < 6; ++j) sel[kb][j] = odd ? rb[kb][j + 2] : rb[kb][j];
           if (atoms == kKAtomsPerStage) {
-            tcgen05_st_x16(tsfa, &ra[0][0]);
+#pragma unroll
+            for (int h = 0; h < kMHalves; ++h) tcgen05_st_x16(tsfa + h * 4 * kKAtomsPerStage, &ra[h][0][0]);
             tcgen05_st_x16(tsfb, &sel[0][0]);
             tcgen05_st_x8(tsfb + 16, &sel[0][0] + 16);
           } else {
 #pragma unroll
             for (uint32_t kb = 0; kb < kKAtomsPerStage; ++kb) {
               if (kb < atoms) {
-                tcgen05_st_x4(tsfa + kb * 4, ra[kb]);
+#pragma unroll
+                for (int h = 0; h < kMHalves; ++h) tcgen05_st_x4(tsfa + h * 4 * kKAtomsPerStage + kb * 4, ra[h][kb]);
                 tcgen05_st_x4(tsfb + kb * 6, sel[kb]);
                 tcgen05_st_x2(tsfb + kb * 6 + 4, sel[kb] + 4);
               }
@@ -781,14 +808,14 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         } else if (atoms == kKAtomsPerStage) {
           // one 16-column store for the A scales, one 16- or 32-column store for the B scales
-          tcgen05_st_x16(tsfa, &ra[0][0]);
+          tcgen05_st_x16(tsfa, &ra[0][0][0]);
           tcgen05_st_x16(tsfb, &rb[0][0]);
           if constexpr (C::kSfBlocks == 2) tcgen05_st_x16(tsfb + 16, &rb[2][0]);
         } else {
 #pragma unroll
           for (uint32_t kb = 0; kb < kKAtomsPerStage; ++kb) {
             if (kb < atoms) {
-              tcgen05_st_x4(tsfa + kb * 4, ra[kb]);
+              tcgen05_st_x4(tsfa + kb * 4, ra[0][kb]);
 #pragma unroll
               for (int i = 0; i < C::kSfBlocks; ++i) tcgen05_st_x4(tsfb + kb * C::kSfbColsPerAtom + i * 4, &rb[kb][4 * i]);
             }
@@ -821,17 +848,17 @@ __global__ void __launch_bounds__(kThreads, 1)
     OutT* out = static_cast<OutT*>(p.out);
     OutT* aux = static_cast<OutT*>(p.aux);
     uint32_t acc = 0, acc_phase = 0, store_buf = 0, tile_iter = 0;
-    const uint32_t my_bias = smem_bias + eg * C::kBiasSlots * 128 * 4;
+    const uint32_t my_bias = smem_bias + eg * kBlockN * 4;
     const float* my_bias_gen = reinterpret_cast<const float*>(smem_gen + (my_bias - smem_base));
     const uint32_t my_store = smem_store + eg * kRing * kStoreStageBytes;
     const float gb = p.mode == NVFP4_GS_NONE ? 1.0f : __ldg(p.b_global);
     const float ga_scalar = p.mode == NVFP4_GS_TENSOR ? __ldg(p.a_global) : 1.0f;
-    // the row's global scale of a tile is fetched one tile ahead: its load latency would
+    // the rows' global scales of a tile are fetched one tile ahead: their load latency would
     // otherwise sit between the accumulator becoming ready and the first store
-    auto row_scale = [&](uint32_t w) {
+    auto row_scale = [&](uint32_t w, uint32_t h) {
       uint32_t mb, nb, sp;
       decode(w, mb, nb, sp);
-      const uint32_t r = mb * kBlockM + gtid;
+      const uint32_t r = mb * kBlockM + h * kRowBlock + gtid;
       return (p.mode == NVFP4_GS_ROWWISE_A && r < p.m) ? __ldg(p.a_global + r) : 0.0f;
     };
     // The bias slice of a tile travels the same way: its values are fetched into registers one tile ahead
@@ -852,12 +879,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     };
     if (w_begin < w_end) fetch_bias(w_begin);
-    float ga_next = w_begin < w_end ? row_scale(w_begin) : 0.0f;
+    float ga_next[kMHalves];
+#pragma unroll
+    for (int h = 0; h < kMHalves; ++h) ga_next[h] = w_begin < w_end ? row_scale(w_begin, h) : 0.0f;
     for (uint32_t w = w_begin; w < w_end; w += w_step, ++tile_iter) {
       uint32_t m_blk, n_blk, split;
       decode(w, m_blk, n_blk, split);
-      const float ga_row = ga_next;
-      if (w + w_step < w_end) ga_next = row_scale(w + w_step);
+      float ga_row[kMHalves];
+#pragma unroll
+      for (int h = 0; h < kMHalves; ++h) {
+        ga_row[h] = ga_next[h];
+        if (w + w_step < w_end) ga_next[h] = row_scale(w + w_step, h);
+      }
       // the tile's bias slice goes through shared memory once (every row then reads it broadcast); it is
       // fetched before the wait for the accumulator so that its latency hides behind the main loop.  The
       // group's last barrier of the previous tile comes after that tile's last read of the slice.
@@ -865,7 +898,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (add_bias && n_blk != staged_bias_blk) {  // uniform across the group
 #pragma unroll
         for (int j = 0; j < C::kBiasSlots; ++j)
-          asm volatile("st.shared.f32 [%0], %1;" ::"r"(my_bias + (gtid + 128 * j) * 4), "f"(bias_next[j]) : "memory");
+          if (gtid + 128 * j < static_cast<uint32_t>(kBlockN))
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(my_bias + (gtid + 128 * j) * 4), "f"(bias_next[j]) : "memory");
         epilogue_barrier(eg);
         staged_bias_blk = n_blk;
       }
@@ -876,13 +910,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                                       p.wait_timeout_ns)))
         break;
       tcgen05_fence_after();
-      const uint32_t row = m_blk * kBlockM + gtid;
-      const bool row_ok = row < p.m;
-      const float ga = p.mode == NVFP4_GS_ROWWISE_A ? ga_row : ga_scalar;
       // reference order: (weight * a_scale) * b_scale, then acc * scale
-      const float scale = __fmul_rn(__fmul_rn(p.weight, ga), gb);
-      const uint64_t scale2 = pack_f32x2(scale, scale);
-      const uint32_t taddr_row = tmem_base + acc * kBlockN + ((ew * 32u) << 16);
+      float scale_h[kMHalves];
+#pragma unroll
+      for (int h = 0; h < kMHalves; ++h)
+        scale_h[h] = __fmul_rn(__fmul_rn(p.weight, p.mode == NVFP4_GS_ROWWISE_A ? ga_row[h] : ga_scalar), gb);
+      const uint32_t taddr_row = tmem_base + acc * C::kAccCols + ((ew * 32u) << 16);
       // The accumulator buffer goes back to the MMA warp as soon as this warp's last tcgen05.ld of the
       // tile has landed in registers: scaling, staging and the stores of that last sub-tile then run
       // beside the next tile's main loop.
@@ -894,26 +927,58 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (p.tma_store) {
         // Sub-tiles of 128 rows x 128 bytes go through the group's shared-memory ring and leave
         // with TMA stores (TMA reduce-add for split-K partial sums); rows / columns outside the
-        // matrix are clipped by the tensor map.  The groups take alternate sub-tiles; with an odd
-        // number of sub-tiles per tile (192 bf16 columns = 3) the group that takes two alternates
-        // from tile to tile, which the double-buffered accumulator evens out.
+        // matrix are clipped by the tensor map.  The items of a tile -- (row half, column sub-tile) --
+        // alternate between the two groups; with an odd number of items per tile (192 bf16 columns = 3)
+        // the group that takes two alternates from tile to tile, which the double-buffered accumulator
+        // evens out.
         constexpr int kSub = SubTile<OutT>::kCols;
         constexpr int kNumSub = kBlockN / kSub;
-        const int first_sub = static_cast<int>((kNumSub & 1) ? (eg ^ (tile_iter & 1u)) : eg);
-        // a group whose first sub-tile already lies outside the matrix reads nothing
-        if (n_blk * kBlockN + first_sub * kSub >= p.n) release_accumulator();
-        float row_max = -INFINITY;  // largest value this thread stores for its row in this tile
+        constexpr int kItems = kMHalves * kNumSub;
+        const int first_item = static_cast<int>((kItems & 1) ? (eg ^ (tile_iter & 1u)) : eg);
+        auto item_valid = [&](int item) {  // uniform across the group
+          const uint32_t h = static_cast<uint32_t>(item / kNumSub), sub = static_cast<uint32_t>(item % kNumSub);
+          return n_blk * kBlockN + sub * kSub < p.n && m_blk * kBlockM + h * kRowBlock < p.m;
+        };
+        int last_item = -1;
+#pragma unroll
+        for (int item = first_item; item < kItems; item += 2)
+          if (item_valid(item)) last_item = item;
+        if (last_item < 0) release_accumulator();  // nothing of this tile is for this group to read
+        float row_max = -INFINITY;  // largest value this thread stores for its row in the current row half
+        uint32_t max_h = 0;
+        auto flush_row_max = [&]() {
+          const uint32_t r = m_blk * kBlockM + max_h * kRowBlock + gtid;
+          if (p.row_amax && r < p.m && row_max > 0.0f) {
+            // max over the row of relu(stored value)^2: rounding to the stored type and relu^2 are both
+            // monotonic, so they apply to the maximum instead of to every element; the atomic is skipped
+            // when the row's running maximum already is at least as large
+            const float stored = sizeof(OutT) == 2 ? __bfloat162float(__float2bfloat16_rn(row_max)) : row_max;
+            const uint32_t bits = __float_as_uint(__fmul_rn(stored, stored));
+            unsigned int* slot = reinterpret_cast<unsigned int*>(p.row_amax) + r;
+            if (bits > *reinterpret_cast<volatile unsigned int*>(slot)) atomicMax(slot, bits);
+          }
+          row_max = -INFINITY;
+        };
 #pragma unroll 1
-        for (int c = first_sub * kSub; c < kBlockN; c += 2 * kSub) {
+        for (int item = first_item; item < kItems; item += 2) {
+          if (!item_valid(item)) continue;
+          const uint32_t h = static_cast<uint32_t>(item / kNumSub);
+          const int c = (item % kNumSub) * kSub;
           const uint32_t col0 = n_blk * kBlockN + c;
-          if (col0 >= p.n) break;  // uniform across the group
+          const uint32_t row0 = m_blk * kBlockM + h * kRowBlock;
+          if (h != max_h) {
+            flush_row_max();
+            max_h = h;
+          }
+          const float scale = kMHalves == 1 ? scale_h[0] : (h == 0 ? scale_h[0] : scale_h[kMHalves - 1]);
+          const uint64_t scale2 = pack_f32x2(scale, scale);
           float v[kSub];
           {
             uint32_t r[kSub / 32][32];
 #pragma unroll
-            for (int h = 0; h < kSub / 32; ++h) tcgen05_ld_32x32b_x32(taddr_row + c + 32 * h, r[h]);
+            for (int q = 0; q < kSub / 32; ++q) tcgen05_ld_32x32b_x32(taddr_row + h * kBlockN + c + 32 * q, r[q]);
             tcgen05_wait_ld();
-            if (c + 2 * kSub >= kBlockN || col0 + 2 * kSub >= p.n) release_accumulator();  // the group's last sub-tile
+            if (item == last_item) release_accumulator();  // the group's last read of this tile
             if (add_bias) {
               // acc * scale + bias in one rounding (the reference rounds the product first; the
               // difference is below the f32 ulp and far inside the GEMM tolerance)
@@ -962,65 +1027,66 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (elected) {
               const CUtensorMap* map = is_pre ? &tmap_aux : &tmap_out;
               if (p.k_splits > 1)
-                tma_reduce_add_2d(map, buf, static_cast<int32_t>(col0), static_cast<int32_t>(m_blk * kBlockM));
+                tma_reduce_add_2d(map, buf, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
               else
-                tma_store_2d(map, buf, static_cast<int32_t>(col0), static_cast<int32_t>(m_blk * kBlockM));
+                tma_store_2d(map, buf, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
               bulk_commit_group();
             }
             store_buf = (store_buf + 1) % kRing;
           }
         }
-        if (p.row_amax && row_ok && row_max > 0.0f) {
-          // max over the row of relu(stored value)^2: rounding to the stored type and relu^2 are both
-          // monotonic, so they apply to the maximum instead of to every element
-          const float stored = sizeof(OutT) == 2 ? __bfloat162float(__float2bfloat16_rn(row_max)) : row_max;
-          atomicMax(reinterpret_cast<unsigned int*>(p.row_amax) + row, __float_as_uint(__fmul_rn(stored, stored)));
-        }
+        flush_row_max();
       } else {
 #pragma unroll 1
-      for (int c = eg * 32; c < kBlockN; c += 64) {
-        uint32_t r[32];
-        tcgen05_ld_32x32b_x32(taddr_row + c, r);
-        tcgen05_wait_ld();
-        if (c + 64 >= kBlockN) release_accumulator();
-        const uint32_t col0 = n_blk * kBlockN + c;
-        if (row_ok && col0 < p.n) {
-          const uint32_t valid = min(32u, p.n - col0);
-          float v[32];
+        for (uint32_t h = 0; h < static_cast<uint32_t>(kMHalves); ++h) {
+          const uint32_t row = m_blk * kBlockM + h * kRowBlock + gtid;
+          const bool row_ok = row < p.m;
+          const float scale = kMHalves == 1 ? scale_h[0] : (h == 0 ? scale_h[0] : scale_h[kMHalves - 1]);
+#pragma unroll 1
+          for (int c = eg * 32; c < kBlockN; c += 64) {
+            uint32_t r[32];
+            tcgen05_ld_32x32b_x32(taddr_row + h * kBlockN + c, r);
+            tcgen05_wait_ld();
+            if (h + 1 == static_cast<uint32_t>(kMHalves) && c + 64 >= kBlockN) release_accumulator();
+            const uint32_t col0 = n_blk * kBlockN + c;
+            if (row_ok && col0 < p.n) {
+              const uint32_t valid = min(32u, p.n - col0);
+              float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(__uint_as_float(r[i]), scale);
-          const size_t off = static_cast<size_t>(row) * p.ldo + col0;
-          if (p.k_splits > 1) {
-            // split-K partial sums: f32 reduction into a zero-initialised output; bias joins once
+              for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(__uint_as_float(r[i]), scale);
+              const size_t off = static_cast<size_t>(row) * p.ldo + col0;
+              if (p.k_splits > 1) {
+                // split-K partial sums: f32 reduction into a zero-initialised output; bias joins once
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (static_cast<uint32_t>(i) < valid) {
-                float t = v[i];
-                if (p.epilogue == NVFP4_EPI_BIAS && split == 0) t = __fadd_rn(t, bias_value(p, col0 + i));
-                atomicAdd(reinterpret_cast<float*>(p.out) + off + i, t);
+                for (int i = 0; i < 32; ++i)
+                  if (static_cast<uint32_t>(i) < valid) {
+                    float t = v[i];
+                    if (p.epilogue == NVFP4_EPI_BIAS && split == 0) t = __fadd_rn(t, bias_value(p, col0 + i));
+                    atomicAdd(reinterpret_cast<float*>(p.out) + off + i, t);
+                  }
+              } else {
+                if (p.epilogue != NVFP4_EPI_NONE) {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i)
+                    if (static_cast<uint32_t>(i) < valid) v[i] = __fadd_rn(v[i], bias_value(p, col0 + i));
+                }
+                if (p.epilogue == NVFP4_EPI_RELU2) {
+                  if (aux) store_row32<OutT>(aux + off, v, valid, p.vec_store != 0);
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) {
+                    const float t = fmaxf(v[i], 0.0f);
+                    v[i] = __fmul_rn(t, t);
+                  }
+                } else if (p.epilogue == NVFP4_EPI_RESIDUAL) {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i)
+                    if (static_cast<uint32_t>(i) < valid) v[i] = __fmaf_rn(1.0f, v[i], load_out<OutT>(out + off + i));
+                }
+                store_row32<OutT>(out + off, v, valid, p.vec_store != 0);
               }
-          } else {
-            if (p.epilogue != NVFP4_EPI_NONE) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (static_cast<uint32_t>(i) < valid) v[i] = __fadd_rn(v[i], bias_value(p, col0 + i));
             }
-            if (p.epilogue == NVFP4_EPI_RELU2) {
-              if (aux) store_row32<OutT>(aux + off, v, valid, p.vec_store != 0);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const float t = fmaxf(v[i], 0.0f);
-                v[i] = __fmul_rn(t, t);
-              }
-            } else if (p.epilogue == NVFP4_EPI_RESIDUAL) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (static_cast<uint32_t>(i) < valid) v[i] = __fmaf_rn(1.0f, v[i], load_out<OutT>(out + off + i));
-            }
-            store_row32<OutT>(out + off, v, valid, p.vec_store != 0);
           }
         }
-      }
       }  // direct-store path
       if (++acc == C::kAccStages) {
         acc = 0;
@@ -1137,7 +1203,7 @@ int encode_output_map(CUtensorMap* map, void* base, int dtype, uint32_t rows, ui
   const size_t esz = dtype == NVFP4_DTYPE_F32 ? 4 : 2;
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * esz};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / esz), kBlockM};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / esz), kRowBlock};
   const cuuint32_t elem_strides[2] = {1, 1};
   CUresult r = fn(map, dtype == NVFP4_DTYPE_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                   base, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1184,24 +1250,26 @@ struct GemmTiming {
 
 // Everything the host decides about one launch.
 struct GemmPlan {
-  uint32_t block_n = 128, num_n_blocks = 0, k_splits = 1, k_tiles_per_split = 0;
+  uint32_t block_m = 128, block_n = 128, num_n_blocks = 0, k_splits = 1, k_tiles_per_split = 0;
   uint32_t stages = 0, grid = 0, b_resident = 0, resident_cpn = 0, tma_store = 0, vec_store = 0;
   size_t smem_bytes = 0;
 };
 
 struct TileBytes {
-  int fixed, stream_stage, resident_stage, panel_slot;
+  int fixed, stream_stage, resident_stage, panel_slot, a_stage;
 };
-template <int kBlockN>
+template <int kBlockM, int kBlockN>
 constexpr TileBytes tile_bytes_of() {
-  return {Cfg<kBlockN>::kFixedBytes, Cfg<kBlockN>::kStreamStageBytes, Cfg<kBlockN>::kResidentStageBytes,
-          Cfg<kBlockN>::kPanelSlotBytes};
+  using C = Cfg<kBlockM, kBlockN>;
+  return {C::kFixedBytes, C::kStreamStageBytes, C::kResidentStageBytes, C::kPanelSlotBytes,
+          C::kAStageBytes + C::kSfaStageBytes};
 }
-TileBytes tile_bytes(uint32_t block_n) {
-  return block_n == 256 ? tile_bytes_of<256>() : block_n == 192 ? tile_bytes_of<192>() : tile_bytes_of<128>();
+TileBytes tile_bytes(uint32_t block_m, uint32_t block_n) {
+  if (block_m == 256) return tile_bytes_of<256, 192>();
+  return block_n == 256 ? tile_bytes_of<128, 256>() : block_n == 192 ? tile_bytes_of<128, 192>() : tile_bytes_of<128, 128>();
 }
 
-template <int kBlockN, typename OutT>
+template <int kBlockM, int kBlockN, typename OutT>
 int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
                    const CUtensorMap& mx, const GemmParams& p, const GemmPlan& pl) {
   // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel
@@ -1210,7 +1278,7 @@ int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb,
   if (dev < 0) return static_cast<int>(cudaErrorInvalidDevice);
   int st = attr_state[dev].load(std::memory_order_acquire);
   if (st == 0) {
-    const cudaError_t e = cudaFuncSetAttribute(nvfp4_gemm_tcgen05_kernel<kBlockN, OutT>,
+    const cudaError_t e = cudaFuncSetAttribute(nvfp4_gemm_tcgen05_kernel<kBlockM, kBlockN, OutT>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     st = e == cudaSuccess ? 1 : -static_cast<int>(e);
     attr_state[dev].store(st, std::memory_order_release);
@@ -1225,22 +1293,37 @@ int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb,
     rec->flops = 2.0 * p.m * p.n * p.k;
     cudaEventRecord(rec->start, s);
   }
-  nvfp4_gemm_tcgen05_kernel<kBlockN, OutT><<<pl.grid, kThreads, pl.smem_bytes, s>>>(ma, mb, mo, mx, p);
+  nvfp4_gemm_tcgen05_kernel<kBlockM, kBlockN, OutT><<<pl.grid, kThreads, pl.smem_bytes, s>>>(ma, mb, mo, mx, p);
   count_launch();
   const int rc = static_cast<int>(cudaGetLastError());
   if (rec) cudaEventRecord(rec->stop, s);
   return rc;
 }
 
-std::atomic<int> g_tile_override{-1};       // -1 = read NVFP4_GEMM_TILE once, 0 = automatic, else forced width
+std::atomic<int> g_tile_override{-1};  // -1 = read NVFP4_GEMM_TILE once, 0 = automatic, else (block_m << 16) | block_n
+std::atomic<bool> g_allow_tall{true};  // the automatic choice may take the 256 x 192 tile
 std::atomic<uint64_t> g_wait_timeout_ns{kDefaultWaitTimeoutNs};
 std::atomic<uint32_t> g_debug_flags{0};
+bool tile_shape_ok(int bm, int bn) {
+  return (bm == 128 && (bn == 128 || bn == 192 || bn == 256)) || (bm == 256 && bn == 192);
+}
+
 int tile_override() {
   int v = g_tile_override.load(std::memory_order_relaxed);
   if (v < 0) {
+    // NVFP4_GEMM_TILE = "<width>" (128-row tile) or "<height>x<width>"
     const char* env = std::getenv("NVFP4_GEMM_TILE");
-    v = env ? std::atoi(env) : 0;
-    if (v != 128 && v != 192 && v != 256) v = 0;
+    int bm = 128, bn = 0;
+    if (env) {
+      const char* x = std::strchr(env, 'x');
+      if (x) {
+        bm = std::atoi(env);
+        bn = std::atoi(x + 1);
+      } else {
+        bn = std::atoi(env);
+      }
+    }
+    v = tile_shape_ok(bm, bn) ? ((bm << 16) | bn) : 0;
     g_tile_override.store(v, std::memory_order_relaxed);
   }
   return v;
@@ -1271,29 +1354,32 @@ int validate_gemm(const nvfp4_gemm_args& a) {
 void plan_gemm(const nvfp4_gemm_args& a, int sms, GemmPlan& pl) {
   const uint32_t k_atoms = a.k / 64;
   const uint32_t num_k_tiles = (k_atoms + kKAtomsPerStage - 1) / kKAtomsPerStage;
-  const uint32_t num_m_blocks = (a.m + kBlockM - 1) / kBlockM;
+  const uint32_t m_blocks128 = (a.m + kRowBlock - 1) / kRowBlock;
   const uint32_t usms = static_cast<uint32_t>(sms);
-  // Tile width.  A block-scaled FP4 tcgen05.mma occupies the tensor pipe for about as long at N = 128 as
+  // Tile shape.  A block-scaled FP4 tcgen05.mma occupies the tensor pipe for about as long at N = 128 as
   // at N = 256 (the 128-column form is bound by shared-memory operand reads), so wide tiles do more work
   // per instruction and are preferred whenever the shape can still fill the SMs:
   //  * long K: enough wide tiles, or (f32 output, linear epilogue) enough tiles x K splits;
   //  * short K with many row blocks: wide tile with its whole B panel resident in shared memory.
-  // 192 columns keep a double-buffered accumulator (the drain of one tile hides behind the next main
-  // loop); 256 columns have one buffer; 128 columns remain for everything else.
+  // 128 x 192 keeps a double-buffered accumulator (the drain of one tile hides behind the next main loop);
+  // 128 x 256 has one buffer; the tall 256 x 192 tile moves the fewest operand bytes per flop and is for
+  // streamed long-K GEMMs; 128 x 128 remains for everything else.
   const bool can_split = a.out_dtype == NVFP4_DTYPE_F32 &&
                          (a.epilogue == NVFP4_EPI_NONE || a.epilogue == NVFP4_EPI_BIAS) && num_k_tiles >= 16;
-  // Work items, waves and an estimated duration (SM cycles) of a candidate width.  The constants are fits
-  // to B200 measurements of the training step's shapes: a streamed k-tile costs what its operand bytes take
-  // through the SM's L2 port (128: 700, 192: 980, 256: 1150 cycles), a tile adds the part of its epilogue
-  // that the next main loop does not hide (one accumulator buffer: all of the drain).
+  // Work items, waves and an estimated duration (SM cycles) of a candidate shape.  The constants are fits to
+  // B200 measurements of the training step's shapes: a streamed k-tile costs what its operand bytes take
+  // through the SM's L2 port (about 47 bytes per cycle: 128 x 128 700, 128 x 192 980, 128 x 256 1150,
+  // 256 x 192 1360 cycles), a tile adds the part of its epilogue that the next main loop does not hide (one
+  // accumulator buffer: all of the drain).
   struct Candidate {
     uint32_t splits;
     uint64_t cost;
   };
-  auto evaluate = [&](uint32_t bn) {
-    const uint32_t tiles = num_m_blocks * ((a.n + bn - 1) / bn);
-    const uint64_t ck = bn == 256 ? 1150 : bn == 192 ? 980 : 700;
-    const uint64_t ce = bn == 256 ? 3500 : bn == 192 ? 2000 : 1500;
+  auto tiles_of = [&](uint32_t bm, uint32_t bn) { return ((a.m + bm - 1) / bm) * ((a.n + bn - 1) / bn); };
+  auto evaluate = [&](uint32_t bm, uint32_t bn) {
+    const uint32_t tiles = tiles_of(bm, bn);
+    const uint64_t ck = bm == 256 ? 1360 : bn == 256 ? 1150 : bn == 192 ? 980 : 700;
+    const uint64_t ce = bm == 256 ? 5000 : bn == 256 ? 3500 : bn == 192 ? 2000 : 1500;
     Candidate best{1, ~0ull};
     uint32_t max_splits = 1;
     if (can_split && tiles < 2 * usms) {
@@ -1311,39 +1397,49 @@ void plan_gemm(const nvfp4_gemm_args& a, int sms, GemmPlan& pl) {
     }
     return best;
   };
-  uint32_t block_n = 128;
+  uint32_t block_m = 128, block_n = 128;
   const int forced = tile_override();
   if (forced) {
-    block_n = static_cast<uint32_t>(forced);
+    block_m = static_cast<uint32_t>(forced) >> 16;
+    block_n = static_cast<uint32_t>(forced) & 0xffffu;
   } else {
-    const uint32_t tiles192 = num_m_blocks * ((a.n + 191) / 192);
-    const uint32_t tiles256 = num_m_blocks * ((a.n + 255) / 256);
+    const uint32_t tiles192 = tiles_of(128, 192), tiles256 = tiles_of(128, 256), tiles_tall = tiles_of(256, 192);
     // columns of the last 192-wide block that lie outside the matrix, as a share of all columns computed
     const uint32_t cols192 = (a.n + 191) / 192 * 192;
-    const bool fits192 = (cols192 - a.n) * 16u <= cols192;  // at most 1/16 wasted
-    const bool ok192 = fits192 && a.n >= 192 && (tiles192 >= usms || can_split);
+    const bool fits192 = (cols192 - a.n) * 16u <= cols192 && a.n >= 192;  // at most 1/16 wasted
+    const bool ok192 = fits192 && (tiles192 >= usms || can_split);
     const bool wide_shape = a.n % 256 == 0 || a.n > 1024;
     const bool ok256 = wide_shape && ((num_k_tiles >= 4 && (tiles256 >= usms || can_split)) ||
                                       (a.n % 256 == 0 && num_k_tiles <= 3 && tiles256 >= 4u * usms));
+    // the tall tile: streamed long-K GEMMs only (its A stages leave no room for a resident panel, and short-K
+    // GEMMs are bound by writing their output)
+    const bool ok_tall = fits192 && num_k_tiles >= 6 && (tiles_tall >= usms || can_split);
     if (ok192 && ok256) {
       // short K (resident B panel, bound by writing the output): the wider tile; otherwise the cheaper estimate
       if (num_k_tiles <= 3)
         block_n = a.n % 256 == 0 ? 256 : 192;
       else
-        block_n = evaluate(192).cost < evaluate(256).cost ? 192 : 256;
+        block_n = evaluate(128, 192).cost < evaluate(128, 256).cost ? 192 : 256;
     } else if (ok256) {
       block_n = 256;
     } else if (ok192) {
       block_n = 192;
     }
+    if (ok_tall && g_allow_tall.load(std::memory_order_relaxed) && evaluate(256, 192).cost < evaluate(128, block_n).cost) {
+      block_m = 256;
+      block_n = 192;
+    }
   }
+  pl.block_m = block_m;
   pl.block_n = block_n;
   pl.num_n_blocks = (a.n + block_n - 1) / block_n;
+  const uint32_t num_m_blocks = (a.m + block_m - 1) / block_m;
+  (void)m_blocks128;
   const uint32_t tiles = num_m_blocks * pl.num_n_blocks;
 
   // split-K for long GEMMs with few tiles (dW = dY^T.X): f32 output, linear epilogue only; the split count is
   // the one that minimises waves x (main loop + exposed epilogue) of one work item
-  pl.k_splits = evaluate(block_n).splits;
+  pl.k_splits = evaluate(block_m, block_n).splits;
   pl.k_tiles_per_split = (num_k_tiles + pl.k_splits - 1) / pl.k_splits;
   pl.k_splits = (num_k_tiles + pl.k_tiles_per_split - 1) / pl.k_tiles_per_split;
 
@@ -1362,8 +1458,8 @@ void plan_gemm(const nvfp4_gemm_args& a, int sms, GemmPlan& pl) {
   // Short K and many row blocks: keep the B panel resident and stream only A (halves the
   // operand traffic per tile; these shapes are otherwise bound by L2 -> SM bandwidth).
   const bool want_resident =
-      pl.k_splits == 1 && num_k_tiles <= (block_n == 256 ? 3u : 4u) && tiles >= 4 * pl.grid;
-  const TileBytes tb = tile_bytes(block_n);
+      block_m == 128 && pl.k_splits == 1 && num_k_tiles <= (block_n == 256 ? 3u : 4u) && tiles >= 4 * pl.grid;
+  const TileBytes tb = tile_bytes(block_m, block_n);
   const int budget = kSmemBudget - tb.fixed;
   pl.b_resident = 0;
   pl.resident_cpn = 0;
@@ -1383,8 +1479,7 @@ void plan_gemm(const nvfp4_gemm_args& a, int sms, GemmPlan& pl) {
     pl.stages = static_cast<uint32_t>(st > kMaxStages ? kMaxStages : st);
   }
   const uint32_t b_slots = pl.b_resident ? num_k_tiles : pl.stages;
-  pl.smem_bytes = tb.fixed + static_cast<size_t>(pl.stages) * (kAStageBytes + kSfaStageBytes) +
-                  static_cast<size_t>(b_slots) * tb.panel_slot;
+  pl.smem_bytes = tb.fixed + static_cast<size_t>(pl.stages) * tb.a_stage + static_cast<size_t>(b_slots) * tb.panel_slot;
 }
 
 }  // namespace
@@ -1449,8 +1544,9 @@ int gemm_plan_query(const nvfp4_gemm_args& a, nvfp4_gemm_plan* out) {
   plan_gemm(a, sm_count(), pl);
   // the kernel falls back to direct stores when the output map cannot be encoded; that cannot happen for
   // outputs that pass the alignment test above, so the plan reports the test's verdict
+  out->block_m = pl.block_m;
   out->block_n = pl.block_n;
-  out->acc_stages = pl.block_n == 256 ? 1 : 2;
+  out->acc_stages = (pl.block_n == 256 || pl.block_m == 256) ? 1 : 2;
   out->k_splits = pl.k_splits;
   out->b_resident = pl.b_resident;
   out->resident_cpn = pl.resident_cpn;
@@ -1461,8 +1557,8 @@ int gemm_plan_query(const nvfp4_gemm_args& a, nvfp4_gemm_plan* out) {
   return 0;
 }
 
-void gemm_set_tile_override(int block_n) {
-  g_tile_override.store((block_n == 128 || block_n == 192 || block_n == 256) ? block_n : 0, std::memory_order_relaxed);
+void gemm_set_tile_override(int block_m, int block_n) {
+  g_tile_override.store(tile_shape_ok(block_m, block_n) ? ((block_m << 16) | block_n) : 0, std::memory_order_relaxed);
 }
 void gemm_set_wait_timeout_ns(uint64_t ns) { g_wait_timeout_ns.store(ns ? ns : kDefaultWaitTimeoutNs, std::memory_order_relaxed); }
 void gemm_set_debug_flags(uint32_t flags) { g_debug_flags.store(flags, std::memory_order_relaxed); }
@@ -1477,8 +1573,10 @@ int gemm_prepare_operand_maps(const uint8_t* a_bytes, const uint8_t* b_bytes, ui
     return static_cast<int>(cudaErrorInvalidValue);
   }
   CUtensorMap tmp;
-  int rc = encode_operand_map(&tmp, a_bytes, m, k, kBlockM);
-  // B is read with a box as tall as the tile the launch will choose: encode all three
+  // operands are read with boxes as tall as the tile the launch will choose: encode every candidate
+  int rc = 0;
+  for (uint32_t box : {128u, 256u})
+    if (!rc) rc = encode_operand_map(&tmp, a_bytes, m, k, box);
   for (uint32_t box : {128u, 192u, 256u})
     if (!rc) rc = encode_operand_map(&tmp, b_bytes, n, k, box);
   return rc;
@@ -1516,8 +1614,9 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   p.weight = a.weight_global_scale;
   p.k_atoms = a.k / 64;
   p.num_k_tiles = (p.k_atoms + kKAtomsPerStage - 1) / kKAtomsPerStage;
-  p.num_m_blocks = (a.m + kBlockM - 1) / kBlockM;
+  p.num_m_blocks = (a.m + pl.block_m - 1) / pl.block_m;
   p.num_n_blocks = pl.num_n_blocks;
+  p.sfa_blocks128 = (a.m + 127) / 128;
   p.sfb_blocks128 = (a.n + 127) / 128;
   p.k_splits = pl.k_splits;
   p.k_tiles_per_split = pl.k_tiles_per_split;
@@ -1530,7 +1629,7 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   p.debug_flags = g_debug_flags.load(std::memory_order_relaxed);
 
   CUtensorMap ma, mb, mo, mx;
-  rc = encode_operand_map(&ma, a.a_bytes, a.m, a.k, kBlockM);
+  rc = encode_operand_map(&ma, a.a_bytes, a.m, a.k, pl.block_m);
   if (rc) return rc;
   rc = encode_operand_map(&mb, a.b_bytes, a.n, a.k, pl.block_n);
   if (rc) return rc;
@@ -1556,16 +1655,19 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   }
 
   const bool f32 = a.out_dtype == NVFP4_DTYPE_F32;
+  if (pl.block_m == 256)
+    return f32 ? launch_variant<256, 192, float>(s, ma, mb, mo, mx, p, pl)
+               : launch_variant<256, 192, __nv_bfloat16>(s, ma, mb, mo, mx, p, pl);
   switch (pl.block_n) {
     case 256:
-      return f32 ? launch_variant<256, float>(s, ma, mb, mo, mx, p, pl)
-                 : launch_variant<256, __nv_bfloat16>(s, ma, mb, mo, mx, p, pl);
+      return f32 ? launch_variant<128, 256, float>(s, ma, mb, mo, mx, p, pl)
+                 : launch_variant<128, 256, __nv_bfloat16>(s, ma, mb, mo, mx, p, pl);
     case 192:
-      return f32 ? launch_variant<192, float>(s, ma, mb, mo, mx, p, pl)
-                 : launch_variant<192, __nv_bfloat16>(s, ma, mb, mo, mx, p, pl);
+      return f32 ? launch_variant<128, 192, float>(s, ma, mb, mo, mx, p, pl)
+                 : launch_variant<128, 192, __nv_bfloat16>(s, ma, mb, mo, mx, p, pl);
     default:
-      return f32 ? launch_variant<128, float>(s, ma, mb, mo, mx, p, pl)
-                 : launch_variant<128, __nv_bfloat16>(s, ma, mb, mo, mx, p, pl);
+      return f32 ? launch_variant<128, 128, float>(s, ma, mb, mo, mx, p, pl)
+                 : launch_variant<128, 128, __nv_bfloat16>(s, ma, mb, mo, mx, p, pl);
   }
 }
 

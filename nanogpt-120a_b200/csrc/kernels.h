@@ -68,9 +68,9 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a);
 int gemm_plan_query(const nvfp4_gemm_args& a, nvfp4_gemm_plan* out);
 // Encodes (and keeps in the calling thread's cache) the operand tensor maps of a GEMM ahead of its launch.
 int gemm_prepare_operand_maps(const uint8_t* a_bytes, const uint8_t* b_bytes, uint32_t m, uint32_t k, uint32_t n);
-// Measurement / test aids: forced tile width (0 = automatic), limit of the kernel's bounded waits,
+// Measurement / test aids: forced tile shape (block_n 0 = automatic), limit of the kernel's bounded waits,
 // debug flags (bit 0: CTA 0 of every GEMM never loads its first k-tile), tensor-map cache counters.
-void gemm_set_tile_override(int block_n);
+void gemm_set_tile_override(int block_m, int block_n);
 void gemm_set_wait_timeout_ns(uint64_t ns);
 void gemm_set_debug_flags(uint32_t flags);
 void gemm_map_cache_stats(uint64_t* hits, uint64_t* misses);

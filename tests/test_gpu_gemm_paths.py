@@ -91,8 +91,8 @@ def no_timeouts(pkg):
 @pytest.fixture
 def tile(pkg):
     """Force a tile width for one test and restore the automatic choice afterwards."""
-    def force(n):
-        pkg.set_gemm_tile_override(n)
+    def force(n, m=128):
+        pkg.set_gemm_tile_override(n, m)
     yield force
     pkg.set_gemm_tile_override(0)
 
@@ -151,33 +151,33 @@ def test_resident_contiguous_vocab(pkg, oracle, dev, tile, width, epi):
 
 def test_training_step_shapes_take_tested_paths(pkg, dev):
     """What the automatic choice picks for every GEMM of the GPT-2-small training step at 65536 tokens on a
-    148-SM part: (tile width, K splits > 1, resident).  Each combination is covered by a parity test of this
+    148-SM part: (tile height, tile width, K splits > 1, resident).  Each combination is covered by a parity test of this
     file with the same width, output type and schedule; a change of the heuristics shows up here first."""
     if torch.cuda.get_device_properties(dev).multi_processor_count != 148:
         pytest.skip("the expectations are for a 148-SM part")
     gemm = pkg.Nvfp4GemmModule()
     T, d, h, v = 65536, 768, 3072, 32000
     bf, f32 = torch.bfloat16, torch.float32
-    want = {  # name: (m, n, k, out dtype, epilogue) -> (block_n, split, resident)
-        "fwd c_attn": ((T, 3 * d, d, bf, 1), (256, False, 1)), "fwd c_proj": ((T, d, d, bf, 1), (256, False, 1)),
-        "fwd fc": ((T, h, d, bf, 1), (256, False, 1)), "fwd proj": ((T, d, h, bf, 1), (256, False, 0)),
-        "fwd lm_head": ((T, v, d, bf, 0), (256, False, 1)), "dX c_attn": ((T, d, 3 * d, bf, 0), (192, False, 0)),
-        "dX c_proj": ((T, d, d, bf, 0), (256, False, 1)), "dX fc": ((T, d, h, bf, 0), (256, False, 0)),
-        "dX proj": ((T, h, d, bf, 0), (256, False, 1)), "dX lm_head": ((T, d, v, bf, 0), (256, False, 0)),
-        "dW c_attn": ((3 * d, d, T, f32, 0), (256, True, 0)), "dW c_proj": ((d, d, T, f32, 0), (256, True, 0)),
-        "dW fc": ((h, d, T, f32, 0), (256, True, 0)), "dW proj": ((d, h, T, f32, 0), (256, True, 0)),
-        "dW lm_head": ((v, d, T, f32, 0), (192, False, 0)),
+    want = {  # name: (m, n, k, out dtype, epilogue) -> (block_m, block_n, split, resident)
+        "fwd c_attn": ((T, 3 * d, d, bf, 1), (128, 256, False, 1)), "fwd c_proj": ((T, d, d, bf, 1), (128, 256, False, 1)),
+        "fwd fc": ((T, h, d, bf, 1), (128, 256, False, 1)), "fwd proj": ((T, d, h, bf, 1), (256, 192, False, 0)),
+        "fwd lm_head": ((T, v, d, bf, 0), (128, 256, False, 1)), "dX c_attn": ((T, d, 3 * d, bf, 0), (256, 192, False, 0)),
+        "dX c_proj": ((T, d, d, bf, 0), (128, 256, False, 1)), "dX fc": ((T, d, h, bf, 0), (256, 192, False, 0)),
+        "dX proj": ((T, h, d, bf, 0), (128, 256, False, 1)), "dX lm_head": ((T, d, v, bf, 0), (256, 192, False, 0)),
+        "dW c_attn": ((3 * d, d, T, f32, 0), (256, 192, True, 0)), "dW c_proj": ((d, d, T, f32, 0), (256, 192, True, 0)),
+        "dW fc": ((h, d, T, f32, 0), (256, 192, True, 0)), "dW proj": ((d, h, T, f32, 0), (256, 192, True, 0)),
+        "dW lm_head": ((v, d, T, f32, 0), (256, 192, False, 0)),
     }
     one = torch.ones(1, device=dev)
-    for name, ((m, n, k, dt, epi), (block_n, split, resident)) in want.items():
+    for name, ((m, n, k, dt, epi), (block_m, block_n, split, resident)) in want.items():
         # the plan depends on shapes, types and alignment only: tiny placeholder buffers stand in for the operands
         stub = torch.zeros(16, dtype=torch.uint8, device=dev)
         A = pkg.Nvfp4Tensor(stub, stub, one, m, k, packed=True, rowwise=True)
         B = pkg.Nvfp4Tensor(stub, stub, one, n, k, packed=True, rowwise=False)
         out = torch.empty(16, dtype=dt, device=dev)
         plan = gemm.plan(A, B, out=out, epilogue=epi, bias=one if epi else None)
-        got = (plan.block_n, plan.k_splits > 1, plan.b_resident)
-        assert got == (block_n, split, resident), (name, got)
+        got = (plan.block_m, plan.block_n, plan.k_splits > 1, plan.b_resident)
+        assert got == (block_m, block_n, split, resident), (name, got)
 
 
 # ------------------------------------------------------------------------------------------ streaming (long K)
@@ -192,22 +192,37 @@ def test_streaming_wide(pkg, oracle, dev, n, k, block_n, resident, out_dtype):
              want_plan=dict(block_n=block_n, b_resident=resident))
 
 
-@pytest.mark.parametrize("width", [128, 192, 256])
+SHAPES = [(128, 128), (128, 192), (128, 256), (256, 192)]  # (tile height, tile width)
+
+
+@pytest.mark.parametrize("height,width", SHAPES)
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("epi", [0, 1, 2])
-def test_every_width_with_tails(pkg, oracle, dev, tile, width, out_dtype, epi):
-    """Each tile width forced on one shape whose M, N and K are all ragged: 1000 columns (a last block of 104 /
-    40 / 232 columns, odd and even 192-column blocks), 10000 rows, K = 448 = a full k-tile and a 3-atom one."""
-    tile(width)
-    run_case(pkg, oracle, dev, 10000, 1000, 448, out_dtype=out_dtype, epi=epi, want_plan=dict(block_n=width))
+def test_every_tile_shape_with_tails(pkg, oracle, dev, tile, height, width, out_dtype, epi):
+    """Each tile shape forced on one GEMM whose M, N and K are all ragged: 1000 columns (a last block of 104 /
+    40 / 232 columns, odd and even 192-column blocks), 10000 rows (the last 256-row block holds 16 rows: its
+    second half lies below the matrix), K = 448 = a full k-tile and a 3-atom one."""
+    tile(width, height)
+    run_case(pkg, oracle, dev, 10000, 1000, 448, out_dtype=out_dtype, epi=epi,
+             want_plan=dict(block_m=height, block_n=width))
 
 
-@pytest.mark.parametrize("width", [128, 192, 256])
-def test_every_width_streaming_odd_k(pkg, oracle, dev, tile, width):
-    """Streaming schedule with a k-tile tail (K = 1216 = 19 atoms) for every width, f32 output."""
-    tile(width)
-    run_case(pkg, oracle, dev, 2000, 600, 1216, out_dtype=torch.float32, epi=1,
-             want_plan=dict(block_n=width, b_resident=0))
+@pytest.mark.parametrize("height,width", SHAPES)
+def test_every_tile_shape_streaming_odd_k(pkg, oracle, dev, tile, height, width):
+    """Streaming schedule with a k-tile tail (K = 1216 = 19 atoms) for every shape, f32 output; 2200 rows end in
+    the second half of a 256-row block."""
+    tile(width, height)
+    run_case(pkg, oracle, dev, 2200, 600, 1216, out_dtype=torch.float32, epi=1,
+             want_plan=dict(block_m=height, block_n=width, b_resident=0))
+
+
+@pytest.mark.parametrize("n,k", [(768, 2304), (768, 3072), (3072, 768 * 2)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_tall_tile_streaming_auto(pkg, oracle, dev, n, k, out_dtype):
+    """dX-shaped GEMMs with enough rows: the automatic choice is the 256 x 192 tile (two MMAs per k-atom over one
+    B stage, single-buffered accumulators, two scale-factor column sets)."""
+    run_case(pkg, oracle, dev, 19072 + 128, n, k, out_dtype=out_dtype, epi=0,
+             want_plan=dict(block_m=256, block_n=192, b_resident=0, acc_stages=1))
 
 
 # ------------------------------------------------------------------------------------------ split-K (dW)
@@ -222,12 +237,12 @@ def test_split_k_dw_shapes(pkg, oracle, dev, m, n, k):
     assert plan.k_splits >= 2 or plan.grid >= 96, (plan.k_splits, plan.grid)
 
 
-@pytest.mark.parametrize("width", [192, 256])
-def test_lm_head_dw_unsplit_wide_f32(pkg, oracle, dev, tile, width):
-    """LM-head dW: enough tiles to fill the SMs without a split -- the unsplit wide f32 instantiation."""
-    tile(width)
+@pytest.mark.parametrize("height,width", [(128, 192), (128, 256), (256, 192)])
+def test_lm_head_dw_unsplit_wide_f32(pkg, oracle, dev, tile, height, width):
+    """LM-head dW: enough tiles to fill the SMs without a split -- the unsplit wide f32 instantiations."""
+    tile(width, height)
     run_case(pkg, oracle, dev, 32000, 768, 4096, out_dtype=torch.float32, epi=0,
-             want_plan=dict(block_n=width, k_splits=1, b_resident=0))
+             want_plan=dict(block_m=height, block_n=width, k_splits=1, b_resident=0))
 
 
 # ------------------------------------------------------------------------------------------ huge output
@@ -240,13 +255,13 @@ def test_output_larger_than_4gb(pkg, oracle, dev):
 
 # ------------------------------------------------------------------------------------------ NVFP4 bias, row amax
 
-@pytest.mark.parametrize("width", [128, 192, 256])
+@pytest.mark.parametrize("height,width", SHAPES)
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-def test_nvfp4_bias_and_relu2_row_amax(pkg, oracle, dev, tile, width, out_dtype):
+def test_nvfp4_bias_and_relu2_row_amax(pkg, oracle, dev, tile, height, width, out_dtype):
     """An NVFP4-encoded bias decoded in the epilogue equals the f32 bias of its decoded values, and the
     epilogue's by-product row amax of relu(stored)^2 equals the one computed from the stored tensor, bit for
     bit; the ReLU^2-on-load quantizer fed with it produces the bytes of quantizing relu(stored)^2."""
-    tile(width)
+    tile(width, height)
     q, gemm = pkg.Nvfp4QuantModule(), pkg.Nvfp4GemmModule()
     m, n, k = 1500, 832, 256
     rng = np.random.default_rng(width)
@@ -527,8 +542,8 @@ def test_bounded_wait_runs_out_and_kernel_returns(pkg, oracle, dev):
     pkg.set_gemm_wait_timeout_ns(5_000_000)
     pkg.set_gemm_debug_flags(1)
     try:
-        for width in (128, 192, 256):
-            pkg.set_gemm_tile_override(width)
+        for height, width in SHAPES:
+            pkg.set_gemm_tile_override(width, height)
             gemm.gemm(A, B)
             torch.cuda.synchronize()  # returns: nothing is left spinning
             status = pkg.read_device_status()
@@ -538,8 +553,8 @@ def test_bounded_wait_runs_out_and_kernel_returns(pkg, oracle, dev):
         pkg.set_gemm_debug_flags(0)
         pkg.set_gemm_wait_timeout_ns(0)
         pkg.set_gemm_tile_override(0)
-    for width in (128, 192, 256):
-        pkg.set_gemm_tile_override(width)
+    for height, width in SHAPES:
+        pkg.set_gemm_tile_override(width, height)
         out = gemm.gemm(A, B)
         assert rel_fro(cpu(out), oracle.gemm(a, b, m, k, n, 2)) <= GEMM_TOL
     pkg.set_gemm_tile_override(0)
