@@ -79,7 +79,7 @@ def build_step_library(force: bool = False) -> str:
     deps = [src, build()] + [os.path.join(include, f) for f in ("nvfp4_b200.h", "nvfp4_b200.hpp", "nvfp4_b200_step.h",
                                                                 "nvfp4_b200_step.hpp")]
     if force or _stale(STEP_LIB, deps):
-        subprocess.check_call([_nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-I", include, src, "-o",
+        subprocess.check_call([_nvcc(), *ARCH, "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-I", include, src, "-o",
                                STEP_LIB, "-L", HERE, "-lnvfp4_b200", "-ldl", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"])
     return STEP_LIB
 
@@ -95,7 +95,7 @@ def build_cpp_driver(force: bool = False) -> str:
     deps = [src, os.path.join(include, "nvfp4_b200.hpp"), os.path.join(include, "nvfp4_b200.h"), build()]
     if force or _stale(exe, deps):
         os.makedirs(out_dir, exist_ok=True)
-        subprocess.check_call([_nvcc(), "-O2", "-std=c++17", "-I", include, src, "-o", exe, "-L", HERE,
+        subprocess.check_call([_nvcc(), *ARCH, "-O2", "-std=c++17", "-I", include, src, "-o", exe, "-L", HERE,
                                "-lnvfp4_b200", "-Xlinker", "-rpath", "-Xlinker", HERE])
     return exe
 

@@ -1403,7 +1403,7 @@ void plan_gemm(const nvfp4_gemm_args& a, int sms, GemmPlan& pl) {
     block_m = static_cast<uint32_t>(forced) >> 16;
     block_n = static_cast<uint32_t>(forced) & 0xffffu;
   } else {
-    const uint32_t tiles192 = tiles_of(128, 192), tiles256 = tiles_of(128, 256), tiles_tall = tiles_of(256, 192);
+    const uint32_t tiles192 = tiles_of(128, 192), tiles256 = tiles_of(128, 256);
     // columns of the last 192-wide block that lie outside the matrix, as a share of all columns computed
     const uint32_t cols192 = (a.n + 191) / 192 * 192;
     const bool fits192 = (cols192 - a.n) * 16u <= cols192 && a.n >= 192;  // at most 1/16 wasted
@@ -1412,8 +1412,9 @@ void plan_gemm(const nvfp4_gemm_args& a, int sms, GemmPlan& pl) {
     const bool ok256 = wide_shape && ((num_k_tiles >= 4 && (tiles256 >= usms || can_split)) ||
                                       (a.n % 256 == 0 && num_k_tiles <= 3 && tiles256 >= 4u * usms));
     // the tall tile: streamed long-K GEMMs only (its A stages leave no room for a resident panel, and short-K
-    // GEMMs are bound by writing their output)
-    const bool ok_tall = fits192 && num_k_tiles >= 6 && (tiles_tall >= usms || can_split);
+    // GEMMs are bound by writing their output); the wave count in the estimate decides against it when its
+    // tiles are too few
+    const bool ok_tall = fits192 && num_k_tiles >= 6;
     if (ok192 && ok256) {
       // short K (resident B panel, bound by writing the output): the wider tile; otherwise the cheaper estimate
       if (num_k_tiles <= 3)
