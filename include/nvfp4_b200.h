@@ -648,6 +648,41 @@ int nvfp4_tc_matmul_ms_eden(void* stream, const float* a, const float* b_t, floa
                             uint32_t sign_seed, uint32_t scale_seed);
 
 
+/* ---- NVFP4 checkpoint container ----------------------------------------------------------------------------
+ * src/checkpoint/format/writer.rs:15-38 (CheckpointWriter::write_header / write_tensor / finish),
+ * src/checkpoint/format/reader.rs:22-67 (CheckpointReader::read_header / read_tensor), constants
+ * src/checkpoint/format.rs:7-8.  Little-endian: magic "GPT2_NVFP4_CHECKPOINT\n", u32 version (2), u32 tensor
+ * count; per tensor u32 name_len, u64 len, u64 byte_len, u64 scale_len, f32 global_scale, name, bytes, scales.
+ * Scale bytes in a checkpoint are in the logical row-major layout.  Files are byte-identical to the reference's
+ * for the same tensors.  The *_device forms copy each member through pinned host memory and synchronize the
+ * stream, as src/checkpoint/save/tensor.rs:14-20 and load/tensor.rs:17-23 do; reading for the device also applies
+ * the length checks of load/tensor.rs:27-39 (bytes = len / 2, scales = len / 16). */
+typedef struct nvfp4_checkpoint_tensor_info {
+  char name[256];        /* NUL-terminated copy of the tensor's name                          */
+  uint64_t len;          /* elements                                                           */
+  uint64_t byte_len;     /* nibble bytes stored                                                */
+  uint64_t scale_len;    /* scale bytes stored                                                 */
+  float global_scale;
+} nvfp4_checkpoint_tensor_info;
+int nvfp4_checkpoint_writer_open(const char* path, uint32_t tensor_count, void** writer_out);
+int nvfp4_checkpoint_write_tensor(void* writer, const char* name, uint64_t len, float global_scale,
+                                  const uint8_t* bytes /* host */, uint64_t byte_len, const uint8_t* scales /* host */,
+                                  uint64_t scale_len);
+int nvfp4_checkpoint_write_tensor_device(void* writer, void* stream, const char* name, uint64_t len,
+                                         const float* global_scale /* device f32[1] */, const uint8_t* bytes /* device */,
+                                         uint64_t byte_len, const uint8_t* scales /* device */, uint64_t scale_len);
+/* Flushes and closes; an error if fewer tensors were written than the header declares. */
+int nvfp4_checkpoint_writer_close(void* writer);
+int nvfp4_checkpoint_reader_open(const char* path, void** reader_out, uint32_t* tensor_count_out);
+/* Reads the next tensor's header and name; its payload must then be taken with one of the two calls below. */
+int nvfp4_checkpoint_next_tensor(void* reader, nvfp4_checkpoint_tensor_info* info);
+int nvfp4_checkpoint_read_payload(void* reader, uint8_t* bytes /* host */, uint64_t byte_capacity,
+                                  uint8_t* scales /* host */, uint64_t scale_capacity);
+int nvfp4_checkpoint_read_payload_device(void* reader, void* stream, uint8_t* bytes /* device */,
+                                         uint8_t* scales /* device */, float* global_scale /* device f32[1] */);
+int nvfp4_checkpoint_reader_close(void* reader);
+
+
 #ifdef __cplusplus
 }
 #endif

@@ -114,6 +114,12 @@ class LinearBackwardArgs(Structure):
     ]
 
 
+class CheckpointTensorInfo(Structure):
+    """`nvfp4_checkpoint_tensor_info`."""
+    _fields_ = [("name", ctypes.c_char * 256), ("len", ctypes.c_uint64), ("byte_len", ctypes.c_uint64),
+                ("scale_len", ctypes.c_uint64), ("global_scale", c_float)]
+
+
 _P, _U, _F = c_void_p, c_uint32, c_float
 # name -> argument ctypes (all return int unless listed in _SPECIAL_RESTYPE)
 _SIGNATURES = {
@@ -195,6 +201,16 @@ _SIGNATURES = {
     "nvfp4_linear_bias_grad_bf16": [_P, _P, _P, _U, _U],
     "nvfp4_linear_backward_ms_eden": [_P, POINTER(LinearBackwardArgs)],
     "nvfp4_linear_backward_prepare_weight_t": [_P, POINTER(LinearBackwardArgs)],
+    "nvfp4_checkpoint_writer_open": [c_char_p, _U, POINTER(c_void_p)],
+    "nvfp4_checkpoint_write_tensor": [_P, c_char_p, ctypes.c_uint64, _F, _P, ctypes.c_uint64, _P, ctypes.c_uint64],
+    "nvfp4_checkpoint_write_tensor_device": [_P, _P, c_char_p, ctypes.c_uint64, _P, _P, ctypes.c_uint64, _P,
+                                             ctypes.c_uint64],
+    "nvfp4_checkpoint_writer_close": [_P],
+    "nvfp4_checkpoint_reader_open": [c_char_p, POINTER(c_void_p), POINTER(c_uint32)],
+    "nvfp4_checkpoint_next_tensor": [_P, POINTER(CheckpointTensorInfo)],
+    "nvfp4_checkpoint_read_payload": [_P, _P, ctypes.c_uint64, _P, ctypes.c_uint64],
+    "nvfp4_checkpoint_read_payload_device": [_P, _P, _P, _P, _P],
+    "nvfp4_checkpoint_reader_close": [_P],
 }
 _SPECIAL = {
     "nvfp4_abi_version": (c_int, []),
@@ -1107,6 +1123,86 @@ class LinearBackwardModule:
 # Convenience: one projection, forward, the way the model graph calls it
 # (crates/gpt2-nvfp4/src/types/l3_mlp/forward.rs:15-67).
 # =============================================================================================
+
+class CheckpointWriter:
+    """`CheckpointWriter` (src/checkpoint/format/writer.rs:11-38): header on construction, one `write_tensor` per
+    NVFP4 triple, `finish` to flush.  Tensors may be host (`bytes`-like / CPU tensors) or device tensors."""
+
+    def __init__(self, path: str, tensor_count: int):
+        self._h = c_void_p()
+        _call("nvfp4_checkpoint_writer_open", os.fsencode(path), tensor_count, ctypes.byref(self._h))
+
+    def write_tensor(self, name: str, length: int, global_scale, fp4_bytes, scales) -> None:
+        """Arguments in the reference's order: name, len (elements), global_scale, bytes, scales."""
+        if isinstance(fp4_bytes, torch.Tensor) and fp4_bytes.is_cuda:
+            gs = global_scale if isinstance(global_scale, torch.Tensor) else torch.tensor(
+                [global_scale], dtype=torch.float32, device=fp4_bytes.device)
+            _call("nvfp4_checkpoint_write_tensor_device", self._h, _stream(), name.encode(), length, _ptr(gs),
+                  _ptr(fp4_bytes), fp4_bytes.numel(), _ptr(scales), scales.numel())
+            return
+        b, sc = _host_bytes(fp4_bytes), _host_bytes(scales)
+        gs = float(global_scale.item() if isinstance(global_scale, torch.Tensor) else global_scale)
+        _call("nvfp4_checkpoint_write_tensor", self._h, name.encode(), length, gs, b, len(b), sc, len(sc))
+
+    def finish(self) -> None:
+        h, self._h = self._h, c_void_p()
+        if h:
+            _call("nvfp4_checkpoint_writer_close", h)
+
+
+class CheckpointTensor:
+    """`CheckpointTensor` (src/checkpoint/format/reader.rs:10-16)."""
+
+    def __init__(self, name, len, global_scale, bytes, scales):
+        self.name, self.len, self.global_scale, self.bytes, self.scales = name, len, global_scale, bytes, scales
+
+
+class CheckpointReader:
+    """`CheckpointReader` (src/checkpoint/format/reader.rs:18-67): `read_header()` returns the tensor count,
+    `read_tensor()` the next triple on the host, `read_tensor_device(device)` uploads it with the length checks
+    of src/checkpoint/load/tensor.rs:27-39."""
+
+    def __init__(self, path: str):
+        self._h = c_void_p()
+        count = c_uint32()
+        _call("nvfp4_checkpoint_reader_open", os.fsencode(path), ctypes.byref(self._h), ctypes.byref(count))
+        self._count = count.value
+
+    def read_header(self) -> int:
+        return self._count
+
+    def _next(self) -> CheckpointTensorInfo:
+        info = CheckpointTensorInfo()
+        _call("nvfp4_checkpoint_next_tensor", self._h, ctypes.byref(info))
+        return info
+
+    def read_tensor(self) -> CheckpointTensor:
+        info = self._next()
+        b = ctypes.create_string_buffer(max(1, info.byte_len))
+        sc = ctypes.create_string_buffer(max(1, info.scale_len))
+        _call("nvfp4_checkpoint_read_payload", self._h, b, info.byte_len, sc, info.scale_len)
+        return CheckpointTensor(info.name.decode(), info.len, info.global_scale, b.raw[:info.byte_len],
+                                sc.raw[:info.scale_len])
+
+    def read_tensor_device(self, device) -> CheckpointTensor:
+        info = self._next()
+        b = torch.empty(max(1, info.byte_len), dtype=torch.uint8, device=device)[:info.byte_len]
+        sc = torch.empty(max(1, info.scale_len), dtype=torch.uint8, device=device)[:info.scale_len]
+        gs = torch.empty(1, dtype=torch.float32, device=device)
+        _call("nvfp4_checkpoint_read_payload_device", self._h, _stream(), _ptr(b), _ptr(sc), _ptr(gs))
+        return CheckpointTensor(info.name.decode(), info.len, gs, b, sc)
+
+    def close(self) -> None:
+        h, self._h = self._h, c_void_p()
+        if h:
+            _call("nvfp4_checkpoint_reader_close", h)
+
+
+def _host_bytes(x) -> bytes:
+    if isinstance(x, torch.Tensor):
+        return x.detach().cpu().contiguous().numpy().tobytes()
+    return x if isinstance(x, bytes) else memoryview(x).tobytes()
+
 
 def projection_forward(x: torch.Tensor, weight: Nvfp4Tensor, bias: Optional[torch.Tensor] = None,
                        epilogue: Optional[int] = None, out_dtype: torch.dtype = torch.bfloat16,

@@ -26,6 +26,7 @@ UNITS = [
     ("gemm_tcgen05.cu", []),
     ("api.cu", []),
     ("tensor_amax_static.cu", []),
+    ("checkpoint.cu", []),
 ]
 
 

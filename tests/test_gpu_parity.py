@@ -890,3 +890,38 @@ def test_split_k_deterministic_switch(pkg, oracle, dev):
     want = oracle.gemm(a, b, m, k, n, 2)
     assert rel_fro(first, want) <= GEMM_TOL and rel_fro(fast, want) <= GEMM_TOL
     assert_no_timeouts(pkg)
+
+
+@pytest.mark.gpu
+def test_checkpoint_device_round_trip(pkg, oracle, dev, tmp_path):
+    """A quantized weight and its bias leave the device through the checkpoint writer and come back through the
+    reader byte for byte; the file equals the CPU restatement of the reference's container, and a tensor whose
+    member lengths break bytes = len / 2, scales = len / 16 is refused on upload."""
+    from oracle import checkpoint as oracle_ckpt
+    q = pkg.Nvfp4QuantModule()
+    w = torch.randn(384, 256, device=dev)
+    t = q.quantize_four_six(w, packed=False)
+    b = q.quantize_four_six(torch.randn(1, 384, device=dev), packed=False)
+    path = str(tmp_path / "w.ckpt")
+    wr = pkg.CheckpointWriter(path, 2)
+    wr.write_tensor("blocks.0.attn_qkv.weight", 384 * 256, t.global_scales, t.bytes, t.scales)
+    wr.write_tensor("blocks.0.attn_qkv.bias", 384, b.global_scales, b.bytes, b.scales)
+    wr.finish()
+    want = oracle_ckpt.write_checkpoint([
+        ("blocks.0.attn_qkv.weight", 384 * 256, float(t.global_scales.item()), cpu(t.bytes).tobytes(), cpu(t.scales).tobytes()),
+        ("blocks.0.attn_qkv.bias", 384, float(b.global_scales.item()), cpu(b.bytes).tobytes(), cpu(b.scales).tobytes())])
+    assert open(path, "rb").read() == want
+    r = pkg.CheckpointReader(path)
+    assert r.read_header() == 2
+    for src, name in ((t, "blocks.0.attn_qkv.weight"), (b, "blocks.0.attn_qkv.bias")):
+        got = r.read_tensor_device(dev)
+        assert got.name == name
+        assert torch.equal(got.bytes, src.bytes.view(-1)) and torch.equal(got.scales, src.scales.view(-1))
+        assert torch.equal(got.global_scale, src.global_scales.view(-1)[:1])
+    r.close()
+    bad = str(tmp_path / "bad.ckpt")
+    open(bad, "wb").write(oracle_ckpt.write_checkpoint([("w", 64, 1.0, bytes(31), bytes(4))]))
+    r = pkg.CheckpointReader(bad)
+    with pytest.raises(pkg.Nvfp4Error, match="len / 2"):
+        r.read_tensor_device(dev)
+    r.close()
