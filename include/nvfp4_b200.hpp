@@ -536,6 +536,62 @@ class LinearBackwardModule {
   }
 };
 
+// ---- checkpoint container (src/checkpoint/format/{writer,reader}.rs of the reference) -------------------
+// CheckpointWriter::{write_header (the constructor's `open`), write_tensor, finish} and
+// CheckpointReader::{read_header, read_tensor}; tensors live on the device as in save/tensor.rs and
+// load/tensor.rs.  Scale bytes in a checkpoint are row-major (NVFP4_SCALES_LOGICAL).
+class CheckpointWriter {
+ public:
+  CheckpointWriter() = default;
+  CheckpointWriter(const CheckpointWriter&) = delete;
+  CheckpointWriter& operator=(const CheckpointWriter&) = delete;
+  ~CheckpointWriter() {
+    if (handle_) nvfp4_checkpoint_writer_close(handle_);
+  }
+  DriverError write_header(const std::string& path, uint32_t tensor_count) {
+    return detail::from_rc(nvfp4_checkpoint_writer_open(path.c_str(), tensor_count, &handle_));
+  }
+  DriverError write_tensor(Stream s, const std::string& name, const Nvfp4TensorView& t) {
+    if (t.rowwise || t.scale_layout != NVFP4_SCALES_LOGICAL)
+      return detail::invalid("checkpoint tensors carry one global scale and row-major scale bytes");
+    return detail::from_rc(nvfp4_checkpoint_write_tensor_device(handle_, s, name.c_str(),
+                                                                static_cast<uint64_t>(t.rows) * t.cols, t.global_scales.ptr,
+                                                                t.bytes.ptr, t.bytes.len, t.scales.ptr, t.scales.len));
+  }
+  DriverError finish() {
+    void* h = handle_;
+    handle_ = nullptr;
+    return detail::from_rc(nvfp4_checkpoint_writer_close(h));
+  }
+
+ private:
+  void* handle_ = nullptr;
+};
+
+class CheckpointReader {
+ public:
+  CheckpointReader() = default;
+  CheckpointReader(const CheckpointReader&) = delete;
+  CheckpointReader& operator=(const CheckpointReader&) = delete;
+  ~CheckpointReader() {
+    if (handle_) nvfp4_checkpoint_reader_close(handle_);
+  }
+  DriverError read_header(const std::string& path, uint32_t* tensor_count) {
+    return detail::from_rc(nvfp4_checkpoint_reader_open(path.c_str(), &handle_, tensor_count));
+  }
+  // header and name of the next tensor; the caller sizes its device buffers from `info`
+  DriverError next_tensor(nvfp4_checkpoint_tensor_info* info) {
+    return detail::from_rc(nvfp4_checkpoint_next_tensor(handle_, info));
+  }
+  // payload of that tensor into device buffers (bytes.len >= info.byte_len, scales.len >= info.scale_len)
+  DriverError read_tensor(Stream s, DeviceBuffer<uint8_t> bytes, DeviceBuffer<uint8_t> scales, DeviceBuffer<float> global_scale) {
+    return detail::from_rc(nvfp4_checkpoint_read_payload_device(handle_, s, bytes.ptr, scales.ptr, global_scale.ptr));
+  }
+
+ private:
+  void* handle_ = nullptr;
+};
+
 // Caps split-K at two splits so that dW is bit-identical from run to run (process-wide; off by default).
 inline void set_deterministic_reductions(bool on) { nvfp4_set_deterministic_reductions(on ? 1 : 0); }
 inline bool deterministic_reductions() { return nvfp4_get_deterministic_reductions() != 0; }
