@@ -120,7 +120,25 @@ struct GemmParams {
   float weight;
   uint64_t wait_timeout_ns;  // limit of every mbarrier wait
   uint32_t debug_flags;      // bit 0: CTA 0 never loads its first k-tile (exercises the bounded waits)
+#ifdef NVFP4_GEMM_TRACE
+  unsigned long long* trace;  // measurement builds only: [5 roles][1024] (clock << 8 | tag) records of CTA 0
+#endif
 };
+
+// Measurement builds (-DNVFP4_GEMM_TRACE) record a time line of CTA 0: one (SM clock, tag) word per event and
+// role (0 producer, 1 MMA issuer, 2 first scale-factor warp, 3 / 4 epilogue groups).  Product builds compile
+// the macro away.
+#ifdef NVFP4_GEMM_TRACE
+#define GEMM_TRACE(role, tag, leader)                                                                      \
+  do {                                                                                                     \
+    if (p.trace && blockIdx.x == 0 && (leader)) {                                                          \
+      const uint32_t trace_i = trace_n++;                                                                  \
+      if (trace_i < 1024u) p.trace[(role) * 1024u + trace_i] = (static_cast<unsigned long long>(clock64()) << 8) | (tag); \
+    }                                                                                                      \
+  } while (0)
+#else
+#define GEMM_TRACE(role, tag, leader) do { } while (0)
+#endif
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
 
@@ -467,6 +485,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   volatile uint32_t* abort_flag = tmem_base_ptr + 1;
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef NVFP4_GEMM_TRACE
+  uint32_t trace_n = 0;
+#endif
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_a)) : "memory");
@@ -581,6 +602,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             ok = false;
             break;
           }
+          GEMM_TRACE(0, 1, true);
           const uint32_t atoms = min(static_cast<uint32_t>(kKAtomsPerStage), p.k_atoms - kt * kKAtomsPerStage);
           const uint32_t sf_bytes = atoms * kSfTileBytes;
           const uint32_t full = bar_full + 8 * stage;
@@ -612,6 +634,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             bulk_load(smem_sfa + stage * kSfaStageBytes + h * kSfBlockStageBytes,
                       p.sfa + (static_cast<size_t>(m_blk * kMHalves + h) * p.k_atoms + kt * kKAtomsPerStage) * kSfTileBytes,
                       sf_bytes, full);
+          GEMM_TRACE(0, 2, true);
           ++issued;
           if (++stage == stages) {
             stage = 0;
@@ -652,10 +675,12 @@ __global__ void __launch_bounds__(kThreads, 1)
           prev_n = n_blk;
           ++runs;
         }
+        GEMM_TRACE(1, 10, lane == 0);
         if (!__all_sync(0xffffffffu, mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kStatusMmaTimeout, p.wait_timeout_ns))) {
           ok = false;
           break;
         }
+        GEMM_TRACE(1, 11, lane == 0);
         tcgen05_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * C::kAccCols;
         for (uint32_t kt = kt_begin; kt < kt_end; ++kt) {
@@ -667,6 +692,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             ok = false;
             break;
           }
+          GEMM_TRACE(1, 12, lane == 0);
           tcgen05_fence_after();
           const uint32_t atoms = min(static_cast<uint32_t>(kKAtomsPerStage), p.k_atoms - kt * kKAtomsPerStage);
           const uint32_t b_slot = p.b_resident ? kt : stage;
@@ -692,6 +718,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             tcgen05_commit(bar_sf_empty + 8 * sf_set);   // ... and the scale-factor column set
           }
           __syncwarp();
+          GEMM_TRACE(1, 13, lane == 0);
           if (++sf_set == C::kSfSets) {
             sf_set = 0;
             sf_phase ^= 1u;
@@ -716,6 +743,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (release_panel) tcgen05_commit(bar_b_empty);
         }
         __syncwarp();
+        GEMM_TRACE(1, 14, lane == 0);
         if (++acc == C::kAccStages) {
           acc = 0;
           acc_phase ^= 1u;
@@ -755,6 +783,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           ok = false;
           break;
         }
+        GEMM_TRACE(2, 20, warp == 8 && lane == 0);
         tcgen05_fence_after();
         const uint32_t atoms = min(static_cast<uint32_t>(kKAtomsPerStage), p.k_atoms - kt * kKAtomsPerStage);
         const uint32_t b_slot = p.b_resident ? kt : stage;
@@ -828,6 +857,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           mbar_arrive(bar_sf_full + 8 * sf_set);  // scale factors visible to the MMA issuer
           mbar_arrive(bar_empty + 8 * stage);     // this warp no longer reads the smem stage
         }
+        GEMM_TRACE(2, 21, warp == 8 && lane == 0);
         if (++sf_set == C::kSfSets) {
           sf_set = 0;
           sf_phase ^= 1u;
@@ -906,9 +936,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (w + w_step < w_end) fetch_bias(w + w_step);
       // go on only if every thread of the group saw the accumulator arrive (no thread may be left in a
       // later barrier of the group when another one gives up)
+      GEMM_TRACE(3 + eg, 30, elected);
       if (!epilogue_all(eg, mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, kStatusEpilogueTimeout,
                                       p.wait_timeout_ns)))
         break;
+      GEMM_TRACE(3 + eg, 31, elected);
       tcgen05_fence_after();
       // reference order: (weight * a_scale) * b_scale, then acc * scale
       float scale_h[kMHalves];
@@ -978,6 +1010,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int q = 0; q < kSub / 32; ++q) tcgen05_ld_32x32b_x32(taddr_row + h * kBlockN + c + 32 * q, r[q]);
             tcgen05_wait_ld();
+            GEMM_TRACE(3 + eg, 32, elected);
             if (item == last_item) release_accumulator();  // the group's last read of this tile
             if (add_bias) {
               // acc * scale + bias in one rounding (the reference rounds the product first; the
@@ -1019,11 +1052,14 @@ __global__ void __launch_bounds__(kThreads, 1)
               if (elected) bulk_wait_group_read<0>();
               epilogue_barrier(eg);
             }
+            GEMM_TRACE(3 + eg, 36, elected);
             SubTile<OutT>::stage(buf + gtid * 128, gtid, v);
             fence_proxy_async_smem();
+            GEMM_TRACE(3 + eg, 33, elected);
             // deeper rings: the buffer written next was last used kRing - 1 stores ago
             if (kRing > 1 && elected) bulk_wait_group_read<(kRing > 1 ? kRing - 2 : 0)>();
             epilogue_barrier(eg);
+            GEMM_TRACE(3 + eg, 34, elected);
             if (elected) {
               const CUtensorMap* map = is_pre ? &tmap_aux : &tmap_out;
               if (p.k_splits > 1)
@@ -1032,6 +1068,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 tma_store_2d(map, buf, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
               bulk_commit_group();
             }
+            GEMM_TRACE(3 + eg, 35, elected);
             store_buf = (store_buf + 1) % kRing;
           }
         }
@@ -1304,6 +1341,9 @@ std::atomic<int> g_tile_override{-1};  // -1 = read NVFP4_GEMM_TILE once, 0 = au
 std::atomic<bool> g_allow_tall{true};  // the automatic choice may take the 256 x 192 tile
 std::atomic<uint64_t> g_wait_timeout_ns{kDefaultWaitTimeoutNs};
 std::atomic<uint32_t> g_debug_flags{0};
+#ifdef NVFP4_GEMM_TRACE
+std::atomic<unsigned long long*> g_trace_buffer{nullptr};
+#endif
 bool tile_shape_ok(int bm, int bn) {
   return (bm == 128 && (bn == 128 || bn == 192 || bn == 256)) || (bm == 256 && bn == 192);
 }
@@ -1492,6 +1532,12 @@ static std::atomic<int> g_deterministic_splits{0};
 void gemm_set_deterministic(int on) { g_deterministic_splits.store(on ? 1 : 0, std::memory_order_relaxed); }
 int gemm_get_deterministic() { return g_deterministic_splits.load(std::memory_order_relaxed); }
 
+#ifdef NVFP4_GEMM_TRACE
+extern "C" void nvfp4_gemm_set_trace_buffer(unsigned long long* device_words) {
+  g_trace_buffer.store(device_words, std::memory_order_relaxed);
+}
+#endif
+
 int gemm_timing_begin(uint32_t max_records) {
   std::lock_guard<std::mutex> lock(g_timing.mu);
   while (g_timing.pool.size() < max_records) {
@@ -1628,6 +1674,9 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   p.tma_store = static_cast<int>(pl.tma_store);
   p.wait_timeout_ns = g_wait_timeout_ns.load(std::memory_order_relaxed);
   p.debug_flags = g_debug_flags.load(std::memory_order_relaxed);
+#ifdef NVFP4_GEMM_TRACE
+  p.trace = g_trace_buffer.load(std::memory_order_relaxed);
+#endif
 
   CUtensorMap ma, mb, mo, mx;
   rc = encode_operand_map(&ma, a.a_bytes, a.m, a.k, pl.block_m);
