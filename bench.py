@@ -433,18 +433,23 @@ def run_gpu(args):
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
     def time_steps(step, steps, warmup):
-        """(ms per step on the device, max over ranks; host milliseconds spent enqueueing one step)."""
+        """(ms per step on the device, max over ranks; host milliseconds to enqueue one step on an empty queue)."""
         for _ in range(warmup):
             step()
         barrier()
         start.record()
-        h0 = time.perf_counter()
         for _ in range(steps):
             step()
-        host_ms = (time.perf_counter() - h0) * 1e3 / steps
         stop.record()
         barrier()
-        return max_over_ranks(start.elapsed_time(stop)) / steps, host_ms
+        ms = max_over_ranks(start.elapsed_time(stop)) / steps
+        # host cost of enqueueing one step, measured on an empty launch queue (inside the timed loop the host
+        # runs ahead until the queue is full and then waits for the device, so its time there is the device's)
+        h0 = time.perf_counter()
+        step()
+        host_ms = (time.perf_counter() - h0) * 1e3
+        torch.cuda.synchronize()
+        return ms, host_ms
 
     def make(shape, tokens_rank, total, with_comm=True, seed=1234):
         ps = ProjectionSet(shape, tokens_rank, dev, seed=seed, token_offset=rank * tokens_rank, total_tokens=total,

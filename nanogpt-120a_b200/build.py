@@ -61,10 +61,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 print(" ".join(cmd), flush=True)
             subprocess.check_call(cmd)
     if force or _stale(LIB, objs):
-        cmd = [nvcc, *ARCH, "-shared", "-o", LIB, *objs]
+        tmp = LIB + ".tmp"
+        cmd = [nvcc, *ARCH, "-shared", "-o", tmp, *objs]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.check_call(cmd)
+        os.replace(tmp, LIB)  # readers see the old library or the new one, never a partial file
     return LIB
 
 

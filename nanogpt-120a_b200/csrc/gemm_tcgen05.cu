@@ -982,12 +982,12 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint32_t r = m_blk * kBlockM + max_h * kRowBlock + gtid;
           if (p.row_amax && r < p.m && row_max > 0.0f) {
             // max over the row of relu(stored value)^2: rounding to the stored type and relu^2 are both
-            // monotonic, so they apply to the maximum instead of to every element; the atomic is skipped
-            // when the row's running maximum already is at least as large
+            // monotonic, so they apply to the maximum instead of to every element; a reduction without a
+            // return value, so the thread does not wait for it
             const float stored = sizeof(OutT) == 2 ? __bfloat162float(__float2bfloat16_rn(row_max)) : row_max;
             const uint32_t bits = __float_as_uint(__fmul_rn(stored, stored));
-            unsigned int* slot = reinterpret_cast<unsigned int*>(p.row_amax) + r;
-            if (bits > *reinterpret_cast<volatile unsigned int*>(slot)) atomicMax(slot, bits);
+            asm volatile("red.global.max.u32 [%0], %1;" ::"l"(reinterpret_cast<unsigned int*>(p.row_amax) + r), "r"(bits)
+                         : "memory");
           }
           row_max = -INFINITY;
         };
@@ -1031,9 +1031,22 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (p.row_amax) {
             // columns past n hold zero-filled operands (acc = 0): only real columns count
             const uint32_t valid = min(static_cast<uint32_t>(kSub), p.n - col0);
+            if (valid == static_cast<uint32_t>(kSub)) {
+              // four independent chains instead of one of kSub dependent maxima
+              float m0 = v[0], m1 = v[1], m2 = v[2], m3 = v[3];
 #pragma unroll
-            for (int i = 0; i < kSub; ++i)
-              if (static_cast<uint32_t>(i) < valid) row_max = fmaxf(row_max, v[i]);
+              for (int i = 4; i < kSub; i += 4) {
+                m0 = fmaxf(m0, v[i]);
+                m1 = fmaxf(m1, v[i + 1]);
+                m2 = fmaxf(m2, v[i + 2]);
+                m3 = fmaxf(m3, v[i + 3]);
+              }
+              row_max = fmaxf(row_max, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+            } else {
+#pragma unroll
+              for (int i = 0; i < kSub; ++i)
+                if (static_cast<uint32_t>(i) < valid) row_max = fmaxf(row_max, v[i]);
+            }
           }
           const int passes = (p.epilogue == NVFP4_EPI_RELU2 && p.aux) ? 2 : 1;
           for (int pass = 0; pass < passes; ++pass) {
@@ -1047,6 +1060,26 @@ __global__ void __launch_bounds__(kThreads, 1)
               }
             }
             const uint32_t buf = my_store + store_buf * kStoreStageBytes;
+            if (p.debug_flags & 2u) {
+              // every warp stores its own 32-row slab: no barrier of the group on the store path
+              if (lane == 0) bulk_wait_group_read<kRing - 1>();  // the store that last read this slab is done with it
+              __syncwarp();
+              SubTile<OutT>::stage(buf + gtid * 128, gtid, v);
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                if (row0 + ew * 32u < p.m) {
+                  const CUtensorMap* map = is_pre ? &tmap_aux : &tmap_out;
+                  if (p.k_splits > 1)
+                    tma_reduce_add_2d(map, buf + ew * 4096u, static_cast<int32_t>(col0), static_cast<int32_t>(row0 + ew * 32u));
+                  else
+                    tma_store_2d(map, buf + ew * 4096u, static_cast<int32_t>(col0), static_cast<int32_t>(row0 + ew * 32u));
+                }
+                bulk_commit_group();
+              }
+              store_buf = (store_buf + 1) % kRing;
+              continue;
+            }
             if (kRing == 1) {
               // single staging buffer: the previous store must have read it before it is rewritten
               if (elected) bulk_wait_group_read<0>();
@@ -1130,7 +1163,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         acc_phase ^= 1u;
       }
     }
-    if (p.tma_store && elected) bulk_wait_group0();  // stores complete before the CTA exits
+    if (p.tma_store && (elected || ((p.debug_flags & 2u) && lane == 0))) bulk_wait_group0();  // stores complete before the CTA exits
   }
 
   // ===================== teardown =====================
@@ -1226,9 +1259,10 @@ int encode_operand_map(CUtensorMap* map, const uint8_t* base, uint32_t rows, uin
 }
 
 // Output matrix [rows][ld] of f32 / bf16; box = 128 bytes x 128 rows, 128-byte swizzle.
-int encode_output_map(CUtensorMap* map, void* base, int dtype, uint32_t rows, uint32_t cols, uint32_t ld) {
+int encode_output_map(CUtensorMap* map, void* base, int dtype, uint32_t rows, uint32_t cols, uint32_t ld,
+                      uint32_t box_rows) {
   MapCache& cache = map_cache();
-  const MapKey key{reinterpret_cast<uint64_t>(base), dtype == NVFP4_DTYPE_F32 ? 1u : 2u, rows, cols, ld};
+  const MapKey key{reinterpret_cast<uint64_t>(base), (dtype == NVFP4_DTYPE_F32 ? 1u : 2u) | (box_rows << 8), rows, cols, ld};
   auto it = cache.maps.find(key);
   if (it != cache.maps.end()) {
     ++cache.hits;
@@ -1240,7 +1274,7 @@ int encode_output_map(CUtensorMap* map, void* base, int dtype, uint32_t rows, ui
   const size_t esz = dtype == NVFP4_DTYPE_F32 ? 4 : 2;
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * esz};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / esz), kRowBlock};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / esz), box_rows};
   const cuuint32_t elem_strides[2] = {1, 1};
   CUresult r = fn(map, dtype == NVFP4_DTYPE_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                   base, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1686,8 +1720,9 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   mo = ma;
   mx = ma;
   if (p.tma_store) {
-    if (encode_output_map(&mo, a.out, a.out_dtype, a.m, a.n, a.ldo) != 0) p.tma_store = 0;
-    if (p.tma_store && a.aux && encode_output_map(&mx, a.aux, a.out_dtype, a.m, a.n, a.ldo) != 0) p.tma_store = 0;
+    const uint32_t box_rows = (p.debug_flags & 2u) ? 32u : static_cast<uint32_t>(kRowBlock);
+    if (encode_output_map(&mo, a.out, a.out_dtype, a.m, a.n, a.ldo, box_rows) != 0) p.tma_store = 0;
+    if (p.tma_store && a.aux && encode_output_map(&mx, a.aux, a.out_dtype, a.m, a.n, a.ldo, box_rows) != 0) p.tma_store = 0;
     if (!p.tma_store && a.relu2_row_amax) {
       set_last_error("nvfp4_gemm: relu2_row_amax needs an output the TMA store path accepts");
       return static_cast<int>(cudaErrorInvalidValue);
