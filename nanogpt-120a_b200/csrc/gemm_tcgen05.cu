@@ -447,7 +447,7 @@ struct SubTile<__nv_bfloat16> {
 // Streaming mode: one B slot per pipeline stage.  Resident mode (short K): the whole
 // [kBlockN x K] B panel of the current column block stays in shared memory -- one slot per
 // k-tile -- while a CTA walks down the row blocks, so only A tiles stream through the ring.
-template <int kBlockM, int kBlockN, typename OutT>
+template <int kBlockM, int kBlockN, typename OutT, bool kTmaStore>
 __global__ void __launch_bounds__(kThreads, 1)
     nvfp4_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                               const __grid_constant__ CUtensorMap tmap_out,
@@ -492,7 +492,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_a)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_b)) : "memory");
-    if (p.tma_store) {
+    if (kTmaStore) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_out)) : "memory");
       if (p.aux) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_aux)) : "memory");
     }
@@ -903,7 +903,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int j = 0; j < C::kBiasSlots; ++j) {
         const uint32_t in_tile = gtid + 128 * j;
         const uint32_t col = nb * kBlockN + in_tile;
-        bias_next[j] = (p.tma_store && p.epilogue != NVFP4_EPI_NONE && in_tile < static_cast<uint32_t>(kBlockN) && col < p.n)
+        bias_next[j] = (kTmaStore && p.epilogue != NVFP4_EPI_NONE && in_tile < static_cast<uint32_t>(kBlockN) && col < p.n)
                            ? bias_value(p, col)
                            : 0.0f;
       }
@@ -924,7 +924,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       // the tile's bias slice goes through shared memory once (every row then reads it broadcast); it is
       // fetched before the wait for the accumulator so that its latency hides behind the main loop.  The
       // group's last barrier of the previous tile comes after that tile's last read of the slice.
-      const bool add_bias = p.tma_store && p.epilogue != NVFP4_EPI_NONE && (p.k_splits == 1 || split == 0);
+      const bool add_bias = kTmaStore && p.epilogue != NVFP4_EPI_NONE && (p.k_splits == 1 || split == 0);
       if (add_bias && n_blk != staged_bias_blk) {  // uniform across the group
 #pragma unroll
         for (int j = 0; j < C::kBiasSlots; ++j)
@@ -956,7 +956,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * acc);
       };
-      if (p.tma_store) {
+      if (kTmaStore) {
         // Sub-tiles of 128 rows x 128 bytes go through the group's shared-memory ring and leave
         // with TMA stores (TMA reduce-add for split-K partial sums); rows / columns outside the
         // matrix are clipped by the tensor map.  The items of a tile -- (row half, column sub-tile) --
@@ -1060,26 +1060,6 @@ __global__ void __launch_bounds__(kThreads, 1)
               }
             }
             const uint32_t buf = my_store + store_buf * kStoreStageBytes;
-            if (p.debug_flags & 2u) {
-              // every warp stores its own 32-row slab: no barrier of the group on the store path
-              if (lane == 0) bulk_wait_group_read<kRing - 1>();  // the store that last read this slab is done with it
-              __syncwarp();
-              SubTile<OutT>::stage(buf + gtid * 128, gtid, v);
-              fence_proxy_async_smem();
-              __syncwarp();
-              if (lane == 0) {
-                if (row0 + ew * 32u < p.m) {
-                  const CUtensorMap* map = is_pre ? &tmap_aux : &tmap_out;
-                  if (p.k_splits > 1)
-                    tma_reduce_add_2d(map, buf + ew * 4096u, static_cast<int32_t>(col0), static_cast<int32_t>(row0 + ew * 32u));
-                  else
-                    tma_store_2d(map, buf + ew * 4096u, static_cast<int32_t>(col0), static_cast<int32_t>(row0 + ew * 32u));
-                }
-                bulk_commit_group();
-              }
-              store_buf = (store_buf + 1) % kRing;
-              continue;
-            }
             if (kRing == 1) {
               // single staging buffer: the previous store must have read it before it is rewritten
               if (elected) bulk_wait_group_read<0>();
@@ -1163,7 +1143,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         acc_phase ^= 1u;
       }
     }
-    if (p.tma_store && (elected || ((p.debug_flags & 2u) && lane == 0))) bulk_wait_group0();  // stores complete before the CTA exits
+    if (kTmaStore && elected) bulk_wait_group0();  // stores complete before the CTA exits
   }
 
   // ===================== teardown =====================
@@ -1259,10 +1239,9 @@ int encode_operand_map(CUtensorMap* map, const uint8_t* base, uint32_t rows, uin
 }
 
 // Output matrix [rows][ld] of f32 / bf16; box = 128 bytes x 128 rows, 128-byte swizzle.
-int encode_output_map(CUtensorMap* map, void* base, int dtype, uint32_t rows, uint32_t cols, uint32_t ld,
-                      uint32_t box_rows) {
+int encode_output_map(CUtensorMap* map, void* base, int dtype, uint32_t rows, uint32_t cols, uint32_t ld) {
   MapCache& cache = map_cache();
-  const MapKey key{reinterpret_cast<uint64_t>(base), (dtype == NVFP4_DTYPE_F32 ? 1u : 2u) | (box_rows << 8), rows, cols, ld};
+  const MapKey key{reinterpret_cast<uint64_t>(base), dtype == NVFP4_DTYPE_F32 ? 1u : 2u, rows, cols, ld};
   auto it = cache.maps.find(key);
   if (it != cache.maps.end()) {
     ++cache.hits;
@@ -1274,7 +1253,7 @@ int encode_output_map(CUtensorMap* map, void* base, int dtype, uint32_t rows, ui
   const size_t esz = dtype == NVFP4_DTYPE_F32 ? 4 : 2;
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * esz};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / esz), box_rows};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / esz), kRowBlock};
   const cuuint32_t elem_strides[2] = {1, 1};
   CUresult r = fn(map, dtype == NVFP4_DTYPE_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                   base, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1340,16 +1319,16 @@ TileBytes tile_bytes(uint32_t block_m, uint32_t block_n) {
   return block_n == 256 ? tile_bytes_of<128, 256>() : block_n == 192 ? tile_bytes_of<128, 192>() : tile_bytes_of<128, 128>();
 }
 
-template <int kBlockM, int kBlockN, typename OutT>
-int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
-                   const CUtensorMap& mx, const GemmParams& p, const GemmPlan& pl) {
+template <int kBlockM, int kBlockN, typename OutT, bool kTmaStore>
+int launch_store_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
+                         const CUtensorMap& mx, const GemmParams& p, const GemmPlan& pl) {
   // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel
   static std::atomic<int> attr_state[kMaxDevices];  // 0 = not set, 1 = set, -(error) = failed
   const int dev = current_device();
   if (dev < 0) return static_cast<int>(cudaErrorInvalidDevice);
   int st = attr_state[dev].load(std::memory_order_acquire);
   if (st == 0) {
-    const cudaError_t e = cudaFuncSetAttribute(nvfp4_gemm_tcgen05_kernel<kBlockM, kBlockN, OutT>,
+    const cudaError_t e = cudaFuncSetAttribute(nvfp4_gemm_tcgen05_kernel<kBlockM, kBlockN, OutT, kTmaStore>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     st = e == cudaSuccess ? 1 : -static_cast<int>(e);
     attr_state[dev].store(st, std::memory_order_release);
@@ -1364,11 +1343,21 @@ int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb,
     rec->flops = 2.0 * p.m * p.n * p.k;
     cudaEventRecord(rec->start, s);
   }
-  nvfp4_gemm_tcgen05_kernel<kBlockM, kBlockN, OutT><<<pl.grid, kThreads, pl.smem_bytes, s>>>(ma, mb, mo, mx, p);
+  nvfp4_gemm_tcgen05_kernel<kBlockM, kBlockN, OutT, kTmaStore><<<pl.grid, kThreads, pl.smem_bytes, s>>>(ma, mb, mo, mx, p);
   count_launch();
   const int rc = static_cast<int>(cudaGetLastError());
   if (rec) cudaEventRecord(rec->stop, s);
   return rc;
+}
+
+// The store path is a compile-time property of the kernel (TMA stores through the staging ring, or direct
+// stores for outputs a tensor map cannot describe and for the in-place residual epilogue): each variant
+// carries only its own epilogue code.
+template <int kBlockM, int kBlockN, typename OutT>
+int launch_variant(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
+                   const CUtensorMap& mx, const GemmParams& p, const GemmPlan& pl) {
+  return p.tma_store ? launch_store_variant<kBlockM, kBlockN, OutT, true>(s, ma, mb, mo, mx, p, pl)
+                     : launch_store_variant<kBlockM, kBlockN, OutT, false>(s, ma, mb, mo, mx, p, pl);
 }
 
 std::atomic<int> g_tile_override{-1};  // -1 = read NVFP4_GEMM_TILE once, 0 = automatic, else (block_m << 16) | block_n
@@ -1720,9 +1709,8 @@ int launch_gemm(cudaStream_t s, const nvfp4_gemm_args& a) {
   mo = ma;
   mx = ma;
   if (p.tma_store) {
-    const uint32_t box_rows = (p.debug_flags & 2u) ? 32u : static_cast<uint32_t>(kRowBlock);
-    if (encode_output_map(&mo, a.out, a.out_dtype, a.m, a.n, a.ldo, box_rows) != 0) p.tma_store = 0;
-    if (p.tma_store && a.aux && encode_output_map(&mx, a.aux, a.out_dtype, a.m, a.n, a.ldo, box_rows) != 0) p.tma_store = 0;
+    if (encode_output_map(&mo, a.out, a.out_dtype, a.m, a.n, a.ldo) != 0) p.tma_store = 0;
+    if (p.tma_store && a.aux && encode_output_map(&mx, a.aux, a.out_dtype, a.m, a.n, a.ldo) != 0) p.tma_store = 0;
     if (!p.tma_store && a.relu2_row_amax) {
       set_last_error("nvfp4_gemm: relu2_row_amax needs an output the TMA store path accepts");
       return static_cast<int>(cudaErrorInvalidValue);
