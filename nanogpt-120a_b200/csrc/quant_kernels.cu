@@ -13,6 +13,7 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -2069,13 +2070,18 @@ int launch_ms_eden_pair(cudaStream_t s, const nvfp4_ms_eden_args& r, const nvfp4
       ms_eden_pair_kernel<__nv_bfloat16>
           <<<grid, 256, 2 * PairTile<__nv_bfloat16>::kStageBytes, s>>>(p, tiles_x, tile_count);
     } else {
-      static std::once_flag once;
-      static cudaError_t attr_err = cudaSuccess;
-      std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(ms_eden_pair_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        2 * PairTile<float>::kStageBytes);
-      });
-      if (attr_err != cudaSuccess) return static_cast<int>(attr_err);
+      // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel
+      static std::atomic<int> attr_state[64];  // per device ordinal: 0 = not set, 1 = set, -(error) = failed
+      int dev = 0;
+      if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return static_cast<int>(cudaErrorInvalidDevice);
+      int st = attr_state[dev].load(std::memory_order_acquire);
+      if (st == 0) {
+        const cudaError_t e = cudaFuncSetAttribute(ms_eden_pair_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   2 * PairTile<float>::kStageBytes);
+        st = e == cudaSuccess ? 1 : -static_cast<int>(e);
+        attr_state[dev].store(st, std::memory_order_release);
+      }
+      if (st < 0) return -st;
       ms_eden_pair_kernel<float><<<grid, 256, 2 * PairTile<float>::kStageBytes, s>>>(p, tiles_x, tile_count);
     }
   } else if (r.src_dtype == NVFP4_DTYPE_BF16) {
