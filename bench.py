@@ -182,6 +182,31 @@ def cuda_time_us(torch, fn, iters, warmup=3):
     return a.elapsed_time(b) * 1e3 / iters
 
 
+def graph_time_us(torch, fn, calls, replays=6):
+    """Device time per call of `fn`, with `calls` consecutive calls captured into one CUDA graph and the graph
+    replayed: the Python / ctypes cost of a call (about 10 us, more than these kernels take) stays out."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(calls):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(calls):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(replays):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / (replays * calls)
+
+
 def quantize_records(pkg, torch, dev, peak_gbs):
     """The quantizer on [8192 x 768] bf16 (201 MB over 16 rotating buffers, larger than L2): rowwise scale
     with the row amax fused (what the projections call), per-tensor scale (an amax pass, then the quantizer),
@@ -224,12 +249,15 @@ def quantize_records(pkg, torch, dev, peak_gbs):
         d.decode(ten_out[k])
 
     out = {"workload": "four-six quantize [8192x768] bf16 -> NVFP4, 16 rotating buffers (201 MB > L2)",
-           "algorithmic_bytes": algo}
+           "algorithmic_bytes": algo,
+           "timing": "us = device time per call, 32 calls replayed from a CUDA graph; us_python_loop = the same calls "
+                     "issued one by one from Python (bound by the host's per-call cost at this size)"}
     for name, fn in (("rowwise_fused_amax", rowwise), ("rowwise_amax_given", rowwise_given_amax),
                      ("per_tensor_amax_plus_quantize", per_tensor), ("per_tensor_round_trip_with_dequantize", round_trip)):
-        us = cuda_time_us(torch, fn, 80)
+        us_loop = cuda_time_us(torch, fn, 80)
+        us = graph_time_us(torch, fn, 2 * nbuf)
         gbs = algo / (us * 1e-6) / 1e9
-        out[name] = {"us": us, "achieved_gbs": gbs, "frac_of_hbm_peak": gbs / peak_gbs}
+        out[name] = {"us": us, "achieved_gbs": gbs, "frac_of_hbm_peak": gbs / peak_gbs, "us_python_loop": us_loop}
     out["us"] = out["rowwise_fused_amax"]["us"]
     out["achieved_gbs"] = out["rowwise_fused_amax"]["achieved_gbs"]
     out["frac_of_hbm_peak"] = out["rowwise_fused_amax"]["frac_of_hbm_peak"]
@@ -325,13 +353,15 @@ def small_configs(pkg, torch, dev, peaks, write_gbs):
         gemm.gemm(xq, wq, bias=bias, epilogue=pkg.EPI_BIAS, out=y)
 
     flops = 2.0 * m * n * k
-    us_g = cuda_time_us(torch, gemm_only, 60)
-    us_qg = cuda_time_us(torch, quantize_and_gemm, 60)
+    us_g_loop = cuda_time_us(torch, gemm_only, 60)
+    us_g = graph_time_us(torch, gemm_only, 2 * len(sets))   # device time: the Python cost of a call stays out
+    us_qg = graph_time_us(torch, quantize_and_gemm, 2 * len(sets))
     t_compute = flops / (NOMINAL_FP4_DENSE_TFLOPS * 1e12) * 1e6
     t_write = m * n * 2 / (write_gbs * 1e9) * 1e6
     c2 = {"workload": "c_attn forward projection, X [8192x768] W [2304x768], NVFP4 x NVFP4, bias, bf16 out",
           "gemm_us": us_g, "gemm_tflops": flops / (us_g * 1e-6) / 1e12,
-          "quantize_x_plus_gemm_us": us_qg,
+          "quantize_x_plus_gemm_us": us_qg, "gemm_us_python_loop": us_g_loop,
+          "timing": "12 calls replayed from a CUDA graph (device time); the Python loop figure is bound by the host",
           "roofline_us": {"tensor": t_compute, "output_write": t_write, "bound": "output_write" if t_write > t_compute else "tensor"},
           "frac_of_min_roofline": max(t_compute, t_write) / us_g}
     del sets
