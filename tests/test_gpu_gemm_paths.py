@@ -237,6 +237,16 @@ def test_split_k_dw_shapes(pkg, oracle, dev, m, n, k):
     assert plan.k_splits >= 2 or plan.grid >= 96, (plan.k_splits, plan.grid)
 
 
+@pytest.mark.parametrize("height,width", SHAPES)
+def test_split_k_with_bias_every_tile_shape(pkg, oracle, dev, tile, height, width):
+    """Split-K with a linear bias epilogue: the bias joins the sum exactly once (with the first split's partial
+    tile), whatever the tile shape; ragged N so the last column block is clipped by the reduce-add."""
+    tile(width, height)
+    plan, _ = run_case(pkg, oracle, dev, 700, 840, 16384, out_dtype=torch.float32, epi=1,
+                       want_plan=dict(block_m=height, block_n=width, b_resident=0))
+    assert plan.k_splits >= 2, plan.k_splits
+
+
 @pytest.mark.parametrize("height,width", [(128, 192), (128, 256), (256, 192)])
 def test_lm_head_dw_unsplit_wide_f32(pkg, oracle, dev, tile, height, width):
     """LM-head dW: enough tiles to fill the SMs without a split -- the unsplit wide f32 instantiations."""
